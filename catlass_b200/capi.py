@@ -1,0 +1,120 @@
+"""ctypes binding of the C ABI in include/catlass_b200.h.
+
+Used by the tests and the benchmark to call the library exactly as a C caller would: PODs, raw device
+pointers, a stream handle.  Loading fails loudly when the shared object is missing; nothing here computes.
+"""
+import ctypes
+import os
+
+from . import build as _build
+
+SUCCESS, INVALID, CUDA_ERROR, DEVICE_TIMEOUT = 0, 1, 2, 3
+ROW_MAJOR, COLUMN_MAJOR = 0, 1
+GROUP_LIST_INT64, GROUP_LIST_INT32 = 0, 1
+
+_u32, _u64, _vp = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
+
+
+class QuantMatmulArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("layout_a", _u32), ("layout_b", _u32),
+        ("a", _vp), ("b", _vp), ("scale", _vp), ("per_token_scale", _vp), ("d", _vp), ("acc", _vp),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+    ]
+
+
+class GroupedQuantMatmulArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("layout_b", _u32),
+        ("group_list_type", _u32),
+        ("a", _vp), ("b", _vp), ("group_list", _vp), ("scale", _vp), ("per_token_scale", _vp), ("d", _vp),
+        ("acc", _vp), ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+    ]
+
+
+_lib = None
+
+
+def library_path():
+    return _build.LIB_PATH
+
+
+def load():
+    """The loaded shared library. Raises if it has not been built (python -m catlass_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise RuntimeError(
+            f"{path} is missing: build it with `python -m catlass_b200.build` (needs nvcc). "
+            "There is no fallback path.")
+    lib = ctypes.CDLL(path)
+    for name, args_t in (("cb200_quant_matmul", QuantMatmulArgs),
+                         ("cb200_grouped_quant_matmul_slice_m", GroupedQuantMatmulArgs)):
+        getattr(lib, name + "_can_implement").argtypes = [ctypes.POINTER(args_t)]
+        getattr(lib, name + "_can_implement").restype = ctypes.c_int
+        getattr(lib, name + "_workspace_size").argtypes = [ctypes.POINTER(args_t)]
+        getattr(lib, name + "_workspace_size").restype = _u64
+        getattr(lib, name).argtypes = [ctypes.POINTER(args_t), _vp]
+        getattr(lib, name).restype = ctypes.c_int
+    lib.cb200_device_status.argtypes = [ctypes.POINTER(_u32)]
+    lib.cb200_device_status.restype = ctypes.c_int
+    lib.cb200_last_cuda_error.restype = ctypes.c_int
+    lib.cb200_launch_count.restype = _u64
+    lib.cb200_version.restype = ctypes.c_char_p
+    _lib = lib
+    return lib
+
+
+class CallError(RuntimeError):
+    def __init__(self, what, status):
+        super().__init__(f"{what} returned status {status} (cuda error {load().cb200_last_cuda_error()})")
+        self.status = status
+
+
+def _check(what, status):
+    if status != SUCCESS:
+        raise CallError(what, status)
+
+
+def device_status():
+    """(status, code): synchronises the device and reads the kernels' status word."""
+    code = _u32(0)
+    st = load().cb200_device_status(ctypes.byref(code))
+    return st, code.value
+
+
+def launch_count():
+    return int(load().cb200_launch_count())
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        stream = torch.cuda.current_stream()
+    return ctypes.c_void_p(stream.cuda_stream)
+
+
+def quant_matmul(a, b, scale, per_token, d, m, n, k, layout_b=COLUMN_MAJOR, acc=None, stream=None,
+                 block_num=0, layout_a=ROW_MAJOR):
+    """Enqueue the dense W8A8 dequant matmul. Arguments are torch CUDA tensors used as raw buffers."""
+    args = QuantMatmulArgs(m=m, n=n, k=k, layout_a=layout_a, layout_b=layout_b, a=_p(a), b=_p(b),
+                           scale=_p(scale), per_token_scale=_p(per_token), d=_p(d), acc=_p(acc),
+                           workspace=None, workspace_bytes=0, block_num=block_num, reserved=0)
+    _check("cb200_quant_matmul", load().cb200_quant_matmul(ctypes.byref(args), _stream(stream)))
+
+
+def grouped_quant_matmul(a, b, group_list, scale, per_token, d, m, n, k, group_count, layout_b=ROW_MAJOR,
+                         acc=None, stream=None, block_num=0, group_list_type=GROUP_LIST_INT64):
+    args = GroupedQuantMatmulArgs(m=m, n=n, k=k, group_count=group_count, layout_b=layout_b,
+                                  group_list_type=group_list_type, a=_p(a), b=_p(b),
+                                  group_list=_p(group_list), scale=_p(scale), per_token_scale=_p(per_token),
+                                  d=_p(d), acc=_p(acc), workspace=None, workspace_bytes=0,
+                                  block_num=block_num, reserved=0)
+    _check("cb200_grouped_quant_matmul_slice_m",
+           load().cb200_grouped_quant_matmul_slice_m(ctypes.byref(args), _stream(stream)))

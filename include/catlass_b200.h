@@ -1,0 +1,128 @@
+/*
+ * catlass_b200 - C ABI of the B200 (sm_100a) quantized-matmul library.
+ *
+ * Plain C: PODs, raw device pointers and sizes only.  Every operator comes as a triple that mirrors the
+ * reference's device adapter (include/catlass/gemm/device/device_gemm.hpp:47-97):
+ *     <op>_can_implement(args)   -> status            (DeviceGemm::CanImplement)
+ *     <op>_workspace_size(args)  -> bytes             (DeviceGemm::GetWorkspaceSize)
+ *     <op>(args, stream)         -> status, async     (DeviceGemm::Initialize + operator())
+ * The caller owns all buffers, including the workspace (args->workspace, at least _workspace_size bytes,
+ * 256-byte aligned).  Calls enqueue work on `stream` (a cudaStream_t passed as void*) and return without
+ * synchronising.  All pointers are device pointers unless stated otherwise.
+ *
+ * Status: 0 = success (Catlass::Status::kSuccess, include/catlass/status.hpp:16-20), 1 = invalid
+ * arguments / unsupported problem (Status::kInvalid), >= 2 = runtime failures listed below.
+ */
+#ifndef CATLASS_B200_H
+#define CATLASS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define CB200_API
+#else
+#define CB200_API __attribute__((visibility("default")))
+#endif
+
+/* ---- status ---- */
+#define CB200_SUCCESS 0
+#define CB200_INVALID 1        /* bad descriptor: null pointer, misaligned buffer, unsupported layout */
+#define CB200_CUDA_ERROR 2     /* a CUDA runtime/driver call failed (see cb200_last_cuda_error) */
+#define CB200_DEVICE_TIMEOUT 3 /* a kernel gave up on a bounded wait (see cb200_device_status) */
+
+/* ---- matrix layouts (include/catlass/layout/matrix.hpp: RowMajor :24, ColumnMajor :168, zN :475) ---- */
+#define CB200_ROW_MAJOR 0
+#define CB200_COLUMN_MAJOR 1
+
+/* ---- group list element type (the reference accepts int32 or int64 prefix sums) ---- */
+#define CB200_GROUP_LIST_INT64 0
+#define CB200_GROUP_LIST_INT32 1
+
+/*
+ * Dense W8A8 matmul with per-token / per-channel dequant:
+ *     D[i,j] = bf16_rne( (float(sum_k A[i,k]*B[k,j]) * scale[j]) * per_token_scale[i] )
+ * Replaces the kernels behind examples 12 / 42 / 103:
+ *     Gemm::Kernel::QuantMatmulMultiStageWorkspace::Arguments
+ *         (include/catlass/gemm/kernel/quant_matmul_multistage_workspace.hpp:92-100),
+ *     operand order of tests/optest/kernels/12_quant_matmul/quant_matmul_impl.cpp:103-105
+ *         (inputs A, B, scale, perTokenScale; output D).
+ * A: int8 m x k, B: int8 k x n, each row- or column-major and densely packed; D: bf16 m x n row-major.
+ */
+typedef struct cb200_quant_matmul_args {
+    uint32_t m, n, k;
+    uint32_t layout_a;            /* CB200_ROW_MAJOR only */
+    uint32_t layout_b;            /* CB200_ROW_MAJOR or CB200_COLUMN_MAJOR */
+    const void *a;                /* int8 */
+    const void *b;                /* int8 */
+    const float *scale;           /* n per-channel scales */
+    const float *per_token_scale; /* m per-token scales */
+    void *d;                      /* bf16 out */
+    int32_t *acc;                 /* optional: raw int32 accumulators, m x n row-major (NULL = off) */
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;           /* upper bound on the CTAs launched; 0 = one per SM */
+    uint32_t reserved;
+} cb200_quant_matmul_args;
+
+CB200_API int cb200_quant_matmul_can_implement(const cb200_quant_matmul_args *args);
+CB200_API uint64_t cb200_quant_matmul_workspace_size(const cb200_quant_matmul_args *args);
+CB200_API int cb200_quant_matmul(const cb200_quant_matmul_args *args, void *stream);
+
+/*
+ * Grouped (MoE) slice-M W8A8 matmul with per-token dequant.  group_list holds `group_count` ascending
+ * prefix sums of rows; group g owns rows [group_list[g-1], group_list[g]) of A and D, weight matrix
+ * B + g*k*n and channel scales scale + g*n.  Rows at or beyond group_list[group_count-1] are not written.
+ * Replaces the kernels behind examples 07 / 10 / 47:
+ *     Gemm::Kernel::GroupedMatmulSliceMPerTokenDequant::Arguments
+ *         (include/catlass/gemm/kernel/grouped_matmul_slice_m_per_token_dequant.hpp:125-137),
+ *     operand order of tests/optest/kernels/07_grouped_matmul_slice_m_per_token_dequant_moe/
+ *         grouped_matmul_slice_m_per_token_dequant_moe_impl.cpp:98-102
+ *         (inputs A, B, groupList, scale, perTokenScale; batch = group count).
+ * m is the row capacity of A / D / per_token_scale (group_list entries are clamped to it).
+ */
+typedef struct cb200_grouped_quant_matmul_args {
+    uint32_t m, n, k;
+    uint32_t group_count;         /* 1 .. 1024 */
+    uint32_t layout_b;            /* layout of each k x n weight matrix */
+    uint32_t group_list_type;     /* CB200_GROUP_LIST_INT64 / _INT32 */
+    const void *a;                /* int8 m x k row-major */
+    const void *b;                /* int8 [group_count][k x n] */
+    const void *group_list;       /* device pointer */
+    const float *scale;           /* [group_count][n] */
+    const float *per_token_scale; /* [m] */
+    void *d;                      /* bf16 m x n row-major */
+    int32_t *acc;                 /* optional raw accumulators */
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t reserved;
+} cb200_grouped_quant_matmul_args;
+
+CB200_API int cb200_grouped_quant_matmul_slice_m_can_implement(const cb200_grouped_quant_matmul_args *args);
+CB200_API uint64_t cb200_grouped_quant_matmul_slice_m_workspace_size(const cb200_grouped_quant_matmul_args *args);
+CB200_API int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args *args, void *stream);
+
+/* ---- library / device state ---- */
+
+/* Reads and clears the status word kernels of this library write on the current device when a bounded
+ * wait expires.  Synchronises the device.  *code = 0 when every kernel ran to completion.  Returns
+ * CB200_SUCCESS, CB200_DEVICE_TIMEOUT (when *code != 0) or CB200_CUDA_ERROR. */
+CB200_API int cb200_device_status(uint32_t *code);
+
+/* Last CUDA error code (cudaError_t / CUresult as int) seen by this thread inside the library. */
+CB200_API int cb200_last_cuda_error(void);
+
+/* Number of kernels this library has launched from the calling process (all threads). */
+CB200_API uint64_t cb200_launch_count(void);
+
+CB200_API const char *cb200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CATLASS_B200_H */

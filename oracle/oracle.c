@@ -1,0 +1,317 @@
+/*
+ * CPU oracle: plain-C restatement of the CATLASS CPU goldens for the quantized-matmul path.
+ * TEST INFRASTRUCTURE ONLY - see oracle.h for what each function follows and how it is pinned.
+ *
+ * Build with -ffp-contract=off: the goldens multiply and add in separate fp32 operations and the
+ * comparisons against the GPU are bit-exact, so the compiler must not fuse them.
+ */
+#include "oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ------------------------------------------------------------------ bf16 */
+
+uint16_t orc_bf16_rne(float x)
+{
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) { /* NaN: keep sign, force quiet */
+        return (uint16_t)((u >> 16) | 0x0040u);
+    }
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+void orc_bf16_rne_array(const float *x, uint16_t *y, size_t count)
+{
+    for (size_t i = 0; i < count; ++i) {
+        y[i] = orc_bf16_rne(x[i]);
+    }
+}
+
+float orc_bf16_to_float(uint16_t v)
+{
+    uint32_t u = (uint32_t)v << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* ------------------------------------------------------------------ W8A8 */
+
+/* acc_row[j] = sum_k a_row[k] * B[k,j] for one row of A. Loop order is chosen per layout so that the
+ * inner loop walks memory contiguously; integer sums do not depend on the order. */
+static void int8_row_times_matrix(uint32_t n, uint32_t k, const int8_t *a_row, size_t a_stride,
+                                  const int8_t *b, int layout_b, int32_t *acc_row)
+{
+    if (layout_b == ORC_COL_MAJOR) { /* column j is k contiguous bytes */
+        for (uint32_t j = 0; j < n; ++j) {
+            const int8_t *col = b + (size_t)j * k;
+            int32_t s = 0;
+            for (uint32_t kk = 0; kk < k; ++kk) {
+                s += (int32_t)a_row[(size_t)kk * a_stride] * (int32_t)col[kk];
+            }
+            acc_row[j] = s;
+        }
+    } else { /* row kk of B is n contiguous bytes */
+        for (uint32_t j = 0; j < n; ++j) {
+            acc_row[j] = 0;
+        }
+        for (uint32_t kk = 0; kk < k; ++kk) {
+            int32_t av = (int32_t)a_row[(size_t)kk * a_stride];
+            const int8_t *row = b + (size_t)kk * n;
+            for (uint32_t j = 0; j < n; ++j) {
+                acc_row[j] += av * (int32_t)row[j];
+            }
+        }
+    }
+}
+
+void orc_quant_matmul(uint32_t m, uint32_t n, uint32_t k, const int8_t *a, int layout_a,
+                      const int8_t *b, int layout_b, const float *scale, const float *per_token,
+                      float *out, int32_t *acc)
+{
+    int32_t *row_acc = (int32_t *)malloc(sizeof(int32_t) * (n ? n : 1));
+    for (uint32_t i = 0; i < m; ++i) {
+        const int8_t *a_row = (layout_a == ORC_ROW_MAJOR) ? a + (size_t)i * k : a + i;
+        size_t a_stride = (layout_a == ORC_ROW_MAJOR) ? 1 : m;
+        int8_row_times_matrix(n, k, a_row, a_stride, b, layout_b, row_acc);
+        for (uint32_t j = 0; j < n; ++j) {
+            float t = (float)row_acc[j] * scale[j];
+            out[(size_t)i * n + j] = t * per_token[i];
+        }
+        if (acc) {
+            memcpy(acc + (size_t)i * n, row_acc, sizeof(int32_t) * n);
+        }
+    }
+    free(row_acc);
+}
+
+void orc_grouped_quant_matmul_slice_m(uint32_t m, uint32_t n, uint32_t k, uint32_t group_count,
+                                      const int64_t *group_list, const int8_t *a, const int8_t *b,
+                                      int layout_b, const float *scale, const float *per_token,
+                                      float *out, int32_t *acc)
+{
+    (void)m;
+    int32_t *row_acc = (int32_t *)malloc(sizeof(int32_t) * (n ? n : 1));
+    int64_t start_row = 0;
+    for (uint32_t g = 0; g < group_count; ++g) {
+        const int8_t *bg = b + (size_t)g * k * n;
+        const float *sg = scale + (size_t)g * n;
+        for (int64_t i = start_row; i < group_list[g]; ++i) {
+            int8_row_times_matrix(n, k, a + (size_t)i * k, 1, bg, layout_b, row_acc);
+            for (uint32_t j = 0; j < n; ++j) {
+                float t = (float)row_acc[j] * sg[j];
+                out[(size_t)i * n + j] = t * per_token[i];
+            }
+            if (acc) {
+                memcpy(acc + (size_t)i * n, row_acc, sizeof(int32_t) * n);
+            }
+        }
+        start_row = group_list[g]; /* as the golden does, also for a list that is not ascending */
+    }
+    free(row_acc);
+}
+
+/* ------------------------------------------------------------------ W4A8 */
+
+void orc_w4a8_matmul_per_group(uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
+                               const int8_t *a, const uint8_t *w_packed, const float *sw,
+                               const float *sa, float *out)
+{
+    uint32_t groups = k / group_size;
+    size_t col_bytes = k / 2;
+    for (uint32_t i = 0; i < m; ++i) {
+        const int8_t *a_row = a + (size_t)i * k;
+        for (uint32_t j = 0; j < n; ++j) {
+            const uint8_t *col = w_packed + (size_t)j * col_bytes;
+            float y = 0.0f;
+            for (uint32_t g = 0; g < groups; ++g) {
+                int32_t s = 0;
+                uint32_t k0 = g * group_size;
+                for (uint32_t kk = k0; kk < k0 + group_size; kk += 2) {
+                    uint8_t byte = col[kk >> 1];
+                    s += (int32_t)a_row[kk] * orc_int4(byte & 0xF);
+                    s += (int32_t)a_row[kk + 1] * orc_int4(byte >> 4);
+                }
+                float t = (float)s * sw[(size_t)g * n + j];
+                y = y + t;
+            }
+            out[(size_t)i * n + j] = y * sa[i];
+        }
+    }
+}
+
+void orc_w4a8_matmul_per_tensor(uint32_t m, uint32_t n, uint32_t k, const int8_t *a,
+                                const uint8_t *w_packed, float scalar, float *out)
+{
+    size_t col_bytes = (k + 1) / 2;
+    for (uint32_t i = 0; i < m; ++i) {
+        const int8_t *a_row = a + (size_t)i * k;
+        for (uint32_t j = 0; j < n; ++j) {
+            const uint8_t *col = w_packed + (size_t)j * col_bytes;
+            int32_t s = 0;
+            for (uint32_t kk = 0; kk < k; ++kk) {
+                uint8_t byte = col[kk >> 1];
+                int w = (kk & 1) ? orc_int4(byte >> 4) : orc_int4(byte & 0xF);
+                s += (int32_t)a_row[kk] * w;
+            }
+            out[(size_t)i * n + j] = scalar * (float)s;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ MX */
+
+float orc_e4m3_to_float(uint8_t v)
+{
+    int sign = v >> 7;
+    int e = (v >> 3) & 0xF;
+    int mant = v & 7;
+    float r;
+    if (e == 0xF && mant == 7) {
+        r = NAN;
+    } else if (e == 0) {
+        r = ldexpf((float)mant, -9); /* subnormal: mant/8 * 2^-6 */
+    } else {
+        r = ldexpf((float)(8 + mant), e - 10); /* (1+mant/8) * 2^(e-7) */
+    }
+    return sign ? -r : r;
+}
+
+float orc_e2m1_to_float(uint8_t v)
+{
+    static const float mag[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+    float r = mag[v & 7];
+    return (v & 8) ? -r : r;
+}
+
+float orc_e8m0_to_float(uint8_t v)
+{
+    if (v == 0xFF) {
+        return NAN;
+    }
+    return ldexpf(1.0f, (int)v - 127);
+}
+
+/* Snap |x| to the nearest representable magnitude of the format; on a tie take the smaller magnitude
+ * (the reference's lowest-index argmin rule).  Returns the element code without sign. */
+static uint8_t snap_magnitude(float mag, int fmt)
+{
+    int count = (fmt == ORC_MX_E4M3) ? 127 : 8; /* E4M3 code 0x7F is NaN: 0..0x7E are magnitudes */
+    int lo = 0;
+    int hi = count - 1;
+    /* largest code whose value <= mag */
+    while (lo < hi) {
+        int mid = (lo + hi + 1) / 2;
+        float v = (fmt == ORC_MX_E4M3) ? orc_e4m3_to_float((uint8_t)mid) : orc_e2m1_to_float((uint8_t)mid);
+        if (v <= mag) {
+            lo = mid;
+        } else {
+            hi = mid - 1;
+        }
+    }
+    if (lo == count - 1) {
+        return (uint8_t)lo;
+    }
+    float lower = (fmt == ORC_MX_E4M3) ? orc_e4m3_to_float((uint8_t)lo) : orc_e2m1_to_float((uint8_t)lo);
+    float upper =
+        (fmt == ORC_MX_E4M3) ? orc_e4m3_to_float((uint8_t)(lo + 1)) : orc_e2m1_to_float((uint8_t)(lo + 1));
+    return ((mag - lower) <= (upper - mag)) ? (uint8_t)lo : (uint8_t)(lo + 1);
+}
+
+void orc_mx_quantize(uint32_t rows, uint32_t cols, int fmt, const float *x, uint8_t *q, uint8_t *sf,
+                     float *deq)
+{
+    const int emax = (fmt == ORC_MX_E4M3) ? 8 : 2;
+    const float max_value = (fmt == ORC_MX_E4M3) ? 448.0f : 6.0f;
+    const uint8_t sign_bit = (fmt == ORC_MX_E4M3) ? 0x80 : 0x08;
+    uint32_t blocks = (cols + 31) / 32;
+    for (uint32_t r = 0; r < rows; ++r) {
+        for (uint32_t b = 0; b < blocks; ++b) {
+            uint32_t c0 = b * 32;
+            uint32_t c1 = c0 + 32 < cols ? c0 + 32 : cols;
+            float max_abs = 0.0f;
+            for (uint32_t c = c0; c < c1; ++c) {
+                float v = fabsf(x[(size_t)r * cols + c]);
+                if (v > max_abs) {
+                    max_abs = v;
+                }
+            }
+            int exp = 0;
+            if (!(max_abs < 1e-12f)) {
+                uint32_t bits;
+                memcpy(&bits, &max_abs, 4);
+                exp = (int)((bits >> 23) & 0xFF) - 127 - emax;
+                if (exp < -128) {
+                    exp = -128;
+                }
+                if (exp > 127) {
+                    exp = 127;
+                }
+            }
+            /* torch.float8_e8m0fnu stores 2^exp as exp+127; 2^-128 is not representable and rounds
+             * to the smallest code. */
+            int code = exp + 127;
+            if (code < 0) {
+                code = 0;
+            }
+            sf[(size_t)r * blocks + b] = (uint8_t)code;
+            float scale = ldexpf(1.0f, exp);
+            for (uint32_t c = c0; c < c1; ++c) {
+                float v = x[(size_t)r * cols + c] / scale;
+                if (v > max_value) {
+                    v = max_value;
+                }
+                if (v < -max_value) {
+                    v = -max_value;
+                }
+                uint8_t code_mag = snap_magnitude(fabsf(v), fmt);
+                uint8_t out = code_mag;
+                if (v < 0.0f && code_mag != 0) {
+                    out |= sign_bit;
+                }
+                q[(size_t)r * cols + c] = out;
+                if (deq) {
+                    float e = (fmt == ORC_MX_E4M3) ? orc_e4m3_to_float(out) : orc_e2m1_to_float(out);
+                    deq[(size_t)r * cols + c] = e * scale;
+                }
+            }
+        }
+    }
+}
+
+void orc_mx_matmul(uint32_t m, uint32_t n, uint32_t k, int fmt, const uint8_t *aq, const uint8_t *sfa,
+                   const uint8_t *bq, const uint8_t *sfb, float *out)
+{
+    uint32_t blocks = (k + 31) / 32;
+    float *a_deq = (float *)malloc(sizeof(float) * (size_t)(k ? k : 1));
+    float *b_deq = (float *)malloc(sizeof(float) * (size_t)n * (k ? k : 1));
+    for (uint32_t j = 0; j < n; ++j) {
+        for (uint32_t kk = 0; kk < k; ++kk) {
+            uint8_t e = bq[(size_t)j * k + kk];
+            float v = (fmt == ORC_MX_E4M3) ? orc_e4m3_to_float(e) : orc_e2m1_to_float(e);
+            b_deq[(size_t)j * k + kk] = v * orc_e8m0_to_float(sfb[(size_t)j * blocks + kk / 32]);
+        }
+    }
+    for (uint32_t i = 0; i < m; ++i) {
+        for (uint32_t kk = 0; kk < k; ++kk) {
+            uint8_t e = aq[(size_t)i * k + kk];
+            float v = (fmt == ORC_MX_E4M3) ? orc_e4m3_to_float(e) : orc_e2m1_to_float(e);
+            a_deq[kk] = v * orc_e8m0_to_float(sfa[(size_t)i * blocks + kk / 32]);
+        }
+        for (uint32_t j = 0; j < n; ++j) {
+            const float *bc = b_deq + (size_t)j * k;
+            double s = 0.0;
+            for (uint32_t kk = 0; kk < k; ++kk) {
+                s += (double)a_deq[kk] * (double)bc[kk];
+            }
+            out[(size_t)i * n + j] = (float)s;
+        }
+    }
+    free(a_deq);
+    free(b_deq);
+}

@@ -1,0 +1,116 @@
+/*
+ * CPU oracle for the quantized-matmul path: a plain-C restatement of the CATLASS CPU goldens.
+ *
+ * TEST INFRASTRUCTURE ONLY.  Nothing in the shipped library links, loads or calls this code; it exists so
+ * that the CUDA kernels can be checked against an independent, obviously-correct implementation, and so
+ * that a CPU baseline can be timed next to the GPU numbers.
+ *
+ * Parity status of each function is stated beside it:
+ *   - "pinned: reference golden"  the restatement is checked against the reference's own C++ golden
+ *                                 (compiled from the reference tree into oracle/_ref) and against
+ *                                 committed vectors produced by it;
+ *   - "pinned: reference python"  checked against committed vectors produced by the reference's Python
+ *                                 data generators;
+ *   - "parity unpinned"           the reference holds no golden for this exact formula; the restatement
+ *                                 follows the published formula only.
+ */
+#ifndef CB200_ORACLE_H
+#define CB200_ORACLE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Layout tags (same numbering as the shipped C ABI). */
+#define ORC_ROW_MAJOR 0
+#define ORC_COL_MAJOR 1
+
+/*
+ * Dense W8A8 with per-token / per-channel dequant.            [pinned: reference golden]
+ * Follows golden::QuantMatmul, examples/common/golden/matmul.hpp:303-324:
+ *   acc[i,j]  = sum_k int32(A[i,k]) * int32(B[k,j])
+ *   out[i,j]  = (float(acc) * scale[j]) * perToken[i]      (two separate fp32 multiplies, left to right)
+ * A is m x k, B is k x n, each row- or column-major; out is row-major fp32.
+ * acc (may be NULL) receives the raw int32 accumulators, row-major.
+ */
+void orc_quant_matmul(uint32_t m, uint32_t n, uint32_t k,
+                      const int8_t *a, int layout_a, const int8_t *b, int layout_b,
+                      const float *scale, const float *per_token, float *out, int32_t *acc);
+
+/*
+ * Grouped slice-M W8A8 with per-token dequant.                [pinned: reference golden]
+ * Follows golden::ComputeGroupedMatmulPerTokenDequant, examples/common/golden/matmul.hpp:271-301:
+ * group_list holds ascending prefix sums of rows; group g owns rows [group_list[g-1], group_list[g]),
+ * uses weight matrix B + g*k*n and channel scales scale + g*n.  Rows at or beyond group_list[G-1]
+ * are left untouched.
+ */
+void orc_grouped_quant_matmul_slice_m(uint32_t m, uint32_t n, uint32_t k, uint32_t group_count,
+                                      const int64_t *group_list, const int8_t *a,
+                                      const int8_t *b, int layout_b, const float *scale,
+                                      const float *per_token, float *out, int32_t *acc);
+
+/*
+ * W4A8 with per-group weight scales.                          [parity unpinned]
+ * The reference holds a per-TENSOR W4A8 golden only (examples/32_w4a8_matmul/gen_data.py:111-131,
+ * out = 1.5 * (A @ B)); the per-group formula restated here is:
+ *   acc_g[i,j] = sum_{kk in group g} int32(A[i,kk]) * int32(W[kk,j])          (int32, exact)
+ *   y[i,j]     = sum_g float(acc_g) * sw[g,j]      (fp32; separate multiply and add; g ascending)
+ *   out[i,j]   = y * sa[i]
+ * Weights are signed 4-bit, packed two per byte along K: byte t of column j holds W[2t,j] in bits 0-3
+ * and W[2t+1,j] in bits 4-7 (nibble order of examples/32_w4a8_matmul/gen_data.py:102-105), columns
+ * stored one after another (column-major B, k/2 bytes per column).  k must be even; group_size divides k.
+ */
+void orc_w4a8_matmul_per_group(uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
+                               const int8_t *a, const uint8_t *w_packed, const float *sw,
+                               const float *sa, float *out);
+
+/*
+ * W4A8 per-tensor (the reference's example 32).               [pinned: reference python]
+ * out[i,j] = scalar * float(sum_k A[i,k]*W[k,j])   (examples/32_w4a8_matmul/gen_data.py:111-131).
+ */
+void orc_w4a8_matmul_per_tensor(uint32_t m, uint32_t n, uint32_t k, const int8_t *a,
+                                const uint8_t *w_packed, float scalar, float *out);
+
+/* Unpack one signed 4-bit value (sign-extend bits 0-3). */
+static inline int orc_int4(uint8_t nibble) { return (int)((nibble & 0xF) ^ 8) - 8; }
+
+/*
+ * MX (OCP microscaling) helpers.                              [pinned: reference python]
+ * Follow examples/53_ascend950_fp8_mx_matmul/gen_data.py:186-207 (shared exponent),
+ * :216-265 (snap to grid, ties toward zero), and examples/54_ascend950_fp4_mx_matmul/gen_data.py:46-95.
+ *
+ * orc_mx_quantize: rows x cols fp32 matrix, blocks of 32 along the contiguous (cols) axis.
+ *   fmt = 0: E4M3 (emax 8, max 448);  fmt = 1: E2M1 (emax 2, max 6).
+ *   q      : one byte per element (E4M3 bit pattern, or E2M1 code 0..15 in the low nibble)
+ *   sf     : rows x ceil(cols/32) E8M0 bytes (exponent + 127)
+ *   deq    : (may be NULL) dequantised fp32 values, rows x cols
+ */
+#define ORC_MX_E4M3 0
+#define ORC_MX_E2M1 1
+void orc_mx_quantize(uint32_t rows, uint32_t cols, int fmt, const float *x, uint8_t *q, uint8_t *sf,
+                     float *deq);
+float orc_e4m3_to_float(uint8_t v);
+float orc_e2m1_to_float(uint8_t v);
+float orc_e8m0_to_float(uint8_t v);
+
+/*
+ * MX block-scaled matmul golden: out = A_deq @ B_deq in fp32 (gen_data.py:417 of example 53).
+ * aq: m x k element bytes, row-major (K contiguous); bq: n x k element bytes (column-major B, K contiguous);
+ * sfa: m x ceil(k/32), sfb: n x ceil(k/32).  Products are accumulated in double and rounded once to fp32,
+ * which lies inside the reference's own tolerance band (rtol 1/128) around its fp32 matmul.
+ */
+void orc_mx_matmul(uint32_t m, uint32_t n, uint32_t k, int fmt, const uint8_t *aq, const uint8_t *sfa,
+                   const uint8_t *bq, const uint8_t *sfb, float *out);
+
+/* fp32 -> bf16 bits, round to nearest even (NaN kept quiet). */
+uint16_t orc_bf16_rne(float x);
+void orc_bf16_rne_array(const float *x, uint16_t *y, size_t count);
+float orc_bf16_to_float(uint16_t v);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
