@@ -322,27 +322,34 @@ def run_dense(args, rank, world, local):
     scale = torch.empty(n, device=dev).uniform_(1e-3, 1e-2, generator=gen)
     pt = torch.empty(m, device=dev).uniform_(1e-3, 1e-2, generator=gen)
     d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-    flush = torch.empty(256 << 20, dtype=torch.int8, device=dev)  # > L2 (126 MB)
-    decode = m <= 64
+    decode = m <= 128
+    # decode shapes are HBM-bound: rotate over enough copies of the weights that a pass never finds its
+    # copy in L2 (copies x bytes(B) > 2 x L2), instead of flushing with writes that would leave dirty lines
+    copies = 1
+    if decode:
+        copies = int(np.ceil(2 * 126e6 / (n * k))) + 1
+    bs = [b] + [b.clone() for _ in range(copies - 1)]
+    it = [0]
 
     def step():
-        capi.quant_matmul(a, b, scale, pt, d, m, n, k, layout_b=capi.COLUMN_MAJOR)
+        capi.quant_matmul(a, bs[it[0] % copies], scale, pt, d, m, n, k, layout_b=capi.COLUMN_MAJOR)
+        it[0] += 1
 
-    for _ in range(args.warmup):
+    for _ in range(max(args.warmup, copies)):
         step()
     torch.cuda.synchronize()
     sampler = ClockSampler(local)
-    times = []
     launches0 = capi.launch_count()
+    # keep the GPU busy while the host enqueues the K timed launches: otherwise the events would time the
+    # host's launch path (tens of microseconds in Python) instead of kernels that last ten
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(int(2.0e6 * args.steps) + 10_000_000)
+    s0.record()
     for _ in range(args.steps):
-        if decode:
-            flush.fill_(1)  # evict the weights: every timed pass reads them from HBM
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record()
         step()
-        s1.record()
-        torch.cuda.synchronize()
-        times.append(s0.elapsed_time(s1))
+    s1.record()
+    torch.cuda.synchronize()
+    times = [s0.elapsed_time(s1) / args.steps]
     launches = capi.launch_count() - launches0
     clocks = sampler.stop()
     st, code = capi.device_status()
@@ -363,7 +370,8 @@ def run_dense(args, rank, world, local):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
         "config": {"workload": f"{args.workload}: W8A8 dequant GEMM M={m} N={n} K={k}, column-major B, bf16 out",
-                   "l2": "flushed between timed passes (256 MB write)" if decode else "inputs fit L2; steady state"},
+                   "l2": (f"weights rotate over {copies} copies ({copies * n * k / 1e6:.0f} MB > 2 x L2): every pass reads HBM"
+                          if decode else "inputs fit L2; steady state")},
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "traffic": None, "peak_source": peaks["source"], "algorithmic_bytes": nbytes, "ops": ops,
                      "frac_of_8TBs": achieved / 8000.0 if decode else None},

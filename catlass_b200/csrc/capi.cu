@@ -3,8 +3,12 @@
 // has no CPU compute path: without a sm_100 device every launch entry returns an error.
 #include <cuda_bf16.h>
 
+#include <cmath>
+#include <cstdlib>
+
 #include "host_runtime.cuh"
 #include "w8a8_gemm.cuh"
+#include "w8a8_smallm.cuh"
 
 using namespace cb200;
 using namespace cb200::host;
@@ -146,6 +150,162 @@ int launch_w8a8(const W8A8Problem& q, const DeviceState& dev, cudaStream_t strea
     return CB200_SUCCESS;
 }
 
+// Few-token (m <= 128) dense problems: weights on the UMMA M axis, K split over a cluster.
+template <bool kWMn>
+int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t stream)
+{
+    SmallMParams p;
+    p.m = q.m;
+    p.n = q.n;
+    p.k = q.k;
+    p.mt = (q.m + 15u) & ~15u;
+    p.num_k_blocks = (q.k + kBlockKBytes - 1) / kBlockKBytes;
+    // Tile height R (weight rows per CTA) and K split S: one CTA per SM, so the grid should be a whole
+    // number of waves of sm_count CTAs with as little padding as possible.  Cost of a candidate, in
+    // "bytes": every wave pays a fixed start-up/drain equivalent plus its share of the weight stream;
+    // a split adds the cluster reduction.
+    const uint32_t max_by_partials = 1u + (96u * 1024u) / (kSmallMTileN * p.mt * 4u);
+    uint32_t splits = 1, tile_rows = kSmallMTileN;
+    auto kernel = w8a8_smallm_kernel<kWMn>;
+    static bool attr_set[kMaxDevices] = {};
+    static int resident_ctas[kMaxDevices][4] = {};  // co-resident CTAs for cluster sizes 1, 2, 4, 8
+    int devid = 0;
+    CB200_CUDA_TRY(cudaGetDevice(&devid));
+    if (!attr_set[devid]) {
+        CB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        // clusters must sit inside one GPC, so fewer CTAs than SMs may be resident at once: ask the runtime
+        for (int i = 0; i < 4; ++i) {
+            cudaLaunchConfig_t oc = {};
+            oc.gridDim = dim3(static_cast<unsigned>(dev.sm_count) * 8u, 1, 1);
+            oc.blockDim = dim3(kSmallMThreads, 1, 1);
+            oc.dynamicSmemBytes = 200 * 1024;  // one CTA per SM, as launched below
+            cudaLaunchAttribute oa[1];
+            oa[0].id = cudaLaunchAttributeClusterDimension;
+            oa[0].val.clusterDim.x = 1u << i;
+            oa[0].val.clusterDim.y = 1;
+            oa[0].val.clusterDim.z = 1;
+            oc.attrs = oa;
+            oc.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &oc) != cudaSuccess || clusters <= 0) {
+                clusters = dev.sm_count >> i;
+                (void)cudaGetLastError();
+            }
+            resident_ctas[devid][i] = clusters << i;
+        }
+        attr_set[devid] = true;
+    }
+    {
+        const double sm_all = static_cast<double>(dev.sm_count);
+        const double fixed = 3.5e-6 * 6.5e12 / sm_all;   // per-CTA start-up + epilogue, as bytes at full rate
+        const double reduce = 2.0e-6 * 6.5e12 / sm_all;  // cluster barrier + DSMEM reduction
+        double best = 1e300;
+        int si = 0;
+        for (uint32_t s = 1; s <= static_cast<uint32_t>(kSmallMMaxSplits); s *= 2, ++si) {
+            if (s > max_by_partials || s > p.num_k_blocks) {
+                break;
+            }
+            const double sm = static_cast<double>(resident_ctas[devid][si]);
+            for (uint32_t r = kSmallMTileN; r >= 64; r -= 8) {
+                if (kWMn && r != static_cast<uint32_t>(kSmallMTileN)) {
+                    break;  // row-major weights: a tile is 128 contiguous bytes of n
+                }
+                const uint32_t tiles = (q.n + r - 1) / r;
+                const double ctas = static_cast<double>(tiles) * s;
+                const double waves = ceil(ctas / sm);
+                const double kb_per = ceil(static_cast<double>(p.num_k_blocks) / s);
+                const double cta_bytes = static_cast<double>(r + p.mt) * kb_per * kBlockKBytes;
+                const double cost = waves * (fixed + (s > 1 ? reduce : 0.0) + cta_bytes);
+                if (cost < best) {
+                    best = cost;
+                    splits = s;
+                    tile_rows = r;
+                }
+            }
+        }
+    }
+    p.tile_rows = tile_rows;
+    // a ring stage holds 4 neighbouring K blocks: 512 contiguous bytes per weight row are requested together
+    uint32_t kbs = 4;
+    if (const char* e = getenv("CB200_SMALLM_KBS")) {
+        const uint32_t v = static_cast<uint32_t>(atoi(e));
+        if (v >= 1 && v <= 8) {
+            kbs = v;
+        }
+    }
+    while (kbs > 1 && 2 * smallm_stage_bytes(p.mt, kbs) > 216u * 1024u) {
+        kbs /= 2;  // wide token panels: keep at least two stages
+    }
+    p.kbs = kbs;
+    const uint32_t stage_bytes = smallm_stage_bytes(p.mt, kbs);
+    uint32_t stages = (216u * 1024u) / stage_bytes;  // one CTA per SM
+    // developer knobs for tuning runs: CB200_SMALLM_SPLITS / CB200_SMALLM_STAGES override the heuristic
+    if (const char* e = getenv("CB200_SMALLM_SPLITS")) {
+        const uint32_t v = static_cast<uint32_t>(atoi(e));
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= max_by_partials && v <= p.num_k_blocks) {
+            splits = v;
+        }
+    }
+    if (const char* e = getenv("CB200_SMALLM_ROWS")) {
+        const uint32_t v = static_cast<uint32_t>(atoi(e));
+        if (!kWMn && v >= 8 && v <= 128 && v % 8 == 0) {
+            p.tile_rows = v;
+        }
+    }
+    if (const char* e = getenv("CB200_SMALLM_STAGES")) {
+        const uint32_t v = static_cast<uint32_t>(atoi(e));
+        if (v >= 2 && v * stage_bytes <= 216u * 1024u) {
+            stages = v;
+        }
+    }
+    p.splits = splits;
+    stages = stages > static_cast<uint32_t>(kSmallMMaxStages) ? kSmallMMaxStages : (stages < 2 ? 2 : stages);
+    p.stages = stages;
+    p.scale = q.scale;
+    p.per_token = q.per_token;
+    p.d = static_cast<__nv_bfloat16*>(q.d);
+    p.acc = q.acc;
+    p.status = dev.status;
+
+    CUtensorMap tmap_w, tmap_x;
+    {
+        const uint64_t dims_k[2] = {q.k, q.n};
+        const uint64_t dims_n[2] = {q.n, q.k};
+        const uint64_t strides[1] = {kWMn ? q.n : q.k};
+        const uint32_t box[2] = {128, kWMn ? 128u : p.tile_rows};
+        int rc = encode_tmap_u8(&tmap_w, q.b, 2, kWMn ? dims_n : dims_k, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    {
+        const uint64_t dims[2] = {q.k, q.m};
+        const uint64_t strides[1] = {q.k};
+        const uint32_t box[2] = {kBlockKBytes, p.mt};
+        int rc = encode_tmap_u8(&tmap_x, q.a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    const uint32_t smem = smallm_smem_bytes(p.mt, p.stages, p.splits, p.kbs);
+    const uint32_t n_tiles = (q.n + p.tile_rows - 1) / p.tile_rows;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles * p.splits, 1, 1);
+    cfg.blockDim = dim3(kSmallMThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmap_w, tmap_x, p));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return CB200_SUCCESS;
+}
+
 int run_w8a8(const W8A8Problem& q, uint32_t layout_a, void* stream_v)
 {
     int rc = check_w8a8(q, layout_a);
@@ -170,6 +330,9 @@ int run_w8a8(const W8A8Problem& q, uint32_t layout_a, void* stream_v)
         return CB200_SUCCESS;
     }
     const bool b_mn = q.layout_b == CB200_ROW_MAJOR;
+    if (q.group_count == 0 && q.m <= 128) {
+        return b_mn ? launch_smallm<true>(q, *dev, stream) : launch_smallm<false>(q, *dev, stream);
+    }
     if (q.n > 128) {
         return b_mn ? launch_w8a8<256, true>(q, *dev, stream) : launch_w8a8<256, false>(q, *dev, stream);
     }

@@ -1,0 +1,318 @@
+// W8A8 dequant GEMM for few tokens (M <= 128): the decode-shaped, HBM-bound case.
+//
+// The problem is transposed onto the tensor core: a tile is 128 WEIGHT rows (output channels n) on the
+// UMMA M axis / TMEM lanes and all MT = round_up(M, 16) tokens on the UMMA N axis, so a token panel as small
+// as 16 wastes nothing of the 128-lane datapath and every weight byte is read from HBM exactly once.
+// K is split over the `splits` CTAs of a thread-block cluster; each streams its slice of the weight panel
+// through a deep TMA ring, accumulates int32 in TMEM, and the partial sums are added - still as int32, so
+// the result stays bit-exact - in the shared memory of the cluster's first CTA (distributed shared memory,
+// no global workspace, no atomics).  That CTA applies (float(acc) * scale[n]) * per_token[m] and writes bf16.
+//
+// Covers what the reference's decode-oriented variants are for: the A-resident kernel
+// (include/catlass/gemm/kernel/quant_matmul_full_loadA_tla.hpp) and multi-core split-K
+// (examples/52_quant_multi_core_splitk_matmul_tla), with the reduction kept on chip.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+#include "w8a8_gemm.cuh"
+
+namespace cb200 {
+
+constexpr int kSmallMThreads = 192;
+constexpr int kSmallMTileN = 128;     // weight rows per tile
+constexpr int kSmallMMaxStages = 8;
+constexpr int kSmallMMaxSplits = 8;   // portable cluster size
+
+struct SmallMParams {
+    uint32_t m, n, k;
+    uint32_t mt;            // tokens padded to a multiple of 16 (<= 128)
+    uint32_t splits;        // cluster size along K (1, 2, 4 or 8)
+    uint32_t num_k_blocks;  // ceil(k / 128)
+    uint32_t stages;        // ring depth (fits the dynamic smem given at launch)
+    uint32_t kbs;           // 128-byte K blocks per ring stage: one stage = kbs*128 contiguous bytes per weight row
+    uint32_t tile_rows;     // weight rows a CTA owns (<= 128, multiple of 8): chosen so the tiles fill the SMs
+    const float* scale;     // [n]
+    const float* per_token; // [m]
+    __nv_bfloat16* d;       // [m][n]
+    int32_t* acc;           // optional [m][n]
+    unsigned* status;
+};
+
+// dynamic smem: [1024 align pad][stages x (16 KB W + mt*128 B X)][(splits-1) x 128 x mt x 4 B partials,
+// aliased onto the ring][barriers]
+__host__ __device__ inline uint32_t smallm_block_bytes(uint32_t mt)
+{
+    return kSmallMTileN * kBlockKBytes + mt * kBlockKBytes;
+}
+__host__ __device__ inline uint32_t smallm_stage_bytes(uint32_t mt, uint32_t kbs)
+{
+    return kbs * smallm_block_bytes(mt);
+}
+__host__ __device__ inline uint32_t smallm_smem_bytes(uint32_t mt, uint32_t stages, uint32_t splits, uint32_t kbs)
+{
+    uint32_t ring = stages * smallm_stage_bytes(mt, kbs);
+    uint32_t partials = (splits - 1) * kSmallMTileN * mt * 4;
+    uint32_t body = ring > partials ? ring : partials;
+    return 1024 + body + (2 * kSmallMMaxStages + 1) * 8 + 16;
+}
+
+template <bool kWMnMajor>
+__global__ void __launch_bounds__(kSmallMThreads)
+w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                   const SmallMParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t ring = raw_addr + pad;
+
+    const uint32_t block_bytes = smallm_block_bytes(p.mt);
+    const uint32_t stage_bytes = smallm_stage_bytes(p.mt, p.kbs);
+    const uint32_t ring_bytes = p.stages * stage_bytes;
+    const uint32_t partial_bytes = (p.splits - 1) * kSmallMTileN * p.mt * 4;
+    const uint32_t body = ring_bytes > partial_bytes ? ring_bytes : partial_bytes;
+    uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + body);
+    const uint32_t bar_full = smem_u32(s_bars);
+    const uint32_t bar_empty = bar_full + kSmallMMaxStages * 8;
+    const uint32_t bar_tmem_full = bar_empty + kSmallMMaxStages * 8;
+    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 2 * kSmallMMaxStages + 1);
+    volatile uint32_t* s_abort = s_tmem_ptr + 1;
+    int32_t* s_partials = reinterpret_cast<int32_t*>(smem);  // [(splits-1)][128][mt], leader CTA only
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+#ifdef CB200_DEBUG
+    __shared__ unsigned long long s_ts[8];
+    if (threadIdx.x == 0) {
+        s_ts[0] = globaltimer_ns();
+    }
+#define CB200_TS(i) s_ts[i] = globaltimer_ns()
+#else
+#define CB200_TS(i)
+#endif
+    const uint32_t split = p.splits > 1 ? cluster_ctarank() : 0;
+    const uint32_t tile = blockIdx.x / p.splits;
+    const int32_t n0 = static_cast<int32_t>(tile * p.tile_rows);
+
+    // this CTA's slice of K, in 128-byte blocks
+    const uint32_t kb_per = (p.num_k_blocks + p.splits - 1) / p.splits;
+    const uint32_t kb_begin = split * kb_per < p.num_k_blocks ? split * kb_per : p.num_k_blocks;
+    const uint32_t kb_end = kb_begin + kb_per < p.num_k_blocks ? kb_begin + kb_per : p.num_k_blocks;
+    const uint32_t my_kb = kb_end - kb_begin;
+
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < p.mt) {
+        tmem_cols <<= 1;
+    }
+
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        mbar_init(bar_tmem_full, 1);
+        fence_mbar_init();
+        prefetch_tmap(&tmap_w);
+        prefetch_tmap(&tmap_x);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(s_tmem_ptr), tmem_cols);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *s_tmem_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t kb = kb_begin; kb < kb_end; kb += p.kbs) {
+                if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer)) {
+                    break;
+                }
+                const uint32_t full = bar_full + stage * 8;
+                const uint32_t nsub = kb_end - kb < p.kbs ? kb_end - kb : p.kbs;
+                // the W box holds tile_rows rows; the UMMA still reads 128: the rows behind are never stored
+                mbar_expect_tx(full, nsub * (p.tile_rows + p.mt) * kBlockKBytes);
+                // the sub-blocks of a stage are neighbours in K: each weight row is read in runs of
+                // nsub*128 contiguous bytes issued together
+                for (uint32_t sub = 0; sub < nsub; ++sub) {
+                    const uint32_t sw = ring + stage * stage_bytes + sub * block_bytes;
+                    const int32_t k0 = static_cast<int32_t>(kb + sub) * kBlockKBytes;
+                    if constexpr (kWMnMajor) {
+                        tma_load_2d(sw, &tmap_w, full, n0, k0);  // rows = k, 128 bytes of n
+                    } else {
+                        tma_load_2d(sw, &tmap_w, full, k0, n0);  // rows = n, 128 bytes of k
+                    }
+                }
+                for (uint32_t sub = 0; sub < nsub; ++sub) {
+                    const uint32_t sx = ring + stage * stage_bytes + sub * block_bytes + kSmallMTileN * kBlockKBytes;
+                    tma_load_2d(sx, &tmap_x, full, static_cast<int32_t>(kb + sub) * kBlockKBytes, 0);
+                }
+                if (++stage == p.stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && my_kb != 0) {
+            const uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, kWMnMajor, false, kSmallMTileN, p.mt);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            CB200_TS(1);
+            for (uint32_t kb = 0; kb < my_kb; kb += p.kbs) {
+                ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
+                if (!ok) {
+                    break;
+                }
+                if (kb == 0) {
+                    CB200_TS(2);
+                }
+                tcgen05_fence_after();
+                const uint32_t nsub = my_kb - kb < p.kbs ? my_kb - kb : p.kbs;
+                for (uint32_t sub = 0; sub < nsub; ++sub) {
+                    const uint32_t sw = ring + stage * stage_bytes + sub * block_bytes;
+                    const uint32_t sx = sw + kSmallMTileN * kBlockKBytes;
+#pragma unroll
+                    for (int j = 0; j < kBlockKBytes / kUmmaK; ++j) {
+                        uint64_t dw;
+                        if constexpr (kWMnMajor) {
+                            dw = make_smem_desc_sw128(sw + j * (kUmmaK * 128), kBlockKBytes * 128, 1024);
+                        } else {
+                            dw = make_smem_desc_sw128(sw + j * kUmmaK, 16, 1024);
+                        }
+                        const uint64_t dx = make_smem_desc_sw128(sx + j * kUmmaK, 16, 1024);
+                        umma_i8<1>(tmem_base, dw, dx, idesc, (kb | sub | j) != 0 ? 1u : 0u);
+                    }
+                }
+                umma_commit<1>(bar_empty + stage * 8);
+                if (++stage == p.stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (ok) {
+                umma_commit<1>(bar_tmem_full);
+            }
+            CB200_TS(3);
+        }
+        __syncwarp();
+    }
+
+    // ---- epilogue: warps 2..5 own the accumulator rows; every thread of the cluster passes both cluster
+    // barriers, whatever happened before, so no CTA can be left waiting for a peer
+    const bool epi = warp >= 2;
+    const uint32_t quad = warp & 3;
+    const uint32_t row = quad * 32 + lane;  // weight row inside the tile = TMEM lane
+    bool have = false;                      // this thread's accumulator row is valid
+    if (epi && my_kb != 0) {
+        bool ok = mbar_wait(bar_tmem_full, 0, s_abort, p.status, kDevTimeoutEpilogue);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tcgen05_fence_after();
+            have = true;
+        }
+        if (threadIdx.x == 64) {
+            CB200_TS(4);
+        }
+    }
+    const uint32_t taddr = tmem_base + ((quad * 32u) << 16);
+    const uint32_t chunks = p.mt / 16;
+
+    if (p.splits > 1) {
+        cluster_sync();  // the leader's ring is idle from here on: it becomes the partial-sum buffer
+        if (split != 0 && epi) {
+            // remote address of slot (split-1), this thread's row
+            const uint32_t local = smem_u32(s_partials) + ((split - 1) * kSmallMTileN + row) * p.mt * 4;
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0u));
+            for (uint32_t c = 0; c < chunks; ++c) {
+                uint32_t r[16];
+                if (have) {
+                    tmem_ld_32x32b_x16(taddr + c * 16, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        r[i] = 0;
+                    }
+                }
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(remote + c * 64 + v * 16),
+                                 "r"(r[v * 4]), "r"(r[v * 4 + 1]), "r"(r[v * 4 + 2]), "r"(r[v * 4 + 3])
+                                 : "memory");
+                }
+            }
+        }
+        cluster_sync();  // partial sums have landed in the leader's smem
+    }
+
+    if (split == 0 && epi) {
+        const uint32_t ncol = static_cast<uint32_t>(n0) + row;
+        const bool n_ok = ncol < p.n && row < p.tile_rows;
+        const float sc = n_ok ? __ldg(p.scale + ncol) : 0.0f;
+        for (uint32_t c = 0; c < chunks; ++c) {
+            uint32_t r[16];
+            if (have) {
+                tmem_ld_32x32b_x16(taddr + c * 16, r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    r[i] = 0;
+                }
+            }
+            for (uint32_t s = 1; s < p.splits; ++s) {
+                const uint4* src =
+                    reinterpret_cast<const uint4*>(s_partials + ((s - 1) * kSmallMTileN + row) * p.mt + c * 16);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const uint4 q = src[v];
+                    r[v * 4] += q.x;
+                    r[v * 4 + 1] += q.y;
+                    r[v * 4 + 2] += q.z;
+                    r[v * 4 + 3] += q.w;
+                }
+            }
+            if (n_ok) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t mrow = c * 16 + i;
+                    if (mrow < p.m) {
+                        const float x = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[i])), sc),
+                                                  __ldg(p.per_token + mrow));
+                        p.d[static_cast<size_t>(mrow) * p.n + ncol] = __float2bfloat16_rn(x);
+                        if (p.acc != nullptr) {
+                            p.acc[static_cast<size_t>(mrow) * p.n + ncol] = static_cast<int32_t>(r[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<1>(tmem_base, tmem_cols);
+    }
+#ifdef CB200_DEBUG
+    if (threadIdx.x == 0 && (blockIdx.x % 97) == 0) {
+        const unsigned long long t5 = globaltimer_ns();
+        printf("[ts] cta %u split %u: setup %llu first_full %llu mma_done_issue %llu tmem_full %llu end %llu (ns from start) start_abs %llu\n",
+               blockIdx.x, split, s_ts[1] - s_ts[0], s_ts[2] - s_ts[0], s_ts[3] - s_ts[0], s_ts[4] - s_ts[0],
+               t5 - s_ts[0], s_ts[0] % 100000000ull);
+    }
+#endif
+}
+
+}  // namespace cb200

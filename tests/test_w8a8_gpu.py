@@ -85,6 +85,19 @@ def test_dense_row_major_b(cuda, m, n, k):
     run_dense(cuda, m, n, k, False, seed=m * 5 + n + k)
 
 
+# few-token (decode) shapes: the transposed split-K kernel, 1/2/4/8-way clusters, token padding
+SMALL_M_CASES = [
+    (16, 14336, 4096, True), (16, 4096, 14336, True), (16, 1024, 4096, False), (1, 384, 2048, True),
+    (33, 640, 2048, False), (64, 512, 8192, True), (128, 256, 16384, False), (17, 200, 1040, True),
+    (5, 128, 640, True),
+]
+
+
+@pytest.mark.parametrize("m,n,k,col", SMALL_M_CASES)
+def test_dense_few_tokens(cuda, m, n, k, col):
+    run_dense(cuda, m, n, k, col, seed=m + n + k)
+
+
 def test_dense_extreme_values(cuda):
     """All operands at +-127/-128: the largest accumulator magnitudes the int8 path can produce."""
     from catlass_b200 import capi
