@@ -379,6 +379,60 @@ def run_dense(args, rank, world, local):
     }
 
 
+def run_w4a8(args, rank, world, local):
+    """M=128, N=8192, K=8192, group 128: int4 weights packed along K, HBM-bound."""
+    import torch
+    from catlass_b200 import capi
+    m, n, k, gs = 128, 8192, 8192, 128
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4321)
+    a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev, generator=gen)
+    copies = int(np.ceil(2 * 126e6 / (n * k // 2))) + 1
+    ws = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=gen) for _ in range(copies)]
+    sw = torch.empty((k // gs, n), device=dev).uniform_(1e-3, 1e-2, generator=gen)
+    sa = torch.empty(m, device=dev).uniform_(1e-3, 1e-2, generator=gen)
+    d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    it = [0]
+
+    def step():
+        capi.w4a8_matmul(a, ws[it[0] % copies], sw, sa, d, m, n, k, gs)
+        it[0] += 1
+
+    for _ in range(max(args.warmup, copies)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    launches0 = capi.launch_count()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(int(2.0e6 * args.steps) + 10_000_000)
+    s0.record()
+    for _ in range(args.steps):
+        step()
+    s1.record()
+    torch.cuda.synchronize()
+    ms = s0.elapsed_time(s1) / args.steps
+    launches = capi.launch_count() - launches0
+    clocks = sampler.stop()
+    st, code = capi.device_status()
+    if st != 0:
+        raise SystemExit(f"device status {st} code {code:#x}")
+    nbytes = m * k + k * n // 2 + 4 * (k // gs) * n + 4 * m + 2 * m * n
+    peaks = measured_peaks()
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    return {
+        "metric": "w4a8_gemm_hbm_gbs", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4xint8->int32->f32", "data": "synthetic",
+        "config": {"workload": f"w4a8: M={m} N={n} K={k} group {gs}, int4 weights packed along K, bf16 out",
+                   "l2": f"weights rotate over {copies} copies: every pass reads HBM"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "algorithmic_bytes": nbytes, "frac_of_8TBs": achieved / 8000.0},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+
+
 def run_reference(args):
     """The reference arm: the reference's CPU golden on the host cores, bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
@@ -413,7 +467,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "moe_small"] + sorted(DENSE))
+    ap.add_argument("--workload", default="moe", choices=["moe", "moe_small", "w4a8"] + sorted(DENSE))
     ap.add_argument("--placement", default="split", choices=["split", "whole"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -434,6 +488,8 @@ def main():
     rank, world, local = dist_setup(args.gpus)
     if args.workload in ("moe", "moe_small"):
         res = run_moe(args, rank, world, local)
+    elif args.workload == "w4a8":
+        res = run_w4a8(args, rank, world, local)
     else:
         if world != 1:
             raise SystemExit("dense workloads are single-GPU")

@@ -32,6 +32,14 @@ class GroupedQuantMatmulArgs(ctypes.Structure):
     ]
 
 
+class W4A8MatmulArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("group_size", _u32),
+        ("a", _vp), ("w_packed", _vp), ("weight_scale", _vp), ("per_token_scale", _vp), ("d", _vp),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+    ]
+
+
 _lib = None
 
 
@@ -51,7 +59,8 @@ def load():
             "There is no fallback path.")
     lib = ctypes.CDLL(path)
     for name, args_t in (("cb200_quant_matmul", QuantMatmulArgs),
-                         ("cb200_grouped_quant_matmul_slice_m", GroupedQuantMatmulArgs)):
+                         ("cb200_grouped_quant_matmul_slice_m", GroupedQuantMatmulArgs),
+                         ("cb200_w4a8_matmul", W4A8MatmulArgs)):
         getattr(lib, name + "_can_implement").argtypes = [ctypes.POINTER(args_t)]
         getattr(lib, name + "_can_implement").restype = ctypes.c_int
         getattr(lib, name + "_workspace_size").argtypes = [ctypes.POINTER(args_t)]
@@ -118,3 +127,10 @@ def grouped_quant_matmul(a, b, group_list, scale, per_token, d, m, n, k, group_c
                                   block_num=block_num, reserved=0)
     _check("cb200_grouped_quant_matmul_slice_m",
            load().cb200_grouped_quant_matmul_slice_m(ctypes.byref(args), _stream(stream)))
+
+
+def w4a8_matmul(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, stream=None):
+    args = W4A8MatmulArgs(m=m, n=n, k=k, group_size=group_size, a=_p(a), w_packed=_p(w_packed),
+                          weight_scale=_p(weight_scale), per_token_scale=_p(per_token), d=_p(d), workspace=None,
+                          workspace_bytes=0, block_num=0, reserved=0)
+    _check("cb200_w4a8_matmul", load().cb200_w4a8_matmul(ctypes.byref(args), _stream(stream)))

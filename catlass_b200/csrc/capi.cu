@@ -9,6 +9,7 @@
 #include "host_runtime.cuh"
 #include "w8a8_gemm.cuh"
 #include "w8a8_smallm.cuh"
+#include "w4a8_gemm.cuh"
 
 using namespace cb200;
 using namespace cb200::host;
@@ -339,9 +340,107 @@ int run_w8a8(const W8A8Problem& q, uint32_t layout_a, void* stream_v)
     return b_mn ? launch_w8a8<128, true>(q, *dev, stream) : launch_w8a8<128, false>(q, *dev, stream);
 }
 
+int check_w4a8(const cb200_w4a8_matmul_args* a)
+{
+    if (a == nullptr) {
+        return CB200_INVALID;
+    }
+    if (a->m == 0 || a->n == 0) {
+        return CB200_SUCCESS;
+    }
+    if (a->a == nullptr || a->w_packed == nullptr || a->weight_scale == nullptr || a->per_token_scale == nullptr ||
+        a->d == nullptr) {
+        return CB200_INVALID;
+    }
+    if (a->k == 0 || a->group_size == 0 || (a->k % 128u) != 0 || (a->group_size % 128u) != 0 ||
+        (a->k % a->group_size) != 0) {
+        return CB200_INVALID;
+    }
+    if (a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u) {
+        return CB200_INVALID;
+    }
+    if (!aligned16(a->a) || !aligned16(a->w_packed) || (reinterpret_cast<uintptr_t>(a->d) & 1u) != 0 ||
+        (reinterpret_cast<uintptr_t>(a->weight_scale) & 3u) != 0 ||
+        (reinterpret_cast<uintptr_t>(a->per_token_scale) & 3u) != 0) {
+        return CB200_INVALID;
+    }
+    if ((a->n & 7u) == 0 && !aligned16(a->d)) {
+        return CB200_INVALID;  // vector stores of 8 bf16
+    }
+    return CB200_SUCCESS;
+}
+
 }  // namespace
 
 extern "C" {
+
+int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args* args)
+{
+    return check_w4a8(args);
+}
+
+uint64_t cb200_w4a8_matmul_workspace_size(const cb200_w4a8_matmul_args* args)
+{
+    (void)args;
+    return 0;  // weights are unpacked between two shared-memory buffers, never through global memory
+}
+
+int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
+{
+    int rc = check_w4a8(args);
+    if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
+        return rc;
+    }
+    DeviceState* dev = nullptr;
+    rc = device_state(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    W4A8Params p;
+    p.m = args->m;
+    p.n = args->n;
+    p.k = args->k;
+    p.mt = args->m >= static_cast<uint32_t>(kW4TileM) ? kW4TileM : ((args->m + 15u) & ~15u);
+    p.blocks_per_group = args->group_size / 128u;
+    p.num_k_blocks = args->k / 128u;
+    p.sw = args->weight_scale;
+    p.sa = args->per_token_scale;
+    p.d = static_cast<__nv_bfloat16*>(args->d);
+    p.status = dev->status;
+    CUtensorMap tmap_w, tmap_x;
+    {
+        const uint64_t dims[2] = {args->k / 2u, args->n};
+        const uint64_t strides[1] = {args->k / 2u};
+        const uint32_t box[2] = {64, kW4TileN};
+        rc = encode_tmap_u8(&tmap_w, args->w_packed, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    {
+        const uint64_t dims[2] = {args->k, args->m};
+        const uint64_t strides[1] = {args->k};
+        const uint32_t box[2] = {128, p.mt};
+        rc = encode_tmap_u8(&tmap_x, args->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    static bool attr_set[kMaxDevices] = {};
+    int devid = 0;
+    CB200_CUDA_TRY(cudaGetDevice(&devid));
+    if (!attr_set[devid]) {
+        CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            W4A8Smem::kTotalBytes));
+        attr_set[devid] = true;
+    }
+    const dim3 grid((args->n + kW4TileN - 1) / kW4TileN, (args->m + kW4TileM - 1) / kW4TileM, 1);
+    w4a8_gemm_kernel<<<grid, kW4Threads, W4A8Smem::kTotalBytes, static_cast<cudaStream_t>(stream_v)>>>(tmap_w,
+                                                                                                       tmap_x, p);
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return CB200_SUCCESS;
+}
 
 int cb200_quant_matmul_can_implement(const cb200_quant_matmul_args* args)
 {

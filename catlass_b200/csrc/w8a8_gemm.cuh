@@ -19,9 +19,6 @@
 #pragma once
 
 #include <cuda_bf16.h>
-#ifdef CB200_DEBUG
-#include <cstdio>
-#endif
 
 #include "ptx.cuh"
 
@@ -245,14 +242,6 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     tcgen05_fence_after();
                     const uint32_t sa = ring + stage * S::kStageBytes;
                     const uint32_t sb = sa + S::kStageABytes;
-#ifdef CB200_DEBUG
-                    if (blockIdx.x == 0 && kb == 0) {
-                        const uint32_t* wa = reinterpret_cast<const uint32_t*>(smem + stage * S::kStageBytes);
-                        const uint32_t* wb = wa + S::kStageABytes / 4;
-                        printf("[dbg] tmem_base=%x ring=%x sa=%x sb=%x A=%08x %08x %08x %08x B=%08x %08x %08x %08x idesc=%x\n",
-                               tmem_base, ring, sa, sb, wa[0], wa[1], wa[2], wa[3], wb[0], wb[1], wb[2], wb[3], idesc);
-                    }
-#endif
 #pragma unroll
                     for (int j = 0; j < kBlockKBytes / kUmmaK; ++j) {
                         const uint64_t da = make_smem_desc_sw128(sa + j * kUmmaK, 16, 1024);
@@ -322,12 +311,6 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
                 const uint32_t col0 = t.n0 + c * 32;
-#ifdef CB200_DEBUG
-                if (blockIdx.x == 0 && c == 0 && lane == 0) {
-                    printf("[dbg] epi warp %u quad %u row %d taddr=%x r0..3=%d %d %d %d\n", warp, quad, row, taddr,
-                           (int)r[0], (int)r[1], (int)r[2], (int)r[3]);
-                }
-#endif
                 if (row_ok && col0 < p.n) {
                     const float* scc = sc + c * 32;
                     if (vec_ok && col0 + 32 <= p.n) {

@@ -84,15 +84,6 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-#ifdef CB200_DEBUG
-    __shared__ unsigned long long s_ts[8];
-    if (threadIdx.x == 0) {
-        s_ts[0] = globaltimer_ns();
-    }
-#define CB200_TS(i) s_ts[i] = globaltimer_ns()
-#else
-#define CB200_TS(i)
-#endif
     const uint32_t split = p.splits > 1 ? cluster_ctarank() : 0;
     const uint32_t tile = blockIdx.x / p.splits;
     const int32_t n0 = static_cast<int32_t>(tile * p.tile_rows);
@@ -166,14 +157,10 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             const uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, kWMnMajor, false, kSmallMTileN, p.mt);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            CB200_TS(1);
             for (uint32_t kb = 0; kb < my_kb; kb += p.kbs) {
                 ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
                 if (!ok) {
                     break;
-                }
-                if (kb == 0) {
-                    CB200_TS(2);
                 }
                 tcgen05_fence_after();
                 const uint32_t nsub = my_kb - kb < p.kbs ? my_kb - kb : p.kbs;
@@ -201,7 +188,6 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             if (ok) {
                 umma_commit<1>(bar_tmem_full);
             }
-            CB200_TS(3);
         }
         __syncwarp();
     }
@@ -218,9 +204,6 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         if (ok) {
             tcgen05_fence_after();
             have = true;
-        }
-        if (threadIdx.x == 64) {
-            CB200_TS(4);
         }
     }
     const uint32_t taddr = tmem_base + ((quad * 32u) << 16);
@@ -305,14 +288,6 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         tcgen05_fence_after();
         tmem_dealloc<1>(tmem_base, tmem_cols);
     }
-#ifdef CB200_DEBUG
-    if (threadIdx.x == 0 && (blockIdx.x % 97) == 0) {
-        const unsigned long long t5 = globaltimer_ns();
-        printf("[ts] cta %u split %u: setup %llu first_full %llu mma_done_issue %llu tmem_full %llu end %llu (ns from start) start_abs %llu\n",
-               blockIdx.x, split, s_ts[1] - s_ts[0], s_ts[2] - s_ts[0], s_ts[3] - s_ts[0], s_ts[4] - s_ts[0],
-               t5 - s_ts[0], s_ts[0] % 100000000ull);
-    }
-#endif
 }
 
 }  // namespace cb200

@@ -107,6 +107,37 @@ CB200_API int cb200_grouped_quant_matmul_slice_m_can_implement(const cb200_group
 CB200_API uint64_t cb200_grouped_quant_matmul_slice_m_workspace_size(const cb200_grouped_quant_matmul_args *args);
 CB200_API int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args *args, void *stream);
 
+/*
+ * W4A8 matmul with per-group weight scales:
+ *     acc_g[i,j] = sum_{k in group g} A[i,k] * W[k,j]                       (int32)
+ *     y[i,j]     = fma(float(acc_g), weight_scale[g,j], y), g ascending     (fp32)
+ *     D[i,j]     = bf16_rne(y * per_token_scale[i])
+ * W holds signed 4-bit values, two per byte along K (even k in bits 0-3, odd k in bits 4-7), column after
+ * column (k/2 bytes each): the packing of the reference's example 32 for a column-major B
+ * (examples/32_w4a8_matmul/gen_data.py:77-105).  Replaces Gemm::Kernel::W4A8Matmul::Arguments
+ * (include/catlass/gemm/kernel/w4a8_matmul.hpp:83-93; operand order A, packed B of
+ * tests/optest/kernels/32_w4a8_matmul/w4a8_matmul_impl.cpp:101-103).  The reference's own kernel applies one
+ * per-tensor scalar; that case is group_size = k with weight_scale all ones and per_token_scale = scalar.
+ * Requirements: k and group_size multiples of 128, group_size divides k.
+ */
+typedef struct cb200_w4a8_matmul_args {
+    uint32_t m, n, k;
+    uint32_t group_size;
+    const void *a;                /* int8 m x k row-major */
+    const void *w_packed;         /* n columns of k/2 bytes */
+    const float *weight_scale;    /* [k / group_size][n] */
+    const float *per_token_scale; /* [m] */
+    void *d;                      /* bf16 m x n row-major */
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t reserved;
+} cb200_w4a8_matmul_args;
+
+CB200_API int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args *args);
+CB200_API uint64_t cb200_w4a8_matmul_workspace_size(const cb200_w4a8_matmul_args *args);
+CB200_API int cb200_w4a8_matmul(const cb200_w4a8_matmul_args *args, void *stream);
+
 /* ---- library / device state ---- */
 
 /* Reads and clears the status word kernels of this library write on the current device when a bounded

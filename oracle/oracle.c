@@ -137,8 +137,7 @@ void orc_w4a8_matmul_per_group(uint32_t m, uint32_t n, uint32_t k, uint32_t grou
                     s += (int32_t)a_row[kk] * orc_int4(byte & 0xF);
                     s += (int32_t)a_row[kk + 1] * orc_int4(byte >> 4);
                 }
-                float t = (float)s * sw[(size_t)g * n + j];
-                y = y + t;
+                y = fmaf((float)s, sw[(size_t)g * n + j], y);
             }
             out[(size_t)i * n + j] = y * sa[i];
         }

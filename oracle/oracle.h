@@ -57,7 +57,7 @@ void orc_grouped_quant_matmul_slice_m(uint32_t m, uint32_t n, uint32_t k, uint32
  * The reference holds a per-TENSOR W4A8 golden only (examples/32_w4a8_matmul/gen_data.py:111-131,
  * out = 1.5 * (A @ B)); the per-group formula restated here is:
  *   acc_g[i,j] = sum_{kk in group g} int32(A[i,kk]) * int32(W[kk,j])          (int32, exact)
- *   y[i,j]     = sum_g float(acc_g) * sw[g,j]      (fp32; separate multiply and add; g ascending)
+ *   y[i,j]     = fma(float(acc_g), sw[g,j], y)    (fp32, one rounding per group; g ascending from y = 0)
  *   out[i,j]   = y * sa[i]
  * Weights are signed 4-bit, packed two per byte along K: byte t of column j holds W[2t,j] in bits 0-3
  * and W[2t+1,j] in bits 4-7 (nibble order of examples/32_w4a8_matmul/gen_data.py:102-105), columns

@@ -169,7 +169,8 @@ def test_w4a8_per_group_formula():
     y = np.zeros((m, n), np.float32)
     for g in range(k // gs):
         acc = a[:, g * gs:(g + 1) * gs].astype(np.int32) @ w[g * gs:(g + 1) * gs].astype(np.int32)
-        y = (y + acc.astype(np.float32) * sw[g][None, :]).astype(np.float32)
+        # fused multiply-add: the product of two fp32 values is exact in fp64, one rounding at the end
+        y = (acc.astype(np.float64) * sw[g][None, :].astype(np.float64) + y.astype(np.float64)).astype(np.float32)
     want = (y * sa[:, None]).astype(np.float32)
     assert np.array_equal(bits(out), bits(want))
     # one group and unit scales reduce to the per-tensor reference formula with scalar 1
