@@ -433,6 +433,57 @@ def run_w4a8(args, rank, world, local):
     }
 
 
+def run_mx(args, rank, world, local):
+    """MXFP8 / MXFP4 block-scaled matmul at M=N=K=8192 (random element codes and exponents: timing only)."""
+    import torch
+    from catlass_b200 import capi
+    fp4 = args.workload == "mxfp4"
+    m = n = k = 8192
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(88)
+    row_bytes = k // 2 if fp4 else k
+    # element bytes: any bit pattern is a finite E2M1 pair; for E4M3 clear the exponent's top bit so that no
+    # byte is the NaN code 0x7F/0xFF
+    a = torch.randint(0, 256, (m, row_bytes), dtype=torch.uint8, device=dev, generator=gen)
+    b = torch.randint(0, 256, (n, row_bytes), dtype=torch.uint8, device=dev, generator=gen)
+    if not fp4:
+        a &= 0xBF
+        b &= 0xBF
+    sfa = torch.randint(120, 135, (m, k // 32), dtype=torch.uint8, device=dev, generator=gen)
+    sfb = torch.randint(120, 135, (n, k // 32), dtype=torch.uint8, device=dev, generator=gen)
+    d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    fmt = capi.MX_E2M1 if fp4 else capi.MX_E4M3
+    ws = torch.empty(capi.mx_matmul_workspace_size(m, n, k, fmt), dtype=torch.uint8, device=dev)
+
+    def step():
+        capi.mx_matmul(a, b, sfa, sfb, d, m, n, k, fmt, ws)
+
+    sampler = ClockSampler(local)
+    ms, _, launches = time_steps(step, args.steps, args.warmup, 1)
+    clocks = sampler.stop()
+    st, code = capi.device_status()
+    if st != 0:
+        raise SystemExit(f"device status {st} code {code:#x}")
+    ms /= args.steps
+    flops = 2.0 * m * n * k
+    peaks = measured_peaks()
+    factor = 4.0 if fp4 else 2.0   # dense fp4 / fp8 rate relative to bf16 on the same tensor cores
+    achieved = flops / (ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"] * factor
+    return {
+        "metric": "mxfp4_gemm_tflops" if fp4 else "mxfp8_gemm_tflops", "value": achieved, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "e2m1xe8m0" if fp4 else "e4m3xe8m0", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: M=N=K=8192 block-scaled (32-element E8M0 blocks), bf16 out, "
+                               "step = scale re-tiling (2 launches) + matmul",
+                   "l2": "operands exceed L2" if not fp4 else "operands 64 MB + 134 MB output per pass"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": f"{factor:.0f} x {peaks['source']} cuBLAS bf16 burst"},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+
+
 def run_reference(args):
     """The reference arm: the reference's CPU golden on the host cores, bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
@@ -467,7 +518,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "moe_small", "w4a8"] + sorted(DENSE))
+    ap.add_argument("--workload", default="moe", choices=["moe", "moe_small", "w4a8", "mxfp8", "mxfp4"] + sorted(DENSE))
     ap.add_argument("--placement", default="split", choices=["split", "whole"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -490,6 +541,8 @@ def main():
         res = run_moe(args, rank, world, local)
     elif args.workload == "w4a8":
         res = run_w4a8(args, rank, world, local)
+    elif args.workload in ("mxfp8", "mxfp4"):
+        res = run_mx(args, rank, world, local)
     else:
         if world != 1:
             raise SystemExit("dense workloads are single-GPU")

@@ -40,6 +40,16 @@ class W4A8MatmulArgs(ctypes.Structure):
     ]
 
 
+class MxMatmulArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("format", _u32), ("layout_a", _u32), ("layout_b", _u32),
+        ("a", _vp), ("b", _vp), ("scale_a", _vp), ("scale_b", _vp), ("d", _vp),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+    ]
+
+
+MX_E4M3, MX_E2M1 = 0, 1
+
 _lib = None
 
 
@@ -60,7 +70,8 @@ def load():
     lib = ctypes.CDLL(path)
     for name, args_t in (("cb200_quant_matmul", QuantMatmulArgs),
                          ("cb200_grouped_quant_matmul_slice_m", GroupedQuantMatmulArgs),
-                         ("cb200_w4a8_matmul", W4A8MatmulArgs)):
+                         ("cb200_w4a8_matmul", W4A8MatmulArgs),
+                         ("cb200_mx_matmul", MxMatmulArgs)):
         getattr(lib, name + "_can_implement").argtypes = [ctypes.POINTER(args_t)]
         getattr(lib, name + "_can_implement").restype = ctypes.c_int
         getattr(lib, name + "_workspace_size").argtypes = [ctypes.POINTER(args_t)]
@@ -134,3 +145,19 @@ def w4a8_matmul(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, st
                           weight_scale=_p(weight_scale), per_token_scale=_p(per_token), d=_p(d), workspace=None,
                           workspace_bytes=0, block_num=0, reserved=0)
     _check("cb200_w4a8_matmul", load().cb200_w4a8_matmul(ctypes.byref(args), _stream(stream)))
+
+
+def mx_matmul_workspace_size(m, n, k, fmt):
+    args = MxMatmulArgs(m=m, n=n, k=k, format=fmt, layout_a=ROW_MAJOR, layout_b=COLUMN_MAJOR, a=256, b=256,
+                        scale_a=256, scale_b=256, d=256)
+    return int(load().cb200_mx_matmul_workspace_size(ctypes.byref(args)))
+
+
+def mx_matmul(a, b, scale_a, scale_b, d, m, n, k, fmt, workspace, stream=None):
+    """a: [m][k] elements (E2M1: k/2 bytes per row), b: [n][k] (column-major B); scales [rows][k/32] bytes.
+    workspace: a CUDA byte tensor of at least mx_matmul_workspace_size bytes."""
+    args = MxMatmulArgs(m=m, n=n, k=k, format=fmt, layout_a=ROW_MAJOR, layout_b=COLUMN_MAJOR, a=_p(a), b=_p(b),
+                        scale_a=_p(scale_a), scale_b=_p(scale_b), d=_p(d), workspace=_p(workspace),
+                        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(),
+                        block_num=0, reserved=0)
+    _check("cb200_mx_matmul", load().cb200_mx_matmul(ctypes.byref(args), _stream(stream)))

@@ -10,6 +10,7 @@
 #include "w8a8_gemm.cuh"
 #include "w8a8_smallm.cuh"
 #include "w4a8_gemm.cuh"
+#include "mx_gemm.cuh"
 
 using namespace cb200;
 using namespace cb200::host;
@@ -370,9 +371,149 @@ int check_w4a8(const cb200_w4a8_matmul_args* a)
     return CB200_SUCCESS;
 }
 
+uint64_t mx_workspace_bytes(const cb200_mx_matmul_args* a)
+{
+    const uint64_t kq = a->k / 128u;
+    return (static_cast<uint64_t>((a->m + 127u) / 128u) + (a->n + 127u) / 128u) * kq * 512u;
+}
+
+int check_mx(const cb200_mx_matmul_args* a)
+{
+    if (a == nullptr) {
+        return CB200_INVALID;
+    }
+    if (a->m == 0 || a->n == 0) {
+        return CB200_SUCCESS;
+    }
+    if (a->a == nullptr || a->b == nullptr || a->scale_a == nullptr || a->scale_b == nullptr || a->d == nullptr) {
+        return CB200_INVALID;
+    }
+    if (a->format != CB200_MX_E4M3 && a->format != CB200_MX_E2M1) {
+        return CB200_INVALID;
+    }
+    if (a->layout_a != CB200_ROW_MAJOR || a->layout_b != CB200_COLUMN_MAJOR) {
+        return CB200_INVALID;  // both operands K-contiguous, as the block scales run along K
+    }
+    const uint32_t kmul = a->format == CB200_MX_E2M1 ? 256u : 128u;
+    if (a->k == 0 || (a->k % kmul) != 0) {
+        return CB200_INVALID;
+    }
+    if (a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u) {
+        return CB200_INVALID;
+    }
+    if (!aligned16(a->a) || !aligned16(a->b) || (reinterpret_cast<uintptr_t>(a->scale_a) & 3u) != 0 ||
+        (reinterpret_cast<uintptr_t>(a->scale_b) & 3u) != 0 || (reinterpret_cast<uintptr_t>(a->d) & 1u) != 0) {
+        return CB200_INVALID;
+    }
+    if ((a->n & 7u) == 0 && !aligned16(a->d)) {
+        return CB200_INVALID;
+    }
+    return CB200_SUCCESS;
+}
+
+template <bool kFp4>
+int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStream_t stream)
+{
+    const uint32_t row_bytes = kFp4 ? args->k / 2u : args->k;
+    MxParams p;
+    p.m = args->m;
+    p.n = args->n;
+    p.k = args->k;
+    p.fp4 = kFp4 ? 1u : 0u;
+    p.num_k_blocks = row_bytes / 128u;
+    p.words_per_stage = kFp4 ? 2u : 1u;
+    p.kq_total = args->k / 128u;
+    uint8_t* ws = static_cast<uint8_t*>(args->workspace);
+    const uint64_t sfa_bytes = static_cast<uint64_t>((args->m + 127u) / 128u) * p.kq_total * 512u;
+    p.sfa = ws;
+    p.sfb = ws + sfa_bytes;
+    p.d = static_cast<__nv_bfloat16*>(args->d);
+    p.status = dev.status;
+
+    const uint32_t kblocks = args->k / 32u;
+    mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(static_cast<const uint8_t*>(args->scale_a), ws,
+                                                                args->m, kblocks);
+    mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(static_cast<const uint8_t*>(args->scale_b),
+                                                                ws + sfa_bytes, args->n, kblocks);
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(2, std::memory_order_relaxed);
+
+    CUtensorMap tmap_a, tmap_b;
+    {
+        const uint64_t dims[2] = {row_bytes, args->m};
+        const uint64_t strides[1] = {row_bytes};
+        const uint32_t box[2] = {kBlockKBytes, kBlockM};
+        int rc = encode_tmap_u8(&tmap_a, args->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    {
+        const uint64_t dims[2] = {row_bytes, args->n};
+        const uint64_t strides[1] = {row_bytes};
+        const uint32_t box[2] = {kBlockKBytes, kMxBlockN};
+        int rc = encode_tmap_u8(&tmap_b, args->b, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    auto kernel = mx_gemm_kernel<kFp4>;
+    static bool attr_set[kMaxDevices] = {};
+    int devid = 0;
+    CB200_CUDA_TRY(cudaGetDevice(&devid));
+    if (!attr_set[devid]) {
+        CB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem::kTotalBytes));
+        attr_set[devid] = true;
+    }
+    const uint64_t tiles = static_cast<uint64_t>((args->m + kBlockM - 1) / kBlockM) * ((args->n + kMxBlockN - 1) / kMxBlockN);
+    uint32_t grid = static_cast<uint32_t>(dev.sm_count);
+    if (args->block_num != 0 && args->block_num < grid) {
+        grid = args->block_num;
+    }
+    if (tiles < grid) {
+        grid = static_cast<uint32_t>(tiles);
+    }
+    kernel<<<grid, kMxThreads, MxSmem::kTotalBytes, stream>>>(tmap_a, tmap_b, p);
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return CB200_SUCCESS;
+}
+
 }  // namespace
 
 extern "C" {
+
+int cb200_mx_matmul_can_implement(const cb200_mx_matmul_args* args)
+{
+    return check_mx(args);
+}
+
+uint64_t cb200_mx_matmul_workspace_size(const cb200_mx_matmul_args* args)
+{
+    if (args == nullptr || check_mx(args) != CB200_SUCCESS) {
+        return 0;
+    }
+    return mx_workspace_bytes(args);
+}
+
+int cb200_mx_matmul(const cb200_mx_matmul_args* args, void* stream_v)
+{
+    int rc = check_mx(args);
+    if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
+        return rc;
+    }
+    if (args->workspace == nullptr || args->workspace_bytes < mx_workspace_bytes(args) ||
+        (reinterpret_cast<uintptr_t>(args->workspace) & 255u) != 0) {
+        return CB200_INVALID;
+    }
+    DeviceState* dev = nullptr;
+    rc = device_state(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    return args->format == CB200_MX_E2M1 ? launch_mx<true>(args, *dev, stream) : launch_mx<false>(args, *dev, stream);
+}
 
 int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args* args)
 {

@@ -1,0 +1,289 @@
+// MXFP8 (E4M3) and MXFP4 (E2M1) block-scaled matmul for sm_100a:
+//     D[m,n] = bf16_rne( sum_k (a[m,k] * 2^(ea[m,k/32]-127)) * (b[k,n] * 2^(eb[n,k/32]-127)) ),  fp32 accumulate
+// with one E8M0 scale per 32 contiguous K elements of every row of A and every column of B.
+//
+// What the reference's MxMatmulTla / BlockMmadTla<MmadMx> compute
+// (include/catlass/gemm/kernel/mx_matmul_tla.hpp:29-393, include/catlass/gemm/block/block_mmad_mx_tla.hpp:291-647):
+// there too the scaling happens inside the matrix unit; here it is tcgen05.mma.kind::mxf8f6f4 / kind::mxf4 with
+// .block_scale, the scale factors sitting in TMEM next to the accumulator.
+//
+// Two kernels:
+//   mx_pack_scales_kernel  rewrites the caller's scale arrays ([rows][K/32] bytes, the reference's layout:
+//                          include/tla/layout.hpp:609-660, examples/53_ascend950_fp8_mx_matmul/gen_data.py:390-401)
+//                          into the tile order the tensor core's scale copy wants: per 128 rows x 4 scale
+//                          blocks a 512-byte block [row % 32][row / 32][4 bytes].  Output goes to the
+//                          caller-provided workspace.
+//   mx_gemm_kernel         persistent, warp-specialised like the W8A8 kernel: TMA producer (operand tiles +
+//                          packed scale blocks), one MMA thread (tcgen05.cp scale blocks smem -> TMEM, then the
+//                          block-scaled MMAs), four epilogue warps (fp32 -> bf16), two accumulators in TMEM.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+#include "w8a8_gemm.cuh"
+
+namespace cb200 {
+
+constexpr int kMxBlockN = 128;
+constexpr int kMxStages = 6;
+constexpr int kMxThreads = 192;
+
+struct MxParams {
+    uint32_t m, n, k;
+    uint32_t fp4;              // 0: E4M3 bytes, 1: E2M1 packed two per byte
+    uint32_t num_k_blocks;     // K bytes per row / 128
+    uint32_t words_per_stage;  // scale words (4 scale blocks = 128 K elements) per 128-byte stage: 1 (fp8), 2 (fp4)
+    uint32_t kq_total;         // scale words per row = K / 128
+    const uint8_t* sfa;        // packed scales of A: [ceil(m/128)][kq_total][512]
+    const uint8_t* sfb;        // packed scales of B: [ceil(n/128)][kq_total][512]
+    __nv_bfloat16* d;
+    unsigned* status;
+};
+
+struct MxSmem {
+    static constexpr int kABytes = kBlockM * kBlockKBytes;      // 16 KB
+    static constexpr int kBBytes = kMxBlockN * kBlockKBytes;    // 16 KB
+    static constexpr int kSfBytes = 2 * 2 * 512;                // A and B, up to two scale words each
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;  // 34 KB
+    static constexpr int kRingBytes = kMxStages * kStageBytes;
+    static constexpr int kBarrierBytes = (2 * kMxStages + 4) * 8 + 16;
+    static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
+};
+
+// in : [rows][kblocks] bytes (kblocks = K/32), out: [ceil(rows/128)][kblocks/4][512]
+// Rows past the end get the neutral scale 2^0.
+__global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t rows,
+                                      uint32_t kblocks)
+{
+    const uint32_t kq_total = kblocks / 4;
+    const uint32_t row_blocks = (rows + 127) / 128;
+    const size_t words = static_cast<size_t>(row_blocks) * kq_total * 128;
+    for (size_t w = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; w < words;
+         w += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        // consecutive threads walk consecutive scale words of one row: coalesced reads
+        const uint32_t kq = static_cast<uint32_t>(w % kq_total);
+        const uint32_t row = static_cast<uint32_t>(w / kq_total);  // padded row index
+        uint32_t v = 0x7F7F7F7Fu;
+        if (row < rows) {
+            v = *reinterpret_cast<const uint32_t*>(in + static_cast<size_t>(row) * kblocks + kq * 4);
+        }
+        const uint32_t rb = row / 128, r = row % 128;
+        uint8_t* dst = out + (static_cast<size_t>(rb) * kq_total + kq) * 512 + (r % 32) * 16 + (r / 32) * 4;
+        *reinterpret_cast<uint32_t*>(dst) = v;
+    }
+}
+
+template <bool kFp4>
+__global__ void __launch_bounds__(kMxThreads, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const MxParams p)
+{
+    using S = MxSmem;
+    constexpr uint32_t kAccCols = 2 * kMxBlockN;        // two fp32 accumulators
+    constexpr uint32_t kSfCols = 2 * 16;                // two scale slots of (A: 8 + B: 8) columns
+    constexpr uint32_t kTmemCols = 512;                 // power of two >= kAccCols + kSfCols
+    constexpr uint32_t kWords = kFp4 ? 2 : 1;
+    static_assert(kAccCols + kSfCols <= kTmemCols, "TMEM budget");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t ring = raw_addr + pad;
+    uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes);
+    const uint32_t bar_full = smem_u32(s_bars);
+    const uint32_t bar_empty = bar_full + kMxStages * 8;
+    const uint32_t bar_tmem_full = bar_empty + kMxStages * 8;
+    const uint32_t bar_tmem_empty = bar_tmem_full + 2 * 8;
+    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 2 * kMxStages + 4);
+    volatile uint32_t* s_abort = s_tmem_ptr + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t m_tiles = (p.m + kBlockM - 1) / kBlockM;
+    const uint32_t n_tiles = (p.n + kMxBlockN - 1) / kMxBlockN;
+    const uint32_t total_tiles = m_tiles * n_tiles;
+    const uint32_t num_kb = p.num_k_blocks;
+
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (int s = 0; s < kMxStages; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tmem_full + a * 8, 1);
+            mbar_init(bar_tmem_empty + a * 8, 4);
+        }
+        fence_mbar_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(s_tmem_ptr), kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *s_tmem_ptr;
+    constexpr uint32_t kStageTx = S::kABytes + S::kBBytes + 2 * kWords * 512;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+                const uint32_t mt = idx / n_tiles, nt = idx - mt * n_tiles;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer);
+                    if (!ok) {
+                        break;
+                    }
+                    const uint32_t full = bar_full + stage * 8;
+                    const uint32_t sa = ring + stage * S::kStageBytes;
+                    const uint32_t sb = sa + S::kABytes;
+                    const uint32_t ssf = sb + S::kBBytes;
+                    const int32_t k0 = static_cast<int32_t>(kb) * kBlockKBytes;
+                    mbar_expect_tx(full, kStageTx);
+                    tma_load_2d(sa, &tmap_a, full, k0, static_cast<int32_t>(mt) * kBlockM);
+                    tma_load_2d(sb, &tmap_b, full, k0, static_cast<int32_t>(nt) * kMxBlockN);
+                    const size_t kq = static_cast<size_t>(kb) * kWords;
+                    bulk_load(ssf, p.sfa + (static_cast<size_t>(mt) * p.kq_total + kq) * 512, kWords * 512, full);
+                    bulk_load(ssf + 1024, p.sfb + (static_cast<size_t>(nt) * p.kq_total + kq) * 512, kWords * 512, full);
+                    if (++stage == kMxStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t fmt = kFp4 ? kFmtMxf4E2M1 : kFmtE4M3;
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, sf_slot = 0;
+            bool ok = true;
+            for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+                ok = mbar_wait(bar_tmem_empty + acc * 8, acc_phase ^ 1, s_abort, p.status, kDevTimeoutMmaTmem);
+                if (!ok) {
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * kMxBlockN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
+                    if (!ok) {
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t sa = ring + stage * S::kStageBytes;
+                    const uint32_t sb = sa + S::kABytes;
+                    const uint32_t ssf = sb + S::kBBytes;
+                    // scale blocks of this stage: smem -> TMEM (32 rows x 16 bytes each, replicated to the four
+                    // lane quarters); the copies and the MMAs below execute in issue order
+                    const uint32_t t_sfa = tmem_base + kAccCols + sf_slot * 16;
+                    const uint32_t t_sfb = t_sfa + 8;
+#pragma unroll
+                    for (uint32_t w = 0; w < kWords; ++w) {
+                        tmem_cp_32x128b_warpx4(t_sfa + w * 4, make_smem_desc_noswizzle(ssf + w * 512, 16, 128));
+                        tmem_cp_32x128b_warpx4(t_sfb + w * 4, make_smem_desc_noswizzle(ssf + 1024 + w * 512, 16, 128));
+                    }
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        const uint64_t da = make_smem_desc_sw128(sa + j * 32, 16, 1024);
+                        const uint64_t db = make_smem_desc_sw128(sb + j * 32, 16, 1024);
+                        // fp8: MMA j covers scale block j of the stage's single word (byte j)
+                        // fp4: MMA j covers 64 elements = scale blocks 2j, 2j+1: word j/2, bytes (j%2)*2..+1
+                        const uint32_t word = kFp4 ? (j >> 1) : 0;
+                        const uint32_t sf_id = kFp4 ? ((j & 1) * 2) : j;
+                        const uint32_t idesc = make_idesc_mx(fmt, fmt, kBlockM, kMxBlockN, sf_id, sf_id);
+                        umma_mx<kFp4>(tmem_d, da, db, idesc, (kb | j) != 0 ? 1u : 0u, t_sfa + word * 4,
+                                      t_sfb + word * 4);
+                    }
+                    umma_commit<1>(bar_empty + stage * 8);
+                    sf_slot ^= 1;
+                    if (++stage == kMxStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                umma_commit<1>(bar_tmem_full + acc * 8);
+                acc ^= 1;
+                if (acc == 0) {
+                    acc_phase ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const uint32_t quad = warp & 3;
+        const bool vec_ok = (p.n & 7u) == 0;
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+            const uint32_t mt = idx / n_tiles, nt = idx - mt * n_tiles;
+            ok = mbar_wait(bar_tmem_full + acc * 8, acc_phase, s_abort, p.status, kDevTimeoutEpilogue);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t row = mt * kBlockM + quad * 32 + lane;
+            const bool row_ok = row < p.m;
+            const uint32_t taddr = tmem_base + acc * kMxBlockN + ((quad * 32u) << 16);
+            __nv_bfloat16* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
+#pragma unroll 1
+            for (int c = 0; c < kMxBlockN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                const uint32_t col0 = nt * kMxBlockN + c * 32;
+                if (row_ok && col0 < p.n) {
+                    if (vec_ok && col0 + 32 <= p.n) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint32_t packed[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + e * 2]),
+                                                                               __uint_as_float(r[v * 8 + e * 2 + 1]));
+                                packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(drow + col0 + v * 8) =
+                                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) {
+                                drow[col0 + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_tmem_empty + acc * 8);
+            }
+            acc ^= 1;
+            if (acc == 0) {
+                acc_phase ^= 1;
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace cb200

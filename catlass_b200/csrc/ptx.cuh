@@ -198,6 +198,14 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
         : "memory");
 }
 
+// Plain (untiled) bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int32_t x, int32_t y)
 {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
@@ -279,6 +287,29 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
     return d;
 }
 
+// Descriptor of an unswizzled K-major tile: 8-row x 16-byte core matrices stored contiguously (128 bytes),
+// `sbo_bytes` between core matrices along the rows, `lbo_bytes` between core matrices along K.
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                             uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= 1ull << 46;
+    return d;
+}
+
+// Instruction descriptor of the block-scaled kinds (mxf8f6f4, mxf4) with E8M0 scale factors:
+//   bits 4-5 which byte of the B scale column this MMA uses, 7-9 A format, 10-12 B format, 15/16 A/B MN-major,
+//   17-22 N/8, 23 scale format (1 = E8M0), 24-28 M/16, 29-30 byte of the A scale column.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
+                                                     uint32_t a_sf_id, uint32_t b_sf_id)
+{
+    return (b_sf_id << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) |
+           (a_sf_id << 29);
+}
+
 // Instruction descriptor fields (32-bit) shared by the dense kinds.
 //   bits 4-5 accumulator format (1 = f32, 2 = s32), 7-9 A format, 10-12 B format, 15 A is MN-major,
 //   16 B is MN-major, 17-22 N/8, 24-28 M/16.
@@ -292,6 +323,7 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_fmt, uint32_t a_fmt
 constexpr uint32_t kFmtS8 = 1;     // signed 8-bit integer operand (kind::i8)
 constexpr uint32_t kFmtE4M3 = 0;   // kind::f8f6f4 / mxf8f6f4
 constexpr uint32_t kFmtE2M1 = 5;   // 4-bit operand in kind::mxf8f6f4 (unpacked in smem)
+constexpr uint32_t kFmtMxf4E2M1 = 1;  // packed 4-bit operand of kind::mxf4
 constexpr uint32_t kAccS32 = 2;
 constexpr uint32_t kAccF32 = 1;
 

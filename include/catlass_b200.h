@@ -138,6 +138,41 @@ CB200_API int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args *args
 CB200_API uint64_t cb200_w4a8_matmul_workspace_size(const cb200_w4a8_matmul_args *args);
 CB200_API int cb200_w4a8_matmul(const cb200_w4a8_matmul_args *args, void *stream);
 
+/*
+ * MX block-scaled matmul (OCP microscaling): elements E4M3 (one byte) or E2M1 (two per byte, even k in bits
+ * 0-3), one E8M0 scale byte per 32 contiguous K elements of every row of A and every column of B:
+ *     D[i,j] = bf16_rne( sum_k (A[i,k] * 2^(scale_a[i,k/32]-127)) * (B[k,j] * 2^(scale_b[j,k/32]-127)) )
+ * accumulated in fp32 inside the tensor core.  Replaces Gemm::Kernel::MxMatmulTla::Arguments
+ * (include/catlass/gemm/kernel/mx_matmul_tla.hpp:95-108; operand order A, B, scaleA, scaleB of
+ * tests/optest/kernels/53_ascend950_fp8_mx_matmul/fp8_mx_matmul_impl.cpp:80-84).
+ * A is m x k row-major, B is k x n column-major (each column k contiguous elements); scale_a is
+ * [m][k/32] bytes and scale_b is [n][k/32] bytes: the reference's [rows, k/64, 2] scale arrays
+ * (examples/53_ascend950_fp8_mx_matmul/gen_data.py:390-401).  k must be a multiple of 128 (E4M3) or 256 (E2M1).
+ * The workspace (cb200_mx_matmul_workspace_size bytes) receives the scales re-tiled for the tensor core.
+ */
+#define CB200_MX_E4M3 0
+#define CB200_MX_E2M1 1
+
+typedef struct cb200_mx_matmul_args {
+    uint32_t m, n, k;
+    uint32_t format;              /* CB200_MX_E4M3 / CB200_MX_E2M1 */
+    uint32_t layout_a;            /* CB200_ROW_MAJOR */
+    uint32_t layout_b;            /* CB200_COLUMN_MAJOR */
+    const void *a;
+    const void *b;
+    const void *scale_a;          /* E8M0 bytes */
+    const void *scale_b;
+    void *d;                      /* bf16 m x n row-major */
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t reserved;
+} cb200_mx_matmul_args;
+
+CB200_API int cb200_mx_matmul_can_implement(const cb200_mx_matmul_args *args);
+CB200_API uint64_t cb200_mx_matmul_workspace_size(const cb200_mx_matmul_args *args);
+CB200_API int cb200_mx_matmul(const cb200_mx_matmul_args *args, void *stream);
+
 /* ---- library / device state ---- */
 
 /* Reads and clears the status word kernels of this library write on the current device when a bounded
