@@ -8,7 +8,7 @@ import os
 
 from . import build as _build
 
-SUCCESS, INVALID, CUDA_ERROR, DEVICE_TIMEOUT = 0, 1, 2, 3
+SUCCESS, INVALID, CUDA_ERROR, DEVICE_TIMEOUT, SCRATCH_TOO_SMALL = 0, 1, 2, 3, 4
 ROW_MAJOR, COLUMN_MAJOR = 0, 1
 GROUP_LIST_INT64, GROUP_LIST_INT32 = 0, 1
 
@@ -78,6 +78,9 @@ def load():
         getattr(lib, name + "_workspace_size").restype = _u64
         getattr(lib, name).argtypes = [ctypes.POINTER(args_t), _vp]
         getattr(lib, name).restype = ctypes.c_int
+    lib.cb200_mx_matmul_static.argtypes = [ctypes.POINTER(MxMatmulArgs), _vp]
+    lib.cb200_mx_matmul_static.restype = ctypes.c_int
+    lib.cb200_mx_matmul_static_scratch_bytes.restype = _u64
     lib.cb200_device_status.argtypes = [ctypes.POINTER(_u32)]
     lib.cb200_device_status.restype = ctypes.c_int
     lib.cb200_last_cuda_error.restype = ctypes.c_int
@@ -161,3 +164,11 @@ def mx_matmul(a, b, scale_a, scale_b, d, m, n, k, fmt, workspace, stream=None):
                         workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(),
                         block_num=0, reserved=0)
     _check("cb200_mx_matmul", load().cb200_mx_matmul(ctypes.byref(args), _stream(stream)))
+
+
+def mx_matmul_static(a, b, scale_a, scale_b, d, m, n, k, fmt, stream=None):
+    """cb200_mx_matmul_static: as mx_matmul, scale scratch inside the library image, no workspace argument."""
+    args = MxMatmulArgs(m=m, n=n, k=k, format=fmt, layout_a=ROW_MAJOR, layout_b=COLUMN_MAJOR, a=_p(a), b=_p(b),
+                        scale_a=_p(scale_a), scale_b=_p(scale_b), d=_p(d), workspace=None, workspace_bytes=0,
+                        block_num=0, reserved=0)
+    _check("cb200_mx_matmul_static", load().cb200_mx_matmul_static(ctypes.byref(args), _stream(stream)))

@@ -637,6 +637,76 @@ int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args* ar
     return run_w8a8(q, CB200_ROW_MAJOR, stream);
 }
 
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// Fixed-scratch variant of the MX matmul for callers that may not allocate device memory (a server that owns
+// all of HBM through its own arena, a loop that cannot take cudaMalloc's device-wide synchronisation).
+// The scratch is part of the library image: every GPU that loads the library holds these bytes until exit.
+namespace {
+
+constexpr uint64_t kMxStaticScratchBytes = 8ull << 20;
+static __device__ __align__(256) uint8_t g_mx_static_scratch[kMxStaticScratchBytes];
+
+// In host code the name g_mx_static_scratch is only a handle for the runtime, not a device address: the
+// address a kernel may use is looked up once per device, with that device current.
+int mx_static_scratch(uint8_t** out)
+{
+    static uint8_t* ptrs[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = 0;
+    CB200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) {
+        return CB200_INVALID;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        uint8_t* p = nullptr;
+        CB200_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_mx_static_scratch));
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return CB200_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint64_t cb200_mx_matmul_static_scratch_bytes(void)
+{
+    return kMxStaticScratchBytes;
+}
+
+// Same kernels and same results as cb200_mx_matmul; the re-tiled scales go to the library's own array.
+// Allocates nothing.  The first call on a device performs the address look-up above.
+int cb200_mx_matmul_static(const cb200_mx_matmul_args* args, void* stream_v)
+{
+    int rc = check_mx(args);
+    if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
+        return rc;
+    }
+    if (mx_workspace_bytes(args) > kMxStaticScratchBytes) {
+        return CB200_SCRATCH_TOO_SMALL;
+    }
+    DeviceState* dev = nullptr;
+    rc = device_state(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    uint8_t* scratch = nullptr;
+    rc = mx_static_scratch(&scratch);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    cb200_mx_matmul_args with_scratch = *args;
+    with_scratch.workspace = scratch;
+    with_scratch.workspace_bytes = kMxStaticScratchBytes;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    return args->format == CB200_MX_E2M1 ? launch_mx<true>(&with_scratch, *dev, stream)
+                                         : launch_mx<false>(&with_scratch, *dev, stream);
+}
+
 int cb200_device_status(uint32_t* code)
 {
     if (code == nullptr) {

@@ -34,6 +34,7 @@ extern "C" {
 #define CB200_INVALID 1        /* bad descriptor: null pointer, misaligned buffer, unsupported layout */
 #define CB200_CUDA_ERROR 2     /* a CUDA runtime/driver call failed (see cb200_last_cuda_error) */
 #define CB200_DEVICE_TIMEOUT 3 /* a kernel gave up on a bounded wait (see cb200_device_status) */
+#define CB200_SCRATCH_TOO_SMALL 4 /* the problem needs more scratch than a fixed-scratch entry point owns */
 
 /* ---- matrix layouts (include/catlass/layout/matrix.hpp: RowMajor :24, ColumnMajor :168, zN :475) ---- */
 #define CB200_ROW_MAJOR 0
@@ -172,6 +173,30 @@ typedef struct cb200_mx_matmul_args {
 CB200_API int cb200_mx_matmul_can_implement(const cb200_mx_matmul_args *args);
 CB200_API uint64_t cb200_mx_matmul_workspace_size(const cb200_mx_matmul_args *args);
 CB200_API int cb200_mx_matmul(const cb200_mx_matmul_args *args, void *stream);
+
+/*
+ * cb200_mx_matmul_static: the MX matmul above for callers that cannot give it a workspace.
+ * (No counterpart in the reference: every reference kernel takes its workspace from the caller or allocates
+ * it per call, examples/shared_lib/src/common/common.hpp:36-46.)
+ *
+ * Some hosts of this library never get to call cudaMalloc: an inference server that hands all of HBM to its
+ * own arena at start-up and forbids plug-ins to allocate behind its back, or a latency-critical loop that
+ * cannot afford the device-wide synchronisation an allocation implies.  For them the re-tiled scale factors
+ * go into a buffer that is part of the library image itself: a file-scope __device__ array of
+ * cb200_mx_matmul_static_scratch_bytes() bytes (8 MiB), resident on every GPU that loads the library until
+ * the process exits.  args->workspace and args->workspace_bytes are ignored; inputs and output are passed
+ * as usual.  The call allocates nothing and calls no allocating routine.
+ *
+ *  - Limit: (ceil(m/128) + ceil(n/128)) * (k/128) * 512 bytes must fit the array; m = n = k = 8192 needs
+ *    4 MiB.  Larger problems return CB200_SCRATCH_TOO_SMALL and launch nothing.
+ *  - The first call on a device looks up the array's device address (with that device current) and keeps it;
+ *    make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Each call rewrites every byte of it that it later reads, so
+ *    nothing has to be cleared between calls, but two calls that overlap on the GPU (different streams)
+ *    race on it: serialise them.
+ */
+CB200_API int cb200_mx_matmul_static(const cb200_mx_matmul_args *args, void *stream);
+CB200_API uint64_t cb200_mx_matmul_static_scratch_bytes(void);
 
 /* ---- library / device state ---- */
 
