@@ -177,6 +177,47 @@ def test_grouped_zipf_moe_slice(cuda):
     run_grouped(cuda, sizes, 512, 7168, False, seed=12)
 
 
+def test_grouped_full_moe_config_sampled_rows(cuda):
+    """The benchmark configuration at full size (64 experts, K=7168, N=4096, 131072 rows, Zipf loads) on the
+    GPU; the oracle recomputes sampled rows of every expert: its first and last row, the rows on either side
+    of its first 128-row tile boundary, and a random one."""
+    import torch
+    from catlass_b200 import capi
+    g, n, k, rows = 64, 4096, 7168, 131072
+    sizes = P.zipf_group_sizes(rows, g, seed=20240)
+    gl = np.cumsum(sizes).astype(np.int64)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(5)
+    a = torch.randint(-127, 128, (rows, k), dtype=torch.int8, device=cuda, generator=gen)
+    b = torch.randint(-127, 128, (g, k, n), dtype=torch.int8, device=cuda, generator=gen)
+    scale = torch.empty((g, n), device=cuda).uniform_(1e-3, 1e-2, generator=gen)
+    pt = torch.empty(rows, device=cuda).uniform_(1e-3, 1e-2, generator=gen)
+    d = torch.zeros((rows, n), dtype=torch.bfloat16, device=cuda)
+    capi.grouped_quant_matmul(a, b, _dev(gl), scale, pt, d, rows, n, k, g, layout_b=capi.ROW_MAJOR)
+    st, code = capi.device_status()
+    assert st == 0, f"device status {st} code {code:#x}"
+    rng = np.random.default_rng(3)
+    starts = np.concatenate([[0], gl[:-1]])
+    bad = 0
+    checked = 0
+    for e in range(g):
+        if sizes[e] == 0:
+            continue
+        local = {0, int(sizes[e]) - 1, int(rng.integers(0, sizes[e]))}
+        if sizes[e] > 128:
+            local |= {127, 128}
+        idx = np.array(sorted(local)) + starts[e]
+        a_rows = a[torch.from_numpy(idx).cuda()].cpu().numpy()
+        want = O.quant_matmul(a_rows, b[e].cpu().numpy(), scale[e].cpu().numpy(), pt[torch.from_numpy(idx).cuda()].cpu().numpy(),
+                              len(idx), n, k, O.ROW_MAJOR, O.ROW_MAJOR)
+        got = d[torch.from_numpy(idx).cuda()].view(torch.int16).cpu().numpy().view(np.uint16)
+        bad += int((got != O.bf16_bits(want)).sum())
+        checked += got.size
+    assert bad == 0, f"{bad} of {checked} sampled outputs differ"
+    # every routed row was written: a row of exact zeros would need an all-zero accumulator row
+    assert int((d.view(torch.int16) != 0).any(dim=1).sum()) == rows
+
+
 def test_k_zero_writes_zeros(cuda):
     from catlass_b200 import capi
     torch = _torch()
