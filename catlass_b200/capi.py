@@ -32,6 +32,14 @@ class GroupedQuantMatmulArgs(ctypes.Structure):
     ]
 
 
+class GroupedQuantMatmulHostArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("layout_b", _u32), ("chunks", _u32),
+        ("a_host", _vp), ("group_list_host", _vp), ("per_token_host", _vp), ("d_host", _vp),
+        ("b", _vp), ("scale", _vp), ("workspace", _vp), ("workspace_bytes", _u64),
+    ]
+
+
 class W4A8MatmulArgs(ctypes.Structure):
     _fields_ = [
         ("m", _u32), ("n", _u32), ("k", _u32), ("group_size", _u32),
@@ -78,6 +86,10 @@ def load():
         getattr(lib, name + "_workspace_size").restype = _u64
         getattr(lib, name).argtypes = [ctypes.POINTER(args_t), _vp]
         getattr(lib, name).restype = ctypes.c_int
+    lib.cb200_grouped_quant_matmul_slice_m_host.argtypes = [ctypes.POINTER(GroupedQuantMatmulHostArgs), _vp]
+    lib.cb200_grouped_quant_matmul_slice_m_host.restype = ctypes.c_int
+    lib.cb200_grouped_quant_matmul_slice_m_host_workspace_size.argtypes = [ctypes.POINTER(GroupedQuantMatmulHostArgs)]
+    lib.cb200_grouped_quant_matmul_slice_m_host_workspace_size.restype = _u64
     lib.cb200_mx_matmul_static.argtypes = [ctypes.POINTER(MxMatmulArgs), _vp]
     lib.cb200_mx_matmul_static.restype = ctypes.c_int
     lib.cb200_mx_matmul_static_scratch_bytes.restype = _u64
@@ -172,3 +184,27 @@ def mx_matmul_static(a, b, scale_a, scale_b, d, m, n, k, fmt, stream=None):
                         scale_a=_p(scale_a), scale_b=_p(scale_b), d=_p(d), workspace=None, workspace_bytes=0,
                         block_num=0, reserved=0)
     _check("cb200_mx_matmul_static", load().cb200_mx_matmul_static(ctypes.byref(args), _stream(stream)))
+
+
+def _host_args(a_host, group_list_host, per_token_host, d_host, b, scale, m, n, k, group_count, layout_b, chunks,
+               workspace):
+    return GroupedQuantMatmulHostArgs(
+        m=m, n=n, k=k, group_count=group_count, layout_b=layout_b, chunks=chunks, a_host=_p(a_host),
+        group_list_host=_p(group_list_host), per_token_host=_p(per_token_host), d_host=_p(d_host), b=_p(b),
+        scale=_p(scale), workspace=_p(workspace),
+        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size())
+
+
+def grouped_quant_matmul_host_workspace_size(m, n, k, group_count, chunks=0):
+    args = GroupedQuantMatmulHostArgs(m=m, n=n, k=k, group_count=group_count, layout_b=ROW_MAJOR, chunks=chunks)
+    return int(load().cb200_grouped_quant_matmul_slice_m_host_workspace_size(ctypes.byref(args)))
+
+
+def grouped_quant_matmul_host(a_host, group_list_host, per_token_host, d_host, b, scale, m, n, k, group_count,
+                              workspace, layout_b=ROW_MAJOR, chunks=0, stream=None):
+    """Host-resident A / per-token scales / int64 group list / D (CPU tensors, pinned for overlap); b, scale and
+    workspace are CUDA tensors."""
+    args = _host_args(a_host, group_list_host, per_token_host, d_host, b, scale, m, n, k, group_count, layout_b,
+                      chunks, workspace)
+    _check("cb200_grouped_quant_matmul_slice_m_host",
+           load().cb200_grouped_quant_matmul_slice_m_host(ctypes.byref(args), _stream(stream)))

@@ -8,6 +8,7 @@
 
 #include "host_runtime.cuh"
 #include "w8a8_gemm.cuh"
+#include "w8a8_gemm_pair.cuh"
 #include "w8a8_smallm.cuh"
 #include "w4a8_gemm.cuh"
 #include "mx_gemm.cuh"
@@ -147,6 +148,74 @@ int launch_w8a8(const W8A8Problem& q, const DeviceState& dev, cudaStream_t strea
         return CB200_SUCCESS;
     }
     kernel<<<grid, kGemmThreads, S::kTotalBytes, stream>>>(tmap_a, tmap_b, p);
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return CB200_SUCCESS;
+}
+
+// 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2): the default for problems with more than 128 columns.
+template <bool kBMn>
+int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t stream)
+{
+    using S = W8A8PairSmem;
+    static_assert(S::kTotalBytes <= 232448, "shared memory budget of one CTA");
+    CUtensorMap tmap_a, tmap_b;
+    const uint32_t groups = q.group_count == 0 ? 1u : q.group_count;
+    {
+        const uint64_t dims[2] = {q.k, q.m};
+        const uint64_t strides[1] = {q.k};
+        const uint32_t box[2] = {kBlockKBytes, kBlockM};
+        int rc = encode_tmap_u8(&tmap_a, q.a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    {
+        // each CTA of a pair loads 128 of the tile's 256 columns
+        const uint64_t dims_mn[3] = {q.n, q.k, groups};
+        const uint64_t dims_k[3] = {q.k, q.n, groups};
+        const uint64_t strides[2] = {kBMn ? q.n : q.k, static_cast<uint64_t>(q.n) * q.k};
+        const uint32_t box[3] = {128, 128, 1};
+        int rc = encode_tmap_u8(&tmap_b, q.b, 3, kBMn ? dims_mn : dims_k, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    W8A8Params p;
+    p.m = q.m;
+    p.n = q.n;
+    p.k = q.k;
+    p.group_count = q.group_count;
+    p.group_list_is_i32 = q.group_list_type == CB200_GROUP_LIST_INT32 ? 1u : 0u;
+    p.num_k_blocks = (q.k + kBlockKBytes - 1) / kBlockKBytes;
+    p.group_list = q.group_list;
+    p.scale = q.scale;
+    p.per_token = q.per_token;
+    p.d = static_cast<__nv_bfloat16*>(q.d);
+    p.acc = q.acc;
+    p.status = dev.status;
+
+    auto kernel = w8a8_pair_kernel<kBMn>;
+    static bool attr_set[kMaxDevices] = {};
+    int devid = 0;
+    CB200_CUDA_TRY(cudaGetDevice(&devid));
+    if (!attr_set[devid]) {
+        CB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotalBytes));
+        attr_set[devid] = true;
+    }
+    const uint64_t n_tiles = (q.n + kPairBN - 1) / kPairBN;
+    const uint64_t max_tiles = (static_cast<uint64_t>((q.m + kPairTileM - 1) / kPairTileM) + groups) * n_tiles;
+    uint32_t pairs = static_cast<uint32_t>(dev.sm_count) / 2u;
+    if (q.block_num != 0 && q.block_num / 2u < pairs) {
+        pairs = q.block_num / 2u == 0 ? 1u : q.block_num / 2u;
+    }
+    if (max_tiles < pairs) {
+        pairs = static_cast<uint32_t>(max_tiles);
+    }
+    if (pairs == 0) {
+        return CB200_SUCCESS;
+    }
+    kernel<<<2 * pairs, kGemmThreads, S::kTotalBytes, stream>>>(tmap_a, tmap_b, p);
     CB200_CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return CB200_SUCCESS;
@@ -336,6 +405,14 @@ int run_w8a8(const W8A8Problem& q, uint32_t layout_a, void* stream_v)
         return b_mn ? launch_smallm<true>(q, *dev, stream) : launch_smallm<false>(q, *dev, stream);
     }
     if (q.n > 128) {
+        // CB200_W8A8_PAIR=0 selects the single-CTA 128 x 256 kernel (developer knob for comparisons)
+        static const bool use_pair = [] {
+            const char* e = getenv("CB200_W8A8_PAIR");
+            return e == nullptr || atoi(e) != 0;
+        }();
+        if (use_pair) {
+            return b_mn ? launch_w8a8_pair<true>(q, *dev, stream) : launch_w8a8_pair<false>(q, *dev, stream);
+        }
         return b_mn ? launch_w8a8<256, true>(q, *dev, stream) : launch_w8a8<256, false>(q, *dev, stream);
     }
     return b_mn ? launch_w8a8<128, true>(q, *dev, stream) : launch_w8a8<128, false>(q, *dev, stream);
@@ -635,6 +712,192 @@ int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args* ar
                   args->b, args->group_list, args->scale, args->per_token_scale, args->d, args->acc,
                   args->block_num};
     return run_w8a8(q, CB200_ROW_MAJOR, stream);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// Host-buffer grouped matmul: chunked copy-in / compute / copy-out overlap (see the header).
+namespace {
+
+constexpr uint32_t kHostDefaultChunks = 8;
+constexpr uint32_t kHostMaxChunks = 64;
+
+struct HostPipe {
+    bool ready = false;
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t start = nullptr, lists_copied = nullptr, all_out = nullptr;
+    cudaEvent_t chunk_in[kHostMaxChunks] = {}, chunk_done[kHostMaxChunks] = {};
+    int64_t* lists_host = nullptr;  // pinned: [chunks][group_count] chunk-local prefix sums
+    size_t lists_capacity = 0;
+};
+
+inline uint64_t align256(uint64_t v)
+{
+    return (v + 255u) & ~static_cast<uint64_t>(255u);
+}
+
+struct HostLayout {
+    uint64_t a, pt, d, lists, total;
+};
+
+HostLayout host_layout(const cb200_grouped_quant_matmul_host_args* a, uint32_t chunks)
+{
+    HostLayout l;
+    l.a = 0;
+    l.pt = align256(static_cast<uint64_t>(a->m) * a->k);
+    l.d = l.pt + align256(static_cast<uint64_t>(a->m) * 4u);
+    l.lists = l.d + align256(static_cast<uint64_t>(a->m) * a->n * 2u);
+    l.total = l.lists + align256(static_cast<uint64_t>(chunks) * a->group_count * 8u);
+    return l;
+}
+
+uint32_t host_chunks(const cb200_grouped_quant_matmul_host_args* a)
+{
+    uint32_t c = a->chunks == 0 ? kHostDefaultChunks : a->chunks;
+    c = c > kHostMaxChunks ? kHostMaxChunks : c;
+    const uint32_t tiles = (a->m + 127u) / 128u;
+    return c > tiles ? (tiles == 0 ? 1u : tiles) : c;
+}
+
+int host_pipe(HostPipe** out, size_t lists_needed)
+{
+    static HostPipe pipes[kMaxDevices];
+    int dev = 0;
+    CB200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) {
+        return CB200_INVALID;
+    }
+    HostPipe& hp = pipes[dev];
+    if (!hp.ready) {
+        CB200_CUDA_TRY(cudaStreamCreateWithFlags(&hp.in, cudaStreamNonBlocking));
+        CB200_CUDA_TRY(cudaStreamCreateWithFlags(&hp.out, cudaStreamNonBlocking));
+        CB200_CUDA_TRY(cudaEventCreateWithFlags(&hp.start, cudaEventDisableTiming));
+        CB200_CUDA_TRY(cudaEventCreateWithFlags(&hp.lists_copied, cudaEventDisableTiming));
+        CB200_CUDA_TRY(cudaEventCreateWithFlags(&hp.all_out, cudaEventDisableTiming));
+        for (uint32_t c = 0; c < kHostMaxChunks; ++c) {
+            CB200_CUDA_TRY(cudaEventCreateWithFlags(&hp.chunk_in[c], cudaEventDisableTiming));
+            CB200_CUDA_TRY(cudaEventCreateWithFlags(&hp.chunk_done[c], cudaEventDisableTiming));
+        }
+        hp.ready = true;
+    }
+    if (hp.lists_capacity < lists_needed) {
+        if (hp.lists_host != nullptr) {
+            CB200_CUDA_TRY(cudaEventSynchronize(hp.lists_copied));
+            CB200_CUDA_TRY(cudaFreeHost(hp.lists_host));
+            hp.lists_host = nullptr;
+        }
+        CB200_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&hp.lists_host), lists_needed, cudaHostAllocDefault));
+        hp.lists_capacity = lists_needed;
+    }
+    *out = &hp;
+    return CB200_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" {
+
+uint64_t cb200_grouped_quant_matmul_slice_m_host_workspace_size(const cb200_grouped_quant_matmul_host_args* args)
+{
+    if (args == nullptr || args->group_count == 0) {
+        return 0;
+    }
+    return host_layout(args, host_chunks(args)).total;
+}
+
+int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_matmul_host_args* args, void* stream_v)
+{
+    if (args == nullptr || args->group_count == 0 || args->group_count > static_cast<uint32_t>(kMaxGroups) ||
+        args->a_host == nullptr || args->group_list_host == nullptr || args->per_token_host == nullptr ||
+        args->d_host == nullptr || args->workspace == nullptr ||
+        (reinterpret_cast<uintptr_t>(args->workspace) & 255u) != 0) {
+        return CB200_INVALID;
+    }
+    if (args->m == 0 || args->n == 0) {
+        return CB200_SUCCESS;
+    }
+    const uint32_t chunks = host_chunks(args);
+    const HostLayout lay = host_layout(args, chunks);
+    if (args->workspace_bytes < lay.total) {
+        return CB200_INVALID;
+    }
+    uint8_t* ws = static_cast<uint8_t*>(args->workspace);
+    int8_t* a_dev = reinterpret_cast<int8_t*>(ws + lay.a);
+    float* pt_dev = reinterpret_cast<float*>(ws + lay.pt);
+    __nv_bfloat16* d_dev = reinterpret_cast<__nv_bfloat16*>(ws + lay.d);
+    int64_t* lists_dev = reinterpret_cast<int64_t*>(ws + lay.lists);
+    // validate once with the whole problem (alignment, layouts, sizes)
+    {
+        W8A8Problem q{args->m, args->n, args->k, args->group_count, CB200_GROUP_LIST_INT64, args->layout_b, a_dev,
+                      args->b, lists_dev, args->scale, pt_dev, d_dev, nullptr, 0};
+        int rc = check_w8a8(q, CB200_ROW_MAJOR);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    HostPipe* hp = nullptr;
+    const uint32_t G = args->group_count;
+    int rc = host_pipe(&hp, static_cast<size_t>(chunks) * G * 8u);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    // rows that take part: [0, last list entry); chunk boundaries on multiples of 128 rows
+    int64_t rows = args->group_list_host[G - 1];
+    rows = rows < 0 ? 0 : (rows > static_cast<int64_t>(args->m) ? static_cast<int64_t>(args->m) : rows);
+    const int64_t per = ((rows + chunks - 1) / chunks + 127) / 128 * 128;
+
+    // chunk-local group lists: entry g of chunk c = rows of groups 0..g that fall inside the chunk
+    CB200_CUDA_TRY(cudaEventSynchronize(hp->lists_copied));  // the previous call's copy has left the buffer
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const int64_t r0 = static_cast<int64_t>(c) * per < rows ? static_cast<int64_t>(c) * per : rows;
+        const int64_t r1 = r0 + per < rows ? r0 + per : rows;
+        for (uint32_t g = 0; g < G; ++g) {
+            int64_t e = args->group_list_host[g];
+            e = e < r0 ? r0 : (e > r1 ? r1 : e);
+            hp->lists_host[static_cast<size_t>(c) * G + g] = e - r0;
+        }
+    }
+    // order the copy-in stream behind whatever the caller has enqueued so far
+    CB200_CUDA_TRY(cudaEventRecord(hp->start, stream));
+    CB200_CUDA_TRY(cudaStreamWaitEvent(hp->in, hp->start, 0));
+    CB200_CUDA_TRY(cudaStreamWaitEvent(hp->out, hp->start, 0));
+    CB200_CUDA_TRY(cudaMemcpyAsync(lists_dev, hp->lists_host, static_cast<size_t>(chunks) * G * 8u,
+                                   cudaMemcpyHostToDevice, hp->in));
+    CB200_CUDA_TRY(cudaEventRecord(hp->lists_copied, hp->in));
+
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const int64_t r0 = static_cast<int64_t>(c) * per < rows ? static_cast<int64_t>(c) * per : rows;
+        const int64_t r1 = r0 + per < rows ? r0 + per : rows;
+        const int64_t cr = r1 - r0;
+        if (cr <= 0) {
+            continue;
+        }
+        CB200_CUDA_TRY(cudaMemcpyAsync(a_dev + r0 * args->k, static_cast<const int8_t*>(args->a_host) + r0 * args->k,
+                                       static_cast<size_t>(cr) * args->k, cudaMemcpyHostToDevice, hp->in));
+        CB200_CUDA_TRY(cudaMemcpyAsync(pt_dev + r0, args->per_token_host + r0, static_cast<size_t>(cr) * 4u,
+                                       cudaMemcpyHostToDevice, hp->in));
+        CB200_CUDA_TRY(cudaEventRecord(hp->chunk_in[c], hp->in));
+        CB200_CUDA_TRY(cudaStreamWaitEvent(stream, hp->chunk_in[c], 0));
+        W8A8Problem q{static_cast<uint32_t>(cr), args->n, args->k, G, CB200_GROUP_LIST_INT64, args->layout_b,
+                      a_dev + r0 * args->k, args->b, lists_dev + static_cast<size_t>(c) * G, args->scale,
+                      pt_dev + r0, d_dev + r0 * args->n, nullptr, 0};
+        rc = run_w8a8(q, CB200_ROW_MAJOR, stream);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        CB200_CUDA_TRY(cudaEventRecord(hp->chunk_done[c], stream));
+        CB200_CUDA_TRY(cudaStreamWaitEvent(hp->out, hp->chunk_done[c], 0));
+        CB200_CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t*>(args->d_host) + static_cast<size_t>(r0) * args->n * 2u,
+                                       d_dev + r0 * args->n, static_cast<size_t>(cr) * args->n * 2u,
+                                       cudaMemcpyDeviceToHost, hp->out));
+    }
+    // the caller's stream completes only after the last copy-out
+    CB200_CUDA_TRY(cudaEventRecord(hp->all_out, hp->out));
+    CB200_CUDA_TRY(cudaStreamWaitEvent(stream, hp->all_out, 0));
+    return CB200_SUCCESS;
 }
 
 }  // extern "C"

@@ -78,7 +78,7 @@ struct TileScheduler {
         uint32_t group;
     };
 
-    template <int BN>
+    template <int BN, int TM = 128>
     __device__ __forceinline__ void get(uint32_t idx, Tile& t)
     {
         while (idx >= tile_begin[group + 1]) {
@@ -87,7 +87,7 @@ struct TileScheduler {
         const uint32_t local = idx - tile_begin[group];
         const uint32_t mt = local / n_tiles;
         const uint32_t nt = local - mt * n_tiles;
-        t.row0 = row_begin[group] + static_cast<int32_t>(mt) * kBlockM;
+        t.row0 = row_begin[group] + static_cast<int32_t>(mt) * TM;
         t.row_end = row_end[group];
         t.n0 = static_cast<int32_t>(nt) * BN;
         t.group = group;

@@ -1,0 +1,331 @@
+// W8A8 GEMM (dense and grouped) on CTA pairs: the tcgen05.mma.cta_group::2 variant of w8a8_gemm_kernel.
+//
+// Two CTAs of a cluster (two neighbouring SMs) compute one 256 x 256 tile.  CTA r of the pair owns rows
+// [r*128, r*128+128) of the tile (its A tile and its 128 x 256 int32 accumulators in its own TMEM) and loads
+// only ONE HALF of the B tile (columns [r*128, r*128+128)); the pair's tensor cores read both halves.  Per
+// 128-byte K step a CTA therefore fills 32 KB of shared memory instead of 48 KB and reads 8 KB instead of
+// 12 KB per MMA: a third less L2->SM traffic, shared-memory bandwidth and power for the same math, and six
+// ring stages instead of four in the same 192 KB.  No multicast load is involved: each CTA fetches its own
+// operands with plain TMA loads whose completion bytes are counted on the leader CTA's barrier.
+//
+// Roles per CTA (6 warps) are those of w8a8_gemm_kernel; only the leader CTA (cluster rank 0) issues MMAs.
+//   full[s]        lives in the leader: 1 arrival (its producer's expect_tx for both CTAs' bytes)
+//   empty[s]       one per CTA: the MMA commit is multicast to both
+//   tmem_full[a]   one per CTA: commit multicast to both, each CTA's epilogue waits on its own
+//   tmem_empty[a]  lives in the leader: 8 arrivals (4 epilogue warps x 2 CTAs, the peer's arrive remotely)
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+#include "w8a8_gemm.cuh"
+
+namespace cb200 {
+
+constexpr int kPairTileM = 256;  // rows of the pair's tile
+constexpr int kPairBN = 256;     // columns of the pair's tile
+
+struct W8A8PairSmem {
+    static constexpr int kStageABytes = kBlockM * kBlockKBytes;         // 16 KB: this CTA's 128 rows
+    static constexpr int kStageBBytes = (kPairBN / 2) * kBlockKBytes;   // 16 KB: this CTA's half of B
+    static constexpr int kStageBytes = kStageABytes + kStageBBytes;
+    static constexpr int kStages = 6;
+    static constexpr int kRingBytes = kStages * kStageBytes;
+    static constexpr int kScaleBytes = 4 * kPairBN * 4;
+    static constexpr int kTableEntries = kMaxGroups + 2;
+    static constexpr int kTableBytes = 3 * kTableEntries * 4;
+    static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kTotalBytes = 1024 + kRingBytes + kScaleBytes + kTableBytes + kBarrierBytes;
+};
+
+// address of `local` (a shared::cta address of this CTA) as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+
+template <bool kBMnMajor>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const W8A8Params p)
+{
+    using S = W8A8PairSmem;
+    constexpr int kStages = S::kStages;
+    constexpr int BN = kPairBN;
+    constexpr uint32_t kTmemCols = 2 * BN;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t ring = raw_addr + pad;
+
+    float* s_scale = reinterpret_cast<float*>(smem + S::kRingBytes);
+    int32_t* s_row_begin = reinterpret_cast<int32_t*>(smem + S::kRingBytes + S::kScaleBytes);
+    int32_t* s_row_end = s_row_begin + S::kTableEntries;
+    uint32_t* s_tile_begin = reinterpret_cast<uint32_t*>(s_row_end + S::kTableEntries);
+    uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes + S::kScaleBytes + S::kTableBytes);
+    const uint32_t bar_full = smem_u32(s_bars);
+    const uint32_t bar_empty = bar_full + kStages * 8;
+    const uint32_t bar_tmem_full = bar_empty + kStages * 8;
+    const uint32_t bar_tmem_empty = bar_tmem_full + 2 * 8;
+    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 2 * kStages + 4);
+    volatile uint32_t* s_abort = s_tmem_ptr + 1;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t cta_rank = cluster_ctarank();  // 0 = leader: issues the MMAs, hosts full / tmem_empty
+    const uint32_t pair = blockIdx.x >> 1;
+    const uint32_t num_pairs = gridDim.x >> 1;
+    const uint32_t n_tiles = (p.n + BN - 1) / BN;
+    const uint32_t groups = p.group_count == 0 ? 1u : p.group_count;
+
+    // ------------------------------------------------------------------ set-up (as in w8a8_gemm_kernel)
+    if (p.group_count == 0) {
+        if (threadIdx.x == 0) {
+            s_row_end[0] = static_cast<int32_t>(p.m);
+        }
+    } else {
+        for (uint32_t g = threadIdx.x; g < groups; g += blockDim.x) {
+            long long e = p.group_list_is_i32 ? static_cast<long long>(static_cast<const int32_t*>(p.group_list)[g])
+                                              : static_cast<const long long*>(p.group_list)[g];
+            e = e < 0 ? 0 : (e > static_cast<long long>(p.m) ? static_cast<long long>(p.m) : e);
+            s_row_end[g] = static_cast<int32_t>(e);
+        }
+    }
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + s * 8, 1);
+            mbar_init(bar_empty + s * 8, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tmem_full + a * 8, 1);
+            mbar_init(bar_tmem_empty + a * 8, 2 * (kEpilogueThreads / 32));
+        }
+        fence_mbar_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t prev = 0;
+        uint32_t tiles = 0;
+        for (uint32_t g = 0; g < groups; ++g) {
+            const int32_t e = s_row_end[g];
+            s_row_begin[g] = prev;
+            s_tile_begin[g] = tiles;
+            if (e > prev) {
+                tiles += static_cast<uint32_t>((e - prev + kPairTileM - 1) / kPairTileM) * n_tiles;
+            }
+            prev = e;
+        }
+        s_tile_begin[groups] = tiles;
+    }
+    if (warp == 1) {
+        tmem_alloc<2>(smem_u32(s_tmem_ptr), kTmemCols);
+        tmem_relinquish<2>();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();  // both CTAs' barriers are initialised and their TMEM allocated before any cross-CTA signal
+    tcgen05_fence_after();
+
+    const uint32_t tmem_base = *s_tmem_ptr;
+    const uint32_t total_tiles = s_tile_begin[groups];
+    const uint32_t num_kb = p.num_k_blocks;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (both CTAs)
+        if (lane == 0) {
+            TileScheduler sched{s_row_begin, s_row_end, s_tile_begin, n_tiles, 0};
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
+                TileScheduler::Tile t;
+                sched.get<BN, kPairTileM>(idx, t);
+                const int32_t bz = (p.group_count == 0) ? 0 : static_cast<int32_t>(t.group);
+                const int32_t row0 = t.row0 + static_cast<int32_t>(cta_rank) * kBlockM;
+                const int32_t ncol0 = t.n0 + static_cast<int32_t>(cta_rank) * (BN / 2);
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer);
+                    if (!ok) {
+                        break;
+                    }
+                    const uint32_t sa = ring + stage * S::kStageBytes;
+                    const uint32_t sb = sa + S::kStageABytes;
+                    const int32_t k0 = static_cast<int32_t>(kb) * kBlockKBytes;
+                    if (cta_rank == 0) {
+                        mbar_expect_tx(bar_full + stage * 8, 2 * S::kStageBytes);  // both CTAs' operands
+                    }
+                    const uint32_t full = map_to_cta(bar_full + stage * 8, 0);    // the leader's barrier
+                    tma_load_2d_pair(sa, &tmap_a, full, k0, row0);
+                    if constexpr (kBMnMajor) {
+                        tma_load_3d_pair(sb, &tmap_b, full, ncol0, k0, bz);  // 128 rows of K x 128 bytes of N
+                    } else {
+                        tma_load_3d_pair(sb, &tmap_b, full, k0, ncol0, bz);  // 128 rows of N x 128 bytes of K
+                    }
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, false, kBMnMajor, kPairTileM, BN);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
+                ok = mbar_wait(bar_tmem_empty + acc * 8, acc_phase ^ 1, s_abort, p.status, kDevTimeoutMmaTmem);
+                if (!ok) {
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
+                    if (!ok) {
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t sa = ring + stage * S::kStageBytes;
+                    const uint32_t sb = sa + S::kStageABytes;
+#pragma unroll
+                    for (int j = 0; j < kBlockKBytes / kUmmaK; ++j) {
+                        // the descriptors name this CTA's tiles; the peer's tiles sit at the same offsets
+                        const uint64_t da = make_smem_desc_sw128(sa + j * kUmmaK, 16, 1024);
+                        uint64_t db;
+                        if constexpr (kBMnMajor) {
+                            db = make_smem_desc_sw128(sb + j * (kUmmaK * 128), kBlockKBytes * 128, 1024);
+                        } else {
+                            db = make_smem_desc_sw128(sb + j * kUmmaK, 16, 1024);
+                        }
+                        umma_i8<2>(tmem_d, da, db, idesc, (kb | j) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(bar_empty + stage * 8, 0x3);  // frees the stage in both CTAs
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                umma_commit_pair(bar_tmem_full + acc * 8, 0x3);  // both CTAs' halves of the accumulator are done
+                acc ^= 1;
+                if (acc == 0) {
+                    acc_phase ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- epilogue warps 2..5 (both CTAs)
+        const uint32_t quad = warp & 3;
+        const bool vec_ok = (p.n & 7u) == 0;
+        TileScheduler sched{s_row_begin, s_row_end, s_tile_begin, n_tiles, 0};
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
+            TileScheduler::Tile t;
+            sched.get<BN, kPairTileM>(idx, t);
+            float* sc = s_scale + (warp - 2) * BN;
+            const float* gscale = p.scale + static_cast<size_t>(p.group_count == 0 ? 0 : t.group) * p.n;
+            __syncwarp();
+            for (uint32_t i = lane; i < BN; i += 32) {
+                const uint32_t col = t.n0 + i;
+                sc[i] = col < p.n ? __ldg(gscale + col) : 0.0f;
+            }
+            __syncwarp();
+
+            ok = mbar_wait(bar_tmem_full + acc * 8, acc_phase, s_abort, p.status, kDevTimeoutEpilogue);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                break;
+            }
+            tcgen05_fence_after();
+
+            const int32_t row = t.row0 + static_cast<int32_t>(cta_rank * kBlockM + quad * 32 + lane);
+            const bool row_ok = row < t.row_end;
+            const float pt = row_ok ? __ldg(p.per_token + row) : 0.0f;
+            const uint32_t taddr = tmem_base + acc * BN + ((quad * 32u) << 16);
+            __nv_bfloat16* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
+            int32_t* arow = p.acc ? p.acc + static_cast<size_t>(row_ok ? row : 0) * p.n : nullptr;
+            // a whole warp without valid rows (ragged tail of a group) skips the drain
+            const bool warp_rows = (t.row0 + static_cast<int32_t>(cta_rank * kBlockM + quad * 32)) < t.row_end;
+
+#pragma unroll 1
+            for (int c = 0; c < BN / 32 && warp_rows; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tmem_ld_wait();
+                const uint32_t col0 = t.n0 + c * 32;
+                if (row_ok && col0 < p.n) {
+                    const float* scc = sc + c * 32;
+                    if (vec_ok && col0 + 32 <= p.n) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint32_t packed[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int j = v * 8 + e * 2;
+                                const float x0 =
+                                    __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), scc[j]), pt);
+                                const float x1 = __fmul_rn(
+                                    __fmul_rn(__int2float_rn(static_cast<int>(r[j + 1])), scc[j + 1]), pt);
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                                packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(drow + col0 + v * 8) =
+                                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) {
+                                const float x =
+                                    __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), scc[j]), pt);
+                                drow[col0 + j] = __float2bfloat16_rn(x);
+                            }
+                        }
+                    }
+                    if (arow != nullptr) {
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) {
+                                arow[col0 + j] = static_cast<int32_t>(r[j]);
+                            }
+                        }
+                    }
+                }
+            }
+            // drained: tell the leader's MMA issuer (remote arrive from the peer CTA)
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive_cluster(bar_tmem_empty + acc * 8, 0);
+            }
+            acc ^= 1;
+            if (acc == 0) {
+                acc_phase ^= 1;
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------ common exit
+    // Every thread of both CTAs gets here (all waits are bounded).  The cluster barrier keeps either CTA's
+    // shared memory and barriers alive until its peer has stopped signalling them.
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc<2>(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace cb200

@@ -109,6 +109,38 @@ CB200_API uint64_t cb200_grouped_quant_matmul_slice_m_workspace_size(const cb200
 CB200_API int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args *args, void *stream);
 
 /*
+ * The grouped matmul for HOST-resident activations and output: what the reference's example mains do around
+ * the kernel (aclrtMemcpy host->device, launch, aclrtMemcpy device->host:
+ * examples/07_grouped_matmul_slice_m_per_token_dequant_moe/grouped_matmul_slice_m_per_token_dequant_moe.cpp:
+ * 78-110, 176-184), folded into one call that overlaps the three phases.  The routed rows are cut into
+ * `chunks` row ranges; chunk c+1 is copied in (PCIe down) while chunk c is computed and chunk c-1 is copied
+ * out (PCIe up), on two library-owned copy streams ordered against `stream` with events.
+ * a_host, per_token_host, group_list_host, d_host are host pointers (pinned memory for real overlap);
+ * b and scale (the expert weights) stay on the device.  The device workspace
+ * (cb200_grouped_quant_matmul_slice_m_host_workspace_size bytes) stages A, the per-token scales, D and the
+ * per-chunk group lists.  On return all work is enqueued; d_host is complete once `stream` has caught up.
+ */
+typedef struct cb200_grouped_quant_matmul_host_args {
+    uint32_t m, n, k;
+    uint32_t group_count;
+    uint32_t layout_b;
+    uint32_t chunks;                  /* 0 = library default (8) */
+    const void *a_host;               /* int8 m x k */
+    const int64_t *group_list_host;   /* prefix sums */
+    const float *per_token_host;      /* [m] */
+    void *d_host;                     /* bf16 m x n */
+    const void *b;                    /* device: int8 [group_count][k x n] */
+    const float *scale;               /* device: [group_count][n] */
+    void *workspace;                  /* device */
+    uint64_t workspace_bytes;
+} cb200_grouped_quant_matmul_host_args;
+
+CB200_API uint64_t cb200_grouped_quant_matmul_slice_m_host_workspace_size(
+    const cb200_grouped_quant_matmul_host_args *args);
+CB200_API int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_matmul_host_args *args,
+                                                      void *stream);
+
+/*
  * W4A8 matmul with per-group weight scales:
  *     acc_g[i,j] = sum_{k in group g} A[i,k] * W[k,j]                       (int32)
  *     y[i,j]     = fma(float(acc_g), weight_scale[g,j], y), g ascending     (fp32)

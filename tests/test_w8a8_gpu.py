@@ -218,6 +218,32 @@ def test_grouped_full_moe_config_sampled_rows(cuda):
     assert int((d.view(torch.int16) != 0).any(dim=1).sum()) == rows
 
 
+@pytest.mark.parametrize("chunks", [0, 1, 3])
+def test_grouped_host_buffers_entry(cuda, chunks):
+    """Host-resident activations and output through the chunked copy/compute pipeline: same bits as the oracle,
+    rows past the last group untouched in the caller's host buffer."""
+    import torch
+    from catlass_b200 import capi
+    sizes = [0, 300, 1, 127, 700, 0, 129, 64]
+    n, k = 512, 272
+    a, b, scale, pt, gl = P.w8a8_grouped(sizes, n, k, seed=21, m_capacity=sum(sizes) + 33)
+    m, g = a.shape[0], len(sizes)
+    a_h = torch.from_numpy(a).pin_memory()
+    pt_h = torch.from_numpy(pt).pin_memory()
+    gl_h = torch.from_numpy(gl).pin_memory()
+    d_h = torch.full((m, n), 777.0, dtype=torch.bfloat16).pin_memory()
+    ws = torch.empty(capi.grouped_quant_matmul_host_workspace_size(m, n, k, g, chunks), dtype=torch.uint8, device=cuda)
+    for _ in range(2):  # twice: the pipeline's events and pinned list buffer are reused
+        capi.grouped_quant_matmul_host(a_h, gl_h, pt_h, d_h, _dev(b), _dev(scale), m, n, k, g, ws, chunks=chunks)
+        torch.cuda.current_stream().synchronize()
+    st, code = capi.device_status()
+    assert st == 0, f"device status {st} code {code:#x}"
+    init = np.full((m, n), 777.0, np.float32)
+    want = O.grouped_quant_matmul(a, b, gl, scale, pt, m, n, k, O.ROW_MAJOR, out_init=init)
+    got = d_h.view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(got, O.bf16_bits(want))
+
+
 def test_k_zero_writes_zeros(cuda):
     from catlass_b200 import capi
     torch = _torch()
