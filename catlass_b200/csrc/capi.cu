@@ -304,12 +304,20 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
             kbs = v;
         }
     }
-    while (kbs > 1 && 2 * smallm_stage_bytes(p.mt, kbs) > 216u * 1024u) {
+    // ring budget per CTA (developer knob CB200_SMALLM_RING_KB)
+    uint32_t ring_budget = 216u * 1024u;
+    if (const char* e = getenv("CB200_SMALLM_RING_KB")) {
+        const uint32_t v = static_cast<uint32_t>(atoi(e));
+        if (v >= 36 && v <= 216) {
+            ring_budget = v * 1024u;
+        }
+    }
+    while (kbs > 1 && 2 * smallm_stage_bytes(p.mt, kbs) > ring_budget) {
         kbs /= 2;  // wide token panels: keep at least two stages
     }
     p.kbs = kbs;
     const uint32_t stage_bytes = smallm_stage_bytes(p.mt, kbs);
-    uint32_t stages = (216u * 1024u) / stage_bytes;  // one CTA per SM
+    uint32_t stages = ring_budget / stage_bytes;
     // developer knobs for tuning runs: CB200_SMALLM_SPLITS / CB200_SMALLM_STAGES override the heuristic
     if (const char* e = getenv("CB200_SMALLM_SPLITS")) {
         const uint32_t v = static_cast<uint32_t>(atoi(e));
@@ -365,13 +373,21 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
     cfg.blockDim = dim3(kSmallMThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: this kernel's set-up and first weight loads may overlap the tail of the
+    // kernel before it on the stream; it waits (griddepcontrol.wait) before it reads activations or writes D
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    static const bool use_pdl = [] {
+        const char* e = getenv("CB200_SMALLM_PDL");
+        return e == nullptr || atoi(e) != 0;
+    }();
+    cfg.numAttrs = use_pdl ? 2 : 1;
     CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmap_w, tmap_x, p));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return CB200_SUCCESS;

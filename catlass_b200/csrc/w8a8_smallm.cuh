@@ -118,16 +118,15 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_ptr;
+    grid_launch_dependents();  // a dependent launch may start its own set-up and weight prefetch from here on
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            for (uint32_t kb = kb_begin; kb < kb_end; kb += p.kbs) {
-                if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer)) {
-                    break;
-                }
+            // Weights never depend on the kernel launched before this one, activations may: when launched with
+            // programmatic dependent launch, the first ring fill of WEIGHT tiles is issued before
+            // griddepcontrol.wait, the activation tiles (and, transitively, every store to D) after it.
+            auto load_w = [&](uint32_t stage, uint32_t kb, uint32_t nsub) {
                 const uint32_t full = bar_full + stage * 8;
-                const uint32_t nsub = kb_end - kb < p.kbs ? kb_end - kb : p.kbs;
                 // the W box holds tile_rows rows; the UMMA still reads 128: the rows behind are never stored
                 mbar_expect_tx(full, nsub * (p.tile_rows + p.mt) * kBlockKBytes);
                 // the sub-blocks of a stage are neighbours in K: each weight row is read in runs of
@@ -141,10 +140,35 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                         tma_load_2d(sw, &tmap_w, full, k0, n0);  // rows = n, 128 bytes of k
                     }
                 }
+            };
+            auto load_x = [&](uint32_t stage, uint32_t kb, uint32_t nsub) {
+                const uint32_t full = bar_full + stage * 8;
                 for (uint32_t sub = 0; sub < nsub; ++sub) {
                     const uint32_t sx = ring + stage * stage_bytes + sub * block_bytes + kSmallMTileN * kBlockKBytes;
                     tma_load_2d(sx, &tmap_x, full, static_cast<int32_t>(kb + sub) * kBlockKBytes, 0);
                 }
+            };
+            const uint32_t iters = (my_kb + p.kbs - 1) / p.kbs;
+            const uint32_t pre = iters < p.stages ? iters : p.stages;  // the ring is empty: no waits needed
+            for (uint32_t i = 0; i < pre; ++i) {
+                const uint32_t kb = kb_begin + i * p.kbs;
+                load_w(i, kb, kb_end - kb < p.kbs ? kb_end - kb : p.kbs);
+            }
+            grid_dependency_wait();
+            for (uint32_t i = 0; i < pre; ++i) {
+                const uint32_t kb = kb_begin + i * p.kbs;
+                load_x(i, kb, kb_end - kb < p.kbs ? kb_end - kb : p.kbs);
+            }
+            uint32_t stage = pre == p.stages ? 0 : pre;
+            uint32_t phase = pre == p.stages ? 1 : 0;
+            for (uint32_t i = pre; i < iters; ++i) {
+                if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer)) {
+                    break;
+                }
+                const uint32_t kb = kb_begin + i * p.kbs;
+                const uint32_t nsub = kb_end - kb < p.kbs ? kb_end - kb : p.kbs;
+                load_w(stage, kb, nsub);
+                load_x(stage, kb, nsub);
                 if (++stage == p.stages) {
                     stage = 0;
                     phase ^= 1;
