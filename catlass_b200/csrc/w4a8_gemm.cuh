@@ -14,10 +14,14 @@
 // A CTA owns 64 output channels (so each weight byte is unpacked exactly once per 128-token row tile) and up
 // to 128 tokens: tokens on the TMEM lanes (UMMA M = 128), channels on the UMMA N axis (N = 64).
 //
-// Warp roles (14 warps):
-//   warp 0      TMA producer: packed weight tile (64 x 64 B) + token tile (mt x 128 B) per 128-wide K block
-//   warp 1      MMA issuer (tcgen05.mma.kind::i8, 128 x 64 x 32); eight int32 accumulators in TMEM, one per group
-//               in flight, so the issuer never waits for the epilogue's hand-back
+// Warp roles (15 warps):
+//   warp 0      TMA producer: packed weight tiles (64 x 64 B, 12 in flight: they come from HBM) and token tiles
+//               (mt x 128 B, 6 in flight: they come from L2) into two rings fed by one non-blocking loop
+//   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x 64 x 32), alternate K blocks.  Every K block gets its
+//               own int32 accumulator in TMEM and ONE tcgen05.commit: the same barrier tells the producer and
+//               the unpack warps that the block's shared-memory tiles are free and the epilogue that its
+//               accumulator is complete.  Six blocks in flight (token tiles, unpacked tiles, accumulators).
+//               Issuing an MMA costs its thread ~70 ns, more than an MMA this small runs: hence two issuers.
 //   warps 2-5   unpack: nibble -> int8 holding 16*w (the nibble moved to the high half of the byte: no sign
 //               fix-up needed), written in the 128B-swizzled K-major operand layout, then handed to the MMA
 //               through a proxy fence + mbarrier.  The factor 16 is removed again, exactly, when the epilogue
@@ -34,11 +38,16 @@
 
 namespace cb200 {
 
-constexpr int kW4Threads = 448;
-constexpr int kW4TileN = 64;       // output channels per CTA (UMMA N)
-constexpr int kW4TileM = 128;      // tokens per CTA (UMMA M)
-constexpr int kW4Stages = 7;
-constexpr int kW4Accs = 8;        // group accumulators in TMEM (8 x 64 columns): hides the MMA<->epilogue hand-off latency
+constexpr int kW4Threads = 480;      // 15 warps: producer, MMA issuer A, 4 unpack, 8 epilogue, MMA issuer B
+constexpr int kW4TileN = 64;        // output channels per CTA (UMMA N)
+constexpr int kW4TileM = 128;       // tokens per CTA (UMMA M)
+constexpr int kW4Batch = 1;         // K blocks per batch (one commit per batch)
+constexpr int kW4InFlight = 6;      // batches whose tiles / accumulators exist at the same time
+constexpr int kW4Issuers = 2;       // MMA-issuing threads (batches alternate between them)
+constexpr int kW4TokenSlots = kW4Batch * kW4InFlight;
+constexpr int kW4CookedSlots = kW4Batch * kW4InFlight;
+constexpr int kW4Accs = kW4Batch * kW4InFlight;
+constexpr int kW4PackedSlots = 12;  // packed-weight tiles in flight (4 KB each): covers HBM latency
 
 struct W4A8Params {
     uint32_t m, n, k;
@@ -55,11 +64,15 @@ struct W4A8Smem {
     static constexpr int kTokenBytes = kW4TileM * 128;   // 16 KB: UMMA A operand
     static constexpr int kCookedBytes = kW4TileN * 128;  //  8 KB: unpacked int8 weights, UMMA B operand
     static constexpr int kPackedBytes = kW4TileN * 64;   //  4 KB: packed weights as loaded
-    static constexpr int kStageBytes = kTokenBytes + kCookedBytes + kPackedBytes;  // 28 KB
-    static constexpr int kRingBytes = kW4Stages * kStageBytes;
+    static constexpr int kTokenRing = 0;
+    static constexpr int kCookedRing = kTokenRing + kW4TokenSlots * kTokenBytes;
+    static constexpr int kPackedRing = kCookedRing + kW4CookedSlots * kCookedBytes;
+    static constexpr int kRingBytes = kPackedRing + kW4PackedSlots * kPackedBytes;
     static constexpr int kScaleSlots = 8;                // per epilogue warp: ring of 32-channel scale rows
     static constexpr int kScaleBytes = 8 * kScaleSlots * 32 * 4;
-    static constexpr int kBarrierBytes = (3 * kW4Stages + 2 * kW4Accs) * 8 + 16;
+    // p_full, p_empty [packed]; x_full [token]; c_full [cooked]; batch_done, tmem_empty [in flight]
+    static constexpr int kBarriers = 2 * kW4PackedSlots + kW4TokenSlots + kW4CookedSlots + 2 * kW4InFlight;
+    static constexpr int kBarrierBytes = kBarriers * 8 + 16;
     static constexpr int kTotalBytes = 1024 + kRingBytes + kScaleBytes + kBarrierBytes;
 };
 
@@ -110,12 +123,13 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     float* s_scales = reinterpret_cast<float*>(smem + S::kRingBytes);
     uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes + S::kScaleBytes);
-    const uint32_t bar_full = smem_u32(s_bars);               // TMA landed (tx bytes)
-    const uint32_t bar_cooked = bar_full + kW4Stages * 8;     // an unpack warp finished the stage
-    const uint32_t bar_empty = bar_cooked + kW4Stages * 8;    // MMAs that read the stage completed
-    const uint32_t bar_tmem_full = bar_empty + kW4Stages * 8;
-    const uint32_t bar_tmem_empty = bar_tmem_full + kW4Accs * 8;
-    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 3 * kW4Stages + 2 * kW4Accs);
+    const uint32_t bar_p_full = smem_u32(s_bars);                   // packed tile landed (TMA bytes)
+    const uint32_t bar_p_empty = bar_p_full + kW4PackedSlots * 8;    // an unpack warp has read it
+    const uint32_t bar_x_full = bar_p_empty + kW4PackedSlots * 8;    // token tile landed
+    const uint32_t bar_c_full = bar_x_full + kW4TokenSlots * 8;      // unpacked tile written
+    const uint32_t bar_batch_done = bar_c_full + kW4CookedSlots * 8; // all MMAs of a batch completed
+    const uint32_t bar_tmem_empty = bar_batch_done + kW4InFlight * 8;  // epilogue drained a batch's accumulators
+    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + S::kBarriers);
     volatile uint32_t* s_abort = s_tmem_ptr + 1;
 
     const uint32_t warp = threadIdx.x >> 5;
@@ -124,18 +138,26 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const int32_t m0 = static_cast<int32_t>(blockIdx.y) * kW4TileM;
     const uint32_t num_kb = p.num_k_blocks;
     const uint32_t bpg = p.blocks_per_group;
-    constexpr uint32_t kTmemCols = kW4Accs * kW4TileN;
+    const uint32_t unit = bpg < static_cast<uint32_t>(kW4Batch) ? bpg : kW4Batch;  // K blocks per accumulator
+    const uint32_t num_batches = (num_kb + kW4Batch - 1) / kW4Batch;
+    constexpr uint32_t kTmemCols = 512;  // power of two >= kW4Accs * 64
+    static_assert(kW4Accs * kW4TileN <= 512, "TMEM budget");
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
-        for (int s = 0; s < kW4Stages; ++s) {
-            mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_cooked + s * 8, 1);
-            mbar_init(bar_empty + s * 8, 1);
+        for (int i = 0; i < kW4PackedSlots; ++i) {
+            mbar_init(bar_p_full + i * 8, 1);
+            mbar_init(bar_p_empty + i * 8, 1);
         }
-        for (int a = 0; a < kW4Accs; ++a) {
-            mbar_init(bar_tmem_full + a * 8, 1);
-            mbar_init(bar_tmem_empty + a * 8, 8);
+        for (int i = 0; i < kW4TokenSlots; ++i) {
+            mbar_init(bar_x_full + i * 8, 1);
+        }
+        for (int i = 0; i < kW4CookedSlots; ++i) {
+            mbar_init(bar_c_full + i * 8, 1);
+        }
+        for (int i = 0; i < kW4InFlight; ++i) {
+            mbar_init(bar_batch_done + i * 8, 1);
+            mbar_init(bar_tmem_empty + i * 8, 8);
         }
         fence_mbar_init();
         prefetch_tmap(&tmap_w);
@@ -149,72 +171,107 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_ptr;
-    const uint32_t stage_tx = S::kPackedBytes + p.mt * 128;
+
+    // Batch B uses barrier slot B % kW4InFlight; it is the (B / kW4InFlight)-th use of that slot.
+    // "the previous user of this slot is done" = wait with the inverted parity (passes at once for the first use).
 
     if (warp == 0) {
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                if (!mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer)) {
-                    break;
+            // One thread feeds two rings of different depth: it polls both "slot free" conditions without
+            // blocking on either, so the deep packed-weight ring keeps running ahead of the token ring.
+            uint32_t kw = 0, kx = 0, idle = 0;
+            unsigned long long t0 = 0;
+            while (kw < num_kb || kx < num_kb) {
+                bool progressed = false;
+                if (kw < num_kb) {
+                    const uint32_t slot = kw % kW4PackedSlots;
+                    if (mbar_try_wait(bar_p_empty + slot * 8, ((kw / kW4PackedSlots) & 1) ^ 1)) {
+                        const uint32_t full = bar_p_full + slot * 8;
+                        mbar_expect_tx(full, S::kPackedBytes);
+                        tma_load_2d(ring + S::kPackedRing + slot * S::kPackedBytes, &tmap_w, full,
+                                    static_cast<int32_t>(kw) * 64, n0);
+                        ++kw;
+                        progressed = true;
+                    }
                 }
-                const uint32_t base = ring + stage * S::kStageBytes;
-                const uint32_t full = bar_full + stage * 8;
-                mbar_expect_tx(full, stage_tx);
-                tma_load_2d(base, &tmap_x, full, static_cast<int32_t>(kb) * 128, m0);
-                tma_load_2d(base + S::kTokenBytes + S::kCookedBytes, &tmap_w, full, static_cast<int32_t>(kb) * 64, n0);
-                if (++stage == kW4Stages) {
-                    stage = 0;
-                    phase ^= 1;
+                if (kx < num_kb) {
+                    const uint32_t batch = kx / kW4Batch;
+                    const uint32_t bslot = batch % kW4InFlight;
+                    if (mbar_try_wait(bar_batch_done + bslot * 8, ((batch / kW4InFlight) & 1) ^ 1)) {
+                        const uint32_t slot = kx % kW4TokenSlots;
+                        const uint32_t full = bar_x_full + slot * 8;
+                        mbar_expect_tx(full, p.mt * 128);
+                        tma_load_2d(ring + S::kTokenRing + slot * S::kTokenBytes, &tmap_x, full,
+                                    static_cast<int32_t>(kx) * 128, m0);
+                        ++kx;
+                        progressed = true;
+                    }
+                }
+                if (progressed) {
+                    idle = 0;
+                    t0 = 0;
+                } else if ((++idle & 0x3f) == 0) {
+                    if (t0 == 0) {
+                        t0 = globaltimer_ns();
+                    }
+                    if (*s_abort != 0) {
+                        break;
+                    }
+                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        *s_abort = 1;
+                        atomicMax(p.status, kDevTimeoutProducer);
+                        break;
+                    }
                 }
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 14) {
+        // Two issuing threads take alternate batches: issuing a tcgen05.mma costs its thread ~70 ns, more than
+        // an MMA of this small shape runs, so one issuer alone would leave the tensor core idle.
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, false, false, kW4TileM, kW4TileN);
-            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (uint32_t kb = 0; ok && kb < num_kb; ++kb) {
-                const uint32_t in_group = kb % bpg;
-                if (in_group == 0) {
-                    ok = mbar_wait(bar_tmem_empty + acc * 8, acc_phase ^ 1, s_abort, p.status, kDevTimeoutMmaTmem);
-                    if (!ok) {
-                        break;
-                    }
-                }
-                ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma) &&
-                     mbar_wait(bar_cooked + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
+            for (uint32_t batch = (warp == 1 ? 0 : 1); ok && batch < num_batches; batch += kW4Issuers) {
+                const uint32_t bslot = batch % kW4InFlight;
+                const uint32_t use = batch / kW4InFlight;
+                ok = mbar_wait(bar_tmem_empty + bslot * 8, (use & 1) ^ 1, s_abort, p.status, kDevTimeoutMmaTmem);
                 if (!ok) {
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t sx_tile = ring + stage * S::kStageBytes;  // tokens: UMMA A operand
-                const uint32_t sw_tile = sx_tile + S::kTokenBytes;       // unpacked weights: UMMA B operand
-                const uint32_t tmem_d = tmem_base + acc * kW4TileN;
+                const uint32_t kb_end = (batch + 1) * kW4Batch < num_kb ? (batch + 1) * kW4Batch : num_kb;
+                for (uint32_t kb = batch * kW4Batch; kb < kb_end; ++kb) {
+                    const uint32_t slot = kb % kW4TokenSlots;  // token and unpacked rings have the same depth
+                    const uint32_t ph = (kb / kW4TokenSlots) & 1;
+                    ok = mbar_wait(bar_x_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma) &&
+                         mbar_wait(bar_c_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma);
+                    if (!ok) {
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t sx_tile = ring + S::kTokenRing + slot * S::kTokenBytes;    // UMMA A operand
+                    const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA B operand
+                    const uint32_t in_batch = kb - batch * kW4Batch;
+                    const uint32_t acc = bslot * kW4Batch + in_batch / unit;
+                    const uint32_t tmem_d = tmem_base + acc * kW4TileN;
+                    const uint32_t first = in_batch % unit;  // 0: this K block starts a new accumulator
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint64_t da = make_smem_desc_sw128(sx_tile + j * kUmmaK, 16, 1024);
-                    const uint64_t db = make_smem_desc_sw128(sw_tile + j * kUmmaK, 16, 1024);
-                    umma_i8<1>(tmem_d, da, db, idesc, (in_group | j) != 0 ? 1u : 0u);
-                }
-                umma_commit<1>(bar_empty + stage * 8);
-                if (in_group == bpg - 1) {
-                    umma_commit<1>(bar_tmem_full + acc * 8);  // this group's accumulator is complete
-                    if (++acc == kW4Accs) {
-                        acc = 0;
-                        acc_phase ^= 1;
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t da = make_smem_desc_sw128(sx_tile + j * kUmmaK, 16, 1024);
+                        const uint64_t db = make_smem_desc_sw128(sw_tile + j * kUmmaK, 16, 1024);
+                        umma_i8<1>(tmem_d, da, db, idesc, (first | j) != 0 ? 1u : 0u);
                     }
                 }
-                if (++stage == kW4Stages) {
-                    stage = 0;
-                    phase ^= 1;
+                if (!ok) {
+                    break;
                 }
+                umma_commit<1>(bar_batch_done + bslot * 8);  // tiles free + accumulators complete, one signal
             }
         }
         __syncwarp();
     } else if (warp < 6) {
-        // ------------------------------------------------------- unpack warps
+        // ------------------------------------------------------- unpack warps (2..5)
         // Warp u of the four handles the K blocks kb = u, u+4, ... on its own (eight independent 16-byte
         // chunks per lane: plenty of instruction-level parallelism, one fence and one arrival per block).
         // Lane l, step i works on row = i*8 + l/4, packed chunk c = l%4.
@@ -224,21 +281,27 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t c = lane & 3;
         const uint32_t rsub = lane >> 2;  // 0..7: row inside a group of eight (= row & 7)
         for (uint32_t kb = u; kb < num_kb; kb += 4) {
-            const uint32_t stage = kb % kW4Stages;
-            const uint32_t phase = (kb / kW4Stages) & 1;
-            bool ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutConvert);
+            const uint32_t ps = kb % kW4PackedSlots, pph = (kb / kW4PackedSlots) & 1;
+            const uint32_t cs = kb % kW4CookedSlots;
+            const uint32_t batch = kb / kW4Batch;
+            const uint32_t bslot = batch % kW4InFlight, buse = batch / kW4InFlight;
+            bool ok = mbar_wait(bar_p_full + ps * 8, pph, s_abort, p.status, kDevTimeoutConvert) &&
+                      mbar_wait(bar_batch_done + bslot * 8, (buse & 1) ^ 1, s_abort, p.status, kDevTimeoutConvert);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
             }
-            uint8_t* base = smem + stage * S::kStageBytes;
-            const uint8_t* packed = base + S::kTokenBytes + S::kCookedBytes;
-            uint8_t* cooked = base + S::kTokenBytes;
+            const uint8_t* packed = smem + S::kPackedRing + ps * S::kPackedBytes;
+            uint8_t* cooked = smem + S::kCookedRing + cs * S::kCookedBytes;
             uint4 q[8];
 #pragma unroll
             for (uint32_t i = 0; i < 8; ++i) {
                 const uint32_t row = i * 8 + rsub;
                 q[i] = *reinterpret_cast<const uint4*>(packed + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_p_empty + ps * 8);  // the packed tile is in registers: its slot can be refilled
             }
 #pragma unroll
             for (uint32_t i = 0; i < 8; ++i) {
@@ -259,7 +322,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(bar_cooked + stage * 8);
+                mbar_arrive(bar_c_full + cs * 8);
             }
         }
     } else {
@@ -274,9 +337,11 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const bool warp_has_rows = static_cast<uint32_t>(m0) + quad * 32 < p.m;  // else: only hand buffers back
         float* sbuf = s_scales + ew * (S::kScaleSlots * 32);  // ring of scale rows, one float per lane
         float y[32];
+        int32_t isum[32];  // int32 sum of a group that spans several batches (exact)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             y[i] = 0.0f;
+            isum[i] = 0;
         }
         // Channel scales stream from global memory into the ring with cp.async, kAhead groups ahead of their
         // use, so that their latency never sits on the per-group critical path.
@@ -298,53 +363,75 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         for (uint32_t g = 0; g < kAhead; ++g) {
             fetch_scale(g);
         }
-        uint32_t acc = 0, acc_phase = 0;
+        const uint32_t accs_per_batch = kW4Batch / unit;
+        uint32_t g = 0;             // group whose scale the next finished accumulator needs
+        uint32_t kb_in_group = 0;   // K blocks of group g already summed
         bool ok = true;
-        for (uint32_t g = 0; g < groups; ++g) {
-            fetch_scale(g + kAhead);
-            ok = mbar_wait(bar_tmem_full + acc * 8, acc_phase, s_abort, p.status, kDevTimeoutEpilogue);
+        for (uint32_t batch = 0; ok && batch < num_batches; ++batch) {
+            const uint32_t bslot = batch % kW4InFlight, buse = batch / kW4InFlight;
+            ok = mbar_wait(bar_batch_done + bslot * 8, buse & 1, s_abort, p.status, kDevTimeoutEpilogue);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
             }
             tcgen05_fence_after();
-            asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // this group's scales landed
-            __syncwarp();
-            if (warp_has_rows) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + acc * kW4TileN + half * 32 + ((quad * 32u) << 16), r);
-                tmem_ld_wait();
-                const float4* sc4 = reinterpret_cast<const float4*>(sbuf + (g % S::kScaleSlots) * 32);
-                if (bpg == 1) {
-                    // one 128-wide K block per group: |16 * acc| <= 16 * 128 * 128 * 8 = 2^21
+            const uint32_t kb0 = batch * kW4Batch;
+            const uint32_t kbs_here = kb0 + kW4Batch <= num_kb ? kW4Batch : num_kb - kb0;
+            for (uint32_t a = 0; a < accs_per_batch && a * unit < kbs_here; ++a) {
+                const uint32_t kb_acc = (a + 1) * unit <= kbs_here ? unit : kbs_here - a * unit;
+                const bool group_ends = kb_in_group + kb_acc == bpg;
+                if (group_ends) {
+                    fetch_scale(g + kAhead);
+                    asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // group g's scales landed
+                    __syncwarp();
+                }
+                if (warp_has_rows) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(
+                        tmem_base + (bslot * kW4Batch + a) * kW4TileN + half * 32 + ((quad * 32u) << 16), r);
+                    tmem_ld_wait();
+                    if (bpg == 1) {
+                        // one 128-wide K block per group: |16 * acc| <= 16 * 128 * 128 * 8 = 2^21
+                        const float4* sc4 = reinterpret_cast<const float4*>(sbuf + (g % S::kScaleSlots) * 32);
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        const float4 s4 = sc4[v];
-                        float f0, f1, f2, f3;
-                        int2float_pair(r[4 * v], r[4 * v + 1], f0, f1);
-                        int2float_pair(r[4 * v + 2], r[4 * v + 3], f2, f3);
-                        fma2(y[4 * v], y[4 * v + 1], f0, f1, s4.x, s4.y);
-                        fma2(y[4 * v + 2], y[4 * v + 3], f2, f3, s4.z, s4.w);
-                    }
-                } else {
+                        for (int v = 0; v < 8; ++v) {
+                            const float4 s4 = sc4[v];
+                            float f0, f1, f2, f3;
+                            int2float_pair(r[4 * v], r[4 * v + 1], f0, f1);
+                            int2float_pair(r[4 * v + 2], r[4 * v + 3], f2, f3);
+                            fma2(y[4 * v], y[4 * v + 1], f0, f1, s4.x, s4.y);
+                            fma2(y[4 * v + 2], y[4 * v + 3], f2, f3, s4.z, s4.w);
+                        }
+                    } else {
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        const float4 s4 = sc4[v];
-                        fma2(y[4 * v], y[4 * v + 1], __int2float_rn(static_cast<int>(r[4 * v])) * 0.0625f,
-                             __int2float_rn(static_cast<int>(r[4 * v + 1])) * 0.0625f, s4.x, s4.y);
-                        fma2(y[4 * v + 2], y[4 * v + 3], __int2float_rn(static_cast<int>(r[4 * v + 2])) * 0.0625f,
-                             __int2float_rn(static_cast<int>(r[4 * v + 3])) * 0.0625f, s4.z, s4.w);
+                        for (int i = 0; i < 32; ++i) {
+                            isum[i] += static_cast<int32_t>(r[i]);
+                        }
+                        if (group_ends) {
+                            const float4* sc4 = reinterpret_cast<const float4*>(sbuf + (g % S::kScaleSlots) * 32);
+#pragma unroll
+                            for (int v = 0; v < 8; ++v) {
+                                const float4 s4 = sc4[v];
+                                // the sums are multiples of 16: the conversion and the scaling by 1/16 are exact
+                                fma2(y[4 * v], y[4 * v + 1], __int2float_rn(isum[4 * v]) * 0.0625f,
+                                     __int2float_rn(isum[4 * v + 1]) * 0.0625f, s4.x, s4.y);
+                                fma2(y[4 * v + 2], y[4 * v + 3], __int2float_rn(isum[4 * v + 2]) * 0.0625f,
+                                     __int2float_rn(isum[4 * v + 3]) * 0.0625f, s4.z, s4.w);
+                                isum[4 * v] = isum[4 * v + 1] = isum[4 * v + 2] = isum[4 * v + 3] = 0;
+                            }
+                        }
                     }
+                }
+                kb_in_group += kb_acc;
+                if (group_ends) {
+                    kb_in_group = 0;
+                    ++g;
                 }
             }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(bar_tmem_empty + acc * 8);
-            }
-            if (++acc == kW4Accs) {
-                acc = 0;
-                acc_phase ^= 1;
+                mbar_arrive(bar_tmem_empty + bslot * 8);
             }
         }
         if (ok && mrow < p.m) {

@@ -30,7 +30,7 @@ def _run(cuda, a, packed, sw, sa, m, n, k, gs):
 
 @pytest.mark.parametrize("m,n,k,gs", [
     (128, 512, 1024, 128), (16, 256, 256, 128), (77, 200, 384, 128), (64, 128, 2048, 256),
-    (130, 136, 512, 128), (1, 128, 128, 128), (33, 1000, 4096, 128),
+    (130, 136, 512, 128), (1, 128, 128, 128), (33, 1000, 4096, 128), (40, 192, 1536, 512), (16, 64, 384, 128), (24, 128, 768, 384),
 ])
 def test_w4a8_per_group_matches_oracle(cuda, m, n, k, gs):
     a, w, packed, sw, sa = _problem(m, n, k, gs, seed=m + n + k)
