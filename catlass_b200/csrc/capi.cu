@@ -467,7 +467,8 @@ int check_w4a8(const cb200_w4a8_matmul_args* a)
 uint64_t mx_workspace_bytes(const cb200_mx_matmul_args* a)
 {
     const uint64_t kq = a->k / 128u;
-    return (static_cast<uint64_t>((a->m + 127u) / 128u) + (a->n + 127u) / 128u) * kq * 512u;
+    // scale blocks of 128 rows; B's are padded to whole 256-column tiles
+    return (static_cast<uint64_t>((a->m + 127u) / 128u) + 2u * ((a->n + 255u) / 256u)) * kq * 512u;
 }
 
 int check_mx(const cb200_mx_matmul_args* a)
@@ -525,9 +526,10 @@ int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStre
 
     const uint32_t kblocks = args->k / 32u;
     mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(static_cast<const uint8_t*>(args->scale_a), ws,
-                                                                args->m, kblocks);
+                                                                args->m, kblocks, (args->m + 127u) / 128u);
     mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(static_cast<const uint8_t*>(args->scale_b),
-                                                                ws + sfa_bytes, args->n, kblocks);
+                                                                ws + sfa_bytes, args->n, kblocks,
+                                                                2u * ((args->n + 255u) / 256u));
     CB200_CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(2, std::memory_order_relaxed);
 

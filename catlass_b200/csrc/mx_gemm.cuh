@@ -12,10 +12,13 @@
 //                          include/tla/layout.hpp:609-660, examples/53_ascend950_fp8_mx_matmul/gen_data.py:390-401)
 //                          into the tile order the tensor core's scale copy wants: per 128 rows x 4 scale
 //                          blocks a 512-byte block [row % 32][row / 32][4 bytes].  Output goes to the
-//                          caller-provided workspace.
+//                          caller-provided workspace; B's blocks are padded to a whole number of 256-wide tiles.
 //   mx_gemm_kernel         persistent, warp-specialised like the W8A8 kernel: TMA producer (operand tiles +
 //                          packed scale blocks), one MMA thread (tcgen05.cp scale blocks smem -> TMEM, then the
-//                          block-scaled MMAs), four epilogue warps (fp32 -> bf16), two accumulators in TMEM.
+//                          block-scaled MMAs), four epilogue warps (fp32 -> bf16).  Tile 128 x 256 with ONE
+//                          accumulator: a 128 x 128 MMA would run shorter than issuing it takes (~70 ns), which
+//                          capped 128-wide tiles at half the tensor rate; 256 columns plus the scale columns do
+//                          not leave room for a second accumulator, so the short epilogue is not overlapped.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -25,8 +28,9 @@
 
 namespace cb200 {
 
-constexpr int kMxBlockN = 128;
-constexpr int kMxStages = 6;
+constexpr int kMxBlockN = 256;  // one tcgen05.mma of 128 x 256 runs about as long as issuing it costs its thread
+constexpr int kMxAccs = 1;      // one accumulator: 256 columns + the scale columns leave no room for a second
+constexpr int kMxStages = 4;
 constexpr int kMxThreads = 192;
 
 struct MxParams {
@@ -43,9 +47,10 @@ struct MxParams {
 
 struct MxSmem {
     static constexpr int kABytes = kBlockM * kBlockKBytes;      // 16 KB
-    static constexpr int kBBytes = kMxBlockN * kBlockKBytes;    // 16 KB
-    static constexpr int kSfBytes = 2 * 2 * 512;                // A and B, up to two scale words each
-    static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;  // 34 KB
+    static constexpr int kBBytes = kMxBlockN * kBlockKBytes;    // 32 KB
+    // scale blocks: A up to two words (1 KB) at +0, B two 128-row blocks x up to two words (2 KB) at +1024
+    static constexpr int kSfBytes = 4096;
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;  // 52 KB
     static constexpr int kRingBytes = kMxStages * kStageBytes;
     static constexpr int kBarrierBytes = (2 * kMxStages + 4) * 8 + 16;
     static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
@@ -54,10 +59,9 @@ struct MxSmem {
 // in : [rows][kblocks] bytes (kblocks = K/32), out: [ceil(rows/128)][kblocks/4][512]
 // Rows past the end get the neutral scale 2^0.
 __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t rows,
-                                      uint32_t kblocks)
+                                      uint32_t kblocks, uint32_t row_blocks)
 {
     const uint32_t kq_total = kblocks / 4;
-    const uint32_t row_blocks = (rows + 127) / 128;
     const size_t words = static_cast<size_t>(row_blocks) * kq_total * 128;
     for (size_t w = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; w < words;
          w += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -80,8 +84,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                const MxParams p)
 {
     using S = MxSmem;
-    constexpr uint32_t kAccCols = 2 * kMxBlockN;        // two fp32 accumulators
-    constexpr uint32_t kSfCols = 2 * 16;                // two scale slots of (A: 8 + B: 8) columns
+    constexpr uint32_t kAccCols = kMxAccs * kMxBlockN;  // fp32 accumulator(s)
+    constexpr uint32_t kSfSlot = 24;                    // one scale slot: A up to 8 columns, B up to 16
+    constexpr uint32_t kSfCols = 2 * kSfSlot;           // two slots, alternating by stage
     constexpr uint32_t kTmemCols = 512;                 // power of two >= kAccCols + kSfCols
     constexpr uint32_t kWords = kFp4 ? 2 : 1;
     static_assert(kAccCols + kSfCols <= kTmemCols, "TMEM budget");
@@ -95,7 +100,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t bar_full = smem_u32(s_bars);
     const uint32_t bar_empty = bar_full + kMxStages * 8;
     const uint32_t bar_tmem_full = bar_empty + kMxStages * 8;
-    const uint32_t bar_tmem_empty = bar_tmem_full + 2 * 8;
+    const uint32_t bar_tmem_empty = bar_tmem_full + 2 * 8;  // (slots for two accumulators are reserved)
     uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 2 * kMxStages + 4);
     volatile uint32_t* s_abort = s_tmem_ptr + 1;
 
@@ -112,7 +117,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(bar_full + s * 8, 1);
             mbar_init(bar_empty + s * 8, 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < kMxAccs; ++a) {
             mbar_init(bar_tmem_full + a * 8, 1);
             mbar_init(bar_tmem_empty + a * 8, 4);
         }
@@ -128,7 +133,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_ptr;
-    constexpr uint32_t kStageTx = S::kABytes + S::kBBytes + 2 * kWords * 512;
+    constexpr uint32_t kStageTx = S::kABytes + S::kBBytes + 3 * kWords * 512;  // A scales + two B scale blocks
 
     if (warp == 0) {
         if (lane == 0) {
@@ -151,7 +156,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     tma_load_2d(sb, &tmap_b, full, k0, static_cast<int32_t>(nt) * kMxBlockN);
                     const size_t kq = static_cast<size_t>(kb) * kWords;
                     bulk_load(ssf, p.sfa + (static_cast<size_t>(mt) * p.kq_total + kq) * 512, kWords * 512, full);
-                    bulk_load(ssf + 1024, p.sfb + (static_cast<size_t>(nt) * p.kq_total + kq) * 512, kWords * 512, full);
+                    // the tile's 256 columns are two 128-row scale blocks of B (the workspace pads to a pair)
+                    bulk_load(ssf + 1024, p.sfb + (static_cast<size_t>(2 * nt) * p.kq_total + kq) * 512, kWords * 512,
+                              full);
+                    bulk_load(ssf + 1024 + kWords * 512, p.sfb + (static_cast<size_t>(2 * nt + 1) * p.kq_total + kq) * 512,
+                              kWords * 512, full);
                     if (++stage == kMxStages) {
                         stage = 0;
                         phase ^= 1;
@@ -183,12 +192,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t ssf = sb + S::kBBytes;
                     // scale blocks of this stage: smem -> TMEM (32 rows x 16 bytes each, replicated to the four
                     // lane quarters); the copies and the MMAs below execute in issue order
-                    const uint32_t t_sfa = tmem_base + kAccCols + sf_slot * 16;
+                    const uint32_t t_sfa = tmem_base + kAccCols + sf_slot * kSfSlot;
                     const uint32_t t_sfb = t_sfa + 8;
+                    // TMEM layout of a slot: A word w at columns [4w, 4w+4); B word w at [8 + 8w, 8 + 8w + 8):
+                    // columns 0-3 of it for the tile's first 128 columns, 4-7 for the second
 #pragma unroll
                     for (uint32_t w = 0; w < kWords; ++w) {
                         tmem_cp_32x128b_warpx4(t_sfa + w * 4, make_smem_desc_noswizzle(ssf + w * 512, 16, 128));
-                        tmem_cp_32x128b_warpx4(t_sfb + w * 4, make_smem_desc_noswizzle(ssf + 1024 + w * 512, 16, 128));
+#pragma unroll
+                        for (uint32_t nb = 0; nb < 2; ++nb) {
+                            tmem_cp_32x128b_warpx4(
+                                t_sfb + w * 8 + nb * 4,
+                                make_smem_desc_noswizzle(ssf + 1024 + (nb * kWords + w) * 512, 16, 128));
+                        }
                     }
 #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j) {
@@ -200,7 +216,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         const uint32_t sf_id = kFp4 ? ((j & 1) * 2) : j;
                         const uint32_t idesc = make_idesc_mx(fmt, fmt, kBlockM, kMxBlockN, sf_id, sf_id);
                         umma_mx<kFp4>(tmem_d, da, db, idesc, (kb | j) != 0 ? 1u : 0u, t_sfa + word * 4,
-                                      t_sfb + word * 4);
+                                      t_sfb + word * 8);
                     }
                     umma_commit<1>(bar_empty + stage * 8);
                     sf_slot ^= 1;
@@ -213,8 +229,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     break;
                 }
                 umma_commit<1>(bar_tmem_full + acc * 8);
-                acc ^= 1;
-                if (acc == 0) {
+                if (++acc == kMxAccs) {
+                    acc = 0;
                     acc_phase ^= 1;
                 }
             }
@@ -271,8 +287,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (lane == 0) {
                 mbar_arrive(bar_tmem_empty + acc * 8);
             }
-            acc ^= 1;
-            if (acc == 0) {
+            if (++acc == kMxAccs) {
+                acc = 0;
                 acc_phase ^= 1;
             }
         }

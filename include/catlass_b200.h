@@ -219,7 +219,7 @@ CB200_API int cb200_mx_matmul(const cb200_mx_matmul_args *args, void *stream);
  * the process exits.  args->workspace and args->workspace_bytes are ignored; inputs and output are passed
  * as usual.  The call allocates nothing and calls no allocating routine.
  *
- *  - Limit: (ceil(m/128) + ceil(n/128)) * (k/128) * 512 bytes must fit the array; m = n = k = 8192 needs
+ *  - Limit: (ceil(m/128) + 2*ceil(n/256)) * (k/128) * 512 bytes must fit the array; m = n = k = 8192 needs
  *    4 MiB.  Larger problems return CB200_SCRATCH_TOO_SMALL and launch nothing.
  *  - The first call on a device looks up the array's device address (with that device current) and keeps it;
  *    make that first call outside any stream capture.
