@@ -93,6 +93,8 @@ def load():
     lib.cb200_mx_matmul_static.argtypes = [ctypes.POINTER(MxMatmulArgs), _vp]
     lib.cb200_mx_matmul_static.restype = ctypes.c_int
     lib.cb200_mx_matmul_static_scratch_bytes.restype = _u64
+    lib.cb200_selftest_wait_timeout.argtypes = [_u32, _vp]
+    lib.cb200_selftest_wait_timeout.restype = ctypes.c_int
     lib.cb200_device_status.argtypes = [ctypes.POINTER(_u32)]
     lib.cb200_device_status.restype = ctypes.c_int
     lib.cb200_last_cuda_error.restype = ctypes.c_int

@@ -988,6 +988,46 @@ int cb200_mx_matmul_static(const cb200_mx_matmul_args* args, void* stream_v)
                                          : launch_mx<false>(&with_scratch, *dev, stream);
 }
 
+}  // extern "C"
+
+namespace {
+// One thread waits on an mbarrier that nobody will ever arrive on, with a short limit: exercises exactly the
+// give-up path of the production kernels (status word, abort flag, orderly exit) without hanging anything.
+__global__ void wait_selftest_kernel(unsigned* status, unsigned long long limit_ns)
+{
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_wait(smem_u32(&bar), 0, &abort_flag, status, kDevTimeoutSelfTest, limit_ns);
+    }
+    __syncthreads();
+}
+}  // namespace
+
+extern "C" {
+
+int cb200_selftest_wait_timeout(uint32_t limit_us, void* stream_v)
+{
+    DeviceState* dev = nullptr;
+    int rc = device_state(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    if (limit_us == 0 || limit_us > 1000000u) {
+        return CB200_INVALID;
+    }
+    wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(dev->status, limit_us * 1000ull);
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return CB200_SUCCESS;
+}
+
 int cb200_device_status(uint32_t* code)
 {
     if (code == nullptr) {

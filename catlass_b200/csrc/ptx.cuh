@@ -18,6 +18,7 @@ constexpr unsigned kDevTimeoutMmaTmem = 0x103;   // MMA issuer waiting for a dra
 constexpr unsigned kDevTimeoutEpilogue = 0x104;  // epilogue waiting for a finished accumulator
 constexpr unsigned kDevTimeoutConvert = 0x105;   // operand converter warps (W4A8) waiting
 constexpr unsigned kDevTimeoutPeerCta = 0x106;   // a CTA of a pair waiting for its peer
+constexpr unsigned kDevTimeoutSelfTest = 0x1F0;  // the wait self-test (a barrier nothing arrives on)
 
 // Upper bound for any single wait.  Far above every legitimate wait (the longest kernel here runs a few
 // milliseconds), so it only fires when the pipeline is broken; copies still in flight have landed by then.
@@ -102,7 +103,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 // (then it records `code` in *status and raises *abort for the other roles) or another role did.
 // The caller must leave its loops and fall through to the kernel's common exit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
-                                          unsigned* status, unsigned code)
+                                          unsigned* status, unsigned code,
+                                          unsigned long long limit_ns = kWaitLimitNs)
 {
     if (mbar_try_wait(bar, parity)) {
         return true;
@@ -117,7 +119,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort != 0) {
                 return false;
             }
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort = 1;
                 atomicMax(status, code);
                 return false;

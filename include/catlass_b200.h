@@ -237,6 +237,12 @@ CB200_API uint64_t cb200_mx_matmul_static_scratch_bytes(void);
  * CB200_SUCCESS, CB200_DEVICE_TIMEOUT (when *code != 0) or CB200_CUDA_ERROR. */
 CB200_API int cb200_device_status(uint32_t *code);
 
+/* Self-test of the bounded-wait path every kernel of the library uses: launches one tiny kernel in which a
+ * thread waits, for at most limit_us microseconds (1 .. 1000000), on a barrier that nothing signals.  The wait
+ * gives up, leaves code 0x1F0 in the device status word and the kernel exits normally; cb200_device_status()
+ * then returns CB200_DEVICE_TIMEOUT once.  Nothing hangs or faults; the context stays usable. */
+CB200_API int cb200_selftest_wait_timeout(uint32_t limit_us, void *stream);
+
 /* Last CUDA error code (cudaError_t / CUresult as int) seen by this thread inside the library. */
 CB200_API int cb200_last_cuda_error(void);
 

@@ -277,3 +277,26 @@ def test_invalid_arguments_are_rejected(cuda):
         capi.quant_matmul(a, b, s, p, d, m, n, k, layout_b=7)
     with pytest.raises(capi.CallError):
         capi.quant_matmul(None, b, s, p, d, m, n, k)
+
+
+def test_bounded_wait_gives_up_and_reports(cuda):
+    """The give-up path of the kernels' waits: a wait that nothing will ever satisfy ends after its limit,
+    the status word carries the code, reading it clears it, and the device keeps working."""
+    import time
+    import torch
+    from catlass_b200 import capi
+    lib = capi.load()
+    assert capi.device_status() == (0, 0)
+    t0 = time.perf_counter()
+    assert lib.cb200_selftest_wait_timeout(2000, ctypes_stream()) == 0   # 2 ms limit
+    st, code = capi.device_status()
+    assert time.perf_counter() - t0 < 5.0
+    assert (st, code) == (capi.DEVICE_TIMEOUT, 0x1F0)
+    assert capi.device_status() == (0, 0)            # cleared by the read
+    run_dense(cuda, 256, 512, 1024, True, seed=1)    # the context is still healthy
+
+
+def ctypes_stream():
+    import ctypes
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
