@@ -9,7 +9,7 @@ import os
 from . import build as _build
 
 SUCCESS, INVALID, CUDA_ERROR, DEVICE_TIMEOUT, SCRATCH_TOO_SMALL = 0, 1, 2, 3, 4
-ROW_MAJOR, COLUMN_MAJOR = 0, 1
+ROW_MAJOR, COLUMN_MAJOR, ZN = 0, 1, 2
 GROUP_LIST_INT64, GROUP_LIST_INT32 = 0, 1
 
 _u32, _u64, _vp = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p

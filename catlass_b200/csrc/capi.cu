@@ -41,7 +41,7 @@ int check_w8a8(const W8A8Problem& q, uint32_t layout_a)
     if (layout_a != CB200_ROW_MAJOR) {
         return CB200_INVALID;
     }
-    if (q.layout_b != CB200_ROW_MAJOR && q.layout_b != CB200_COLUMN_MAJOR) {
+    if (q.layout_b != CB200_ROW_MAJOR && q.layout_b != CB200_COLUMN_MAJOR && q.layout_b != CB200_ZN) {
         return CB200_INVALID;
     }
     if (q.group_count > static_cast<uint32_t>(kMaxGroups)) {
@@ -154,9 +154,10 @@ int launch_w8a8(const W8A8Problem& q, const DeviceState& dev, cudaStream_t strea
 }
 
 // 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2): the default for problems with more than 128 columns.
-template <bool kBMn>
+template <BLayout kB>
 int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t stream)
 {
+    constexpr bool kBMn = kB == BLayout::kRowMajor;
     using S = W8A8PairSmem;
     static_assert(S::kTotalBytes <= 232448, "shared memory budget of one CTA");
     CUtensorMap tmap_a, tmap_b;
@@ -170,7 +171,18 @@ int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t 
             return rc;
         }
     }
-    {
+    if constexpr (kB == BLayout::kZN) {
+        // zN: [group][n/32 panels][round16(k) rows][32 bytes]; a CTA loads four panels x 128 rows
+        const uint64_t k_round = (static_cast<uint64_t>(q.k) + 15u) / 16u * 16u;
+        const uint64_t panels = (static_cast<uint64_t>(q.n) + 31u) / 32u;
+        const uint64_t dims[4] = {32, q.k, panels, groups};
+        const uint64_t strides[3] = {32, k_round * 32u, panels * k_round * 32u};
+        const uint32_t box[4] = {32, 128, 4, 1};
+        int rc = encode_tmap_u8(&tmap_b, q.b, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_32B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    } else {
         // each CTA of a pair loads 128 of the tile's 256 columns
         const uint64_t dims_mn[3] = {q.n, q.k, groups};
         const uint64_t dims_k[3] = {q.k, q.n, groups};
@@ -195,7 +207,7 @@ int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t 
     p.acc = q.acc;
     p.status = dev.status;
 
-    auto kernel = w8a8_pair_kernel<kBMn>;
+    auto kernel = w8a8_pair_kernel<kB>;
     static bool attr_set[kMaxDevices] = {};
     int devid = 0;
     CB200_CUDA_TRY(cudaGetDevice(&devid));
@@ -416,6 +428,9 @@ int run_w8a8(const W8A8Problem& q, uint32_t layout_a, void* stream_v)
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return CB200_SUCCESS;
     }
+    if (q.layout_b == CB200_ZN) {
+        return launch_w8a8_pair<BLayout::kZN>(q, *dev, stream);  // fractal weights: always the pair kernel
+    }
     const bool b_mn = q.layout_b == CB200_ROW_MAJOR;
     if (q.group_count == 0 && q.m <= 128) {
         return b_mn ? launch_smallm<true>(q, *dev, stream) : launch_smallm<false>(q, *dev, stream);
@@ -427,7 +442,8 @@ int run_w8a8(const W8A8Problem& q, uint32_t layout_a, void* stream_v)
             return e == nullptr || atoi(e) != 0;
         }();
         if (use_pair) {
-            return b_mn ? launch_w8a8_pair<true>(q, *dev, stream) : launch_w8a8_pair<false>(q, *dev, stream);
+            return b_mn ? launch_w8a8_pair<BLayout::kRowMajor>(q, *dev, stream)
+                        : launch_w8a8_pair<BLayout::kColumnMajor>(q, *dev, stream);
         }
         return b_mn ? launch_w8a8<256, true>(q, *dev, stream) : launch_w8a8<256, false>(q, *dev, stream);
     }

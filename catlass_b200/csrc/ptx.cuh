@@ -208,6 +208,16 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                  : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar_cluster,
+                                                 int32_t x, int32_t y, int32_t z, int32_t w)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+        "%4, %5, %6}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int32_t x, int32_t y)
 {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
@@ -310,6 +320,20 @@ __host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_fmt, uint32_t b_
 {
     return (b_sf_id << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) |
            (a_sf_id << 29);
+}
+
+// Descriptor of an MN-major tile stored as 32-byte-wide column panels with the 32-byte swizzle (what a TMA
+// load with CU_TENSOR_MAP_SWIZZLE_32B produces from a box whose inner extent is 32 bytes): rows = K index,
+// 32 contiguous bytes of M or N per row; lbo = bytes between panels, sbo = bytes between 8-row groups of K.
+__device__ __forceinline__ uint64_t make_smem_desc_sw32(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= 1ull << 46;
+    d |= 6ull << 61;  // 32-byte swizzle
+    return d;
 }
 
 // Instruction descriptor fields (32-bit) shared by the dense kinds.

@@ -28,6 +28,13 @@ constexpr int kBlockM = 128;        // rows of A per tile = TMEM lanes
 constexpr int kBlockKBytes = 128;   // K bytes per pipeline stage = one 128B swizzle row
 constexpr int kUmmaK = 32;          // K per tcgen05.mma.kind::i8
 constexpr int kMaxGroups = 1024;
+
+// How the weight matrices B[k][n] lie in memory
+enum class BLayout : int {
+    kColumnMajor = 0,  // [n][k]: K contiguous           -> K-major operand tiles, 128-byte swizzle
+    kRowMajor = 1,     // [k][n]: N contiguous           -> MN-major tiles, 128-byte-wide panels
+    kZN = 2,           // [n/32][round16(k)][32]: the reference's zN fractal format -> MN-major, 32-byte panels
+};
 constexpr int kGemmThreads = 192;
 constexpr int kEpilogueThreads = 128;
 

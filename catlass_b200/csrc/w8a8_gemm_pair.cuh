@@ -46,7 +46,7 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
     return remote;
 }
 
-template <bool kBMnMajor>
+template <BLayout kB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const W8A8Params p)
@@ -162,8 +162,11 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     const uint32_t full = map_to_cta(bar_full + stage * 8, 0);    // the leader's barrier
                     tma_load_2d_pair(sa, &tmap_a, full, k0, row0);
-                    if constexpr (kBMnMajor) {
+                    if constexpr (kB == BLayout::kRowMajor) {
                         tma_load_3d_pair(sb, &tmap_b, full, ncol0, k0, bz);  // 128 rows of K x 128 bytes of N
+                    } else if constexpr (kB == BLayout::kZN) {
+                        // four 32-byte-wide panels of 128 K rows each: coordinates (byte in panel, k, panel, group)
+                        tma_load_4d_pair(sb, &tmap_b, full, 0, k0, ncol0 / 32, bz);
                     } else {
                         tma_load_3d_pair(sb, &tmap_b, full, k0, ncol0, bz);  // 128 rows of N x 128 bytes of K
                     }
@@ -178,7 +181,8 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer (leader CTA only)
         if (lane == 0 && cta_rank == 0) {
-            constexpr uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, false, kBMnMajor, kPairTileM, BN);
+            constexpr uint32_t idesc =
+                make_idesc(kAccS32, kFmtS8, kFmtS8, false, kB != BLayout::kColumnMajor, kPairTileM, BN);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
@@ -201,8 +205,12 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         // the descriptors name this CTA's tiles; the peer's tiles sit at the same offsets
                         const uint64_t da = make_smem_desc_sw128(sa + j * kUmmaK, 16, 1024);
                         uint64_t db;
-                        if constexpr (kBMnMajor) {
+                        if constexpr (kB == BLayout::kRowMajor) {
                             db = make_smem_desc_sw128(sb + j * (kUmmaK * 128), kBlockKBytes * 128, 1024);
+                        } else if constexpr (kB == BLayout::kZN) {
+                            // panels of 128 rows x 32 bytes (4 KB apart), 8-row groups 256 bytes apart;
+                            // 32 rows of K further down per MMA
+                            db = make_smem_desc_sw32(sb + j * (kUmmaK * 32), kBlockKBytes * 32, 256);
                         } else {
                             db = make_smem_desc_sw128(sb + j * kUmmaK, 16, 1024);
                         }

@@ -39,6 +39,7 @@ extern "C" {
 /* ---- matrix layouts (include/catlass/layout/matrix.hpp: RowMajor :24, ColumnMajor :168, zN :475) ---- */
 #define CB200_ROW_MAJOR 0
 #define CB200_COLUMN_MAJOR 1
+#define CB200_ZN 2 /* weights only: 16-row x 32-byte fractals, layout::zN::MakeLayout<int8_t>(k, n) */
 
 /* ---- group list element type (the reference accepts int32 or int64 prefix sums) ---- */
 #define CB200_GROUP_LIST_INT64 0
@@ -52,12 +53,13 @@ extern "C" {
  *         (include/catlass/gemm/kernel/quant_matmul_multistage_workspace.hpp:92-100),
  *     operand order of tests/optest/kernels/12_quant_matmul/quant_matmul_impl.cpp:103-105
  *         (inputs A, B, scale, perTokenScale; output D).
- * A: int8 m x k, B: int8 k x n, each row- or column-major and densely packed; D: bf16 m x n row-major.
+ * A: int8 m x k row-major; B: int8 k x n row-major, column-major (densely packed) or in the reference's zN
+ * fractal format (k padded to 16, n to 32: layout::zN::MakeLayout<int8_t>(k, n)); D: bf16 m x n row-major.
  */
 typedef struct cb200_quant_matmul_args {
     uint32_t m, n, k;
     uint32_t layout_a;            /* CB200_ROW_MAJOR only */
-    uint32_t layout_b;            /* CB200_ROW_MAJOR or CB200_COLUMN_MAJOR */
+    uint32_t layout_b;            /* CB200_ROW_MAJOR, CB200_COLUMN_MAJOR or CB200_ZN */
     const void *a;                /* int8 */
     const void *b;                /* int8 */
     const float *scale;           /* n per-channel scales */
@@ -89,7 +91,8 @@ CB200_API int cb200_quant_matmul(const cb200_quant_matmul_args *args, void *stre
 typedef struct cb200_grouped_quant_matmul_args {
     uint32_t m, n, k;
     uint32_t group_count;         /* 1 .. 1024 */
-    uint32_t layout_b;            /* layout of each k x n weight matrix */
+    uint32_t layout_b;            /* layout of each k x n weight matrix (row-major, column-major or zN;
+                                     zN matrices follow each other Capacity() bytes apart) */
     uint32_t group_list_type;     /* CB200_GROUP_LIST_INT64 / _INT32 */
     const void *a;                /* int8 m x k row-major */
     const void *b;                /* int8 [group_count][k x n] */

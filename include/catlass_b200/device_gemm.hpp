@@ -28,6 +28,10 @@ template <>
 struct LayoutTag<layout::ColumnMajor> {
     static constexpr uint32_t value = CB200_COLUMN_MAJOR;
 };
+template <>
+struct LayoutTag<layout::zN> {
+    static constexpr uint32_t value = CB200_ZN;  // weights (B) only
+};
 inline Status ToStatus(int rc)
 {
     return rc == CB200_SUCCESS ? Status::kSuccess : Status::kInvalid;

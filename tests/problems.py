@@ -38,3 +38,21 @@ def w8a8_grouped(group_sizes, n, k, seed, m_capacity=None, lo=-127, hi=127):
     per_token = rng.uniform(1e-3, 1e-2, size=m).astype(np.float32)
     group_list = np.cumsum(group_sizes).astype(np.int64)
     return a, b, scale, per_token, group_list
+
+
+def zn_storage(b_kn):
+    """Logical int8 B[k,n] -> the reference's zN fractal storage (layout::zN::MakeLayout<int8_t>(k, n)):
+    fractals of 16 rows x 32 bytes, rows contiguous inside a fractal, fractals running down a 32-column panel
+    first; k padded to 16 and n to 32 with zeros.  offset(r, c) = (c/32)*(k16*32) + r*32 + c%32."""
+    k, n = b_kn.shape
+    k16, n32 = (k + 15) // 16 * 16, (n + 31) // 32 * 32
+    padded = np.zeros((k16, n32), np.int8)
+    padded[:k, :n] = b_kn
+    # [k16, n32] -> [n32/32 panels, k16, 32]
+    return np.ascontiguousarray(padded.reshape(k16, n32 // 32, 32).transpose(1, 0, 2))
+
+
+def zn_offset(rows, cols, r, c):
+    """Offset of element (r, c) in the int8 zN layout of a rows x cols matrix (the layout class's GetOffset)."""
+    rows16 = (rows + 15) // 16 * 16
+    return (r // 16) * 512 + (c // 32) * (rows16 * 32) + (r % 16) * 32 + (c % 32)

@@ -177,3 +177,19 @@ def test_w4a8_per_group_formula():
     one = O.w4a8_per_group(a, O.pack_int4_along_k(w), np.ones((1, n), np.float32), np.ones(m, np.float32),
                            m, n, k, k)
     assert np.array_equal(bits(one), bits(O.w4a8_per_tensor(a, O.pack_int4_along_k(w), 1.0, m, n, k)))
+
+
+def test_zn_storage_helper_matches_the_reference_layout(w8a8_golden):
+    """The zN packing used by the GPU tests places every element where the reference's layout::zN says."""
+    import problems as P
+    g = w8a8_golden
+    coords = g["layout_coords"]
+    for row in g["layout_table"]:
+        tag, eb, rows, cols = (int(x) for x in row[:4])
+        if tag == 2 and eb == 1:
+            assert [P.zn_offset(rows, cols, int(r), int(c)) for r, c in coords] == [int(x) for x in row[5:]]
+            b = np.arange(rows * cols, dtype=np.int64).reshape(rows, cols).astype(np.int8)
+            flat = P.zn_storage(b).ravel()
+            assert flat.size == int(row[4])   # Capacity()
+            for r, c in coords:
+                assert flat[P.zn_offset(rows, cols, int(r), int(c))] == b[int(r), int(c)]

@@ -98,6 +98,37 @@ def test_dense_few_tokens(cuda, m, n, k, col):
     run_dense(cuda, m, n, k, col, seed=m + n + k)
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (300, 264, 1040), (16, 384, 256), (129, 96, 48),
+                                   (1000, 1024, 2048)])
+def test_dense_zn_weights(cuda, m, n, k):
+    """B in the reference's zN fractal format (16-row x 32-byte fractals, k padded to 16, n to 32)."""
+    from catlass_b200 import capi
+    torch = _torch()
+    a, b, scale, pt = P.w8a8_dense(m, n, k, seed=m + n + k)
+    d = torch.full((m, n), -1.0, dtype=torch.bfloat16, device=cuda)
+    acc = torch.full((m, n), -7, dtype=torch.int32, device=cuda)
+    capi.quant_matmul(_dev(a), _dev(P.zn_storage(b)), _dev(scale), _dev(pt), d, m, n, k, layout_b=capi.ZN, acc=acc)
+    assert capi.device_status()[0] == 0
+    want, want_acc = O.quant_matmul(a, b, scale, pt, m, n, k, O.ROW_MAJOR, O.ROW_MAJOR, want_acc=True)
+    assert np.array_equal(acc.cpu().numpy(), want_acc)
+    check_bf16(d.view(torch.int16).cpu().numpy().view(np.uint16), want, f"zN {m}x{n}x{k}")
+
+
+def test_grouped_zn_weights(cuda):
+    from catlass_b200 import capi
+    torch = _torch()
+    sizes = [200, 0, 129, 700, 31]
+    n, k = 544, 528
+    a, b, scale, pt, gl = P.w8a8_grouped(sizes, n, k, seed=8)
+    m, g = a.shape[0], len(sizes)
+    b_zn = np.stack([P.zn_storage(b[e]) for e in range(g)])
+    d = torch.zeros((m, n), dtype=torch.bfloat16, device=cuda)
+    capi.grouped_quant_matmul(_dev(a), _dev(b_zn), _dev(gl), _dev(scale), _dev(pt), d, m, n, k, g, layout_b=capi.ZN)
+    assert capi.device_status()[0] == 0
+    want = O.grouped_quant_matmul(a, b, gl, scale, pt, m, n, k, O.ROW_MAJOR)
+    check_bf16(d.view(torch.int16).cpu().numpy().view(np.uint16), want, "grouped zN")
+
+
 def test_dense_extreme_values(cuda):
     """All operands at +-127/-128: the largest accumulator magnitudes the int8 path can produce."""
     from catlass_b200 import capi
