@@ -682,13 +682,35 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     int devid = 0;
     CB200_CUDA_TRY(cudaGetDevice(&devid));
     if (!attr_set[devid]) {
-        CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            W4A8Smem::kTotalBytes));
+        CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             W4A8Smem::kTotalBytes));
         attr_set[devid] = true;
     }
     const dim3 grid((args->n + kW4TileN - 1) / kW4TileN, (args->m + kW4TileM - 1) / kW4TileM, 1);
-    w4a8_gemm_kernel<<<grid, kW4Threads, W4A8Smem::kTotalBytes, static_cast<cudaStream_t>(stream_v)>>>(tmap_w,
-                                                                                                       tmap_x, p);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kW4Threads, 1, 1);
+    cfg.dynamicSmemBytes = W4A8Smem::kTotalBytes;
+    cfg.stream = stream;
+    // programmatic dependent launch: set-up and the first weight loads may overlap the tail of the kernel before
+    // this one on the stream; the kernel waits (griddepcontrol.wait) before it reads tokens or writes D
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static const bool use_pdl = [] {
+        const char* e = getenv("CB200_W4A8_PDL");
+        return e == nullptr || atoi(e) != 0;
+    }();
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    if (args->group_size == 128) {
+        CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a8_gemm_kernel<true>, tmap_w, tmap_x, p));
+    } else {
+        CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a8_gemm_kernel<false>, tmap_w, tmap_x, p));
+    }
     CB200_CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return CB200_SUCCESS;

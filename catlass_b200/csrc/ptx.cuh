@@ -99,6 +99,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+// Non-blocking probe of a barrier phase.  (try_wait may suspend the thread for a hardware-chosen time when the
+// phase is not complete; a thread that polls several barriers in turn must not be held up by any one of them.)
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  Returns false when the CTA is being torn down: either this wait exceeded kWaitLimitNs
 // (then it records `code` in *status and raises *abort for the other roles) or another role did.
 // The caller must leave its loops and fall through to the kernel's common exit.
@@ -106,10 +123,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           unsigned* status, unsigned code,
                                           unsigned long long limit_ns = kWaitLimitNs)
 {
-    if (mbar_try_wait(bar, parity)) {
-        return true;
-    }
-    const unsigned long long t0 = globaltimer_ns();
+    // The clock is read only after a run of failed probes: a read of the global timer costs far more than a
+    // probe, and most waits end within the first few.
+    unsigned long long t0 = 0;
     uint32_t spins = 0;
     for (;;) {
         if (mbar_try_wait(bar, parity)) {
@@ -119,7 +135,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort != 0) {
                 return false;
             }
-            if (globaltimer_ns() - t0 > limit_ns) {
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > limit_ns) {
                 *abort = 1;
                 atomicMax(status, code);
                 return false;
@@ -458,6 +477,19 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 __device__ __forceinline__ void tmem_ld_wait()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Wait for an earlier tmem_ld_32x32b_x32 into r that was left in flight.  The registers are operands so that no
+// use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait_x32(uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
 }
 
 // Copy 128-bit x 32 rows from shared memory (described by a no-swizzle descriptor) into the TMEM lanes

@@ -76,40 +76,51 @@ struct W4A8Smem {
     static constexpr int kTotalBytes = 1024 + kRingBytes + kScaleBytes + kBarrierBytes;
 };
 
-// Exact fp32 value of x/16 for an int32 x with |x| < 2^22, without the conversion unit:
-// 0x49400000 is 1.5 * 2^19, whose unit in the last place is 1/16; adding x to the bit pattern yields the
-// float 1.5 * 2^19 + x/16, and subtracting 1.5 * 2^19 again is exact.  Two values per packed subtract.
-// (The accumulators hold 16 times the true sums: see the unpack warps.)
-__device__ __forceinline__ void int2float_pair(uint32_t x0, uint32_t x1, float& f0, float& f1)
-{
-    const float t0 = __uint_as_float(x0 + 0x49400000u);
-    const float t1 = __uint_as_float(x1 + 0x49400000u);
-    asm("{\n\t"
-        ".reg .b64 rt, rc;\n\t"
-        "mov.b64 rt, {%2, %3};\n\t"
-        "mov.b64 rc, {%4, %4};\n\t"
-        "add.rn.f32x2 rt, rt, rc;\n\t"
-        "mov.b64 {%0, %1}, rt;\n\t"
-        "}\n"
-        : "=f"(f0), "=f"(f1)
-        : "f"(t0), "f"(t1), "f"(-786432.0f));
-}
-
-// y += a * s on two independent lanes: one packed IEEE fused multiply-add
-__device__ __forceinline__ void fma2(float& y0, float& y1, float a0, float a1, float s0, float s1)
+// The running sums y are kept as pairs of fp32 in 64-bit registers so that the per-group update is exactly four
+// instructions per two outputs (two integer adds, one packed subtract, one packed fused multiply-add) with no
+// register shuffling in between.
+//
+// scaled_accumulate_pair: y += (x/16) * s for two (x, s, y) triples, x an int32 with |x| < 2^22.
+//   x/16 exactly, without the conversion unit: 0x49400000 is the bit pattern of 1.5 * 2^19, whose unit in the
+//   last place is 1/16; adding x to the pattern yields the float 1.5 * 2^19 + x/16, and subtracting 1.5 * 2^19
+//   again is exact.  (The accumulators hold 16 times the true sums: see the unpack warps.)
+__device__ __forceinline__ void scaled_accumulate_pair(unsigned long long& y2, uint32_t x0, uint32_t x1,
+                                                       unsigned long long s2)
 {
     asm("{\n\t"
-        ".reg .b64 ra, rs, ry;\n\t"
-        "mov.b64 ra, {%2, %3};\n\t"
-        "mov.b64 rs, {%4, %5};\n\t"
-        "mov.b64 ry, {%0, %1};\n\t"
-        "fma.rn.f32x2 ry, ra, rs, ry;\n\t"
-        "mov.b64 {%0, %1}, ry;\n\t"
+        ".reg .b32 lo, hi;\n\t"
+        ".reg .b64 t, c;\n\t"
+        "add.u32 lo, %1, 0x49400000;\n\t"
+        "add.u32 hi, %2, 0x49400000;\n\t"
+        "mov.b64 t, {lo, hi};\n\t"
+        "mov.b64 c, 0xC9400000C9400000;\n\t"   // (-1.5 * 2^19, -1.5 * 2^19)
+        "add.rn.f32x2 t, t, c;\n\t"
+        "fma.rn.f32x2 %0, t, %3, %0;\n\t"
         "}\n"
-        : "+f"(y0), "+f"(y1)
-        : "f"(a0), "f"(a1), "f"(s0), "f"(s1));
+        : "+l"(y2)
+        : "r"(x0), "r"(x1), "l"(s2));
 }
 
+// y += a * s for two lanes, a given as two floats
+__device__ __forceinline__ void fma_pair(unsigned long long& y2, float a0, float a1, unsigned long long s2)
+{
+    asm("{\n\t"
+        ".reg .b64 t;\n\t"
+        "mov.b64 t, {%1, %2};\n\t"
+        "fma.rn.f32x2 %0, t, %3, %0;\n\t"
+        "}\n"
+        : "+l"(y2)
+        : "f"(a0), "f"(a1), "l"(s2));
+}
+
+__device__ __forceinline__ void unpack_pair(unsigned long long v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// kOneBlockGroups: the scale group is exactly one 128-wide K block (the common case).  The epilogue then needs no
+// int32 group sums and reads the next accumulator from TMEM while it does the arithmetic of the current one.
+template <bool kOneBlockGroups>
 __global__ void __launch_bounds__(kW4Threads, 1)
 w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  const W4A8Params p)
@@ -171,6 +182,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_ptr;
+    grid_launch_dependents();  // a dependent launch may start its own set-up and weight prefetch from here on
 
     // Batch B uses barrier slot B % kW4InFlight; it is the (B / kW4InFlight)-th use of that slot.
     // "the previous user of this slot is done" = wait with the inverted parity (passes at once for the first use).
@@ -180,12 +192,13 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             // One thread feeds two rings of different depth: it polls both "slot free" conditions without
             // blocking on either, so the deep packed-weight ring keeps running ahead of the token ring.
             uint32_t kw = 0, kx = 0, idle = 0;
+            bool dep_ok = false;
             unsigned long long t0 = 0;
             while (kw < num_kb || kx < num_kb) {
                 bool progressed = false;
                 if (kw < num_kb) {
                     const uint32_t slot = kw % kW4PackedSlots;
-                    if (mbar_try_wait(bar_p_empty + slot * 8, ((kw / kW4PackedSlots) & 1) ^ 1)) {
+                    if (mbar_test_wait(bar_p_empty + slot * 8, ((kw / kW4PackedSlots) & 1) ^ 1)) {
                         const uint32_t full = bar_p_full + slot * 8;
                         mbar_expect_tx(full, S::kPackedBytes);
                         tma_load_2d(ring + S::kPackedRing + slot * S::kPackedBytes, &tmap_w, full,
@@ -194,10 +207,18 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                         progressed = true;
                     }
                 }
-                if (kx < num_kb) {
+                // Weights and their scales never depend on the kernel launched before this one on the stream; the
+                // tokens may.  Under programmatic dependent launch the first token tile therefore waits for that
+                // kernel, after the packed-weight ring has been filled.  Everything that reads token-dependent
+                // data or writes the output happens after a token tile has landed.
+                if (kx == 0 && kw >= (num_kb < kW4PackedSlots ? num_kb : kW4PackedSlots)) {
+                    grid_dependency_wait();
+                    dep_ok = true;
+                }
+                if (dep_ok && kx < num_kb) {
                     const uint32_t batch = kx / kW4Batch;
                     const uint32_t bslot = batch % kW4InFlight;
-                    if (mbar_try_wait(bar_batch_done + bslot * 8, ((batch / kW4InFlight) & 1) ^ 1)) {
+                    if (mbar_test_wait(bar_batch_done + bslot * 8, ((batch / kW4InFlight) & 1) ^ 1)) {
                         const uint32_t slot = kx % kW4TokenSlots;
                         const uint32_t full = bar_x_full + slot * 8;
                         mbar_expect_tx(full, p.mt * 128);
@@ -336,12 +357,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t groups = num_kb / bpg;
         const bool warp_has_rows = static_cast<uint32_t>(m0) + quad * 32 < p.m;  // else: only hand buffers back
         float* sbuf = s_scales + ew * (S::kScaleSlots * 32);  // ring of scale rows, one float per lane
-        float y[32];
-        int32_t isum[32];  // int32 sum of a group that spans several batches (exact)
+        unsigned long long y2[16];  // running sums of this thread's 32 channels, two fp32 per register
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            y[i] = 0.0f;
-            isum[i] = 0;
+        for (int i = 0; i < 16; ++i) {
+            y2[i] = 0ull;
         }
         // Channel scales stream from global memory into the ring with cp.async, kAhead groups ahead of their
         // use, so that their latency never sits on the per-group critical path.
@@ -363,78 +382,150 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         for (uint32_t g = 0; g < kAhead; ++g) {
             fetch_scale(g);
         }
-        const uint32_t accs_per_batch = kW4Batch / unit;
-        uint32_t g = 0;             // group whose scale the next finished accumulator needs
-        uint32_t kb_in_group = 0;   // K blocks of group g already summed
         bool ok = true;
-        for (uint32_t batch = 0; ok && batch < num_batches; ++batch) {
-            const uint32_t bslot = batch % kW4InFlight, buse = batch / kW4InFlight;
-            ok = mbar_wait(bar_batch_done + bslot * 8, buse & 1, s_abort, p.status, kDevTimeoutEpilogue);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-                break;
-            }
-            tcgen05_fence_after();
-            const uint32_t kb0 = batch * kW4Batch;
-            const uint32_t kbs_here = kb0 + kW4Batch <= num_kb ? kW4Batch : num_kb - kb0;
-            for (uint32_t a = 0; a < accs_per_batch && a * unit < kbs_here; ++a) {
-                const uint32_t kb_acc = (a + 1) * unit <= kbs_here ? unit : kbs_here - a * unit;
-                const bool group_ends = kb_in_group + kb_acc == bpg;
-                if (group_ends) {
-                    fetch_scale(g + kAhead);
-                    asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // group g's scales landed
-                    __syncwarp();
+        if constexpr (kOneBlockGroups) {
+            static_assert(kW4Batch == 1, "one accumulator per batch");
+            // Batch b is K block b is scale group b.  Two register sets alternate: while the sums of batch b are
+            // updated from one set, the TMEM read of batch b+1 into the other set is in flight.
+            uint32_t ra[32], rb[32];
+            auto acquire = [&](uint32_t batch, uint32_t(&r)[32]) -> bool {
+                const uint32_t bslot = batch % kW4InFlight, buse = batch / kW4InFlight;
+                bool got = mbar_wait(bar_batch_done + bslot * 8, buse & 1, s_abort, p.status, kDevTimeoutEpilogue);
+                got = __all_sync(0xffffffffu, got);
+                if (got) {
+                    tcgen05_fence_after();
+                    if (warp_has_rows) {
+                        tmem_ld_32x32b_x32(tmem_base + bslot * kW4TileN + half * 32 + ((quad * 32u) << 16), r);
+                    }
                 }
+                return got;
+            };
+            // the read into r has been issued: wait for it, hand the accumulator back, return with r valid
+            auto settle = [&](uint32_t batch, uint32_t(&r)[32]) {
+                tmem_ld_wait_x32(r);
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_tmem_empty + (batch % kW4InFlight) * 8);
+                }
+            };
+            auto consume = [&](uint32_t batch, const uint32_t(&r)[32]) {
+                fetch_scale(batch + kAhead);
+                asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // this group's scales landed
+                __syncwarp();
                 if (warp_has_rows) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(
-                        tmem_base + (bslot * kW4Batch + a) * kW4TileN + half * 32 + ((quad * 32u) << 16), r);
-                    tmem_ld_wait();
-                    if (bpg == 1) {
-                        // one 128-wide K block per group: |16 * acc| <= 16 * 128 * 128 * 8 = 2^21
-                        const float4* sc4 = reinterpret_cast<const float4*>(sbuf + (g % S::kScaleSlots) * 32);
+                    // |16 * acc| <= 16 * 128 * 128 * 8 = 2^21
+                    const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(sbuf + (batch % S::kScaleSlots) * 32);
 #pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            const float4 s4 = sc4[v];
-                            float f0, f1, f2, f3;
-                            int2float_pair(r[4 * v], r[4 * v + 1], f0, f1);
-                            int2float_pair(r[4 * v + 2], r[4 * v + 3], f2, f3);
-                            fma2(y[4 * v], y[4 * v + 1], f0, f1, s4.x, s4.y);
-                            fma2(y[4 * v + 2], y[4 * v + 3], f2, f3, s4.z, s4.w);
-                        }
-                    } else {
+                    for (int v = 0; v < 8; ++v) {
+                        const ulonglong2 s4 = sc[v];  // scales of channels 4v .. 4v+3
+                        scaled_accumulate_pair(y2[2 * v], r[4 * v], r[4 * v + 1], s4.x);
+                        scaled_accumulate_pair(y2[2 * v + 1], r[4 * v + 2], r[4 * v + 3], s4.y);
+                    }
+                }
+            };
+            ok = num_batches == 0 || acquire(0, ra);
+            for (uint32_t batch = 0; ok && batch < num_batches; batch += 2) {
+                settle(batch, ra);
+                if (batch + 1 < num_batches) {
+                    ok = acquire(batch + 1, rb);
+                    if (!ok) {
+                        break;
+                    }
+                }
+                consume(batch, ra);
+                if (batch + 1 >= num_batches) {
+                    break;
+                }
+                settle(batch + 1, rb);
+                if (batch + 2 < num_batches) {
+                    ok = acquire(batch + 2, ra);
+                    if (!ok) {
+                        break;
+                    }
+                }
+                consume(batch + 1, rb);
+            }
+        } else {
+            int32_t isum[32];  // int32 sum of a group that spans several K blocks (exact)
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            isum[i] += static_cast<int32_t>(r[i]);
-                        }
-                        if (group_ends) {
-                            const float4* sc4 = reinterpret_cast<const float4*>(sbuf + (g % S::kScaleSlots) * 32);
-#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                isum[i] = 0;
+            }
+            const uint32_t accs_per_batch = kW4Batch / unit;
+            uint32_t g = 0;             // group whose scale the next finished accumulator needs
+            uint32_t kb_in_group = 0;   // K blocks of group g already summed
+            for (uint32_t batch = 0; ok && batch < num_batches; ++batch) {
+                const uint32_t bslot = batch % kW4InFlight, buse = batch / kW4InFlight;
+                ok = mbar_wait(bar_batch_done + bslot * 8, buse & 1, s_abort, p.status, kDevTimeoutEpilogue);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t kb0 = batch * kW4Batch;
+                const uint32_t kbs_here = kb0 + kW4Batch <= num_kb ? kW4Batch : num_kb - kb0;
+                for (uint32_t a = 0; a < accs_per_batch && a * unit < kbs_here; ++a) {
+                    const uint32_t kb_acc = (a + 1) * unit <= kbs_here ? unit : kbs_here - a * unit;
+                    const bool group_ends = kb_in_group + kb_acc == bpg;
+                    if (group_ends) {
+                        fetch_scale(g + kAhead);
+                        asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // group g's scales landed
+                        __syncwarp();
+                    }
+                    if (warp_has_rows) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(
+                            tmem_base + (bslot * kW4Batch + a) * kW4TileN + half * 32 + ((quad * 32u) << 16), r);
+                        tmem_ld_wait();
+                        if (bpg == 1) {
+                            // one 128-wide K block per group: |16 * acc| <= 16 * 128 * 128 * 8 = 2^21
+                            const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(sbuf + (g % S::kScaleSlots) * 32);
+    #pragma unroll
                             for (int v = 0; v < 8; ++v) {
-                                const float4 s4 = sc4[v];
-                                // the sums are multiples of 16: the conversion and the scaling by 1/16 are exact
-                                fma2(y[4 * v], y[4 * v + 1], __int2float_rn(isum[4 * v]) * 0.0625f,
-                                     __int2float_rn(isum[4 * v + 1]) * 0.0625f, s4.x, s4.y);
-                                fma2(y[4 * v + 2], y[4 * v + 3], __int2float_rn(isum[4 * v + 2]) * 0.0625f,
-                                     __int2float_rn(isum[4 * v + 3]) * 0.0625f, s4.z, s4.w);
-                                isum[4 * v] = isum[4 * v + 1] = isum[4 * v + 2] = isum[4 * v + 3] = 0;
+                                const ulonglong2 s4 = sc[v];  // scales of channels 4v .. 4v+3
+                                scaled_accumulate_pair(y2[2 * v], r[4 * v], r[4 * v + 1], s4.x);
+                                scaled_accumulate_pair(y2[2 * v + 1], r[4 * v + 2], r[4 * v + 3], s4.y);
+                            }
+                        } else {
+    #pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                isum[i] += static_cast<int32_t>(r[i]);
+                            }
+                            if (group_ends) {
+                                const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(sbuf + (g % S::kScaleSlots) * 32);
+    #pragma unroll
+                                for (int v = 0; v < 8; ++v) {
+                                    const ulonglong2 s4 = sc[v];
+                                    // the sums are multiples of 16: the conversion and the scaling by 1/16 are exact
+                                    fma_pair(y2[2 * v], __int2float_rn(isum[4 * v]) * 0.0625f,
+                                             __int2float_rn(isum[4 * v + 1]) * 0.0625f, s4.x);
+                                    fma_pair(y2[2 * v + 1], __int2float_rn(isum[4 * v + 2]) * 0.0625f,
+                                             __int2float_rn(isum[4 * v + 3]) * 0.0625f, s4.y);
+                                    isum[4 * v] = isum[4 * v + 1] = isum[4 * v + 2] = isum[4 * v + 3] = 0;
+                                }
                             }
                         }
                     }
+                    kb_in_group += kb_acc;
+                    if (group_ends) {
+                        kb_in_group = 0;
+                        ++g;
+                    }
                 }
-                kb_in_group += kb_acc;
-                if (group_ends) {
-                    kb_in_group = 0;
-                    ++g;
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_tmem_empty + bslot * 8);
                 }
-            }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_tmem_empty + bslot * 8);
             }
         }
         if (ok && mrow < p.m) {
+            float y[32];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                unpack_pair(y2[i], y[2 * i], y[2 * i + 1]);
+            }
             const float sa = __ldg(p.sa + mrow);
             __nv_bfloat16* drow = p.d + static_cast<size_t>(mrow) * p.n + col0;
             if ((p.n & 7u) == 0 && col0 + 32 <= p.n) {
