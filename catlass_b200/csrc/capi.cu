@@ -466,6 +466,9 @@ int check_w4a8(const cb200_w4a8_matmul_args* a)
         (a->k % a->group_size) != 0) {
         return CB200_INVALID;
     }
+    if (a->group_size > 16384u) {  // 16 x the int32 sum of a group must stay exactly convertible to fp32
+        return CB200_INVALID;
+    }
     if (a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u) {
         return CB200_INVALID;
     }
@@ -652,9 +655,22 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     p.m = args->m;
     p.n = args->n;
     p.k = args->k;
-    p.mt = args->m >= static_cast<uint32_t>(kW4TileM) ? kW4TileM : ((args->m + 15u) & ~15u);
+    p.mt = args->m >= static_cast<uint32_t>(kW4Tokens) ? kW4Tokens : ((args->m + 15u) & ~15u);
     p.blocks_per_group = args->group_size / 128u;
-    p.num_k_blocks = args->k / 128u;
+    p.num_groups = args->k / args->group_size;
+    // K split over the CTAs of a cluster: as many as still fit the SMs in one wave (and the scale groups allow)
+    const uint32_t tiles = ((args->n + kW4Channels - 1) / kW4Channels) * ((args->m + kW4Tokens - 1) / kW4Tokens);
+    p.splits = 1;
+    while (p.splits < static_cast<uint32_t>(kW4MaxSplits) && tiles * p.splits * 2 <= static_cast<uint32_t>(dev->sm_count) &&
+           p.splits * 2 <= p.num_groups) {
+        p.splits *= 2;
+    }
+    if (const char* e = getenv("CB200_W4A8_SPLITS")) {  // 1 = the bit-exact summation order
+        const uint32_t want = static_cast<uint32_t>(atoi(e));
+        if ((want == 1 || want == 2 || want == 4) && want <= p.num_groups) {
+            p.splits = want;
+        }
+    }
     p.sw = args->weight_scale;
     p.sa = args->per_token_scale;
     p.d = static_cast<__nv_bfloat16*>(args->d);
@@ -663,7 +679,7 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     {
         const uint64_t dims[2] = {args->k / 2u, args->n};
         const uint64_t strides[1] = {args->k / 2u};
-        const uint32_t box[2] = {64, kW4TileN};
+        const uint32_t box[2] = {64, kW4Channels};
         rc = encode_tmap_u8(&tmap_w, args->w_packed, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
         if (rc != CB200_SUCCESS) {
             return rc;
@@ -688,24 +704,28 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
                                             W4A8Smem::kTotalBytes));
         attr_set[devid] = true;
     }
-    const dim3 grid((args->n + kW4TileN - 1) / kW4TileN, (args->m + kW4TileM - 1) / kW4TileM, 1);
+    const dim3 grid(((args->n + kW4Channels - 1) / kW4Channels) * p.splits, (args->m + kW4Tokens - 1) / kW4Tokens, 1);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kW4Threads, 1, 1);
     cfg.dynamicSmemBytes = W4A8Smem::kTotalBytes;
     cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
     // programmatic dependent launch: set-up and the first weight loads may overlap the tail of the kernel before
     // this one on the stream; the kernel waits (griddepcontrol.wait) before it reads tokens or writes D
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     static const bool use_pdl = [] {
         const char* e = getenv("CB200_W4A8_PDL");
         return e == nullptr || atoi(e) != 0;
     }();
-    cfg.numAttrs = use_pdl ? 1 : 0;
+    cfg.numAttrs = use_pdl ? 2 : 1;
     if (args->group_size == 128) {
         CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a8_gemm_kernel<true>, tmap_w, tmap_x, p));
     } else {

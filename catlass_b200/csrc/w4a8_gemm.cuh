@@ -11,24 +11,32 @@
 // include/catlass/gemm/tile/atlasa2/cast_int4_to_int8.hpp:136-146); here the unpack happens between two
 // shared-memory buffers of the same CTA and nothing is staged through global memory.
 //
-// A CTA owns 64 output channels (so each weight byte is unpacked exactly once per 128-token row tile) and up
-// to 128 tokens: tokens on the TMEM lanes (UMMA M = 128), channels on the UMMA N axis (N = 64).
+// Decomposition.  A CTA owns 128 output channels and up to 128 tokens.  The channels sit on the TMEM lanes
+// (UMMA M = 128, A operand = unpacked weights) and the tokens on the UMMA N axis (N = token rows rounded up to
+// 16), so a thread of the epilogue owns ONE channel: the group's weight scale is a scalar in a register.
+// Every CTA has to read the whole token matrix once per pass over K, from L2; with 128 channels per CTA that
+// is 2 token bytes per packed weight byte (64 channels per CTA would double it and made the token stream the
+// limit).  To fill the machine when N/128 tiles are fewer than the SMs, the K range (whole scale groups) is
+// split over the 1, 2 or 4 CTAs of a cluster; each keeps fp32 partial sums y and at the end every CTA reduces
+// and stores one slice of the token columns, the partials travelling through distributed shared memory.
+// With a split the fp32 sums are added in a different order than the sequential definition above: results
+// then agree with it to 1 bf16 ulp instead of bit for bit.  One CTA per cluster (splits = 1) is bit-exact.
 //
-// Warp roles (15 warps):
-//   warp 0      TMA producer: packed weight tiles (64 x 64 B, 12 in flight: they come from HBM) and token tiles
-//               (mt x 128 B, 6 in flight: they come from L2) into two rings fed by one non-blocking loop
-//   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x 64 x 32), alternate K blocks.  Every K block gets its
-//               own int32 accumulator in TMEM and ONE tcgen05.commit: the same barrier tells the producer and
-//               the unpack warps that the block's shared-memory tiles are free and the epilogue that its
-//               accumulator is complete.  Six blocks in flight (token tiles, unpacked tiles, accumulators).
-//               Issuing an MMA costs its thread ~70 ns, more than an MMA this small runs: hence two issuers.
+// Warp roles (16 warps):
+//   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 11 in flight: they come from HBM) and token
+//               tiles (mt x 128 B, 4 in flight: they come from L2), one thread and one ring each
+//   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x mt x 32); one-block scale groups alternate between them
+//               (issuing an MMA costs its thread ~70 ns), longer groups are all issued by warp 1.  A group
+//               accumulates into one of four int32 accumulators in TMEM.  Per K block one commit frees
+//               the token tile and the unpacked tile; per group one more hands the accumulator to the epilogue.
 //   warps 2-5   unpack: nibble -> int8 holding 16*w (the nibble moved to the high half of the byte: no sign
 //               fix-up needed), written in the 128B-swizzled K-major operand layout, then handed to the MMA
 //               through a proxy fence + mbarrier.  The factor 16 is removed again, exactly, when the epilogue
 //               turns the accumulator into fp32.
-//   warps 6-13  epilogue (two warps per TMEM lane quarter, 32 channels each): per group tcgen05.ld,
-//               int->float, packed fma with the group's channel scales into the running sum y held in
-//               registers; after the last group: * sa[m], bf16, 16-byte stores
+//   warps 6-13  epilogue (two warps per TMEM lane quarter, 64 token columns each): per group tcgen05.ld in
+//               16-column pieces (the next piece is in flight while the current one is processed), int->float,
+//               packed fma with the group's scale into the running sums y held in registers; after the last
+//               group: reduction over the cluster, * sa[m], bf16 stores
 #pragma once
 
 #include <cuda_bf16.h>
@@ -38,22 +46,21 @@
 
 namespace cb200 {
 
-constexpr int kW4Threads = 480;      // 15 warps: producer, MMA issuer A, 4 unpack, 8 epilogue, MMA issuer B
-constexpr int kW4TileN = 64;        // output channels per CTA (UMMA N)
-constexpr int kW4TileM = 128;       // tokens per CTA (UMMA M)
-constexpr int kW4Batch = 1;         // K blocks per batch (one commit per batch)
-constexpr int kW4InFlight = 6;      // batches whose tiles / accumulators exist at the same time
-constexpr int kW4Issuers = 2;       // MMA-issuing threads (batches alternate between them)
-constexpr int kW4TokenSlots = kW4Batch * kW4InFlight;
-constexpr int kW4CookedSlots = kW4Batch * kW4InFlight;
-constexpr int kW4Accs = kW4Batch * kW4InFlight;
-constexpr int kW4PackedSlots = 12;  // packed-weight tiles in flight (4 KB each): covers HBM latency
+constexpr int kW4Threads = 512;     // 16 warps: weight producer, MMA issuer A, 4 unpack, 8 epilogue, MMA issuer B,
+                                    // token producer
+constexpr int kW4Channels = 128;    // output channels per CTA (UMMA M)
+constexpr int kW4Tokens = 128;      // tokens per CTA at most (UMMA N)
+constexpr int kW4Accs = 4;          // int32 accumulators in TMEM (128 columns each)
+constexpr int kW4Tiles = 4;         // token tiles / unpacked weight tiles in flight (= unpack warps, see there)
+constexpr int kW4PackedSlots = 11;  // packed-weight tiles in flight (8 KB each): covers HBM latency
+constexpr int kW4MaxSplits = 4;     // CTAs of a cluster sharing one channel tile along K
 
 struct W4A8Params {
     uint32_t m, n, k;
-    uint32_t mt;                // token rows loaded per tile: min(128, round_up(m, 16))
+    uint32_t mt;                // token rows loaded per tile: min(128, round_up(m, 16)); also the UMMA N
     uint32_t blocks_per_group;  // group_size / 128
-    uint32_t num_k_blocks;      // k / 128
+    uint32_t num_groups;        // k / group_size
+    uint32_t splits;            // cluster size along K: 1, 2 or 4
     const float* sw;            // [k / group_size][n]
     const float* sa;            // [m]
     __nv_bfloat16* d;           // [m][n]
@@ -61,20 +68,28 @@ struct W4A8Params {
 };
 
 struct W4A8Smem {
-    static constexpr int kTokenBytes = kW4TileM * 128;   // 16 KB: UMMA A operand
-    static constexpr int kCookedBytes = kW4TileN * 128;  //  8 KB: unpacked int8 weights, UMMA B operand
-    static constexpr int kPackedBytes = kW4TileN * 64;   //  4 KB: packed weights as loaded
+    static constexpr int kTokenBytes = kW4Tokens * 128;     // 16 KB: UMMA B operand
+    static constexpr int kCookedBytes = kW4Channels * 128;  // 16 KB: unpacked int8 weights, UMMA A operand
+    static constexpr int kPackedBytes = kW4Channels * 64;   //  8 KB: packed weights as loaded
     static constexpr int kTokenRing = 0;
-    static constexpr int kCookedRing = kTokenRing + kW4TokenSlots * kTokenBytes;
-    static constexpr int kPackedRing = kCookedRing + kW4CookedSlots * kCookedBytes;
+    static constexpr int kCookedRing = kTokenRing + kW4Tiles * kTokenBytes;
+    static constexpr int kPackedRing = kCookedRing + kW4Tiles * kCookedBytes;
     static constexpr int kRingBytes = kPackedRing + kW4PackedSlots * kPackedBytes;
-    static constexpr int kScaleSlots = 8;                // per epilogue warp: ring of 32-channel scale rows
+    // after the K loop the ring is idle and holds this CTA's fp32 sums (64 KB) followed by the other CTAs'
+    // partial sums: (splits - 1) x (128 / splits) token columns x 128 channels x fp32 <= 48 KB
+    static constexpr int kLandingBytes =
+        kW4Tokens * kW4Channels * 4 + (kW4MaxSplits - 1) * (kW4Tokens / kW4MaxSplits) * kW4Channels * 4;
+    static constexpr int kScaleSlots = 8;                   // per epilogue warp: ring of 32-channel scale rows
     static constexpr int kScaleBytes = 8 * kScaleSlots * 32 * 4;
-    // p_full, p_empty [packed]; x_full [token]; c_full [cooked]; batch_done, tmem_empty [in flight]
-    static constexpr int kBarriers = 2 * kW4PackedSlots + kW4TokenSlots + kW4CookedSlots + 2 * kW4InFlight;
+    // p_full, p_empty [packed]; x_full, c_full, tiles_free [tiles]; acc_full, acc_empty [accumulators]
+    static constexpr int kBarriers = 2 * kW4PackedSlots + 3 * kW4Tiles + 2 * kW4Accs;
     static constexpr int kBarrierBytes = kBarriers * 8 + 16;
     static constexpr int kTotalBytes = 1024 + kRingBytes + kScaleBytes + kBarrierBytes;
 };
+static_assert(W4A8Smem::kTotalBytes <= 227 * 1024, "shared memory budget");
+static_assert(W4A8Smem::kLandingBytes <= W4A8Smem::kRingBytes, "the landing buffer aliases the ring");
+static_assert(kW4Accs * kW4Tokens <= 512, "TMEM budget");
+static_assert(kW4Tiles == 4, "one tile slot per unpack warp");
 
 // The running sums y are kept as pairs of fp32 in 64-bit registers so that the per-group update is exactly four
 // instructions per two outputs (two integer adds, one packed subtract, one packed fused multiply-add) with no
@@ -118,8 +133,33 @@ __device__ __forceinline__ void unpack_pair(unsigned long long v, float& lo, flo
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
 
-// kOneBlockGroups: the scale group is exactly one 128-wide K block (the common case).  The epilogue then needs no
-// int32 group sums and reads the next accumulator from TMEM while it does the arithmetic of the current one.
+__device__ __forceinline__ unsigned long long pack_pair(float lo, float hi)
+{
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+
+// y2[kOff .. kOff+7] (16 token columns) += group sums r[0..15] * s.
+// kMagic: |r| < 2^22 (one 128-wide K block per group).
+template <bool kMagic, int kOff>
+__device__ __forceinline__ void accumulate16(unsigned long long (&y2)[32], const uint32_t (&r)[16], float s)
+{
+    const unsigned long long s2 = pack_pair(s, s);
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+        if constexpr (kMagic) {
+            scaled_accumulate_pair(y2[kOff + v], r[2 * v], r[2 * v + 1], s2);
+        } else {
+            // the sums are multiples of 16 below 2^28: the conversion and the scaling by 1/16 are exact
+            fma_pair(y2[kOff + v], __int2float_rn(static_cast<int32_t>(r[2 * v])) * 0.0625f,
+                     __int2float_rn(static_cast<int32_t>(r[2 * v + 1])) * 0.0625f, s2);
+        }
+    }
+}
+
+// kOneBlockGroups: the scale group is exactly one 128-wide K block (the common case): the int->float step can
+// then use the add-a-constant form.
 template <bool kOneBlockGroups>
 __global__ void __launch_bounds__(kW4Threads, 1)
 w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -134,25 +174,31 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     float* s_scales = reinterpret_cast<float*>(smem + S::kRingBytes);
     uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes + S::kScaleBytes);
-    const uint32_t bar_p_full = smem_u32(s_bars);                   // packed tile landed (TMA bytes)
+    const uint32_t bar_p_full = smem_u32(s_bars);                    // packed tile landed (TMA bytes)
     const uint32_t bar_p_empty = bar_p_full + kW4PackedSlots * 8;    // an unpack warp has read it
     const uint32_t bar_x_full = bar_p_empty + kW4PackedSlots * 8;    // token tile landed
-    const uint32_t bar_c_full = bar_x_full + kW4TokenSlots * 8;      // unpacked tile written
-    const uint32_t bar_batch_done = bar_c_full + kW4CookedSlots * 8; // all MMAs of a batch completed
-    const uint32_t bar_tmem_empty = bar_batch_done + kW4InFlight * 8;  // epilogue drained a batch's accumulators
+    const uint32_t bar_c_full = bar_x_full + kW4Tiles * 8;           // unpacked tile written
+    const uint32_t bar_tiles_free = bar_c_full + kW4Tiles * 8;       // the MMAs that read both tiles completed
+    const uint32_t bar_acc_full = bar_tiles_free + kW4Tiles * 8;     // all MMAs of a scale group completed
+    const uint32_t bar_acc_empty = bar_acc_full + kW4Accs * 8;       // the epilogue has read the accumulator
     uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + S::kBarriers);
     volatile uint32_t* s_abort = s_tmem_ptr + 1;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-    const int32_t n0 = static_cast<int32_t>(blockIdx.x) * kW4TileN;
-    const int32_t m0 = static_cast<int32_t>(blockIdx.y) * kW4TileM;
-    const uint32_t num_kb = p.num_k_blocks;
+    const uint32_t splits = p.splits;
+    const uint32_t rank = splits > 1 ? cluster_ctarank() : 0;  // position along K inside the cluster
+    const int32_t n0 = static_cast<int32_t>(blockIdx.x / splits) * kW4Channels;
+    const int32_t m0 = static_cast<int32_t>(blockIdx.y) * kW4Tokens;
     const uint32_t bpg = p.blocks_per_group;
-    const uint32_t unit = bpg < static_cast<uint32_t>(kW4Batch) ? bpg : kW4Batch;  // K blocks per accumulator
-    const uint32_t num_batches = (num_kb + kW4Batch - 1) / kW4Batch;
-    constexpr uint32_t kTmemCols = 512;  // power of two >= kW4Accs * 64
-    static_assert(kW4Accs * kW4TileN <= 512, "TMEM budget");
+    // this CTA's scale groups [g_begin, g_begin + my_groups) and K blocks [kb_begin, kb_begin + my_kb)
+    const uint32_t groups_per_rank = (p.num_groups + splits - 1) / splits;
+    const uint32_t g_begin = rank * groups_per_rank < p.num_groups ? rank * groups_per_rank : p.num_groups;
+    const uint32_t my_groups =
+        g_begin + groups_per_rank <= p.num_groups ? groups_per_rank : p.num_groups - g_begin;
+    const uint32_t kb_begin = g_begin * bpg;
+    const uint32_t my_kb = my_groups * bpg;
+    constexpr uint32_t kTmemCols = 512;
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
@@ -160,15 +206,14 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             mbar_init(bar_p_full + i * 8, 1);
             mbar_init(bar_p_empty + i * 8, 1);
         }
-        for (int i = 0; i < kW4TokenSlots; ++i) {
+        for (int i = 0; i < kW4Tiles; ++i) {
             mbar_init(bar_x_full + i * 8, 1);
-        }
-        for (int i = 0; i < kW4CookedSlots; ++i) {
             mbar_init(bar_c_full + i * 8, 1);
+            mbar_init(bar_tiles_free + i * 8, 1);
         }
-        for (int i = 0; i < kW4InFlight; ++i) {
-            mbar_init(bar_batch_done + i * 8, 1);
-            mbar_init(bar_tmem_empty + i * 8, 8);
+        for (int i = 0; i < kW4Accs; ++i) {
+            mbar_init(bar_acc_full + i * 8, 1);
+            mbar_init(bar_acc_empty + i * 8, 8);
         }
         fence_mbar_init();
         prefetch_tmap(&tmap_w);
@@ -184,161 +229,161 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t tmem_base = *s_tmem_ptr;
     grid_launch_dependents();  // a dependent launch may start its own set-up and weight prefetch from here on
 
-    // Batch B uses barrier slot B % kW4InFlight; it is the (B / kW4InFlight)-th use of that slot.
-    // "the previous user of this slot is done" = wait with the inverted parity (passes at once for the first use).
+    // running sums of this thread's channel over its 64 token columns, two fp32 per register (epilogue warps)
+    unsigned long long y2[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        y2[i] = 0ull;
+    }
+
+    // Ring discipline: local K block i uses packed slot i % kW4PackedSlots and tile slot i % kW4Tiles; local
+    // group j uses accumulator j % kW4Accs.  "The previous user of this slot is done" = wait with the inverted
+    // parity of the use count (passes at once for the first use).
 
     if (warp == 0) {
+        // ------------------------------------------------------- packed-weight producer
+        // (A thread that issues TMA tile loads in a wait / issue loop sustains about one load per 0.25 us,
+        // whatever the tile's size: weights and tokens each get a thread of their own.)
         if (lane == 0) {
-            // One thread feeds two rings of different depth: it polls both "slot free" conditions without
-            // blocking on either, so the deep packed-weight ring keeps running ahead of the token ring.
-            uint32_t kw = 0, kx = 0, idle = 0;
-            bool dep_ok = false;
-            unsigned long long t0 = 0;
-            while (kw < num_kb || kx < num_kb) {
-                bool progressed = false;
-                if (kw < num_kb) {
-                    const uint32_t slot = kw % kW4PackedSlots;
-                    if (mbar_test_wait(bar_p_empty + slot * 8, ((kw / kW4PackedSlots) & 1) ^ 1)) {
-                        const uint32_t full = bar_p_full + slot * 8;
-                        mbar_expect_tx(full, S::kPackedBytes);
-                        tma_load_2d(ring + S::kPackedRing + slot * S::kPackedBytes, &tmap_w, full,
-                                    static_cast<int32_t>(kw) * 64, n0);
-                        ++kw;
-                        progressed = true;
-                    }
+            bool ok = true;
+            for (uint32_t i = 0; ok && i < my_kb; ++i) {
+                const uint32_t slot = i % kW4PackedSlots;
+                ok = mbar_wait(bar_p_empty + slot * 8, ((i / kW4PackedSlots) & 1) ^ 1, s_abort, p.status,
+                               kDevTimeoutProducer);
+                if (ok) {
+                    const uint32_t full = bar_p_full + slot * 8;
+                    mbar_expect_tx(full, S::kPackedBytes);
+                    tma_load_2d(ring + S::kPackedRing + slot * S::kPackedBytes, &tmap_w, full,
+                                static_cast<int32_t>(kb_begin + i) * 64, n0);
                 }
-                // Weights and their scales never depend on the kernel launched before this one on the stream; the
-                // tokens may.  Under programmatic dependent launch the first token tile therefore waits for that
-                // kernel, after the packed-weight ring has been filled.  Everything that reads token-dependent
-                // data or writes the output happens after a token tile has landed.
-                if (kx == 0 && kw >= (num_kb < kW4PackedSlots ? num_kb : kW4PackedSlots)) {
-                    grid_dependency_wait();
-                    dep_ok = true;
-                }
-                if (dep_ok && kx < num_kb) {
-                    const uint32_t batch = kx / kW4Batch;
-                    const uint32_t bslot = batch % kW4InFlight;
-                    if (mbar_test_wait(bar_batch_done + bslot * 8, ((batch / kW4InFlight) & 1) ^ 1)) {
-                        const uint32_t slot = kx % kW4TokenSlots;
-                        const uint32_t full = bar_x_full + slot * 8;
-                        mbar_expect_tx(full, p.mt * 128);
-                        tma_load_2d(ring + S::kTokenRing + slot * S::kTokenBytes, &tmap_x, full,
-                                    static_cast<int32_t>(kx) * 128, m0);
-                        ++kx;
-                        progressed = true;
-                    }
-                }
-                if (progressed) {
-                    idle = 0;
-                    t0 = 0;
-                } else if ((++idle & 0x3f) == 0) {
-                    if (t0 == 0) {
-                        t0 = globaltimer_ns();
-                    }
-                    if (*s_abort != 0) {
-                        break;
-                    }
-                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-                        *s_abort = 1;
-                        atomicMax(p.status, kDevTimeoutProducer);
-                        break;
-                    }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 15) {
+        // ------------------------------------------------------- token producer
+        // Weights and their scales never depend on the kernel launched before this one on the stream; the
+        // tokens may.  Under programmatic dependent launch this thread therefore waits for that kernel before
+        // its first load, while the weight ring is already filling.  Everything that reads token-dependent data
+        // or writes the output happens after a token tile has landed.
+        if (lane == 0) {
+            grid_dependency_wait();
+            bool ok = true;
+            for (uint32_t i = 0; ok && i < my_kb; ++i) {
+                const uint32_t slot = i % kW4Tiles;
+                ok = mbar_wait(bar_tiles_free + slot * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
+                               kDevTimeoutProducer);
+                if (ok) {
+                    const uint32_t full = bar_x_full + slot * 8;
+                    mbar_expect_tx(full, p.mt * 128);
+                    tma_load_2d(ring + S::kTokenRing + slot * S::kTokenBytes, &tmap_x, full,
+                                static_cast<int32_t>(kb_begin + i) * 128, m0);
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1 || warp == 14) {
-        // Two issuing threads take alternate batches: issuing a tcgen05.mma costs its thread ~70 ns, more than
-        // an MMA of this small shape runs, so one issuer alone would leave the tensor core idle.
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, false, false, kW4TileM, kW4TileN);
+        // ------------------------------------------------------- MMA issuers
+        // One-block groups alternate between the two issuers: tile slots 0,2 and accumulators 0,2 are then only
+        // ever used by the first, 1,3 by the second, so each waits on its barriers one use after the other.
+        // Groups of several blocks accumulate in place and need their MMAs issued in order: one issuer does all.
+        constexpr uint32_t kIssuers = kOneBlockGroups ? 2 : 1;
+        static_assert(kW4Tiles % 2 == 0 && kW4Accs % 2 == 0, "slot ownership of the two issuers");
+        if (lane == 0 && (warp == 1 || kIssuers == 2)) {
+            const uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, false, false, kW4Channels, p.mt);
             bool ok = true;
-            for (uint32_t batch = (warp == 1 ? 0 : 1); ok && batch < num_batches; batch += kW4Issuers) {
-                const uint32_t bslot = batch % kW4InFlight;
-                const uint32_t use = batch / kW4InFlight;
-                ok = mbar_wait(bar_tmem_empty + bslot * 8, (use & 1) ^ 1, s_abort, p.status, kDevTimeoutMmaTmem);
+            for (uint32_t j = (warp == 1 ? 0 : 1); ok && j < my_groups; j += kIssuers) {
+                const uint32_t acc = j % kW4Accs;
+                ok = mbar_wait(bar_acc_empty + acc * 8, ((j / kW4Accs) & 1) ^ 1, s_abort, p.status,
+                               kDevTimeoutMmaTmem);
                 if (!ok) {
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t kb_end = (batch + 1) * kW4Batch < num_kb ? (batch + 1) * kW4Batch : num_kb;
-                for (uint32_t kb = batch * kW4Batch; kb < kb_end; ++kb) {
-                    const uint32_t slot = kb % kW4TokenSlots;  // token and unpacked rings have the same depth
-                    const uint32_t ph = (kb / kW4TokenSlots) & 1;
+                const uint32_t tmem_d = tmem_base + acc * kW4Tokens;
+                for (uint32_t b = 0; b < bpg; ++b) {
+                    const uint32_t i = j * bpg + b;
+                    const uint32_t slot = i % kW4Tiles;
+                    const uint32_t ph = (i / kW4Tiles) & 1;
                     ok = mbar_wait(bar_x_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma) &&
                          mbar_wait(bar_c_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma);
                     if (!ok) {
                         break;
                     }
                     tcgen05_fence_after();
-                    const uint32_t sx_tile = ring + S::kTokenRing + slot * S::kTokenBytes;    // UMMA A operand
-                    const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA B operand
-                    const uint32_t in_batch = kb - batch * kW4Batch;
-                    const uint32_t acc = bslot * kW4Batch + in_batch / unit;
-                    const uint32_t tmem_d = tmem_base + acc * kW4TileN;
-                    const uint32_t first = in_batch % unit;  // 0: this K block starts a new accumulator
+                    const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA A operand
+                    const uint32_t sx_tile = ring + S::kTokenRing + slot * S::kTokenBytes;    // UMMA B operand
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint64_t da = make_smem_desc_sw128(sx_tile + j * kUmmaK, 16, 1024);
-                        const uint64_t db = make_smem_desc_sw128(sw_tile + j * kUmmaK, 16, 1024);
-                        umma_i8<1>(tmem_d, da, db, idesc, (first | j) != 0 ? 1u : 0u);
+                    for (int q = 0; q < 4; ++q) {
+                        const uint64_t da = make_smem_desc_sw128(sw_tile + q * kUmmaK, 16, 1024);
+                        const uint64_t db = make_smem_desc_sw128(sx_tile + q * kUmmaK, 16, 1024);
+                        umma_i8<1>(tmem_d, da, db, idesc, (b | q) != 0 ? 1u : 0u);
                     }
+                    umma_commit<1>(bar_tiles_free + slot * 8);  // both tiles may be overwritten
                 }
                 if (!ok) {
                     break;
                 }
-                umma_commit<1>(bar_batch_done + bslot * 8);  // tiles free + accumulators complete, one signal
+                umma_commit<1>(bar_acc_full + acc * 8);  // the group's accumulator is complete
             }
         }
         __syncwarp();
     } else if (warp < 6) {
         // ------------------------------------------------------- unpack warps (2..5)
-        // Warp u of the four handles the K blocks kb = u, u+4, ... on its own (eight independent 16-byte
-        // chunks per lane: plenty of instruction-level parallelism, one fence and one arrival per block).
-        // Lane l, step i works on row = i*8 + l/4, packed chunk c = l%4.
+        // Warp u of the four handles the local K blocks i = u, u+4, ... on its own: sixteen 16-byte chunks per
+        // lane, one fence and one arrival per block.  With as many tile slots
+        // as unpack warps, slot u is only ever written by warp u, one block after the other: a parity wait can
+        // tell "the previous use is over" from "not yet" only if the waiter is never two uses ahead.
+        // Lane l, step s works on row = s*8 + l/4, packed chunk c = l%4.
         const uint32_t u = warp - 2;
         // the packed tile was loaded with the 64-byte TMA swizzle: 16-byte chunk c of row r sits at
         // chunk c ^ ((r >> 1) & 3); the operand tile uses the 128-byte swizzle: chunk j at j ^ (r & 7)
         const uint32_t c = lane & 3;
         const uint32_t rsub = lane >> 2;  // 0..7: row inside a group of eight (= row & 7)
-        for (uint32_t kb = u; kb < num_kb; kb += 4) {
-            const uint32_t ps = kb % kW4PackedSlots, pph = (kb / kW4PackedSlots) & 1;
-            const uint32_t cs = kb % kW4CookedSlots;
-            const uint32_t batch = kb / kW4Batch;
-            const uint32_t bslot = batch % kW4InFlight, buse = batch / kW4InFlight;
+        for (uint32_t i = u; i < my_kb; i += 4) {
+            const uint32_t ps = i % kW4PackedSlots, pph = (i / kW4PackedSlots) & 1;
+            const uint32_t cs = i % kW4Tiles;
             bool ok = mbar_wait(bar_p_full + ps * 8, pph, s_abort, p.status, kDevTimeoutConvert) &&
-                      mbar_wait(bar_batch_done + bslot * 8, (buse & 1) ^ 1, s_abort, p.status, kDevTimeoutConvert);
+                      mbar_wait(bar_tiles_free + cs * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
+                                kDevTimeoutConvert);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
             }
             const uint8_t* packed = smem + S::kPackedRing + ps * S::kPackedBytes;
             uint8_t* cooked = smem + S::kCookedRing + cs * S::kCookedBytes;
-            uint4 q[8];
+            // (four rounds of four chunks, deliberately not unrolled across rounds: the loop body has to stay
+            // small, the warps of this CTA run five different loops and share one instruction cache)
+#pragma unroll 1
+            for (uint32_t round = 0; round < 4; ++round) {
+                uint4 q[4];
 #pragma unroll
-            for (uint32_t i = 0; i < 8; ++i) {
-                const uint32_t row = i * 8 + rsub;
-                q[i] = *reinterpret_cast<const uint4*>(packed + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
-            }
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_p_empty + ps * 8);  // the packed tile is in registers: its slot can be refilled
-            }
-#pragma unroll
-            for (uint32_t i = 0; i < 8; ++i) {
-                const uint32_t row = i * 8 + rsub;
-                const uint32_t w[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
-                uint32_t o[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t lo = (w[j] << 4) & 0xF0F0F0F0u;  // even k: low nibbles, moved up
-                    const uint32_t hi = w[j] & 0xF0F0F0F0u;         // odd k: high nibbles, in place
-                    o[2 * j] = __byte_perm(lo, hi, 0x5140);
-                    o[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
+                for (uint32_t s = 0; s < 4; ++s) {
+                    const uint32_t row = (round * 4 + s) * 8 + rsub;
+                    q[s] = *reinterpret_cast<const uint4*>(packed + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
                 }
-                uint8_t* crow = cooked + row * 128;
-                *reinterpret_cast<uint4*>(crow + (((2 * c) ^ rsub) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<uint4*>(crow + (((2 * c + 1) ^ rsub) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                if (round == 3) {
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(bar_p_empty + ps * 8);  // the packed tile is in registers: refill its slot
+                    }
+                }
+#pragma unroll
+                for (uint32_t s = 0; s < 4; ++s) {
+                    const uint32_t row = (round * 4 + s) * 8 + rsub;
+                    const uint32_t w[4] = {q[s].x, q[s].y, q[s].z, q[s].w};
+                    uint32_t o[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t lo = (w[j] << 4) & 0xF0F0F0F0u;  // even k: low nibbles, moved up
+                        const uint32_t hi = w[j] & 0xF0F0F0F0u;         // odd k: high nibbles, in place
+                        o[2 * j] = __byte_perm(lo, hi, 0x5140);
+                        o[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
+                    }
+                    uint8_t* crow = cooked + row * 128;
+                    *reinterpret_cast<uint4*>(crow + (((2 * c) ^ rsub) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(crow + (((2 * c + 1) ^ rsub) << 4)) =
+                        make_uint4(o[4], o[5], o[6], o[7]);
+                }
             }
             fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
             __syncwarp();
@@ -348,204 +393,188 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     } else {
         // ------------------------------------------------------- epilogue warps 6..13
-        const uint32_t ew = warp - 6;          // 0..7
-        const uint32_t quad = warp & 3;        // TMEM lane quarter this warp may read
-        const uint32_t half = ew >> 2;         // which 32 of the 64 channels
-        const uint32_t row = quad * 32 + lane;
-        const uint32_t mrow = static_cast<uint32_t>(m0) + row;
-        const uint32_t col0 = static_cast<uint32_t>(n0) + half * 32;
-        const uint32_t groups = num_kb / bpg;
-        const bool warp_has_rows = static_cast<uint32_t>(m0) + quad * 32 < p.m;  // else: only hand buffers back
+        const uint32_t ew = warp - 6;     // 0..7
+        const uint32_t quad = warp & 3;   // TMEM lane quarter this warp may read: channels quad*32 .. +31
+        const uint32_t half = ew >> 2;    // token columns half*64 .. +63
+        const uint32_t cols_mine = p.mt > half * 64 ? (p.mt - half * 64 < 64 ? p.mt - half * 64 : 64) : 0;
+        const uint32_t np = (cols_mine + 31) / 32;  // 32-column halves of this warp's range that hold tokens
         float* sbuf = s_scales + ew * (S::kScaleSlots * 32);  // ring of scale rows, one float per lane
-        unsigned long long y2[16];  // running sums of this thread's 32 channels, two fp32 per register
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            y2[i] = 0ull;
-        }
-        // Channel scales stream from global memory into the ring with cp.async, kAhead groups ahead of their
-        // use, so that their latency never sits on the per-group critical path.
+        // This lane's channel scale of every group streams from global memory into the ring with cp.async,
+        // kAhead groups ahead of its use, so that the latency never sits on the per-group critical path.
         constexpr uint32_t kAhead = 6;
-        const uint32_t scol = col0 + lane;
+        const uint32_t scol = static_cast<uint32_t>(n0) + quad * 32 + lane;
         const bool scol_ok = scol < p.n;
         for (uint32_t i = 0; i < static_cast<uint32_t>(S::kScaleSlots); ++i) {
             sbuf[i * 32 + lane] = 0.0f;
         }
         __syncwarp();
-        auto fetch_scale = [&](uint32_t g) {
-            if (g < groups && scol_ok) {
-                const uint32_t dst = smem_u32(sbuf + (g % S::kScaleSlots) * 32 + lane);
-                const float* src = p.sw + static_cast<size_t>(g) * p.n + scol;
+        auto fetch_scale = [&](uint32_t j) {
+            if (j < my_groups && scol_ok) {
+                const uint32_t dst = smem_u32(sbuf + (j % S::kScaleSlots) * 32 + lane);
+                const float* src = p.sw + static_cast<size_t>(g_begin + j) * p.n + scol;
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        for (uint32_t g = 0; g < kAhead; ++g) {
-            fetch_scale(g);
+        for (uint32_t j = 0; j < kAhead; ++j) {
+            fetch_scale(j);
         }
-        bool ok = true;
-        if constexpr (kOneBlockGroups) {
-            static_assert(kW4Batch == 1, "one accumulator per batch");
-            // Batch b is K block b is scale group b.  Two register sets alternate: while the sums of batch b are
-            // updated from one set, the TMEM read of batch b+1 into the other set is in flight.
-            uint32_t ra[32], rb[32];
-            auto acquire = [&](uint32_t batch, uint32_t(&r)[32]) -> bool {
-                const uint32_t bslot = batch % kW4InFlight, buse = batch / kW4InFlight;
-                bool got = mbar_wait(bar_batch_done + bslot * 8, buse & 1, s_abort, p.status, kDevTimeoutEpilogue);
-                got = __all_sync(0xffffffffu, got);
-                if (got) {
-                    tcgen05_fence_after();
-                    if (warp_has_rows) {
-                        tmem_ld_32x32b_x32(tmem_base + bslot * kW4TileN + half * 32 + ((quad * 32u) << 16), r);
-                    }
-                }
-                return got;
-            };
-            // the read into r has been issued: wait for it, hand the accumulator back, return with r valid
-            auto settle = [&](uint32_t batch, uint32_t(&r)[32]) {
-                tmem_ld_wait_x32(r);
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bar_tmem_empty + (batch % kW4InFlight) * 8);
-                }
-            };
-            auto consume = [&](uint32_t batch, const uint32_t(&r)[32]) {
-                fetch_scale(batch + kAhead);
-                asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // this group's scales landed
-                __syncwarp();
-                if (warp_has_rows) {
-                    // |16 * acc| <= 16 * 128 * 128 * 8 = 2^21
-                    const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(sbuf + (batch % S::kScaleSlots) * 32);
-#pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        const ulonglong2 s4 = sc[v];  // scales of channels 4v .. 4v+3
-                        scaled_accumulate_pair(y2[2 * v], r[4 * v], r[4 * v + 1], s4.x);
-                        scaled_accumulate_pair(y2[2 * v + 1], r[4 * v + 2], r[4 * v + 3], s4.y);
-                    }
-                }
-            };
-            ok = num_batches == 0 || acquire(0, ra);
-            for (uint32_t batch = 0; ok && batch < num_batches; batch += 2) {
-                settle(batch, ra);
-                if (batch + 1 < num_batches) {
-                    ok = acquire(batch + 1, rb);
-                    if (!ok) {
-                        break;
-                    }
-                }
-                consume(batch, ra);
-                if (batch + 1 >= num_batches) {
+        auto scale_of = [&](uint32_t j) -> float {
+            fetch_scale(j + kAhead);
+            asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // group j's scale has landed
+            return sbuf[(j % S::kScaleSlots) * 32 + lane];
+        };
+        auto acquire = [&](uint32_t j) -> bool {
+            bool got = mbar_wait(bar_acc_full + (j % kW4Accs) * 8, (j / kW4Accs) & 1, s_abort, p.status,
+                                 kDevTimeoutEpilogue);
+            got = __all_sync(0xffffffffu, got);
+            if (got) {
+                tcgen05_fence_after();
+            }
+            return got;
+        };
+        auto release = [&](uint32_t j) {
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_acc_empty + (j % kW4Accs) * 8);
+            }
+        };
+        const uint32_t tmem_mine = tmem_base + half * 64 + ((quad * 32u) << 16);
+        auto issue = [&](uint32_t j, uint32_t piece, uint32_t(&r)[16]) {
+            tmem_ld_32x32b_x16(tmem_mine + (j % kW4Accs) * kW4Tokens + piece * 16, r);
+        };
+        if (np == 0) {
+            // no token columns here (few tokens): only keep the accumulator hand-shake going
+            for (uint32_t j = 0; j < my_groups; ++j) {
+                if (!acquire(j)) {
                     break;
                 }
-                settle(batch + 1, rb);
-                if (batch + 2 < num_batches) {
-                    ok = acquire(batch + 2, ra);
-                    if (!ok) {
-                        break;
-                    }
-                }
-                consume(batch + 1, rb);
+                release(j);
             }
         } else {
-            int32_t isum[32];  // int32 sum of a group that spans several K blocks (exact)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                isum[i] = 0;
+            // Two register sets alternate over the 16-column pieces of a group; the read of the next piece (of
+            // the next group, at the end) is in flight while the sums of the current one are updated.
+            uint32_t ra[16], rb[16];
+            bool ok = my_groups == 0 || acquire(0);
+            if (ok && my_groups != 0) {
+                issue(0, 0, ra);
             }
-            const uint32_t accs_per_batch = kW4Batch / unit;
-            uint32_t g = 0;             // group whose scale the next finished accumulator needs
-            uint32_t kb_in_group = 0;   // K blocks of group g already summed
-            for (uint32_t batch = 0; ok && batch < num_batches; ++batch) {
-                const uint32_t bslot = batch % kW4InFlight, buse = batch / kW4InFlight;
-                ok = mbar_wait(bar_batch_done + bslot * 8, buse & 1, s_abort, p.status, kDevTimeoutEpilogue);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    break;
+            for (uint32_t j = 0; ok && j < my_groups; ++j) {
+                const float s = scale_of(j);
+                tmem_ld_wait_x16(ra);
+                issue(j, 1, rb);
+                accumulate16<kOneBlockGroups, 0>(y2, ra, s);
+                tmem_ld_wait_x16(rb);
+                if (np == 2) {
+                    issue(j, 2, ra);
+                    accumulate16<kOneBlockGroups, 8>(y2, rb, s);
+                    tmem_ld_wait_x16(ra);
+                    issue(j, 3, rb);
+                    accumulate16<kOneBlockGroups, 16>(y2, ra, s);
+                    tmem_ld_wait_x16(rb);
                 }
-                tcgen05_fence_after();
-                const uint32_t kb0 = batch * kW4Batch;
-                const uint32_t kbs_here = kb0 + kW4Batch <= num_kb ? kW4Batch : num_kb - kb0;
-                for (uint32_t a = 0; a < accs_per_batch && a * unit < kbs_here; ++a) {
-                    const uint32_t kb_acc = (a + 1) * unit <= kbs_here ? unit : kbs_here - a * unit;
-                    const bool group_ends = kb_in_group + kb_acc == bpg;
-                    if (group_ends) {
-                        fetch_scale(g + kAhead);
-                        asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // group g's scales landed
-                        __syncwarp();
-                    }
-                    if (warp_has_rows) {
-                        uint32_t r[32];
-                        tmem_ld_32x32b_x32(
-                            tmem_base + (bslot * kW4Batch + a) * kW4TileN + half * 32 + ((quad * 32u) << 16), r);
-                        tmem_ld_wait();
-                        if (bpg == 1) {
-                            // one 128-wide K block per group: |16 * acc| <= 16 * 128 * 128 * 8 = 2^21
-                            const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(sbuf + (g % S::kScaleSlots) * 32);
-    #pragma unroll
-                            for (int v = 0; v < 8; ++v) {
-                                const ulonglong2 s4 = sc[v];  // scales of channels 4v .. 4v+3
-                                scaled_accumulate_pair(y2[2 * v], r[4 * v], r[4 * v + 1], s4.x);
-                                scaled_accumulate_pair(y2[2 * v + 1], r[4 * v + 2], r[4 * v + 3], s4.y);
-                            }
-                        } else {
-    #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                isum[i] += static_cast<int32_t>(r[i]);
-                            }
-                            if (group_ends) {
-                                const ulonglong2* sc = reinterpret_cast<const ulonglong2*>(sbuf + (g % S::kScaleSlots) * 32);
-    #pragma unroll
-                                for (int v = 0; v < 8; ++v) {
-                                    const ulonglong2 s4 = sc[v];
-                                    // the sums are multiples of 16: the conversion and the scaling by 1/16 are exact
-                                    fma_pair(y2[2 * v], __int2float_rn(isum[4 * v]) * 0.0625f,
-                                             __int2float_rn(isum[4 * v + 1]) * 0.0625f, s4.x);
-                                    fma_pair(y2[2 * v + 1], __int2float_rn(isum[4 * v + 2]) * 0.0625f,
-                                             __int2float_rn(isum[4 * v + 3]) * 0.0625f, s4.y);
-                                    isum[4 * v] = isum[4 * v + 1] = isum[4 * v + 2] = isum[4 * v + 3] = 0;
-                                }
-                            }
-                        }
-                    }
-                    kb_in_group += kb_acc;
-                    if (group_ends) {
-                        kb_in_group = 0;
-                        ++g;
+                release(j);  // every read of this group's accumulator has completed
+                if (j + 1 < my_groups) {
+                    ok = acquire(j + 1);
+                    if (ok) {
+                        issue(j + 1, 0, ra);
                     }
                 }
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bar_tmem_empty + bslot * 8);
+                if (np == 2) {
+                    accumulate16<kOneBlockGroups, 24>(y2, rb, s);
+                } else {
+                    accumulate16<kOneBlockGroups, 8>(y2, rb, s);
                 }
             }
         }
-        if (ok && mrow < p.m) {
-            float y[32];
+    }
+
+    // ----------------------------------------------------------- reduction over the cluster, output
+    // This part runs once per CTA, from a cold instruction cache: it is written as short rolled loops over
+    // shared memory instead of unrolled code over the register array (every 128 bytes of straight-line code
+    // cost a trip to L2).  The ring is idle by now: the epilogue saw the last accumulator complete, so every
+    // MMA and with it every TMA load and unpack of this CTA is over.
+    //   ytile   [128 token columns][128 channels] fp32: this CTA's sums
+    //   landing [splits - 1][128 / splits columns][128 channels] fp32: the other CTAs' sums for the columns
+    //           this CTA reduces and stores
+    const bool is_epi = warp >= 6 && warp < 14;
+    float* ytile = reinterpret_cast<float*>(smem);
+    float* landing = ytile + kW4Tokens * kW4Channels;
+    const uint32_t split_log2 = splits == 4 ? 2u : (splits == 2 ? 1u : 0u);
+    const uint32_t cps_log2 = 7u - split_log2;  // log2 of the columns per CTA (shifts: no integer division here)
+    const uint32_t cps_mask = (1u << cps_log2) - 1u;
+    const uint32_t et = threadIdx.x - 6 * 32;   // 0..255 among the epilogue threads
+    if (is_epi) {
+        const uint32_t ch = (warp & 3) * 32 + lane;
+        float* dst = ytile + ((warp - 6) >> 2) * 64 * kW4Channels + ch;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                unpack_pair(y2[i], y[2 * i], y[2 * i + 1]);
+        for (int i = 0; i < 32; ++i) {
+            float lo, hi;
+            unpack_pair(y2[i], lo, hi);
+            dst[(2 * i) * kW4Channels] = lo;
+            dst[(2 * i + 1) * kW4Channels] = hi;
+        }
+    }
+    if (splits > 1) {
+        cluster_sync();  // every CTA of the cluster is past its K loop and has written its ytile
+        if (is_epi) {
+            // push the columns other CTAs own into their landing buffers, 16 bytes at a time
+            for (uint32_t v = et; v < kW4Tokens * (kW4Channels / 4); v += 256) {
+                const uint32_t col = v >> 5, c4 = v & 31;
+                const uint32_t owner = col >> cps_log2;
+                if (owner != rank && col < p.mt) {
+                    const uint32_t slot = rank < owner ? rank : rank - 1;
+                    const float4 val = *reinterpret_cast<const float4*>(ytile + col * kW4Channels + c4 * 4);
+                    const uint32_t local =
+                        smem_u32(landing + ((slot << cps_log2) + (col & cps_mask)) * kW4Channels + c4 * 4);
+                    uint32_t remote;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
+                    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(val.x),
+                                 "f"(val.y), "f"(val.z), "f"(val.w)
+                                 : "memory");
+                }
+            }
+        }
+        cluster_sync();  // the partial sums have landed
+    } else if (is_epi) {
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // ytile complete (epilogue warps only)
+    }
+    if (is_epi && *s_abort == 0) {
+        // each thread: one token row, eight channels -> one 16-byte store
+        const bool vec_ok = (p.n & 7u) == 0;
+        for (uint32_t v = et; v < (kW4Channels / 8) << cps_log2; v += 256) {
+            const uint32_t col = (rank << cps_log2) + (v >> 4), c8 = v & 15;
+            const uint32_t mrow = static_cast<uint32_t>(m0) + col;
+            const uint32_t ncol = static_cast<uint32_t>(n0) + c8 * 8;
+            if (mrow >= p.m || ncol >= p.n) {
+                continue;
+            }
+            const float* src = ytile + col * kW4Channels + c8 * 8;
+            float4 a = *reinterpret_cast<const float4*>(src);
+            float4 b = *reinterpret_cast<const float4*>(src + 4);
+            for (uint32_t s = 0; s + 1 < splits; ++s) {  // the other CTAs' sums, in ascending rank order
+                const float* other = landing + ((s << cps_log2) + (col & cps_mask)) * kW4Channels + c8 * 8;
+                const float4 oa = *reinterpret_cast<const float4*>(other);
+                const float4 ob = *reinterpret_cast<const float4*>(other + 4);
+                a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
+                b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
             }
             const float sa = __ldg(p.sa + mrow);
-            __nv_bfloat16* drow = p.d + static_cast<size_t>(mrow) * p.n + col0;
-            if ((p.n & 7u) == 0 && col0 + 32 <= p.n) {
+            const float y[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            __nv_bfloat16* drow = p.d + static_cast<size_t>(mrow) * p.n + ncol;
+            if (vec_ok && ncol + 8 <= p.n) {
+                uint32_t packed[4];
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    uint32_t packed[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(__fmul_rn(y[v * 8 + e * 2], sa),
-                                                                       __fmul_rn(y[v * 8 + e * 2 + 1], sa));
-                        packed[e] = *reinterpret_cast<const uint32_t*>(&h);
-                    }
-                    *reinterpret_cast<uint4*>(drow + v * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                for (int e = 0; e < 4; ++e) {
+                    const __nv_bfloat162 h =
+                        __floats2bfloat162_rn(__fmul_rn(y[2 * e], sa), __fmul_rn(y[2 * e + 1], sa));
+                    packed[e] = *reinterpret_cast<const uint32_t*>(&h);
                 }
+                *reinterpret_cast<uint4*>(drow) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    if (col0 + i < p.n) {
-                        drow[i] = __float2bfloat16_rn(__fmul_rn(y[i], sa));
-                    }
+                for (uint32_t e = 0; e < 8 && ncol + e < p.n; ++e) {
+                    drow[e] = __float2bfloat16_rn(__fmul_rn(y[e], sa));
                 }
             }
         }
