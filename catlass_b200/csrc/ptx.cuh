@@ -125,6 +125,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 {
     // The clock is read only after a run of failed probes: a read of the global timer costs far more than a
     // probe, and most waits end within the first few.
+    if (mbar_test_wait(bar, parity)) {  // the common case in a pipeline that runs ahead: no suspension involved
+        return true;
+    }
     unsigned long long t0 = 0;
     uint32_t spins = 0;
     for (;;) {

@@ -23,7 +23,7 @@
 // then agree with it to 1 bf16 ulp instead of bit for bit.  One CTA per cluster (splits = 1) is bit-exact.
 //
 // Warp roles (16 warps):
-//   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 11 in flight: they come from HBM) and token
+//   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 12 in flight: they come from HBM) and token
 //               tiles (mt x 128 B, 4 in flight: they come from L2), one thread and one ring each
 //   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x mt x 32); one-block scale groups alternate between them
 //               (issuing an MMA costs its thread ~70 ns), longer groups are all issued by warp 1.  A group
@@ -51,8 +51,9 @@ constexpr int kW4Threads = 512;     // 16 warps: weight producer, MMA issuer A, 
 constexpr int kW4Channels = 128;    // output channels per CTA (UMMA M)
 constexpr int kW4Tokens = 128;      // tokens per CTA at most (UMMA N)
 constexpr int kW4Accs = 4;          // int32 accumulators in TMEM (128 columns each)
+constexpr int kW4AccPairs = 2;      // accumulators are handed over two at a time (halves the hand-shakes per group)
 constexpr int kW4Tiles = 4;         // token tiles / unpacked weight tiles in flight (= unpack warps, see there)
-constexpr int kW4PackedSlots = 11;  // packed-weight tiles in flight (8 KB each): covers HBM latency
+constexpr int kW4PackedSlots = 12;  // packed-weight tiles in flight (8 KB each): covers HBM latency
 constexpr int kW4MaxSplits = 4;     // CTAs of a cluster sharing one channel tile along K
 
 struct W4A8Params {
@@ -79,12 +80,10 @@ struct W4A8Smem {
     // partial sums: (splits - 1) x (128 / splits) token columns x 128 channels x fp32 <= 48 KB
     static constexpr int kLandingBytes =
         kW4Tokens * kW4Channels * 4 + (kW4MaxSplits - 1) * (kW4Tokens / kW4MaxSplits) * kW4Channels * 4;
-    static constexpr int kScaleSlots = 8;                   // per epilogue warp: ring of 32-channel scale rows
-    static constexpr int kScaleBytes = 8 * kScaleSlots * 32 * 4;
-    // p_full, p_empty [packed]; x_full, c_full, tiles_free [tiles]; acc_full, acc_empty [accumulators]
-    static constexpr int kBarriers = 2 * kW4PackedSlots + 3 * kW4Tiles + 2 * kW4Accs;
+    // p_full, p_empty [packed]; x_full, c_full, tiles_free [tiles]; acc_full, acc_empty [accumulator pairs]
+    static constexpr int kBarriers = 2 * kW4PackedSlots + 3 * kW4Tiles + 2 * kW4AccPairs;
     static constexpr int kBarrierBytes = kBarriers * 8 + 16;
-    static constexpr int kTotalBytes = 1024 + kRingBytes + kScaleBytes + kBarrierBytes;
+    static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
 };
 static_assert(W4A8Smem::kTotalBytes <= 227 * 1024, "shared memory budget");
 static_assert(W4A8Smem::kLandingBytes <= W4A8Smem::kRingBytes, "the landing buffer aliases the ring");
@@ -102,7 +101,9 @@ static_assert(kW4Tiles == 4, "one tile slot per unpack warp");
 __device__ __forceinline__ void scaled_accumulate_pair(unsigned long long& y2, uint32_t x0, uint32_t x1,
                                                        unsigned long long s2)
 {
-    asm("{\n\t"
+    // (volatile: keeps the arithmetic where the source puts it, between the issue of the next TMEM read and the
+    // wait for it; left to itself the compiler gathers it behind the wait and the read's latency is exposed)
+    asm volatile("{\n\t"
         ".reg .b32 lo, hi;\n\t"
         ".reg .b64 t, c;\n\t"
         "add.u32 lo, %1, 0x49400000;\n\t"
@@ -149,7 +150,15 @@ __device__ __forceinline__ void accumulate16(unsigned long long (&y2)[32], const
 #pragma unroll
     for (int v = 0; v < 8; ++v) {
         if constexpr (kMagic) {
+#ifdef CB200_W4A8_SCALAR_MATH
+            float lo, hi;
+            unpack_pair(y2[kOff + v], lo, hi);
+            lo = __fmaf_rn(__fsub_rn(__uint_as_float(r[2 * v] + 0x49400000u), 786432.0f), s, lo);
+            hi = __fmaf_rn(__fsub_rn(__uint_as_float(r[2 * v + 1] + 0x49400000u), 786432.0f), s, hi);
+            y2[kOff + v] = pack_pair(lo, hi);
+#else
             scaled_accumulate_pair(y2[kOff + v], r[2 * v], r[2 * v + 1], s2);
+#endif
         } else {
             // the sums are multiples of 16 below 2^28: the conversion and the scaling by 1/16 are exact
             fma_pair(y2[kOff + v], __int2float_rn(static_cast<int32_t>(r[2 * v])) * 0.0625f,
@@ -172,15 +181,14 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     uint8_t* smem = smem_raw + pad;
     const uint32_t ring = raw_addr + pad;
 
-    float* s_scales = reinterpret_cast<float*>(smem + S::kRingBytes);
-    uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes + S::kScaleBytes);
+    uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes);
     const uint32_t bar_p_full = smem_u32(s_bars);                    // packed tile landed (TMA bytes)
     const uint32_t bar_p_empty = bar_p_full + kW4PackedSlots * 8;    // an unpack warp has read it
     const uint32_t bar_x_full = bar_p_empty + kW4PackedSlots * 8;    // token tile landed
     const uint32_t bar_c_full = bar_x_full + kW4Tiles * 8;           // unpacked tile written
     const uint32_t bar_tiles_free = bar_c_full + kW4Tiles * 8;       // the MMAs that read both tiles completed
-    const uint32_t bar_acc_full = bar_tiles_free + kW4Tiles * 8;     // all MMAs of a scale group completed
-    const uint32_t bar_acc_empty = bar_acc_full + kW4Accs * 8;       // the epilogue has read the accumulator
+    const uint32_t bar_acc_full = bar_tiles_free + kW4Tiles * 8;     // all MMAs of a pair of scale groups completed
+    const uint32_t bar_acc_empty = bar_acc_full + kW4AccPairs * 8;   // the epilogue has read the pair's accumulators
     uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + S::kBarriers);
     volatile uint32_t* s_abort = s_tmem_ptr + 1;
 
@@ -211,9 +219,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             mbar_init(bar_c_full + i * 8, 1);
             mbar_init(bar_tiles_free + i * 8, 1);
         }
-        for (int i = 0; i < kW4Accs; ++i) {
-            mbar_init(bar_acc_full + i * 8, 1);
-            mbar_init(bar_acc_empty + i * 8, 8);
+        for (int i = 0; i < kW4AccPairs; ++i) {
+            mbar_init(bar_acc_full + i * 8, 2);   // one arrival per group of the pair
+            mbar_init(bar_acc_empty + i * 8, 8);  // one per epilogue warp
         }
         fence_mbar_init();
         prefetch_tmap(&tmap_w);
@@ -293,7 +301,8 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             bool ok = true;
             for (uint32_t j = (warp == 1 ? 0 : 1); ok && j < my_groups; j += kIssuers) {
                 const uint32_t acc = j % kW4Accs;
-                ok = mbar_wait(bar_acc_empty + acc * 8, ((j / kW4Accs) & 1) ^ 1, s_abort, p.status,
+                const uint32_t pair = j >> 1, pslot = pair % kW4AccPairs;
+                ok = mbar_wait(bar_acc_empty + pslot * 8, ((pair / kW4AccPairs) & 1) ^ 1, s_abort, p.status,
                                kDevTimeoutMmaTmem);
                 if (!ok) {
                     break;
@@ -323,7 +332,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (!ok) {
                     break;
                 }
-                umma_commit<1>(bar_acc_full + acc * 8);  // the group's accumulator is complete
+                umma_commit<1>(bar_acc_full + pslot * 8);  // the group's accumulator is complete
+                if (j + 1 == my_groups && (j & 1) == 0) {
+                    mbar_arrive(bar_acc_full + pslot * 8);  // an odd last group: the pair has no second member
+                }
             }
         }
         __syncwarp();
@@ -398,34 +410,23 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t half = ew >> 2;    // token columns half*64 .. +63
         const uint32_t cols_mine = p.mt > half * 64 ? (p.mt - half * 64 < 64 ? p.mt - half * 64 : 64) : 0;
         const uint32_t np = (cols_mine + 31) / 32;  // 32-column halves of this warp's range that hold tokens
-        float* sbuf = s_scales + ew * (S::kScaleSlots * 32);  // ring of scale rows, one float per lane
-        // This lane's channel scale of every group streams from global memory into the ring with cp.async,
-        // kAhead groups ahead of its use, so that the latency never sits on the per-group critical path.
-        constexpr uint32_t kAhead = 6;
+        // This lane's channel scale of every group: plain loads issued three groups ahead of their use and
+        // held in registers, so that the latency never sits on the per-group critical path.
         const uint32_t scol = static_cast<uint32_t>(n0) + quad * 32 + lane;
-        const bool scol_ok = scol < p.n;
-        for (uint32_t i = 0; i < static_cast<uint32_t>(S::kScaleSlots); ++i) {
-            sbuf[i * 32 + lane] = 0.0f;
-        }
-        __syncwarp();
-        auto fetch_scale = [&](uint32_t j) {
-            if (j < my_groups && scol_ok) {
-                const uint32_t dst = smem_u32(sbuf + (j % S::kScaleSlots) * 32 + lane);
-                const float* src = p.sw + static_cast<size_t>(g_begin + j) * p.n + scol;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+        const float* sw_col = p.sw + static_cast<size_t>(g_begin) * p.n + (scol < p.n ? scol : 0);
+        auto load_scale = [&](uint32_t j) -> float {
+            return j < my_groups ? __ldg(sw_col + static_cast<size_t>(j) * p.n) : 0.0f;
         };
-        for (uint32_t j = 0; j < kAhead; ++j) {
-            fetch_scale(j);
-        }
+        float s_now = load_scale(0), s_next1 = load_scale(1), s_next2 = load_scale(2);
         auto scale_of = [&](uint32_t j) -> float {
-            fetch_scale(j + kAhead);
-            asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");  // group j's scale has landed
-            return sbuf[(j % S::kScaleSlots) * 32 + lane];
+            const float s = s_now;
+            s_now = s_next1;
+            s_next1 = s_next2;
+            s_next2 = load_scale(j + 3);
+            return s;
         };
-        auto acquire = [&](uint32_t j) -> bool {
-            bool got = mbar_wait(bar_acc_full + (j % kW4Accs) * 8, (j / kW4Accs) & 1, s_abort, p.status,
+        auto acquire = [&](uint32_t pair) -> bool {
+            bool got = mbar_wait(bar_acc_full + (pair % kW4AccPairs) * 8, (pair / kW4AccPairs) & 1, s_abort, p.status,
                                  kDevTimeoutEpilogue);
             got = __all_sync(0xffffffffu, got);
             if (got) {
@@ -433,11 +434,11 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             }
             return got;
         };
-        auto release = [&](uint32_t j) {
+        auto release = [&](uint32_t pair) {
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(bar_acc_empty + (j % kW4Accs) * 8);
+                mbar_arrive(bar_acc_empty + (pair % kW4AccPairs) * 8);
             }
         };
         const uint32_t tmem_mine = tmem_base + half * 64 + ((quad * 32u) << 16);
@@ -446,11 +447,11 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         };
         if (np == 0) {
             // no token columns here (few tokens): only keep the accumulator hand-shake going
-            for (uint32_t j = 0; j < my_groups; ++j) {
-                if (!acquire(j)) {
+            for (uint32_t pair = 0; 2 * pair < my_groups; ++pair) {
+                if (!acquire(pair)) {
                     break;
                 }
-                release(j);
+                release(pair);
             }
         } else {
             // Two register sets alternate over the 16-column pieces of a group; the read of the next piece (of
@@ -474,9 +475,14 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     accumulate16<kOneBlockGroups, 16>(y2, ra, s);
                     tmem_ld_wait_x16(rb);
                 }
-                release(j);  // every read of this group's accumulator has completed
+                const bool pair_ends = (j & 1) != 0 || j + 1 == my_groups;
+                if (pair_ends) {
+                    release(j >> 1);  // every read of the pair's accumulators has completed
+                }
                 if (j + 1 < my_groups) {
-                    ok = acquire(j + 1);
+                    if (pair_ends) {
+                        ok = acquire((j + 1) >> 1);
+                    }
                     if (ok) {
                         issue(j + 1, 0, ra);
                     }
