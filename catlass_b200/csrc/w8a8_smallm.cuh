@@ -222,6 +222,23 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const uint32_t quad = warp & 3;
     const uint32_t row = quad * 32 + lane;  // weight row inside the tile = TMEM lane
     bool have = false;                      // this thread's accumulator row is valid
+    // The scales are fetched while the K loop runs, not after it: channel scale of this thread's row, and the
+    // per-token scales four to a lane (token t in lane t % 32, register t / 32), handed out by shuffles later.
+    // Loads issued after the accumulator is ready would each cost an L2 round trip on the kernel's tail.
+    float sc = 0.0f;
+    float tok[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (epi && split == 0) {
+        const uint32_t ncol_early = static_cast<uint32_t>(n0) + row;
+        if (ncol_early < p.n && row < p.tile_rows) {
+            sc = __ldg(p.scale + ncol_early);  // weights' scales do not depend on the previous kernel
+        }
+        grid_dependency_wait();                // the per-token scales may
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t t = q * 32 + lane;
+            tok[q] = t < p.m ? __ldg(p.per_token + t) : 0.0f;
+        }
+    }
     if (epi && my_kb != 0) {
         bool ok = mbar_wait(bar_tmem_full, 0, s_abort, p.status, kDevTimeoutEpilogue);
         ok = __all_sync(0xffffffffu, ok);
@@ -265,7 +282,6 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     if (split == 0 && epi) {
         const uint32_t ncol = static_cast<uint32_t>(n0) + row;
         const bool n_ok = ncol < p.n && row < p.tile_rows;
-        const float sc = n_ok ? __ldg(p.scale + ncol) : 0.0f;
         for (uint32_t c = 0; c < chunks; ++c) {
             uint32_t r[16];
             if (have) {
@@ -289,17 +305,18 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                     r[v * 4 + 3] += q.w;
                 }
             }
-            if (n_ok) {
+            // tokens c*16 .. c*16+15 sit in register c/2 of lanes (c%2)*16 .. +15 (all lanes take part in the
+            // shuffles, whether or not their own row is stored)
+            const float tq = (c >> 1) == 0 ? tok[0] : ((c >> 1) == 1 ? tok[1] : ((c >> 1) == 2 ? tok[2] : tok[3]));
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t mrow = c * 16 + i;
-                    if (mrow < p.m) {
-                        const float x = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[i])), sc),
-                                                  __ldg(p.per_token + mrow));
-                        p.d[static_cast<size_t>(mrow) * p.n + ncol] = __float2bfloat16_rn(x);
-                        if (p.acc != nullptr) {
-                            p.acc[static_cast<size_t>(mrow) * p.n + ncol] = static_cast<int32_t>(r[i]);
-                        }
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t mrow = c * 16 + i;
+                const float st = __shfl_sync(0xffffffffu, tq, (c & 1) * 16 + i);
+                if (n_ok && mrow < p.m) {
+                    const float x = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[i])), sc), st);
+                    p.d[static_cast<size_t>(mrow) * p.n + ncol] = __float2bfloat16_rn(x);
+                    if (p.acc != nullptr) {
+                        p.acc[static_cast<size_t>(mrow) * p.n + ncol] = static_cast<int32_t>(r[i]);
                     }
                 }
             }
