@@ -677,19 +677,21 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     p.status = dev->status;
     CUtensorMap tmap_w, tmap_x;
     {
-        const uint64_t dims[2] = {args->k / 2u, args->n};
-        const uint64_t strides[1] = {args->k / 2u};
-        const uint32_t box[2] = {64, kW4Channels};
-        rc = encode_tmap_u8(&tmap_w, args->w_packed, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        // packed weights as (64 bytes of a K block, channel, K block): a box is kW4Load consecutive blocks
+        const uint64_t dims[3] = {64, args->n, args->k / 128u};
+        const uint64_t strides[2] = {args->k / 2u, 64};
+        const uint32_t box[3] = {64, kW4Channels, kW4Load};
+        rc = encode_tmap_u8(&tmap_w, args->w_packed, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
         if (rc != CB200_SUCCESS) {
             return rc;
         }
     }
     {
-        const uint64_t dims[2] = {args->k, args->m};
-        const uint64_t strides[1] = {args->k};
-        const uint32_t box[2] = {128, p.mt};
-        rc = encode_tmap_u8(&tmap_x, args->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        // tokens as (128 bytes of a K block, token, K block)
+        const uint64_t dims[3] = {128, args->m, args->k / 128u};
+        const uint64_t strides[2] = {args->k, 128};
+        const uint32_t box[3] = {128, kW4Tokens, kW4Load};
+        rc = encode_tmap_u8(&tmap_x, args->a, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != CB200_SUCCESS) {
             return rc;
         }

@@ -24,7 +24,8 @@
 //
 // Warp roles (16 warps):
 //   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 12 in flight: they come from HBM) and token
-//               tiles (mt x 128 B, 4 in flight: they come from L2), one thread and one ring each
+//               tiles (128 x 128 B, 4 in flight: they come from L2), one thread and one ring each, two
+//               consecutive K blocks per load (3-D boxes)
 //   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x mt x 32); one-block scale groups alternate between them
 //               (issuing an MMA costs its thread ~70 ns), longer groups are all issued by warp 1.  A group
 //               accumulates into one of four int32 accumulators in TMEM.  Per K block one commit frees
@@ -55,6 +56,10 @@ constexpr int kW4AccPairs = 2;      // accumulators are handed over two at a tim
 constexpr int kW4Tiles = 4;         // token tiles / unpacked weight tiles in flight (= unpack warps, see there)
 constexpr int kW4PackedSlots = 12;  // packed-weight tiles in flight (8 KB each): covers HBM latency
 constexpr int kW4MaxSplits = 4;     // CTAs of a cluster sharing one channel tile along K
+constexpr int kW4Load = 2;          // K blocks per TMA load (a thread sustains ~3-4 tile loads per microsecond
+                                    // whatever their size: one load per block would cap the kernel)
+constexpr int kW4PackedLoads = kW4PackedSlots / kW4Load;  // load slots of the packed-weight ring
+constexpr int kW4TokenLoads = kW4Tiles / kW4Load;         // load slots of the token ring
 
 struct W4A8Params {
     uint32_t m, n, k;
@@ -80,8 +85,9 @@ struct W4A8Smem {
     // partial sums: (splits - 1) x (128 / splits) token columns x 128 channels x fp32 <= 48 KB
     static constexpr int kLandingBytes =
         kW4Tokens * kW4Channels * 4 + (kW4MaxSplits - 1) * (kW4Tokens / kW4MaxSplits) * kW4Channels * 4;
-    // p_full, p_empty [packed]; x_full, c_full, tiles_free [tiles]; acc_full, acc_empty [accumulator pairs]
-    static constexpr int kBarriers = 2 * kW4PackedSlots + 3 * kW4Tiles + 2 * kW4AccPairs;
+    // p_full, p_empty [packed loads]; x_full [token loads]; c_full, tiles_free [tiles]; acc_full, acc_empty
+    // [accumulator pairs]
+    static constexpr int kBarriers = 2 * kW4PackedLoads + kW4TokenLoads + 2 * kW4Tiles + 2 * kW4AccPairs;
     static constexpr int kBarrierBytes = kBarriers * 8 + 16;
     static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
 };
@@ -183,9 +189,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes);
     const uint32_t bar_p_full = smem_u32(s_bars);                    // packed tile landed (TMA bytes)
-    const uint32_t bar_p_empty = bar_p_full + kW4PackedSlots * 8;    // an unpack warp has read it
-    const uint32_t bar_x_full = bar_p_empty + kW4PackedSlots * 8;    // token tile landed
-    const uint32_t bar_c_full = bar_x_full + kW4Tiles * 8;           // unpacked tile written
+    const uint32_t bar_p_empty = bar_p_full + kW4PackedLoads * 8;    // the unpack warps have read both tiles
+    const uint32_t bar_x_full = bar_p_empty + kW4PackedLoads * 8;    // a pair of token tiles landed
+    const uint32_t bar_c_full = bar_x_full + kW4TokenLoads * 8;      // unpacked tile written
     const uint32_t bar_tiles_free = bar_c_full + kW4Tiles * 8;       // the MMAs that read both tiles completed
     const uint32_t bar_acc_full = bar_tiles_free + kW4Tiles * 8;     // all MMAs of a pair of scale groups completed
     const uint32_t bar_acc_empty = bar_acc_full + kW4AccPairs * 8;   // the epilogue has read the pair's accumulators
@@ -210,12 +216,14 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
-        for (int i = 0; i < kW4PackedSlots; ++i) {
+        for (int i = 0; i < kW4PackedLoads; ++i) {
             mbar_init(bar_p_full + i * 8, 1);
-            mbar_init(bar_p_empty + i * 8, 1);
+            mbar_init(bar_p_empty + i * 8, kW4Load);  // one arrival per tile of the load
+        }
+        for (int i = 0; i < kW4TokenLoads; ++i) {
+            mbar_init(bar_x_full + i * 8, 1);
         }
         for (int i = 0; i < kW4Tiles; ++i) {
-            mbar_init(bar_x_full + i * 8, 1);
             mbar_init(bar_c_full + i * 8, 1);
             mbar_init(bar_tiles_free + i * 8, 1);
         }
@@ -254,15 +262,18 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // whatever the tile's size: weights and tokens each get a thread of their own.)
         if (lane == 0) {
             bool ok = true;
-            for (uint32_t i = 0; ok && i < my_kb; ++i) {
-                const uint32_t slot = i % kW4PackedSlots;
-                ok = mbar_wait(bar_p_empty + slot * 8, ((i / kW4PackedSlots) & 1) ^ 1, s_abort, p.status,
+            const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
+            for (uint32_t l = 0; ok && l < loads; ++l) {
+                const uint32_t slot = l % kW4PackedLoads;
+                ok = mbar_wait(bar_p_empty + slot * 8, ((l / kW4PackedLoads) & 1) ^ 1, s_abort, p.status,
                                kDevTimeoutProducer);
                 if (ok) {
+                    // kW4Load consecutive K blocks, one 128 x 64 B tile each (a last, odd block brings the
+                    // neighbouring block or zeros along: the transaction count is always that of a full box)
                     const uint32_t full = bar_p_full + slot * 8;
-                    mbar_expect_tx(full, S::kPackedBytes);
-                    tma_load_2d(ring + S::kPackedRing + slot * S::kPackedBytes, &tmap_w, full,
-                                static_cast<int32_t>(kb_begin + i) * 64, n0);
+                    mbar_expect_tx(full, kW4Load * S::kPackedBytes);
+                    tma_load_3d(ring + S::kPackedRing + slot * (kW4Load * S::kPackedBytes), &tmap_w, full, 0, n0,
+                                static_cast<int32_t>(kb_begin + l * kW4Load));
                 }
             }
         }
@@ -276,15 +287,20 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         if (lane == 0) {
             grid_dependency_wait();
             bool ok = true;
-            for (uint32_t i = 0; ok && i < my_kb; ++i) {
-                const uint32_t slot = i % kW4Tiles;
-                ok = mbar_wait(bar_tiles_free + slot * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
-                               kDevTimeoutProducer);
+            const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
+            for (uint32_t l = 0; ok && l < loads; ++l) {
+                const uint32_t slot = l % kW4TokenLoads;
+                const uint32_t parity = ((l / kW4TokenLoads) & 1) ^ 1;
+                for (uint32_t h = 0; ok && h < kW4Load; ++h) {  // both tile slots of the load must be free
+                    ok = mbar_wait(bar_tiles_free + (slot * kW4Load + h) * 8, parity, s_abort, p.status,
+                                   kDevTimeoutProducer);
+                }
                 if (ok) {
+                    // kW4Load consecutive K blocks of all 128 token rows (rows past m read as zeros)
                     const uint32_t full = bar_x_full + slot * 8;
-                    mbar_expect_tx(full, p.mt * 128);
-                    tma_load_2d(ring + S::kTokenRing + slot * S::kTokenBytes, &tmap_x, full,
-                                static_cast<int32_t>(kb_begin + i) * 128, m0);
+                    mbar_expect_tx(full, kW4Load * S::kTokenBytes);
+                    tma_load_3d(ring + S::kTokenRing + slot * (kW4Load * S::kTokenBytes), &tmap_x, full, 0, m0,
+                                static_cast<int32_t>(kb_begin + l * kW4Load));
                 }
             }
         }
@@ -313,7 +329,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     const uint32_t i = j * bpg + b;
                     const uint32_t slot = i % kW4Tiles;
                     const uint32_t ph = (i / kW4Tiles) & 1;
-                    ok = mbar_wait(bar_x_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma) &&
+                    ok = mbar_wait(bar_x_full + (slot / kW4Load) * 8, ph, s_abort, p.status, kDevTimeoutMma) &&
                          mbar_wait(bar_c_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma);
                     if (!ok) {
                         break;
@@ -352,9 +368,11 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t c = lane & 3;
         const uint32_t rsub = lane >> 2;  // 0..7: row inside a group of eight (= row & 7)
         for (uint32_t i = u; i < my_kb; i += 4) {
-            const uint32_t ps = i % kW4PackedSlots, pph = (i / kW4PackedSlots) & 1;
+            const uint32_t pl = (i / kW4Load) % kW4PackedLoads;          // load slot of this block's packed tile
+            const uint32_t pph = ((i / kW4Load) / kW4PackedLoads) & 1;
+            const uint32_t ps = i % kW4PackedSlots;                      // tile slot inside the ring
             const uint32_t cs = i % kW4Tiles;
-            bool ok = mbar_wait(bar_p_full + ps * 8, pph, s_abort, p.status, kDevTimeoutConvert) &&
+            bool ok = mbar_wait(bar_p_full + pl * 8, pph, s_abort, p.status, kDevTimeoutConvert) &&
                       mbar_wait(bar_tiles_free + cs * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
                                 kDevTimeoutConvert);
             ok = __all_sync(0xffffffffu, ok);
@@ -376,7 +394,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 if (round == 3) {
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive(bar_p_empty + ps * 8);  // the packed tile is in registers: refill its slot
+                        mbar_arrive(bar_p_empty + pl * 8);  // this tile is in registers (the slot refills after both)
                     }
                 }
 #pragma unroll
