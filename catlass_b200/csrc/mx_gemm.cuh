@@ -31,7 +31,7 @@ namespace cb200 {
 constexpr int kMxBlockN = 256;  // one tcgen05.mma of 128 x 256 runs about as long as issuing it costs its thread
 constexpr int kMxAccs = 1;      // one accumulator: 256 columns + the scale columns leave no room for a second
 constexpr int kMxStages = 4;
-constexpr int kMxThreads = 192;
+constexpr int kMxThreads = 224;  // warps: 0 TMA producer, 1 MMA issuer, 2..5 epilogue, 6 scale copier
 
 struct MxParams {
     uint32_t m, n, k;
@@ -52,7 +52,7 @@ struct MxSmem {
     static constexpr int kSfBytes = 4096;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;  // 52 KB
     static constexpr int kRingBytes = kMxStages * kStageBytes;
-    static constexpr int kBarrierBytes = (2 * kMxStages + 4) * 8 + 16;
+    static constexpr int kBarrierBytes = (3 * kMxStages + 4) * 8 + 16;
     static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
 };
 
@@ -86,7 +86,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     using S = MxSmem;
     constexpr uint32_t kAccCols = kMxAccs * kMxBlockN;  // fp32 accumulator(s)
     constexpr uint32_t kSfSlot = 24;                    // one scale slot: A up to 8 columns, B up to 16
-    constexpr uint32_t kSfCols = 2 * kSfSlot;           // two slots, alternating by stage
+    constexpr uint32_t kSfCols = kMxStages * kSfSlot;   // one slot per shared-memory stage
     constexpr uint32_t kTmemCols = 512;                 // power of two >= kAccCols + kSfCols
     constexpr uint32_t kWords = kFp4 ? 2 : 1;
     static_assert(kAccCols + kSfCols <= kTmemCols, "TMEM budget");
@@ -101,7 +101,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t bar_empty = bar_full + kMxStages * 8;
     const uint32_t bar_tmem_full = bar_empty + kMxStages * 8;
     const uint32_t bar_tmem_empty = bar_tmem_full + 2 * 8;  // (slots for two accumulators are reserved)
-    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 2 * kMxStages + 4);
+    const uint32_t bar_sf_full = bar_tmem_empty + 2 * 8;    // the stage's scale blocks have been copied into TMEM
+    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 3 * kMxStages + 4);
     volatile uint32_t* s_abort = s_tmem_ptr + 1;
 
     const uint32_t warp = threadIdx.x >> 5;
@@ -116,6 +117,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int s = 0; s < kMxStages; ++s) {
             mbar_init(bar_full + s * 8, 1);
             mbar_init(bar_empty + s * 8, 1);
+            mbar_init(bar_sf_full + s * 8, 1);
         }
         for (int a = 0; a < kMxAccs; ++a) {
             mbar_init(bar_tmem_full + a * 8, 1);
@@ -151,10 +153,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t sb = sa + S::kABytes;
                     const uint32_t ssf = sb + S::kBBytes;
                     const int32_t k0 = static_cast<int32_t>(kb) * kBlockKBytes;
+                    const size_t kq = static_cast<size_t>(kb) * kWords;
                     mbar_expect_tx(full, kStageTx);
                     tma_load_2d(sa, &tmap_a, full, k0, static_cast<int32_t>(mt) * kBlockM);
                     tma_load_2d(sb, &tmap_b, full, k0, static_cast<int32_t>(nt) * kMxBlockN);
-                    const size_t kq = static_cast<size_t>(kb) * kWords;
                     bulk_load(ssf, p.sfa + (static_cast<size_t>(mt) * p.kq_total + kq) * 512, kWords * 512, full);
                     // the tile's 256 columns are two 128-row scale blocks of B (the workspace pads to a pair)
                     bulk_load(ssf + 1024, p.sfb + (static_cast<size_t>(2 * nt) * p.kq_total + kq) * 512, kWords * 512,
@@ -172,7 +174,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t fmt = kFp4 ? kFmtMxf4E2M1 : kFmtE4M3;
-            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, sf_slot = 0;
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
                 ok = mbar_wait(bar_tmem_empty + acc * 8, acc_phase ^ 1, s_abort, p.status, kDevTimeoutMmaTmem);
@@ -189,23 +191,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     tcgen05_fence_after();
                     const uint32_t sa = ring + stage * S::kStageBytes;
                     const uint32_t sb = sa + S::kABytes;
-                    const uint32_t ssf = sb + S::kBBytes;
-                    // scale blocks of this stage: smem -> TMEM (32 rows x 16 bytes each, replicated to the four
-                    // lane quarters); the copies and the MMAs below execute in issue order
-                    const uint32_t t_sfa = tmem_base + kAccCols + sf_slot * kSfSlot;
-                    const uint32_t t_sfb = t_sfa + 8;
-                    // TMEM layout of a slot: A word w at columns [4w, 4w+4); B word w at [8 + 8w, 8 + 8w + 8):
-                    // columns 0-3 of it for the tile's first 128 columns, 4-7 for the second
-#pragma unroll
-                    for (uint32_t w = 0; w < kWords; ++w) {
-                        tmem_cp_32x128b_warpx4(t_sfa + w * 4, make_smem_desc_noswizzle(ssf + w * 512, 16, 128));
-#pragma unroll
-                        for (uint32_t nb = 0; nb < 2; ++nb) {
-                            tmem_cp_32x128b_warpx4(
-                                t_sfb + w * 8 + nb * 4,
-                                make_smem_desc_noswizzle(ssf + 1024 + (nb * kWords + w) * 512, 16, 128));
-                        }
+                    // the stage's scale blocks are copied into TMEM slot `stage` by the copier warp
+                    ok = mbar_wait(bar_sf_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
+                    if (!ok) {
+                        break;
                     }
+                    tcgen05_fence_after();
+                    const uint32_t t_sfa = tmem_base + kAccCols + stage * kSfSlot;
+                    const uint32_t t_sfb = t_sfa + 8;
 #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j) {
                         const uint64_t da = make_smem_desc_sw128(sa + j * 32, 16, 1024);
@@ -219,7 +212,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                       t_sfb + word * 8);
                     }
                     umma_commit<1>(bar_empty + stage * 8);
-                    sf_slot ^= 1;
                     if (++stage == kMxStages) {
                         stage = 0;
                         phase ^= 1;
@@ -232,6 +224,47 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (++acc == kMxAccs) {
                     acc = 0;
                     acc_phase ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 6) {
+        // ---- scale copier: smem -> TMEM, one thread.  Issuing a tcgen05 instruction costs its thread ~70 ns
+        // whatever it does; three copies on top of four MMAs and a commit per stage made the MMA thread the
+        // limit of the kernel, so the copies have a thread of their own.  TMEM slot `stage` is free when the
+        // stage's "full" barrier fires: the MMAs that read its previous contents completed before the producer
+        // was allowed to refill the stage.
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutConvert);
+                    if (!ok) {
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t ssf = ring + stage * S::kStageBytes + S::kABytes + S::kBBytes;
+                    // TMEM layout of a slot: A word w at columns [4w, 4w+4); B word w at [8 + 8w, 8 + 8w + 8):
+                    // columns 0-3 of it for the tile's first 128 columns, 4-7 for the second.  Each copy moves
+                    // 32 rows x 16 bytes, replicated to the four lane quarters.
+                    const uint32_t t_sfa = tmem_base + kAccCols + stage * kSfSlot;
+                    const uint32_t t_sfb = t_sfa + 8;
+#pragma unroll
+                    for (uint32_t w = 0; w < kWords; ++w) {
+                        tmem_cp_32x128b_warpx4(t_sfa + w * 4, make_smem_desc_noswizzle(ssf + w * 512, 16, 128));
+#pragma unroll
+                        for (uint32_t nb = 0; nb < 2; ++nb) {
+                            tmem_cp_32x128b_warpx4(
+                                t_sfb + w * 8 + nb * 4,
+                                make_smem_desc_noswizzle(ssf + 1024 + (nb * kWords + w) * 512, 16, 128));
+                        }
+                    }
+                    umma_commit<1>(bar_sf_full + stage * 8);  // arrives when the copies have completed
+                    if (++stage == kMxStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
                 }
             }
         }
