@@ -536,6 +536,16 @@ int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStre
     p.num_k_blocks = row_bytes / 128u;
     p.words_per_stage = kFp4 ? 2u : 1u;
     p.kq_total = args->k / 128u;
+    // a band of the tile order holds ~32 MB of A (measured best at 8192^3: 32 row panels for fp8): its row panels
+    // stay in L2 while the band's columns go by
+    p.band_rows = (32u << 20) / (128u * (row_bytes > 0 ? row_bytes : 1u));
+    p.band_rows = p.band_rows < 4u ? 4u : (p.band_rows > 64u ? 64u : p.band_rows);
+    if (const char* e = getenv("CB200_MX_BAND")) {  // developer knob
+        const uint32_t v = static_cast<uint32_t>(atoi(e));
+        if (v >= 1 && v <= 4096) {
+            p.band_rows = v;
+        }
+    }
     uint8_t* ws = static_cast<uint8_t*>(args->workspace);
     const uint64_t sfa_bytes = static_cast<uint64_t>((args->m + 127u) / 128u) * p.kq_total * 512u;
     p.sfa = ws;

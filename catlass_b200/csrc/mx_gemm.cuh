@@ -39,6 +39,7 @@ struct MxParams {
     uint32_t num_k_blocks;     // K bytes per row / 128
     uint32_t words_per_stage;  // scale words (4 scale blocks = 128 K elements) per 128-byte stage: 1 (fp8), 2 (fp4)
     uint32_t kq_total;         // scale words per row = K / 128
+    uint32_t band_rows;        // tile rows per band of the tile order (see mx_tile_coords)
     const uint8_t* sfa;        // packed scales of A: [ceil(m/128)][kq_total][512]
     const uint8_t* sfb;        // packed scales of B: [ceil(n/128)][kq_total][512]
     __nv_bfloat16* d;
@@ -76,6 +77,21 @@ __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* _
         uint8_t* dst = out + (static_cast<size_t>(rb) * kq_total + kq) * 512 + (r % 32) * 16 + (r / 32) * 4;
         *reinterpret_cast<uint32_t*>(dst) = v;
     }
+}
+
+// Tile order: bands of `band_rows` tile rows, walked column by column inside a band.  The 148 tiles in flight at
+// any time then share the band's row panels of A (the host sizes a band to ~32 MB of A) and a few column panels
+// of B, which stay in L2; with a plain row-major order every wave streamed all of B from HBM again (measured at
+// 8192^3 fp8: 7x the operand bytes).
+__device__ __forceinline__ void mx_tile_coords(uint32_t idx, uint32_t m_tiles, uint32_t n_tiles, uint32_t band_rows,
+                                               uint32_t& mt, uint32_t& nt)
+{
+    const uint32_t per_band = band_rows * n_tiles;
+    const uint32_t band = idx / per_band;
+    const uint32_t r = idx - band * per_band;
+    const uint32_t rows = m_tiles - band * band_rows < band_rows ? m_tiles - band * band_rows : band_rows;
+    nt = r / rows;
+    mt = band * band_rows + (r - nt * rows);
 }
 
 template <bool kFp4>
@@ -142,7 +158,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
-                const uint32_t mt = idx / n_tiles, nt = idx - mt * n_tiles;
+                uint32_t mt, nt;
+                mx_tile_coords(idx, m_tiles, n_tiles, p.band_rows, mt, nt);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer);
                     if (!ok) {
@@ -275,7 +292,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
-            const uint32_t mt = idx / n_tiles, nt = idx - mt * n_tiles;
+            uint32_t mt, nt;
+            mx_tile_coords(idx, m_tiles, n_tiles, p.band_rows, mt, nt);
             ok = mbar_wait(bar_tmem_full + acc * 8, acc_phase, s_abort, p.status, kDevTimeoutEpilogue);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
