@@ -154,7 +154,10 @@ CB200_API int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_
  * (include/catlass/gemm/kernel/w4a8_matmul.hpp:83-93; operand order A, packed B of
  * tests/optest/kernels/32_w4a8_matmul/w4a8_matmul_impl.cpp:101-103).  The reference's own kernel applies one
  * per-tensor scalar; that case is group_size = k with weight_scale all ones and per_token_scale = scalar.
- * Requirements: k and group_size multiples of 128, group_size divides k.
+ * Requirements: k and group_size multiples of 128, group_size divides k, group_size <= 16384.
+ * Summation order: shapes with few 128-channel tiles split the groups over the 2 or 4 CTAs of a cluster and add
+ * the fp32 partial sums at the end; D then agrees with the definition above to 1 bf16 ulp.  With the environment
+ * variable CB200_W4A8_SPLITS=1 the groups are summed in ascending order and D is bit-exact.
  */
 typedef struct cb200_w4a8_matmul_args {
     uint32_t m, n, k;
