@@ -1,6 +1,7 @@
 // C-ABI entry points of libcatlass_b200.so (declared in include/catlass_b200.h).
 // Host code only validates arguments, encodes tensor maps and launches; it never touches matrix data and
 // has no CPU compute path: without a sm_100 device every launch entry returns an error.
+#include <cstring>
 #include <cuda_bf16.h>
 
 #include <cmath>
@@ -113,6 +114,7 @@ int launch_w8a8(const W8A8Problem& q, const DeviceState& dev, cudaStream_t strea
     }
 
     W8A8Params p;
+    p.tma_store = 0;
     p.m = q.m;
     p.n = q.n;
     p.k = q.k;
@@ -194,6 +196,7 @@ int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t 
         }
     }
     W8A8Params p;
+    p.tma_store = 0;
     p.m = q.m;
     p.n = q.n;
     p.k = q.k;
@@ -206,6 +209,25 @@ int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t 
     p.d = static_cast<__nv_bfloat16*>(q.d);
     p.acc = q.acc;
     p.status = dev.status;
+    // D as a byte tensor [m][2n] for the epilogue's TMA stores (32 rows x 64 bytes per store): possible when the
+    // row pitch is a multiple of 16 bytes; otherwise every row is stored by its thread
+    CUtensorMap tmap_d;
+    memset(&tmap_d, 0, sizeof(tmap_d));
+    p.tma_store = 0;
+    static const bool allow_tma_store = [] {
+        const char* e = getenv("CB200_W8A8_TMA_STORE");  // developer knob: 0 = per-thread stores only
+        return e == nullptr || atoi(e) != 0;
+    }();
+    if (allow_tma_store && (q.n & 7u) == 0 && aligned16(q.d)) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(q.n) * 2u, q.m};
+        const uint64_t strides[1] = {static_cast<uint64_t>(q.n) * 2u};
+        const uint32_t box[2] = {64, 32};
+        int rc = encode_tmap_u8(&tmap_d, q.d, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        p.tma_store = 1;
+    }
 
     auto kernel = w8a8_pair_kernel<kB>;
     static bool attr_set[kMaxDevices] = {};
@@ -227,7 +249,7 @@ int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t 
     if (pairs == 0) {
         return CB200_SUCCESS;
     }
-    kernel<<<2 * pairs, kGemmThreads, S::kTotalBytes, stream>>>(tmap_a, tmap_b, p);
+    kernel<<<2 * pairs, kGemmThreads, S::kTotalBytes, stream>>>(tmap_a, tmap_b, tmap_d, p);
     CB200_CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return CB200_SUCCESS;

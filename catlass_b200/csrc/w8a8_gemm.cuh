@@ -51,6 +51,7 @@ struct W8A8Params {
     __nv_bfloat16* d;          // [m][n]
     int32_t* acc;              // optional raw accumulators [m][n]
     unsigned* status;          // device status word
+    uint32_t tma_store;        // pair kernel: D has a tensor map, full 32-row slabs leave through TMA stores
 };
 
 template <int BN>

@@ -31,11 +31,14 @@ struct W8A8PairSmem {
     static constexpr int kStageBytes = kStageABytes + kStageBBytes;
     static constexpr int kStages = 6;
     static constexpr int kRingBytes = kStages * kStageBytes;
+    // output staging: per epilogue warp two slabs of 32 rows x 32 bf16 (64 B rows, 64-byte swizzle) for TMA stores
+    static constexpr int kStoreSlabBytes = 32 * 64;
+    static constexpr int kStoreBytes = 4 * 2 * kStoreSlabBytes;
     static constexpr int kScaleBytes = 4 * kPairBN * 4;
     static constexpr int kTableEntries = kMaxGroups + 2;
     static constexpr int kTableBytes = 3 * kTableEntries * 4;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
-    static constexpr int kTotalBytes = 1024 + kRingBytes + kScaleBytes + kTableBytes + kBarrierBytes;
+    static constexpr int kTotalBytes = 1024 + kRingBytes + kStoreBytes + kScaleBytes + kTableBytes + kBarrierBytes;
 };
 
 // address of `local` (a shared::cta address of this CTA) as seen in CTA `rank` of the cluster
@@ -49,7 +52,7 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
 template <BLayout kB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const W8A8Params p)
+                 const __grid_constant__ CUtensorMap tmap_d, const W8A8Params p)
 {
     using S = W8A8PairSmem;
     constexpr int kStages = S::kStages;
@@ -62,11 +65,13 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* smem = smem_raw + pad;
     const uint32_t ring = raw_addr + pad;
 
-    float* s_scale = reinterpret_cast<float*>(smem + S::kRingBytes);
-    int32_t* s_row_begin = reinterpret_cast<int32_t*>(smem + S::kRingBytes + S::kScaleBytes);
+    uint8_t* s_store = smem + S::kRingBytes;
+    float* s_scale = reinterpret_cast<float*>(smem + S::kRingBytes + S::kStoreBytes);
+    int32_t* s_row_begin = reinterpret_cast<int32_t*>(smem + S::kRingBytes + S::kStoreBytes + S::kScaleBytes);
     int32_t* s_row_end = s_row_begin + S::kTableEntries;
     uint32_t* s_tile_begin = reinterpret_cast<uint32_t*>(s_row_end + S::kTableEntries);
-    uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes + S::kScaleBytes + S::kTableBytes);
+    uint64_t* s_bars =
+        reinterpret_cast<uint64_t*>(smem + S::kRingBytes + S::kStoreBytes + S::kScaleBytes + S::kTableBytes);
     const uint32_t bar_full = smem_u32(s_bars);
     const uint32_t bar_empty = bar_full + kStages * 8;
     const uint32_t bar_tmem_full = bar_empty + kStages * 8;
@@ -266,7 +271,12 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             __nv_bfloat16* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
             int32_t* arow = p.acc ? p.acc + static_cast<size_t>(row_ok ? row : 0) * p.n : nullptr;
             // a whole warp without valid rows (ragged tail of a group) skips the drain
-            const bool warp_rows = (t.row0 + static_cast<int32_t>(cta_rank * kBlockM + quad * 32)) < t.row_end;
+            const int32_t warp_row0 = t.row0 + static_cast<int32_t>(cta_rank * kBlockM + quad * 32);
+            const bool warp_rows = warp_row0 < t.row_end;
+            // A warp whose 32 rows all belong to the group stages 32 x 32 outputs in shared memory and hands
+            // them to a TMA store (columns past N are clipped by the tensor map); a ragged warp must not write
+            // the rows below the group's end, which belong to the next group, and stores row by row.
+            const bool slab_store = p.tma_store != 0 && warp_row0 + 32 <= t.row_end;
 
 #pragma unroll 1
             for (int c = 0; c < BN / 32 && warp_rows; ++c) {
@@ -274,7 +284,43 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
                 const uint32_t col0 = t.n0 + c * 32;
-                if (row_ok && col0 < p.n) {
+                if (slab_store && col0 < p.n) {
+                    const float* scc = sc + c * 32;
+                    uint8_t* slab = s_store + ((warp - 2) * 2 + (c & 1)) * S::kStoreSlabBytes;
+                    if (lane == 0) {
+                        tma_store_wait_read<1>();  // the store that read this slab two chunks ago has done so
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int j = v * 8 + e * 2;
+                            const float x0 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), scc[j]), pt);
+                            const float x1 =
+                                __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j + 1])), scc[j + 1]), pt);
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                            packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                        // row = lane, 16-byte chunk v at v ^ ((row >> 1) & 3): the 64-byte swizzle of the map
+                        *reinterpret_cast<uint4*>(slab + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) =
+                            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                    fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmap_d, smem_u32(slab), static_cast<int32_t>(col0 * 2), warp_row0);
+                        tma_store_commit();
+                    }
+                    if (arow != nullptr) {
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) {
+                                arow[col0 + j] = static_cast<int32_t>(r[j]);
+                            }
+                        }
+                    }
+                } else if (row_ok && col0 < p.n) {
                     const float* scc = sc + c * 32;
                     if (vec_ok && col0 + 32 <= p.n) {
 #pragma unroll
@@ -322,6 +368,10 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 acc_phase ^= 1;
             }
         }
+        if (lane == 0) {
+            tma_store_wait_all<0>();  // this thread's TMA stores have been written
+        }
+        __syncwarp();
     }
 
     // ------------------------------------------------------------------ common exit
