@@ -56,8 +56,7 @@ constexpr int kW4AccPairs = 2;      // accumulators are handed over two at a tim
 constexpr int kW4Tiles = 4;         // token tiles / unpacked weight tiles in flight (= unpack warps, see there)
 constexpr int kW4PackedSlots = 12;  // packed-weight tiles in flight (8 KB each): covers HBM latency
 constexpr int kW4MaxSplits = 4;     // CTAs of a cluster sharing one channel tile along K
-constexpr int kW4Load = 2;          // K blocks per TMA load (a thread sustains ~3-4 tile loads per microsecond
-                                    // whatever their size: one load per block would cap the kernel)
+constexpr int kW4Load = 2;          // K blocks per TMA load (3-D boxes): half the loads and barrier round trips
 constexpr int kW4PackedLoads = kW4PackedSlots / kW4Load;  // load slots of the packed-weight ring
 constexpr int kW4TokenLoads = kW4Tiles / kW4Load;         // load slots of the token ring
 
@@ -258,8 +257,8 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     if (warp == 0) {
         // ------------------------------------------------------- packed-weight producer
-        // (A thread that issues TMA tile loads in a wait / issue loop sustains about one load per 0.25 us,
-        // whatever the tile's size: weights and tokens each get a thread of their own.)
+        // (Weights and tokens each have a producer thread of their own: the deep weight ring keeps running ahead
+        // while the token thread waits for a tile slot.)
         if (lane == 0) {
             bool ok = true;
             const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
