@@ -296,9 +296,9 @@ def run_moe(args, rank, world, local):
         "roofline": {
             "bound": "tensor", "achieved": achieved, "peak": peak_tops, "unit": "TFLOP/s",
             "frac": achieved / peak_tops if peak_tops else None,
-            # DRAM bytes per launch: ncu capture of the 1/8-size `moe_small` case (531.7 MB, see profiles/),
+            # DRAM bytes per launch: ncu capture of the 1/8-size `moe_small` case (540.2 MB, see profiles/),
             # scaled by the rows this launch processes (traffic is proportional to rows and experts)
-            "traffic": 531.7e6 * m / 16384.0 if cfg is MOE else None,
+            "traffic": 540.2e6 * m / 16384.0 if cfg is MOE else None,
             "kernel": "w8a8_pair_kernel<row-major B>: 256x256 tiles on CTA pairs (rank 0 launch)", "kernel_ms": kernel_ms,
             "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s); "
                            "int8 ops = 2*rows*N*K; nominal dense int8 is 4500",
