@@ -514,7 +514,12 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": float(np.mean(secs_all)) * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "moe_grouped_slice_m_w8a8 (CPU golden on a bounded row sample per step)"},
+        "config": {
+            "workload": f"moe_grouped_slice_m_w8a8: {cfg['experts']} experts, K={cfg['k']}, N={cfg['n']}, "
+                        f"{cfg['tokens']} tokens x top-{cfg['top_k']} = {cfg['tokens'] * cfg['top_k']} rows, "
+                        f"Zipf({cfg['zipf_s']}) expert loads, B row-major [G,K,N], bf16 out",
+            "measured_on": "the reference's CPU golden, a bounded row sample of this workload per step",
+        },
         "cpu_baseline": {"value": value, "unit": "TOPS", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
