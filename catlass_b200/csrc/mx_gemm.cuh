@@ -31,7 +31,7 @@ namespace cb200 {
 constexpr int kMxBlockN = 256;  // one tcgen05.mma of 128 x 256 runs about as long as issuing it costs its thread
 constexpr int kMxAccs = 1;      // one accumulator: 256 columns + the scale columns leave no room for a second
 constexpr int kMxStages = 4;
-constexpr int kMxThreads = 224;  // warps: 0 TMA producer, 1 MMA issuer, 2..5 epilogue, 6 scale copier
+constexpr int kMxThreads = 352;  // warps: 0 TMA producer, 1 MMA issuer, 2..5 and 7..10 epilogue, 6 scale copier
 
 struct MxParams {
     uint32_t m, n, k;
@@ -137,7 +137,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         for (int a = 0; a < kMxAccs; ++a) {
             mbar_init(bar_tmem_full + a * 8, 1);
-            mbar_init(bar_tmem_empty + a * 8, 4);
+            mbar_init(bar_tmem_empty + a * 8, 8);  // one arrival per epilogue warp
         }
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
@@ -287,7 +287,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         __syncwarp();
     } else {
+        // ---- epilogue: eight warps, two per TMEM lane quarter, 128 columns each.  There is room for one
+        // accumulator only, so a warp first pulls its 128 columns out of TMEM and rounds them to bf16 into
+        // registers (64 per thread), hands the accumulator back, and stores afterwards: the next tile's MMAs wait
+        // for four TMEM reads, not for the stores.
         const uint32_t quad = warp & 3;
+        const uint32_t half = warp >= 7 ? 1u : 0u;
         const bool vec_ok = (p.n & 7u) == 0;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
@@ -302,35 +307,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tcgen05_fence_after();
             const uint32_t row = mt * kBlockM + quad * 32 + lane;
             const bool row_ok = row < p.m;
-            const uint32_t taddr = tmem_base + acc * kMxBlockN + ((quad * 32u) << 16);
+            const uint32_t taddr = tmem_base + acc * kMxBlockN + half * 128 + ((quad * 32u) << 16);
             __nv_bfloat16* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
-#pragma unroll 1
-            for (int c = 0; c < kMxBlockN / 32; ++c) {
+            uint32_t packed[64];  // bf16 pairs: columns 2i, 2i+1 of this warp's 128
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
-                const uint32_t col0 = nt * kMxBlockN + c * 32;
-                if (row_ok && col0 < p.n) {
-                    if (vec_ok && col0 + 32 <= p.n) {
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint32_t packed[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + e * 2]),
-                                                                               __uint_as_float(r[v * 8 + e * 2 + 1]));
-                                packed[e] = *reinterpret_cast<const uint32_t*>(&h);
-                            }
-                            *reinterpret_cast<uint4*>(drow + col0 + v * 8) =
-                                make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        }
-                    } else {
-                        for (int j = 0; j < 32; ++j) {
-                            if (col0 + j < p.n) {
-                                drow[col0 + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                            }
-                        }
-                    }
+                for (int e = 0; e < 16; ++e) {
+                    const __nv_bfloat162 h =
+                        __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+                    packed[c * 16 + e] = *reinterpret_cast<const uint32_t*>(&h);
                 }
             }
             tcgen05_fence_before();
@@ -341,6 +330,27 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (++acc == kMxAccs) {
                 acc = 0;
                 acc_phase ^= 1;
+            }
+            const uint32_t col_base = nt * kMxBlockN + half * 128;
+            if (row_ok && col_base < p.n) {
+                if (vec_ok && col_base + 128 <= p.n) {
+#pragma unroll
+                    for (int v = 0; v < 16; ++v) {
+                        *reinterpret_cast<uint4*>(drow + col_base + v * 8) =
+                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&packed[i]);
+                        if (col_base + 2 * i < p.n) {
+                            drow[col_base + 2 * i] = h.x;
+                        }
+                        if (col_base + 2 * i + 1 < p.n) {
+                            drow[col_base + 2 * i + 1] = h.y;
+                        }
+                    }
+                }
             }
         }
     }
