@@ -830,7 +830,7 @@ int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args* ar
 // Host-buffer grouped matmul: chunked copy-in / compute / copy-out overlap (see the header).
 namespace {
 
-constexpr uint32_t kHostDefaultChunks = 8;
+constexpr uint32_t kHostDefaultChunks = 16;  // measured on the MoE workload: 4: 25.2 ms, 8: 23.2, 16: 22.3, 32: 22.9
 constexpr uint32_t kHostMaxChunks = 64;
 
 struct HostPipe {

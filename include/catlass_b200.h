@@ -127,7 +127,7 @@ typedef struct cb200_grouped_quant_matmul_host_args {
     uint32_t m, n, k;
     uint32_t group_count;
     uint32_t layout_b;
-    uint32_t chunks;                  /* 0 = library default (8) */
+    uint32_t chunks;                  /* 0 = library default (16) */
     const void *a_host;               /* int8 m x k */
     const int64_t *group_list_host;   /* prefix sums */
     const float *per_token_host;      /* [m] */
