@@ -295,9 +295,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                                    kDevTimeoutProducer);
                 }
                 if (ok) {
-                    // kW4Load consecutive K blocks of all 128 token rows (rows past m read as zeros)
+                    // kW4Load consecutive K blocks of the mt token rows (rows past m read as zeros): the tiles of
+                    // a load land back to back, mt * 128 bytes apart
                     const uint32_t full = bar_x_full + slot * 8;
-                    mbar_expect_tx(full, kW4Load * S::kTokenBytes);
+                    mbar_expect_tx(full, kW4Load * p.mt * 128);
                     tma_load_3d(ring + S::kTokenRing + slot * (kW4Load * S::kTokenBytes), &tmap_x, full, 0, m0,
                                 static_cast<int32_t>(kb_begin + l * kW4Load));
                 }
@@ -335,7 +336,8 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     }
                     tcgen05_fence_after();
                     const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA A operand
-                    const uint32_t sx_tile = ring + S::kTokenRing + slot * S::kTokenBytes;    // UMMA B operand
+                    const uint32_t sx_tile = ring + S::kTokenRing + (slot / kW4Load) * (kW4Load * S::kTokenBytes) +
+                                             (slot % kW4Load) * p.mt * 128;                   // UMMA B operand
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint64_t da = make_smem_desc_sw128(sw_tile + q * kUmmaK, 16, 1024);
