@@ -31,7 +31,7 @@ namespace cb200 {
 constexpr int kMxBlockN = 256;  // one tcgen05.mma of 128 x 256 runs about as long as issuing it costs its thread
 constexpr int kMxAccs = 1;      // one accumulator: 256 columns + the scale columns leave no room for a second
 constexpr int kMxStages = 4;
-constexpr int kMxThreads = 352;  // warps: 0 TMA producer, 1 MMA issuer, 2..5 and 7..10 epilogue, 6 scale copier
+constexpr int kMxThreads = 384;  // warps: 0 TMA producer, 1 MMA issuer, 2..5 and 7..10 epilogue, 6 and 11 scale copiers
 
 struct MxParams {
     uint32_t m, n, k;
@@ -133,7 +133,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int s = 0; s < kMxStages; ++s) {
             mbar_init(bar_full + s * 8, 1);
             mbar_init(bar_empty + s * 8, 1);
-            mbar_init(bar_sf_full + s * 8, 1);
+            mbar_init(bar_sf_full + s * 8, kFp4 ? 2 : 1);  // one arrival per scale copier at work
         }
         for (int a = 0; a < kMxAccs; ++a) {
             mbar_init(bar_tmem_full + a * 8, 1);
@@ -245,13 +245,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp == 6) {
+    } else if (warp == 6 || warp == 11) {
         // ---- scale copier: smem -> TMEM, one thread.  Issuing a tcgen05 instruction costs its thread ~70 ns
         // whatever it does; three copies on top of four MMAs and a commit per stage made the MMA thread the
         // limit of the kernel, so the copies have a thread of their own.  TMEM slot `stage` is free when the
         // stage's "full" barrier fires: the MMAs that read its previous contents completed before the producer
         // was allowed to refill the stage.
-        if (lane == 0) {
+        // (fp4 has two scale words per stage, six copies: warp 6 takes word 0, warp 11 word 1)
+        const uint32_t my_word = warp == 6 ? 0u : 1u;
+        if (lane == 0 && my_word < kWords) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
@@ -267,8 +269,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     // 32 rows x 16 bytes, replicated to the four lane quarters.
                     const uint32_t t_sfa = tmem_base + kAccCols + stage * kSfSlot;
                     const uint32_t t_sfb = t_sfa + 8;
-#pragma unroll
-                    for (uint32_t w = 0; w < kWords; ++w) {
+                    {
+                        const uint32_t w = my_word;
                         tmem_cp_32x128b_warpx4(t_sfa + w * 4, make_smem_desc_noswizzle(ssf + w * 512, 16, 128));
 #pragma unroll
                         for (uint32_t nb = 0; nb < 2; ++nb) {
@@ -277,7 +279,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                 make_smem_desc_noswizzle(ssf + 1024 + (nb * kWords + w) * 512, 16, 128));
                         }
                     }
-                    umma_commit<1>(bar_sf_full + stage * 8);  // arrives when the copies have completed
+                    umma_commit<1>(bar_sf_full + stage * 8);  // arrives when this thread's copies have completed
                     if (++stage == kMxStages) {
                         stage = 0;
                         phase ^= 1;
