@@ -404,8 +404,10 @@ def run_w4a8(args, rank, world, local):
     d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
     it = [0]
 
+    split_k = bool(getattr(args, "w4a8_split_k", False))
+
     def step():
-        capi.w4a8_matmul(a, ws[it[0] % copies], sw, sa, d, m, n, k, gs)
+        capi.w4a8_matmul(a, ws[it[0] % copies], sw, sa, d, m, n, k, gs, split_k=split_k)
         it[0] += 1
 
     for _ in range(max(args.warmup, copies)):
@@ -434,6 +436,8 @@ def run_w4a8(args, rank, world, local):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int4xint8->int32->f32", "data": "synthetic",
         "config": {"workload": f"w4a8: M={m} N={n} K={k} group {gs}, int4 weights packed along K, bf16 out",
+                   "summation": "K split over a CTA cluster, fp32 partial sums reassociated (CB200_W4A8_SPLIT_K)"
+                                if split_k else "sequential over the scale groups (default: bit-exact)",
                    "l2": f"weights rotate over {copies} copies: every pass reads HBM"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
@@ -537,6 +541,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=0, help="row chunks of the host-buffer pipeline (0 = default)")
+    ap.add_argument("--w4a8-split-k", action="store_true",
+                    help="w4a8 workload: time the opt-in split-K mode instead of the bit-exact default")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

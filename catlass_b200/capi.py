@@ -157,10 +157,13 @@ def grouped_quant_matmul(a, b, group_list, scale, per_token, d, m, n, k, group_c
            load().cb200_grouped_quant_matmul_slice_m(ctypes.byref(args), _stream(stream)))
 
 
-def w4a8_matmul(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, stream=None):
+W4A8_SPLIT_K = 1  # flags: split the K range over a CTA cluster (faster, fp32 sums reassociated)
+
+
+def w4a8_matmul(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, stream=None, split_k=False):
     args = W4A8MatmulArgs(m=m, n=n, k=k, group_size=group_size, a=_p(a), w_packed=_p(w_packed),
                           weight_scale=_p(weight_scale), per_token_scale=_p(per_token), d=_p(d), workspace=None,
-                          workspace_bytes=0, block_num=0, reserved=0)
+                          workspace_bytes=0, block_num=0, reserved=W4A8_SPLIT_K if split_k else 0)
     _check("cb200_w4a8_matmul", load().cb200_w4a8_matmul(ctypes.byref(args), _stream(stream)))
 
 

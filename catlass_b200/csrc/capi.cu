@@ -687,22 +687,42 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     p.m = args->m;
     p.n = args->n;
     p.k = args->k;
-    p.mt = args->m >= static_cast<uint32_t>(kW4Tokens) ? kW4Tokens : ((args->m + 15u) & ~15u);
     p.blocks_per_group = args->group_size / 128u;
     p.num_groups = args->k / args->group_size;
-    // K split over the CTAs of a cluster: as many as still fit the SMs in one wave (and the scale groups allow)
-    const uint32_t tiles = ((args->n + kW4Channels - 1) / kW4Channels) * ((args->m + kW4Tokens - 1) / kW4Tokens);
+    const uint32_t tiles_n = (args->n + kW4Channels - 1) / kW4Channels;
+    // Default: every CTA runs the whole K range (the sequential fp32 order of the definition: bit-exact).  Token
+    // tiles of 64 rows instead of 128 double the CTAs when the result still fits one wave.
     p.splits = 1;
-    while (p.splits < static_cast<uint32_t>(kW4MaxSplits) && tiles * p.splits * 2 <= static_cast<uint32_t>(dev->sm_count) &&
-           p.splits * 2 <= p.num_groups) {
-        p.splits *= 2;
+    p.tile_m = kW4Tokens;
+    if (args->m > 64u && tiles_n * ((args->m + 63u) / 64u) <= static_cast<uint32_t>(dev->sm_count)) {
+        p.tile_m = 64;
     }
-    if (const char* e = getenv("CB200_W4A8_SPLITS")) {  // 1 = the bit-exact summation order
-        const uint32_t want = static_cast<uint32_t>(atoi(e));
-        if ((want == 1 || want == 2 || want == 4) && want <= p.num_groups) {
-            p.splits = want;
+    // Opt-in (flags bit 0, or the developer knob CB200_W4A8_SPLITS=2|4): the K range split over the CTAs of a
+    // cluster, as many as still fit the SMs in one wave; fp32 partial sums are then added at the end.
+    uint32_t want_splits = (args->reserved & CB200_W4A8_SPLIT_K) ? static_cast<uint32_t>(kW4MaxSplits) : 1u;
+    if (const char* e = getenv("CB200_W4A8_SPLITS")) {
+        const uint32_t v = static_cast<uint32_t>(atoi(e));
+        if (v == 1 || v == 2 || v == 4) {
+            want_splits = v;
         }
     }
+    if (want_splits > 1) {
+        const uint32_t tiles = tiles_n * ((args->m + kW4Tokens - 1) / kW4Tokens);
+        while (p.splits < want_splits && tiles * p.splits * 2 <= static_cast<uint32_t>(dev->sm_count) &&
+               p.splits * 2 <= p.num_groups) {
+            p.splits *= 2;
+        }
+        if (p.splits > 1) {
+            p.tile_m = kW4Tokens;
+        }
+    }
+    if (const char* e = getenv("CB200_W4A8_TILE_M")) {  // developer knob
+        const uint32_t v = static_cast<uint32_t>(atoi(e));
+        if ((v == 64 || v == 128) && p.splits == 1) {
+            p.tile_m = v;
+        }
+    }
+    p.mt = args->m >= p.tile_m ? p.tile_m : ((args->m + 15u) & ~15u);
     p.sw = args->weight_scale;
     p.sa = args->per_token_scale;
     p.d = static_cast<__nv_bfloat16*>(args->d);
@@ -738,7 +758,7 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
                                             W4A8Smem::kTotalBytes));
         attr_set[devid] = true;
     }
-    const dim3 grid(((args->n + kW4Channels - 1) / kW4Channels) * p.splits, (args->m + kW4Tokens - 1) / kW4Tokens, 1);
+    const dim3 grid(tiles_n * p.splits, (args->m + p.tile_m - 1) / p.tile_m, 1);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

@@ -19,8 +19,11 @@
 // limit).  To fill the machine when N/128 tiles are fewer than the SMs, the K range (whole scale groups) is
 // split over the 1, 2 or 4 CTAs of a cluster; each keeps fp32 partial sums y and at the end every CTA reduces
 // and stores one slice of the token columns, the partials travelling through distributed shared memory.
-// With a split the fp32 sums are added in a different order than the sequential definition above: results
-// then agree with it to 1 bf16 ulp instead of bit for bit.  One CTA per cluster (splits = 1) is bit-exact.
+// With a split the fp32 sums are added in a different order than the sequential definition above: results are
+// then no longer bit-identical, and an output whose partial sums nearly cancel can differ by many bf16 ulps of
+// its (tiny) value.  The split is therefore opt-in (CB200_W4A8_SPLIT_K in the arguments).  By default every CTA
+// runs the whole K range, which is bit-exact; to fill the machine then, the token rows are cut into tiles of 64
+// instead of 128 when that still fits one wave of CTAs (each weight tile is then unpacked by two CTAs).
 //
 // Warp roles (16 warps):
 //   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 12 in flight: they come from HBM) and token
@@ -62,7 +65,8 @@ constexpr int kW4TokenLoads = kW4Tiles / kW4Load;         // load slots of the t
 
 struct W4A8Params {
     uint32_t m, n, k;
-    uint32_t mt;                // token rows loaded per tile: min(128, round_up(m, 16)); also the UMMA N
+    uint32_t tile_m;            // token rows per CTA tile: 128, or 64 (twice the CTAs for the same channel tiles)
+    uint32_t mt;                // token rows loaded per tile: min(tile_m, round_up(m, 16)); also the UMMA N
     uint32_t blocks_per_group;  // group_size / 128
     uint32_t num_groups;        // k / group_size
     uint32_t splits;            // cluster size along K: 1, 2 or 4
@@ -202,7 +206,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t splits = p.splits;
     const uint32_t rank = splits > 1 ? cluster_ctarank() : 0;  // position along K inside the cluster
     const int32_t n0 = static_cast<int32_t>(blockIdx.x / splits) * kW4Channels;
-    const int32_t m0 = static_cast<int32_t>(blockIdx.y) * kW4Tokens;
+    const int32_t m0 = static_cast<int32_t>(blockIdx.y * p.tile_m);
     const uint32_t bpg = p.blocks_per_group;
     // this CTA's scale groups [g_begin, g_begin + my_groups) and K blocks [kb_begin, kb_begin + my_kb)
     const uint32_t groups_per_rank = (p.num_groups + splits - 1) / splits;
@@ -426,8 +430,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // ------------------------------------------------------- epilogue warps 6..13
         const uint32_t ew = warp - 6;     // 0..7
         const uint32_t quad = warp & 3;   // TMEM lane quarter this warp may read: channels quad*32 .. +31
-        const uint32_t half = ew >> 2;    // token columns half*64 .. +63
-        const uint32_t cols_mine = p.mt > half * 64 ? (p.mt - half * 64 < 64 ? p.mt - half * 64 : 64) : 0;
+        const uint32_t half = ew >> 2;    // which part of the token columns (see hcols)
+        // the two warps of a lane quarter split the token columns: 64 each, or 32 each when the tile has <= 64
+        const uint32_t hcols = p.mt > 64 ? 64u : 32u;
+        const uint32_t cols_mine = p.mt > half * hcols ? (p.mt - half * hcols < hcols ? p.mt - half * hcols : hcols) : 0;
         const uint32_t np = (cols_mine + 31) / 32;  // 32-column halves of this warp's range that hold tokens
         // This lane's channel scale of every group: plain loads issued three groups ahead of their use and
         // held in registers, so that the latency never sits on the per-group critical path.
@@ -460,7 +466,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 mbar_arrive(bar_acc_empty + (pair % kW4AccPairs) * 8);
             }
         };
-        const uint32_t tmem_mine = tmem_base + half * 64 + ((quad * 32u) << 16);
+        const uint32_t tmem_mine = tmem_base + half * hcols + ((quad * 32u) << 16);
         auto issue = [&](uint32_t j, uint32_t piece, uint32_t(&r)[16]) {
             tmem_ld_32x32b_x16(tmem_mine + (j % kW4Accs) * kW4Tokens + piece * 16, r);
         };
@@ -532,13 +538,16 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t et = threadIdx.x - 6 * 32;   // 0..255 among the epilogue threads
     if (is_epi) {
         const uint32_t ch = (warp & 3) * 32 + lane;
-        float* dst = ytile + ((warp - 6) >> 2) * 64 * kW4Channels + ch;
+        const uint32_t hcols = p.mt > 64 ? 64u : 32u;  // token columns per warp, as in the epilogue loop
+        float* dst = ytile + ((warp - 6) >> 2) * hcols * kW4Channels + ch;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            float lo, hi;
-            unpack_pair(y2[i], lo, hi);
-            dst[(2 * i) * kW4Channels] = lo;
-            dst[(2 * i + 1) * kW4Channels] = hi;
+            if (2u * i < hcols) {
+                float lo, hi;
+                unpack_pair(y2[i], lo, hi);
+                dst[(2 * i) * kW4Channels] = lo;
+                dst[(2 * i + 1) * kW4Channels] = hi;
+            }
         }
     }
     if (splits > 1) {
@@ -572,7 +581,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t col = (rank << cps_log2) + (v >> 4), c8 = v & 15;
             const uint32_t mrow = static_cast<uint32_t>(m0) + col;
             const uint32_t ncol = static_cast<uint32_t>(n0) + c8 * 8;
-            if (mrow >= p.m || ncol >= p.n) {
+            if (col >= p.mt || mrow >= p.m || ncol >= p.n) {  // (columns past mt belong to the next token tile)
                 continue;
             }
             const float* src = ytile + col * kW4Channels + c8 * 8;

@@ -155,10 +155,14 @@ CB200_API int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_
  * tests/optest/kernels/32_w4a8_matmul/w4a8_matmul_impl.cpp:101-103).  The reference's own kernel applies one
  * per-tensor scalar; that case is group_size = k with weight_scale all ones and per_token_scale = scalar.
  * Requirements: k and group_size multiples of 128, group_size divides k, group_size <= 16384.
- * Summation order: shapes with few 128-channel tiles split the groups over the 2 or 4 CTAs of a cluster and add
- * the fp32 partial sums at the end; D then agrees with the definition above to 1 bf16 ulp.  With the environment
- * variable CB200_W4A8_SPLITS=1 the groups are summed in ascending order and D is bit-exact.
+ * Summation order: by default the groups are summed in ascending order, exactly as written above (D is
+ * bit-exact against that definition).  With CB200_W4A8_SPLIT_K in `flags`, shapes with few 128-channel tiles
+ * split the groups over the 2 or 4 CTAs of a cluster and add the fp32 partial sums at the end: faster (M=128,
+ * N=K=8192: 25 us instead of the default's time), but an output whose partial sums nearly cancel can then differ
+ * from the definition by more than one bf16 ulp of its small value; the absolute difference stays below
+ * 2^-20 x the sum of the absolute group terms.
  */
+#define CB200_W4A8_SPLIT_K 1u
 typedef struct cb200_w4a8_matmul_args {
     uint32_t m, n, k;
     uint32_t group_size;
@@ -170,7 +174,7 @@ typedef struct cb200_w4a8_matmul_args {
     void *workspace;
     uint64_t workspace_bytes;
     uint32_t block_num;
-    uint32_t reserved;
+    uint32_t reserved;            /* flags: 0, or CB200_W4A8_SPLIT_K */
 } cb200_w4a8_matmul_args;
 
 CB200_API int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args *args);

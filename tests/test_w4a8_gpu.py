@@ -1,11 +1,10 @@
 """GPU parity of the W4A8 per-group kernel against the CPU oracle, called through the C ABI.
 
-With one CTA per channel tile (CB200_W4A8_SPLITS=1) the kernel performs the oracle's operations in the
-oracle's order and must be bit-exact.  With the K range split over a cluster (the default for shapes that
-would otherwise leave SMs idle) the fp32 partial sums are added in another order: outputs must then agree
-to 1 bf16 ulp, and nearly all of them exactly."""
-import os
-
+Default call: every CTA sums the scale groups in ascending order, exactly like the oracle: outputs must be
+bit-identical.  With the CB200_W4A8_SPLIT_K flag the K range is split over a CTA cluster and fp32 partial sums
+are added at the end: the sum is reassociated, so the bar is |got - want| <= max(1 bf16 ulp of want,
+2^-20 x sa[m] x sum_g |acc_g| x sw[g,n]) -- one ulp wherever the terms do not cancel, the fp32 reassociation
+bound where they do -- and at most 1 % of the outputs may differ at all."""
 import numpy as np
 import pytest
 
@@ -29,36 +28,43 @@ def _ordered(bits):
     return np.where(b & 0x8000, -(b & 0x7FFF), b)
 
 
-def _check(got, want, exact):
+def _abs_terms(a, w, sw, sa, gs):
+    """sa[m] * sum_g |acc_g[m,n]| * sw[g,n] in float64: the scale of the terms an output is summed from."""
+    m, k = a.shape
+    n = w.shape[1]
+    total = np.zeros((m, n), np.float64)
+    for g in range(k // gs):
+        acc = a[:, g * gs:(g + 1) * gs].astype(np.int64) @ w[g * gs:(g + 1) * gs].astype(np.int64)
+        total += np.abs(acc) * sw[g].astype(np.float64)
+    return total * sa.astype(np.float64)[:, None]
+
+
+def _check(got, want, exact, terms=None):
     if exact:
         assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} outputs differ"
         return
     dist = np.abs(_ordered(got) - _ordered(want))
-    assert dist.max() <= 1, f"max distance {dist.max()} bf16 ulp"   # tolerance: 1 bf16 ulp
-    assert (dist != 0).mean() <= 0.01, f"{(dist != 0).mean():.4f} of the outputs are off by one ulp"
+    assert (dist != 0).mean() <= 0.01, f"{(dist != 0).mean():.4f} of the outputs differ"
+    bad = dist > 1
+    if bad.any():
+        diff = np.abs(O.bf16_to_float(got).astype(np.float64) - O.bf16_to_float(want).astype(np.float64))
+        assert terms is not None
+        over = bad & (diff > terms * 2.0 ** -20)
+        assert not over.any(), f"{over.sum()} outputs beyond both bounds (max {dist[over].max()} bf16 ulp)"
 
 
-@pytest.fixture(params=["split", "single"])
+@pytest.fixture(params=["default", "split_k"])
 def exact(request):
-    """Runs a test twice: with the default K split (1-ulp tolerance) and with one CTA per tile (bit-exact)."""
-    old = os.environ.get("CB200_W4A8_SPLITS")
-    if request.param == "single":
-        os.environ["CB200_W4A8_SPLITS"] = "1"
-    else:
-        os.environ.pop("CB200_W4A8_SPLITS", None)
-    yield request.param == "single"
-    if old is None:
-        os.environ.pop("CB200_W4A8_SPLITS", None)
-    else:
-        os.environ["CB200_W4A8_SPLITS"] = old
+    """Runs a test twice: default call (bit-exact) and with the split-K flag (reassociation bound)."""
+    return request.param == "default"
 
 
-def _run(cuda, a, packed, sw, sa, m, n, k, gs):
+def _run(cuda, a, packed, sw, sa, m, n, k, gs, split_k=False):
     import torch
     from catlass_b200 import capi
     dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()  # noqa: E731
     d = torch.full((m, n), -3.0, dtype=torch.bfloat16, device=cuda)
-    capi.w4a8_matmul(dev(a), dev(packed), dev(sw), dev(sa), d, m, n, k, gs)
+    capi.w4a8_matmul(dev(a), dev(packed), dev(sw), dev(sa), d, m, n, k, gs, split_k=split_k)
     st, code = capi.device_status()
     assert st == 0, f"device status {st} code {code:#x}"
     return d.view(torch.int16).cpu().numpy().view(np.uint16)
@@ -66,13 +72,13 @@ def _run(cuda, a, packed, sw, sa, m, n, k, gs):
 
 @pytest.mark.parametrize("m,n,k,gs", [
     (128, 512, 1024, 128), (16, 256, 256, 128), (77, 200, 384, 128), (64, 128, 2048, 256),
-    (130, 136, 512, 128), (1, 128, 128, 128), (128, 4096, 2048, 128), (128, 256, 1024, 1024), (300, 384, 1280, 256), (33, 1000, 4096, 128), (40, 192, 1536, 512), (16, 64, 384, 128), (24, 128, 768, 384),
+    (130, 136, 512, 128), (1, 128, 128, 128), (257, 392, 8192, 1024), (130, 136, 2048, 256), (257, 64, 256, 128), (128, 4096, 2048, 128), (128, 256, 1024, 1024), (300, 384, 1280, 256), (33, 1000, 4096, 128), (40, 192, 1536, 512), (16, 64, 384, 128), (24, 128, 768, 384),
 ])
 def test_w4a8_per_group_matches_oracle(cuda, exact, m, n, k, gs):
     a, w, packed, sw, sa = _problem(m, n, k, gs, seed=m + n + k)
-    got = _run(cuda, a, packed, sw, sa, m, n, k, gs)
+    got = _run(cuda, a, packed, sw, sa, m, n, k, gs, split_k=not exact)
     want = O.bf16_bits(O.w4a8_per_group(a, packed, sw, sa, m, n, k, gs))
-    _check(got, want, exact)
+    _check(got, want, exact, None if exact else _abs_terms(a, w, sw, sa, gs))
 
 
 def test_w4a8_extreme_values(cuda, exact):
@@ -84,8 +90,9 @@ def test_w4a8_extreme_values(cuda, exact):
     sw = np.ones((k // gs, n), np.float32)
     sa = np.ones(m, np.float32)
     packed = O.pack_int4_along_k(w)
-    got = _run(cuda, a, packed, sw, sa, m, n, k, gs)
-    _check(got, O.bf16_bits(O.w4a8_per_group(a, packed, sw, sa, m, n, k, gs)), exact)
+    got = _run(cuda, a, packed, sw, sa, m, n, k, gs, split_k=not exact)
+    _check(got, O.bf16_bits(O.w4a8_per_group(a, packed, sw, sa, m, n, k, gs)), exact,
+           None if exact else _abs_terms(a, w, sw, sa, gs))
 
 
 def test_w4a8_per_tensor_mode_matches_reference_formula(cuda):
@@ -102,11 +109,11 @@ def test_w4a8_full_config_sampled_columns(cuda, exact):
     including both edges of several 128-column tiles."""
     m, n, k, gs = 128, 8192, 8192, 128
     a, w, packed, sw, sa = _problem(m, n, k, gs, seed=7)
-    got = _run(cuda, a, packed, sw, sa, m, n, k, gs)
+    got = _run(cuda, a, packed, sw, sa, m, n, k, gs, split_k=not exact)
     rng = np.random.default_rng(1)
     cols = np.unique(np.concatenate([[0, 127, 128, 255, 4095, 4096, 8191], rng.integers(0, n, 185)]))
     want = O.bf16_bits(O.w4a8_per_group(a, packed[cols], np.ascontiguousarray(sw[:, cols]), sa, m, len(cols), k, gs))
-    _check(got[:, cols], want, exact)
+    _check(got[:, cols], want, exact, None if exact else _abs_terms(a, w[:, cols], sw[:, cols], sa, gs))
 
 
 def test_w4a8_invalid_arguments(cuda):
