@@ -158,7 +158,7 @@ CB200_API int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_
  * Summation order: by default the groups are summed in ascending order, exactly as written above (D is
  * bit-exact against that definition).  With CB200_W4A8_SPLIT_K in `flags`, shapes with few 128-channel tiles
  * split the groups over the 2 or 4 CTAs of a cluster and add the fp32 partial sums at the end: faster (M=128,
- * N=K=8192: 25 us instead of the default's time), but an output whose partial sums nearly cancel can then differ
+ * N=K=8192: 25 us instead of 33 us), but an output whose partial sums nearly cancel can then differ
  * from the definition by more than one bf16 ulp of its small value; the absolute difference stays below
  * 2^-20 x the sum of the absolute group terms.
  */
