@@ -16,8 +16,8 @@
 // 16), so a thread of the epilogue owns ONE channel: the group's weight scale is a scalar in a register.
 // Every CTA has to read the whole token matrix once per pass over K, from L2; with 128 channels per CTA that
 // is 2 token bytes per packed weight byte (64 channels per CTA would double it and made the token stream the
-// limit).  To fill the machine when N/128 tiles are fewer than the SMs, the K range (whole scale groups) is
-// split over the 1, 2 or 4 CTAs of a cluster; each keeps fp32 partial sums y and at the end every CTA reduces
+// limit).  To fill the machine when N/128 tiles are fewer than the SMs, the K range (whole scale groups) can be
+// split over the 2 or 4 CTAs of a cluster; each keeps fp32 partial sums y and at the end every CTA reduces
 // and stores one slice of the token columns, the partials travelling through distributed shared memory.
 // With a split the fp32 sums are added in a different order than the sequential definition above: results are
 // then no longer bit-identical, and an output whose partial sums nearly cancel can differ by many bf16 ulps of
@@ -27,7 +27,7 @@
 //
 // Warp roles (16 warps):
 //   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 12 in flight: they come from HBM) and token
-//               tiles (128 x 128 B, 4 in flight: they come from L2), one thread and one ring each, two
+//               tiles (mt x 128 B, 4 in flight: they come from L2), one thread and one ring each, two
 //               consecutive K blocks per load (3-D boxes)
 //   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x mt x 32); one-block scale groups alternate between them
 //               (issuing an MMA costs its thread ~70 ns), longer groups are all issued by warp 1.  A group
@@ -37,7 +37,7 @@
 //               fix-up needed), written in the 128B-swizzled K-major operand layout, then handed to the MMA
 //               through a proxy fence + mbarrier.  The factor 16 is removed again, exactly, when the epilogue
 //               turns the accumulator into fp32.
-//   warps 6-13  epilogue (two warps per TMEM lane quarter, 64 token columns each): per group tcgen05.ld in
+//   warps 6-13  epilogue (two warps per TMEM lane quarter, 64 or 32 token columns each): per group tcgen05.ld in
 //               16-column pieces (the next piece is in flight while the current one is processed), int->float,
 //               packed fma with the group's scale into the running sums y held in registers; after the last
 //               group: reduction over the cluster, * sa[m], bf16 stores
