@@ -7,12 +7,21 @@ Default workload: the MoE grouped slice-M W8A8 matmul (64 experts, K=7168, N=409
 Zipf(1.1) expert loads), expert/row-sharded over the N ranks with no collective on the data path.
 One step = one pass over all routed rows.  Prints ONE JSON line on rank 0.
 
-Other workloads (single GPU): prefill (4096^3), decode_a (16x14336x4096), decode_b (16x4096x14336).
+The line's `value` is timed over exactly K steps.  Next to it the line carries
+  sustained   the same launch repeated for >= 2 s (power-capped clocks), with the clock samples of that region
+  secondary   (1 GPU only) the other workloads of the metric - decode_a, decode_b, prefill, w4a8, mxfp8, mxfp4 -
+              each replayed from a CUDA graph for >= 1.5 s so that its clock record holds >= 10 samples
+  verify      the shard outputs of all ranks assembled with one all-gather and sampled rows of every expert,
+              including the rows on both sides of every shard and tile boundary, compared with the CPU oracle
+  e2e         the host-buffer entry point: inputs from pinned host memory, output back to it, every step
+
+Other workloads can be run alone (single GPU): prefill, decode_a, decode_b, w4a8, mxfp8, mxfp4, moe_small.
 
 `--impl reference` times the reference's own CPU golden (compiled from the reference tree into
 oracle/_ref, else the oracle's plain-C restatement) on the host cores, on a bounded row sample per step.
 """
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -26,14 +35,16 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MOE = dict(experts=64, k=7168, n=4096, tokens=16384, top_k=8, zipf_s=1.1, seed=20240)
-# same law, 1/8 of the experts and rows: small enough for multi-pass ncu captures, still larger than L2
+# same law, 1/8 of the experts and rows: small enough for multi-pass profiler captures, still larger than L2
 MOE_SMALL = dict(experts=8, k=7168, n=4096, tokens=2048, top_k=8, zipf_s=1.1, seed=20240)
 DENSE = {
     "prefill": (4096, 4096, 4096),
     "decode_a": (16, 14336, 4096),
     "decode_b": (16, 4096, 14336),
 }
+SECONDARY = ["decode_a", "decode_b", "prefill", "w4a8", "mxfp8", "mxfp4"]
 INT8_PER_BF16 = 2.0  # kind::i8 issues at twice the bf16 rate on the same tensor cores
+L2_BYTES = 126e6
 
 
 def measured_peaks():
@@ -54,46 +65,90 @@ def zipf_group_sizes(total_rows, groups, seed, s):
     return rng.multinomial(total_rows, p).astype(np.int64)
 
 
+def moe_workload_string(cfg):
+    return (f"moe_grouped_slice_m_w8a8: {cfg['experts']} experts, K={cfg['k']}, N={cfg['n']}, {cfg['tokens']} tokens x "
+            f"top-{cfg['top_k']} = {cfg['tokens'] * cfg['top_k']} rows, Zipf({cfg['zipf_s']}) expert loads, "
+            "B row-major [G,K,N], bf16 out")
+
+
+def moe_config(cfg, placement, world):
+    """The `config` object of the MoE line; both arms (ours, reference) print exactly this."""
+    from catlass_b200 import sharding
+    rows_total = cfg["tokens"] * cfg["top_k"]
+    sizes = zipf_group_sizes(rows_total, cfg["experts"], cfg["seed"], cfg["zipf_s"])
+    loads = [s.rows for s in sharding.plan(sizes, world, mode=placement)]
+    return {
+        "workload": moe_workload_string(cfg),
+        "placement": placement, "rows_per_rank": loads,
+        "l2": f"inputs exceed L2 ({(rows_total * (cfg['k'] + 2 * cfg['n']) + cfg['experts'] * cfg['k'] * cfg['n']) / 1e9:.2f} GB per pass)",
+        "weights": "resident in HBM across steps",
+    }
+
+
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """Polls nvidia-smi for one GPU's clocks and throttle reasons for as long as the process runs; every timed
+    region asks for the samples that fell inside its own wall-clock window."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, gpu_index):
+    def __init__(self, gpu_index, interval_ms=20):
+        self.samples = []  # (unix time, sm MHz, max MHz, watts, [reasons])
+        self.lock = threading.Lock()
         self.proc = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", str(interval_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
 
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
+    def _read(self):
+        for line in self.proc.stdout:
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 7:
+            if len(f) < 8:
                 continue
             try:
-                sm.append(float(f[0]))
-                mx.append(float(f[1]))
+                t = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                row = (t, float(f[1]), float(f[2]), float(f[3]) if f[3].replace(".", "", 1).isdigit() else None,
+                       [n for n, v in zip(self.NAMES, f[4:8]) if v.lower().startswith("active")])
             except ValueError:
                 continue
-            for name, v in zip(names, f[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+            with self.lock:
+                self.samples.append(row)
+
+    def wait_first_sample(self, timeout=10.0):
+        t0 = time.time()
+        while self.proc is not None and time.time() - t0 < timeout:
+            with self.lock:
+                if self.samples:
+                    return
+            time.sleep(0.02)
+
+    def window(self, t0, t1):
+        """Summary of the samples taken between two time.time() stamps."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
+        with self.lock:
+            rows = [r for r in self.samples if t0 <= r[0] <= t1]
+        sm = [r[1] for r in rows]
+        reasons = sorted({x for r in rows for x in r[4]})
+        watts = [r[3] for r in rows if r[3] is not None]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_mhz_min": min(sm) if sm else None,
+                "sm_max_mhz": max(r[2] for r in rows) if rows else None, "power_w_max": max(watts) if watts else None,
+                "samples": len(rows), "reasons": reasons}
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
 
 
 def dist_setup(n_gpus):
@@ -132,7 +187,8 @@ def max_over_ranks(value, world):
 
 def time_steps(fn, steps, warmup, world):
     """W warm-up steps, then exactly K steps between CUDA events on the launching stream.
-    Returns (max over ranks of the elapsed ms, this rank's elapsed ms, library launches in the timed region)."""
+    Returns (max over ranks of the elapsed ms, this rank's elapsed ms, library launches in the timed region,
+    (wall-clock start, end) of the timed region)."""
     import torch
     from catlass_b200 import capi
     for _ in range(warmup):
@@ -141,15 +197,90 @@ def time_steps(fn, steps, warmup, world):
     launches0 = capi.launch_count()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
     start.record()
     for _ in range(steps):
         fn()
     stop.record()
     torch.cuda.synchronize()
+    t1 = time.time()
     ms = start.elapsed_time(stop)
     launches = capi.launch_count() - launches0
     barrier(world)
-    return max_over_ranks(ms, world), ms, launches
+    return max_over_ranks(ms, world), ms, launches, (t0, t1)
+
+
+def check_device_status():
+    from catlass_b200 import capi
+    st, code = capi.device_status()
+    if st != 0:
+        raise SystemExit(f"device status {st} code {code:#x}")
+
+
+def graph_region(launch, variants, min_seconds, sampler):
+    """Times `launch(i)` (i cycling over `variants` buffer sets) replayed from a CUDA graph: first a short burst
+    region, then back-to-back replays for at least `min_seconds` with the clock samples of that region.
+    Kernels of ten microseconds cannot be timed through a Python launch loop (the host is slower than the GPU);
+    a graph of a few hundred launches keeps the GPU fed.  Returns a dict with ms per launch for both regions."""
+    import torch
+    from catlass_b200 import capi
+    for i in range(max(3, variants)):
+        launch(i)
+    torch.cuda.synchronize()
+    # size the graph to roughly 5 ms of GPU time
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(variants):
+        launch(i)
+    e1.record()
+    torch.cuda.synchronize()
+    rough_ms = max(e0.elapsed_time(e1) / variants, 1e-3)
+    per_graph = int(min(400, max(variants, 5.0 / rough_ms)))
+    per_graph = (per_graph + variants - 1) // variants * variants
+    graph = torch.cuda.CUDAGraph()
+    launches0 = capi.launch_count()
+    try:
+        with torch.cuda.graph(graph):
+            for i in range(per_graph):
+                launch(i % variants)
+        use_graph = True
+    except Exception as exc:  # capture refused: fall back to a plain loop and say so
+        use_graph = False
+        graph_error = str(exc).splitlines()[0][:120]
+        torch.cuda.synchronize()
+    launches_per_graph = capi.launch_count() - launches0 if use_graph else None
+
+    def replay():
+        if use_graph:
+            graph.replay()
+        else:
+            for i in range(per_graph):
+                launch(i % variants)
+
+    replay()
+    torch.cuda.synchronize()
+    time.sleep(0.3)  # let the clocks return to idle: the next region starts from burst clocks
+    e0.record()
+    replay()
+    e1.record()
+    torch.cuda.synchronize()
+    burst_ms = e0.elapsed_time(e1) / per_graph
+    replays = max(2, int(np.ceil(min_seconds * 1e3 / (burst_ms * per_graph) * 1.15)))
+    t0 = time.time()
+    e0.record()
+    for _ in range(replays):
+        replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    sustained_ms = e0.elapsed_time(e1) / (per_graph * replays)
+    out = {"ms": sustained_ms, "burst_ms": burst_ms, "launches_timed": per_graph * replays,
+           "kernels_per_step": (launches_per_graph // per_graph) if use_graph else None,
+           "region_s": (e0.elapsed_time(e1)) / 1e3, "clocks": sampler.window(t0, t1) if sampler else None,
+           "cuda_graph": use_graph}
+    if not use_graph:
+        out["cuda_graph_error"] = graph_error
+    return out
 
 
 # ------------------------------------------------------------------------------------------ CPU baseline
@@ -194,37 +325,153 @@ def cpu_reference_rate(n, k, seconds_target, b_row_major=True):
     return ops / secs / 1e12, cores, kind, sample, secs
 
 
-# ------------------------------------------------------------------------------------------ workloads
+# ------------------------------------------------------------------------------------------ MoE workload
 
 def build_moe_rank(rank, world, mode, cfg):
-    """Device buffers of this rank's shard of the MoE workload."""
+    """ONE global seeded problem (the same on every rank), cut by sharding.plan; returns this rank's device
+    buffers, and what rank 0 needs to check the assembled output."""
     import torch
     from catlass_b200 import sharding
     rows_total = cfg["tokens"] * cfg["top_k"]
     sizes = zipf_group_sizes(rows_total, cfg["experts"], cfg["seed"], cfg["zipf_s"])
     shards = sharding.plan(sizes, world, mode=mode)
     mine = shards[rank]
+    n, k, experts = cfg["n"], cfg["k"], cfg["experts"]
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(cfg["seed"])
+    a_all = torch.randint(-127, 128, (rows_total, k), dtype=torch.int8, device=dev, generator=gen)
+    b_all = torch.randint(-127, 128, (experts, k, n), dtype=torch.int8, device=dev, generator=gen)
+    scale_all = torch.empty((experts, n), device=dev).uniform_(1e-3, 1e-2, generator=gen)
+    pt_all = torch.empty(rows_total, device=dev).uniform_(1e-3, 1e-2, generator=gen)
+
     groups = mine.local_groups()
     gl = np.cumsum([r for _, r in groups]).astype(np.int64)
     m = int(gl[-1]) if len(gl) else 0
-    n, k = cfg["n"], cfg["k"]
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(cfg["seed"] + 1000 * rank)
-    dev = torch.device("cuda")
-    a = torch.randint(-127, 128, (max(m, 1), k), dtype=torch.int8, device=dev, generator=gen)
-    b = torch.randint(-127, 128, (max(len(groups), 1), k, n), dtype=torch.int8, device=dev, generator=gen)
-    scale = torch.empty((max(len(groups), 1), n), device=dev).uniform_(1e-3, 1e-2, generator=gen)
-    pt = torch.empty(max(m, 1), device=dev).uniform_(1e-3, 1e-2, generator=gen)
+    # this rank's rows of the global problem, in its local order (pieces sorted by expert, row)
+    ranges = sharding.global_row_ranges(sizes, mine)
+    row_index = np.concatenate([np.arange(b, b + r) for b, r in ranges]) if ranges else np.zeros(0, np.int64)
+    if world == 1:
+        a, b, scale, pt = a_all, b_all, scale_all, pt_all   # one shard: the global buffers are the rank's own
+    else:
+        idx = torch.from_numpy(row_index).to(dev)
+        a = a_all.index_select(0, idx) if m else a_all[:1].clone()
+        pt = pt_all.index_select(0, idx) if m else pt_all[:1].clone()
+        eidx = torch.tensor([e for e, _ in groups] or [0], device=dev)
+        b = b_all.index_select(0, eidx)
+        scale = scale_all.index_select(0, eidx)
     d = torch.empty((max(m, 1), n), dtype=torch.bfloat16, device=dev)
     gl_dev = torch.from_numpy(gl if len(gl) else np.zeros(1, np.int64)).to(dev)
-    loads = [s.rows for s in shards]
+
+    check = None
+    if rank == 0:
+        check = sample_for_check(sizes, shards, a_all, b_all, scale_all, pt_all, n, cfg["seed"])
+    if world > 1:
+        del a_all, b_all, scale_all, pt_all
+        torch.cuda.empty_cache()
     return dict(a=a, b=b, scale=scale, pt=pt, d=d, gl=gl_dev, m=m, n=n, k=k, groups=len(groups),
-                rows_total=rows_total, loads=loads, sizes=sizes)
+                rows_total=rows_total, loads=[s.rows for s in shards], sizes=sizes, shards=shards,
+                row_index=row_index, check=check)
 
 
-def run_moe(args, rank, world, local):
+def sample_for_check(sizes, shards, a_all, b_all, scale_all, pt_all, n, seed):
+    """Rows and columns of the global problem that the oracle recomputes: per expert its first, last and one random
+    row, the rows on both sides of every shard boundary, of its first 256-row tile boundary and of the start of
+    its last (partial) row tile; a fixed spread of columns including tile edges."""
     import torch
-    from catlass_b200 import capi
+    rng = np.random.default_rng(seed + 1)
+    starts = np.concatenate([[0], np.cumsum(sizes)[:-1]])
+    rows_of = {}
+    for e, size in enumerate(sizes):
+        size = int(size)
+        if size == 0:
+            continue
+        local = {0, size - 1, int(rng.integers(0, size))}
+        if size > 256:
+            local |= {255, 256}
+        tail = (size - 1) // 256 * 256
+        local |= {tail, max(tail - 1, 0), min(tail + 31, size - 1), min(tail + 32, size - 1)}
+        rows_of[e] = local
+    for sh in shards:
+        for p in sh.pieces:
+            if p.row_begin > 0:
+                rows_of[p.expert] |= {p.row_begin - 1, p.row_begin}
+    cols = sorted(set([0, 1, 127, 128, 255, 256, 257, n - 257, n - 256, n - 1]) |
+                  set(int(c) for c in rng.integers(0, n, 118)))
+    cols_t = torch.tensor(cols, device=a_all.device)
+    items = []
+    for e, local in rows_of.items():
+        loc = np.array(sorted(local))
+        g_rows = torch.from_numpy(loc + starts[e]).to(a_all.device)
+        items.append(dict(expert=e, global_rows=(loc + starts[e]),
+                          a=a_all.index_select(0, g_rows).cpu().numpy(),
+                          b=b_all[e].index_select(1, cols_t).contiguous().cpu().numpy(),
+                          scale=scale_all[e].index_select(0, cols_t).cpu().numpy(),
+                          pt=pt_all.index_select(0, g_rows).cpu().numpy()))
+    return dict(cols=cols, items=items)
+
+
+def verify_moe(w, rank, world):
+    """Assembles the ranks' outputs with ONE all-gather (padded to the largest shard) and compares the sampled
+    rows with the CPU oracle on rank 0.  Outside every timed region."""
+    import torch
+    n = w["n"]
+    if world > 1:
+        import torch.distributed as dist
+        max_rows = max(max(w["loads"]), 1)
+        padded = torch.zeros((max_rows, n), dtype=torch.bfloat16, device="cuda")
+        if w["m"]:
+            padded[:w["m"]].copy_(w["d"][:w["m"]])
+        gathered = torch.empty((world, max_rows, n), dtype=torch.bfloat16, device="cuda")
+        dist.all_gather_into_tensor(gathered, padded)
+    else:
+        gathered = w["d"][None]
+    if rank != 0:
+        return None
+    from catlass_b200 import sharding
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as O
+    # where every global row sits: (rank, local row)
+    where_rank = np.empty(w["rows_total"], np.int32)
+    where_row = np.empty(w["rows_total"], np.int64)
+    for sh in w["shards"]:
+        local = 0
+        for begin, rows in sharding.global_row_ranges(w["sizes"], sh):
+            where_rank[begin:begin + rows] = sh.rank
+            where_row[begin:begin + rows] = np.arange(local, local + rows)
+            local += rows
+    cols = w["check"]["cols"]
+    cols_t = torch.tensor(cols, device="cuda")
+    checked = bad = rows_checked = 0
+    results = [None] * len(w["check"]["items"])
+
+    def work(i, it):
+        want = O.quant_matmul(it["a"], it["b"], it["scale"], it["pt"], len(it["global_rows"]), len(cols), w["k"],
+                              O.ROW_MAJOR, O.ROW_MAJOR)
+        results[i] = O.bf16_bits(want)
+
+    threads = [threading.Thread(target=work, args=(i, it)) for i, it in enumerate(w["check"]["items"])]
+    for chunk in range(0, len(threads), 16):
+        for t in threads[chunk:chunk + 16]:
+            t.start()
+        for t in threads[chunk:chunk + 16]:
+            t.join()
+    for it, want_bits in zip(w["check"]["items"], results):
+        g_rows = it["global_rows"]
+        r = torch.from_numpy(where_rank[g_rows].astype(np.int64)).cuda()
+        lr = torch.from_numpy(where_row[g_rows]).cuda()
+        got = gathered[r, lr].index_select(1, cols_t).view(torch.int16).cpu().numpy().view(np.uint16)
+        bad += int((got != want_bits).sum())
+        checked += got.size
+        rows_checked += len(g_rows)
+    return {"rows_checked": rows_checked, "outputs_checked": checked, "mismatches": bad,
+            "columns_per_row": len(cols), "assembled_with": "one NCCL all_gather" if world > 1 else "single shard",
+            "oracle": "CPU oracle (pinned to the reference golden), bf16 bits compared"}
+
+
+def run_moe(args, rank, world, local, sampler):
+    import torch
+    from catlass_b200 import capi, kernel_facts, sharding
     cfg = MOE_SMALL if args.workload == "moe_small" else MOE
     w = build_moe_rank(rank, world, args.placement, cfg)
     m, n, k, g = w["m"], w["n"], w["k"], w["groups"]
@@ -234,12 +481,10 @@ def run_moe(args, rank, world, local):
             capi.grouped_quant_matmul(w["a"], w["b"], w["gl"], w["scale"], w["pt"], w["d"], m, n, k, g,
                                       layout_b=capi.ROW_MAJOR)
 
-    sampler = ClockSampler(local) if rank == 0 else None
-    ms, ms_local, launches_timed = time_steps(step, args.steps, args.warmup, world)
-    clocks = sampler.stop() if sampler else None
-    st, code = capi.device_status()
-    if st != 0:
-        raise SystemExit(f"device status {st} code {code:#x}")
+    ms, ms_local, launches_timed, win = time_steps(step, args.steps, args.warmup, world)
+    clocks = sampler.window(*win) if sampler else None
+    check_device_status()
+    verify = verify_moe(w, rank, world)
 
     total_ops = 2.0 * w["rows_total"] * n * k
     ms_step = ms / args.steps
@@ -248,11 +493,27 @@ def run_moe(args, rank, world, local):
     rank_ops = 2.0 * m * n * k
     peaks = measured_peaks()
     peak_tops = peaks["bf16_tflops"] * INT8_PER_BF16
-
     # one step is one launch of the grouped kernel on each rank: this rank's average launch duration over
     # the timed region is its elapsed time / steps
     kernel_ms = ms_local / args.steps
     achieved = rank_ops / (kernel_ms * 1e-3) / 1e12 if m > 0 else 0.0
+
+    # sustained: the same launch for >= 2 s; the 1 kW power cap then holds the SM clock well below its maximum
+    time.sleep(0.2)
+    sus_steps = max(args.steps, int(np.ceil(args.sustained_seconds * 1e3 / max(ms_step, 1e-3))))
+    sus_ms, sus_local, _, sus_win = time_steps(step, sus_steps, 0, world)
+    sus_clocks = sampler.window(*sus_win) if sampler else None
+    sus_tops = total_ops / (sus_ms / sus_steps * 1e-3) / 1e12
+    sus_achieved = rank_ops / (sus_local / sus_steps * 1e-3) / 1e12 if m > 0 else 0.0
+    sustained_peak = peaks["bf16_tflops_sustained"] * INT8_PER_BF16
+
+    # tile accounting of this rank's launch: issued MMA work over the work the rows need
+    tile_m = 256
+    local_sizes = [r for _, r in w["shards"][rank].local_groups()]
+    full = sum(s // tile_m for s in local_sizes)
+    tails = [s % tile_m for s in local_sizes if s % tile_m]
+    tail_rows_issued = sum((t + 31) // 32 * 32 for t in tails) if capi_has_narrow_tails() else len(tails) * tile_m
+    issued_over_needed = (full * tile_m + tail_rows_issued) / max(m, 1)
 
     # ---- end to end: host buffers in, host buffer out, through the same C-ABI call
     a_h = torch.empty_like(w["a"], device="cpu").pin_memory()
@@ -262,9 +523,6 @@ def run_moe(args, rank, world, local):
     gl_h = torch.empty_like(w["gl"], device="cpu").pin_memory()
     gl_h.copy_(w["gl"])
     d_h = torch.empty_like(w["d"], device="cpu").pin_memory()
-
-    # the library's host-buffer entry: rows are cut into chunks, copy-in / compute / copy-out overlap on
-    # separate streams, the device staging buffers live in the workspace
     ws = None
     if m > 0:
         ws = torch.empty(capi.grouped_quant_matmul_host_workspace_size(m, n, k, g, args.e2e_chunks),
@@ -280,29 +538,31 @@ def run_moe(args, rank, world, local):
     e2e_tops = total_ops / (e2e_ms * 1e-3) / 1e12
     h2d = a_h.numel() * a_h.element_size() + pt_h.numel() * 4 + gl_h.numel() * 8
     d2h = d_h.numel() * d_h.element_size()
+    check_device_status()
 
     result = {
         "metric": "w8a8_grouped_gemm_tops", "value": tops, "unit": "TOPS", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {
-            "workload": f"moe_grouped_slice_m_w8a8: {cfg['experts']} experts, K={k}, N={n}, {cfg['tokens']} tokens x "
-                        f"top-{cfg['top_k']} = {w['rows_total']} rows, Zipf({cfg['zipf_s']}) expert loads, "
-                        "B row-major [G,K,N], bf16 out",
-            "placement": args.placement, "rows_per_rank": w["loads"],
-            "l2": f"inputs exceed L2 ({(w['rows_total'] * (k + 2 * n) + cfg['experts'] * k * n) / 1e9:.2f} GB per pass)",
-            "weights": "resident in HBM across steps",
-        },
+        "config": moe_config(cfg, args.placement, world),
         "roofline": {
             "bound": "tensor", "achieved": achieved, "peak": peak_tops, "unit": "TFLOP/s",
             "frac": achieved / peak_tops if peak_tops else None,
-            # DRAM bytes per launch: ncu capture of the 1/8-size `moe_small` case (540.2 MB, see profiles/),
-            # scaled by the rows this launch processes (traffic is proportional to rows and experts)
-            "traffic": 540.2e6 * m / 16384.0 if cfg is MOE else None,
+            # DRAM bytes per launch: profiler capture of the 1/8-size case scaled by the rows of this launch
+            "traffic": kernel_facts.traffic("w8a8_pair_kernel/moe_small", m / 16384.0) if cfg is MOE else None,
             "kernel": "w8a8_pair_kernel<row-major B>: 256x256 tiles on CTA pairs (rank 0 launch)", "kernel_ms": kernel_ms,
             "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s); "
                            "int8 ops = 2*rows*N*K; nominal dense int8 is 4500",
             "frac_of_nominal_int8": achieved / 4500.0,
+            "regime": f"burst: {args.steps} launches, {ms:.0f} ms",
+            "issued_over_needed_mma_rows": issued_over_needed,
+        },
+        "sustained": {
+            "value": sus_tops, "unit": "TOPS", "steps": sus_steps, "ms_per_step": sus_ms / sus_steps,
+            "region_s": sus_ms / 1e3, "achieved_rank0": sus_achieved,
+            "frac_of_2x_sustained_bf16": sus_achieved / sustained_peak if sustained_peak else None,
+            "frac_of_nominal_int8": sus_achieved / 4500.0, "clocks": sus_clocks,
+            "ms_x_sm_mhz": (sus_ms / sus_steps) * sus_clocks["sm_mhz"] if sus_clocks and sus_clocks.get("sm_mhz") else None,
         },
         "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "ms_per_step": e2e_ms, "steps": e2e_steps,
@@ -311,18 +571,25 @@ def run_moe(args, rank, world, local):
                         "whose copy-in, compute and copy-out overlap; expert weights stay resident"},
         "gpu_launches": int(launches_timed),
         "clocks": clocks,
+        "verify": verify,
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        v, cores, kind, sample, secs = cpu_reference_rate(n, k, args.cpu_seconds)
-        result["cpu_baseline"] = {"value": v, "unit": "TOPS", "cores": cores, "kind": kind, "sample": sample,
-                                  "seconds": secs}
-    return result
+    if clocks and clocks.get("sm_mhz"):
+        result["ms_x_sm_mhz"] = ms_step * clocks["sm_mhz"]
+    del a_h, d_h, ws
+    return result, w
 
 
-def run_dense(args, rank, world, local):
-    import torch
+def capi_has_narrow_tails():
     from catlass_b200 import capi
-    m, n, k = DENSE[args.workload]
+    return bool(getattr(capi, "NARROW_GROUP_TAILS", False))
+
+
+# ------------------------------------------------------------------------------------------ other workloads
+
+def run_dense(name, sampler, seconds):
+    import torch
+    from catlass_b200 import capi, kernel_facts
+    m, n, k = DENSE[name]
     dev = torch.device("cuda")
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234)
@@ -334,123 +601,94 @@ def run_dense(args, rank, world, local):
     decode = m <= 128
     # decode shapes are HBM-bound: rotate over enough copies of the weights that a pass never finds its
     # copy in L2 (copies x bytes(B) > 2 x L2), instead of flushing with writes that would leave dirty lines
-    copies = 1
-    if decode:
-        copies = int(np.ceil(2 * 126e6 / (n * k))) + 1
+    copies = int(np.ceil(2 * L2_BYTES / (n * k))) + 1 if decode else 1
     bs = [b] + [b.clone() for _ in range(copies - 1)]
-    it = [0]
 
-    def step():
-        capi.quant_matmul(a, bs[it[0] % copies], scale, pt, d, m, n, k, layout_b=capi.COLUMN_MAJOR)
-        it[0] += 1
+    def launch(i):
+        # B is a fixed weight reused across calls (parameters): declared static, so the few-token kernel may
+        # stream it while the previous launch drains
+        capi.quant_matmul(a, bs[i % copies], scale, pt, d, m, n, k, layout_b=capi.COLUMN_MAJOR, static_weights=True)
 
-    for _ in range(max(args.warmup, copies)):
-        step()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    launches0 = capi.launch_count()
-    # keep the GPU busy while the host enqueues the K timed launches: otherwise the events would time the
-    # host's launch path (tens of microseconds in Python) instead of kernels that last ten
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda._sleep(int(2.0e6 * args.steps) + 10_000_000)
-    s0.record()
-    for _ in range(args.steps):
-        step()
-    s1.record()
-    torch.cuda.synchronize()
-    times = [s0.elapsed_time(s1) / args.steps]
-    launches = capi.launch_count() - launches0
-    clocks = sampler.stop()
-    st, code = capi.device_status()
-    if st != 0:
-        raise SystemExit(f"device status {st} code {code:#x}")
-    ms = float(np.mean(times))
+    r = graph_region(launch, copies, seconds, sampler)
+    check_device_status()
     ops = 2.0 * m * n * k
     nbytes = m * k + k * n + 4 * (m + n) + 2 * m * n
     peaks = measured_peaks()
+    ms = r["ms"]
     if decode:
-        achieved, peak, unit, bound = nbytes / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
-        metric, value, vunit = "w8a8_decode_gemm_hbm_gbs", achieved, "GB/s"
+        value, unit, peak, bound = nbytes / (ms * 1e-3) / 1e9, "GB/s", peaks["hbm_gbs"], "hbm"
+        burst = nbytes / (r["burst_ms"] * 1e-3) / 1e9
+        metric = "w8a8_decode_gemm_hbm_gbs"
+        traffic = kernel_facts.traffic("w8a8_smallm_kernel/decode_a") if name == "decode_a" else None
     else:
-        achieved, peak, unit, bound = ops / (ms * 1e-3) / 1e12, peaks["bf16_tflops"] * INT8_PER_BF16, "TFLOP/s", "tensor"
-        metric, value, vunit = "w8a8_dense_gemm_tops", achieved, "TOPS"
+        value, unit, peak, bound = ops / (ms * 1e-3) / 1e12, "TOPS", peaks["bf16_tflops_sustained"] * INT8_PER_BF16, "tensor"
+        burst = ops / (r["burst_ms"] * 1e-3) / 1e12
+        metric = "w8a8_dense_gemm_tops"
+        traffic = None
     return {
-        "metric": metric, "value": value, "unit": vunit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
-        "data": "synthetic",
-        "config": {"workload": f"{args.workload}: W8A8 dequant GEMM M={m} N={n} K={k}, column-major B, bf16 out",
+        "name": name, "metric": metric, "value": value, "unit": unit, "ms_per_step": ms,
+        "burst_value": burst, "burst_ms_per_step": r["burst_ms"],
+        "regime": f"sustained: {r['launches_timed']} launches back to back, {r['region_s']:.2f} s",
+        "config": {"workload": f"{name}: W8A8 dequant GEMM M={m} N={n} K={k}, column-major B (static weights), bf16 out",
                    "l2": (f"weights rotate over {copies} copies ({copies * n * k / 1e6:.0f} MB > 2 x L2): every pass reads HBM"
-                          if decode else "inputs fit L2; steady state")},
-        "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                     "traffic": None, "peak_source": peaks["source"], "algorithmic_bytes": nbytes, "ops": ops,
-                     "frac_of_8TBs": achieved / 8000.0 if decode else None},
-        "gpu_launches": int(launches), "clocks": clocks,
+                          if decode else "operands (50 MB) stay in L2: steady state of a reused weight")},
+        "roofline": {"bound": bound, "achieved": value, "peak": peak, "unit": "GB/s" if decode else "TFLOP/s",
+                     "frac": value / peak, "traffic": traffic,
+                     "peak_source": (f"{peaks['source']} HBM copy rate" if decode else
+                                     f"2 x {peaks['source']} cuBLAS bf16 sustained ({peaks['bf16_tflops_sustained']} TF/s)"),
+                     "burst_frac": burst / (peak if decode else peaks["bf16_tflops"] * INT8_PER_BF16),
+                     "algorithmic_bytes": nbytes, "ops": ops,
+                     "frac_of_8TBs": value / 8000.0 if decode else None,
+                     "frac_of_nominal_int8": None if decode else value / 4500.0},
+        "gpu_launches": r["launches_timed"], "cuda_graph": r["cuda_graph"], "clocks": r["clocks"],
     }
 
 
-def run_w4a8(args, rank, world, local):
+def run_w4a8(sampler, seconds, split_k=False):
     """M=128, N=8192, K=8192, group 128: int4 weights packed along K, HBM-bound."""
     import torch
-    from catlass_b200 import capi
+    from catlass_b200 import capi, kernel_facts
     m, n, k, gs = 128, 8192, 8192, 128
     dev = torch.device("cuda")
     gen = torch.Generator(device="cuda")
     gen.manual_seed(4321)
     a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev, generator=gen)
-    copies = int(np.ceil(2 * 126e6 / (n * k // 2))) + 1
+    copies = int(np.ceil(2 * L2_BYTES / (n * k // 2))) + 1
     ws = [torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=gen) for _ in range(copies)]
     sw = torch.empty((k // gs, n), device=dev).uniform_(1e-3, 1e-2, generator=gen)
     sa = torch.empty(m, device=dev).uniform_(1e-3, 1e-2, generator=gen)
     d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-    it = [0]
 
-    split_k = bool(getattr(args, "w4a8_split_k", False))
+    def launch(i):
+        capi.w4a8_matmul(a, ws[i % copies], sw, sa, d, m, n, k, gs, split_k=split_k, static_weights=True)
 
-    def step():
-        capi.w4a8_matmul(a, ws[it[0] % copies], sw, sa, d, m, n, k, gs, split_k=split_k)
-        it[0] += 1
-
-    for _ in range(max(args.warmup, copies)):
-        step()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    launches0 = capi.launch_count()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda._sleep(int(2.0e6 * args.steps) + 10_000_000)
-    s0.record()
-    for _ in range(args.steps):
-        step()
-    s1.record()
-    torch.cuda.synchronize()
-    ms = s0.elapsed_time(s1) / args.steps
-    launches = capi.launch_count() - launches0
-    clocks = sampler.stop()
-    st, code = capi.device_status()
-    if st != 0:
-        raise SystemExit(f"device status {st} code {code:#x}")
+    r = graph_region(launch, copies, seconds, sampler)
+    check_device_status()
     nbytes = m * k + k * n // 2 + 4 * (k // gs) * n + 4 * m + 2 * m * n
     peaks = measured_peaks()
-    achieved = nbytes / (ms * 1e-3) / 1e9
+    value = nbytes / (r["ms"] * 1e-3) / 1e9
+    burst = nbytes / (r["burst_ms"] * 1e-3) / 1e9
     return {
-        "metric": "w4a8_gemm_hbm_gbs", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int4xint8->int32->f32", "data": "synthetic",
-        "config": {"workload": f"w4a8: M={m} N={n} K={k} group {gs}, int4 weights packed along K, bf16 out",
+        "name": "w4a8", "metric": "w4a8_gemm_hbm_gbs", "value": value, "unit": "GB/s", "ms_per_step": r["ms"],
+        "burst_value": burst, "burst_ms_per_step": r["burst_ms"],
+        "regime": f"sustained: {r['launches_timed']} launches back to back, {r['region_s']:.2f} s",
+        "config": {"workload": f"w4a8: M={m} N={n} K={k} group {gs}, int4 weights packed along K (static weights), bf16 out",
                    "summation": "K split over a CTA cluster, fp32 partial sums reassociated (CB200_W4A8_SPLIT_K)"
                                 if split_k else "sequential over the scale groups (default: bit-exact)",
                    "l2": f"weights rotate over {copies} copies: every pass reads HBM"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                     "algorithmic_bytes": nbytes, "frac_of_8TBs": achieved / 8000.0},
-        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": value / peaks["hbm_gbs"], "traffic": kernel_facts.traffic("w4a8_gemm_kernel/w4a8"),
+                     "peak_source": f"{peaks['source']} HBM copy rate", "burst_frac": burst / peaks["hbm_gbs"],
+                     "algorithmic_bytes": nbytes, "frac_of_8TBs": value / 8000.0},
+        "gpu_launches": r["launches_timed"], "cuda_graph": r["cuda_graph"], "clocks": r["clocks"],
     }
 
 
-def run_mx(args, rank, world, local):
+def run_mx(name, sampler, seconds):
     """MXFP8 / MXFP4 block-scaled matmul at M=N=K=8192 (random element codes and exponents: timing only)."""
     import torch
-    from catlass_b200 import capi
-    fp4 = args.workload == "mxfp4"
+    from catlass_b200 import capi, kernel_facts
+    fp4 = name == "mxfp4"
     m = n = k = 8192
     dev = torch.device("cuda")
     gen = torch.Generator(device="cuda")
@@ -469,32 +707,52 @@ def run_mx(args, rank, world, local):
     fmt = capi.MX_E2M1 if fp4 else capi.MX_E4M3
     ws = torch.empty(capi.mx_matmul_workspace_size(m, n, k, fmt), dtype=torch.uint8, device=dev)
 
-    def step():
+    def launch(i):
         capi.mx_matmul(a, b, sfa, sfb, d, m, n, k, fmt, ws)
 
-    sampler = ClockSampler(local)
-    ms, _, launches = time_steps(step, args.steps, args.warmup, 1)
-    clocks = sampler.stop()
-    st, code = capi.device_status()
-    if st != 0:
-        raise SystemExit(f"device status {st} code {code:#x}")
-    ms /= args.steps
+    r = graph_region(launch, 1, seconds, sampler)
+    check_device_status()
     flops = 2.0 * m * n * k
     peaks = measured_peaks()
     factor = 4.0 if fp4 else 2.0   # dense fp4 / fp8 rate relative to bf16 on the same tensor cores
-    achieved = flops / (ms * 1e-3) / 1e12
-    peak = peaks["bf16_tflops"] * factor
+    value = flops / (r["ms"] * 1e-3) / 1e12
+    burst = flops / (r["burst_ms"] * 1e-3) / 1e12
+    peak = peaks["bf16_tflops_sustained"] * factor
     return {
-        "metric": "mxfp4_gemm_tflops" if fp4 else "mxfp8_gemm_tflops", "value": achieved, "unit": "TFLOP/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "e2m1xe8m0" if fp4 else "e4m3xe8m0", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: M=N=K=8192 block-scaled (32-element E8M0 blocks), bf16 out, "
-                               "step = scale re-tiling (2 launches) + matmul",
+        "name": name, "metric": "mxfp4_gemm_tflops" if fp4 else "mxfp8_gemm_tflops", "value": value,
+        "unit": "TFLOP/s", "ms_per_step": r["ms"], "burst_value": burst, "burst_ms_per_step": r["burst_ms"],
+        "regime": f"sustained: {r['launches_timed']} steps back to back, {r['region_s']:.2f} s",
+        "config": {"workload": f"{name}: M=N=K=8192 block-scaled (32-element E8M0 blocks), bf16 out, "
+                               "step = scale re-tiling + matmul",
                    "l2": "operands exceed L2" if not fp4 else "operands 64 MB + 134 MB output per pass"},
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": f"{factor:.0f} x {peaks['source']} cuBLAS bf16 burst"},
-        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
+                     "traffic": kernel_facts.traffic("mx_gemm_kernel/" + name),
+                     "peak_source": f"{factor:.0f} x {peaks['source']} cuBLAS bf16 sustained "
+                                    f"({peaks['bf16_tflops_sustained']} TF/s)",
+                     "burst_frac": burst / (peaks["bf16_tflops"] * factor),
+                     "frac_of_nominal": value / (2250.0 * factor)},
+        "gpu_launches": r["launches_timed"], "kernels_per_step": r["kernels_per_step"], "cuda_graph": r["cuda_graph"],
+        "clocks": r["clocks"],
     }
+
+
+def run_secondary(name, sampler, seconds, args):
+    if name in DENSE:
+        return run_dense(name, sampler, seconds)
+    if name == "w4a8":
+        return run_w4a8(sampler, seconds, split_k=bool(args.w4a8_split_k))
+    return run_mx(name, sampler, seconds)
+
+
+def standalone_line(entry, args):
+    """A secondary workload run on its own (--workload NAME) as a full bench line."""
+    line = {"metric": entry["metric"], "value": entry["value"], "unit": entry["unit"], "n_gpus": 1,
+            "steps": entry["gpu_launches"], "warmup": args.warmup, "ms_per_step": entry["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"w4a8": "int4xint8->int32->f32", "mxfp8": "e4m3xe8m0", "mxfp4": "e2m1xe8m0"}.get(entry["name"], "int8"),
+            "data": "synthetic"}
+    line.update({k: v for k, v in entry.items() if k not in ("name", "metric", "value", "unit", "ms_per_step")})
+    return line
 
 
 def run_reference(args):
@@ -513,17 +771,14 @@ def run_reference(args):
             vals.append(v)
             secs_all.append(secs)
     value = float(np.mean(vals))
+    config = moe_config(cfg, args.placement, args.gpus)
+    config["measured_on"] = "the reference's CPU golden, a bounded row sample of this workload per step"
     return {
         "impl": "reference", "metric": "w8a8_grouped_gemm_tops", "value": value, "unit": "TOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": float(np.mean(secs_all)) * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {
-            "workload": f"moe_grouped_slice_m_w8a8: {cfg['experts']} experts, K={cfg['k']}, N={cfg['n']}, "
-                        f"{cfg['tokens']} tokens x top-{cfg['top_k']} = {cfg['tokens'] * cfg['top_k']} rows, "
-                        f"Zipf({cfg['zipf_s']}) expert loads, B row-major [G,K,N], bf16 out",
-            "measured_on": "the reference's CPU golden, a bounded row sample of this workload per step",
-        },
+        "config": config,
         "cpu_baseline": {"value": value, "unit": "TOPS", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -536,10 +791,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "moe_small", "w4a8", "mxfp8", "mxfp4"] + sorted(DENSE))
+    ap.add_argument("--workload", default="moe", choices=["moe", "moe_small"] + SECONDARY)
     ap.add_argument("--placement", default="split", choices=["split", "whole"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="moe workload: skip the other workloads of the metric")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0)
+    ap.add_argument("--secondary-seconds", type=float, default=1.6)
     ap.add_argument("--e2e-chunks", type=int, default=0, help="row chunks of the host-buffer pipeline (0 = default)")
     ap.add_argument("--w4a8-split-k", action="store_true",
                     help="w4a8 workload: time the opt-in split-K mode instead of the bit-exact default")
@@ -558,16 +816,29 @@ def main():
     from catlass_b200 import capi
     capi.load()  # fails loudly when the CUDA library is missing
     rank, world, local = dist_setup(args.gpus)
-    if args.workload in ("moe", "moe_small"):
-        res = run_moe(args, rank, world, local)
-    elif args.workload == "w4a8":
-        res = run_w4a8(args, rank, world, local)
-    elif args.workload in ("mxfp8", "mxfp4"):
-        res = run_mx(args, rank, world, local)
-    else:
-        if world != 1:
-            raise SystemExit("dense workloads are single-GPU")
-        res = run_dense(args, rank, world, local)
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.wait_first_sample()
+    try:
+        if args.workload in ("moe", "moe_small"):
+            res, w = run_moe(args, rank, world, local, sampler)
+            if rank == 0 and world == 1:
+                n, k = w["n"], w["k"]
+                del w
+                torch.cuda.empty_cache()
+                if args.workload == "moe" and not args.no_secondary:
+                    res["secondary"] = [run_secondary(name, sampler, args.secondary_seconds, args) for name in SECONDARY]
+                if not args.no_cpu_baseline:
+                    v, cores, kind, sample, secs = cpu_reference_rate(n, k, args.cpu_seconds)
+                    res["cpu_baseline"] = {"value": v, "unit": "TOPS", "cores": cores, "kind": kind, "sample": sample,
+                                           "seconds": secs}
+        else:
+            if world != 1:
+                raise SystemExit("this workload is single-GPU")
+            res = standalone_line(run_secondary(args.workload, sampler, max(args.secondary_seconds, 0.2), args), args)
+    finally:
+        if sampler:
+            sampler.stop()
     if rank == 0:
         print(json.dumps(res), flush=True)
     if world > 1:

@@ -11,6 +11,9 @@ from . import build as _build
 SUCCESS, INVALID, CUDA_ERROR, DEVICE_TIMEOUT, SCRATCH_TOO_SMALL = 0, 1, 2, 3, 4
 ROW_MAJOR, COLUMN_MAJOR, ZN = 0, 1, 2
 GROUP_LIST_INT64, GROUP_LIST_INT32 = 0, 1
+DTYPE_F32, DTYPE_BF16, DTYPE_F16, DTYPE_F32_IN_U64 = 0, 1, 2, 3
+FLAG_STATIC_WEIGHTS = 2
+QUANT_PER_TENSOR, QUANT_PER_CHANNEL = 0, 1
 
 _u32, _u64, _vp = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
 
@@ -19,7 +22,8 @@ class QuantMatmulArgs(ctypes.Structure):
     _fields_ = [
         ("m", _u32), ("n", _u32), ("k", _u32), ("layout_a", _u32), ("layout_b", _u32),
         ("a", _vp), ("b", _vp), ("scale", _vp), ("per_token_scale", _vp), ("d", _vp), ("acc", _vp),
-        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("flags", _u32),
+        ("scale_type", _u32), ("d_type", _u32),
     ]
 
 
@@ -28,7 +32,18 @@ class GroupedQuantMatmulArgs(ctypes.Structure):
         ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("layout_b", _u32),
         ("group_list_type", _u32),
         ("a", _vp), ("b", _vp), ("group_list", _vp), ("scale", _vp), ("per_token_scale", _vp), ("d", _vp),
-        ("acc", _vp), ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+        ("acc", _vp), ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("flags", _u32),
+        ("scale_type", _u32), ("d_type", _u32),
+    ]
+
+
+class GroupedFixpipeDequantArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("layout_b", _u32),
+        ("group_list_type", _u32), ("quant_mode", _u32), ("scale_per_tensor", ctypes.c_float),
+        ("a", _vp), ("b", _vp), ("group_list", _vp), ("per_channel_scale", _vp), ("d", _vp), ("acc", _vp),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("per_channel_scale_type", _u32),
+        ("d_type", _u32), ("flags", _u32),
     ]
 
 
@@ -44,7 +59,8 @@ class W4A8MatmulArgs(ctypes.Structure):
     _fields_ = [
         ("m", _u32), ("n", _u32), ("k", _u32), ("group_size", _u32),
         ("a", _vp), ("w_packed", _vp), ("weight_scale", _vp), ("per_token_scale", _vp), ("d", _vp),
-        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("flags", _u32),
+        ("d_type", _u32), ("reserved", _u32),
     ]
 
 
@@ -78,6 +94,7 @@ def load():
     lib = ctypes.CDLL(path)
     for name, args_t in (("cb200_quant_matmul", QuantMatmulArgs),
                          ("cb200_grouped_quant_matmul_slice_m", GroupedQuantMatmulArgs),
+                         ("cb200_grouped_matmul_slice_m_fixpipe_dequant", GroupedFixpipeDequantArgs),
                          ("cb200_w4a8_matmul", W4A8MatmulArgs),
                          ("cb200_mx_matmul", MxMatmulArgs)):
         getattr(lib, name + "_can_implement").argtypes = [ctypes.POINTER(args_t)]
@@ -138,32 +155,50 @@ def _stream(stream):
 
 
 def quant_matmul(a, b, scale, per_token, d, m, n, k, layout_b=COLUMN_MAJOR, acc=None, stream=None,
-                 block_num=0, layout_a=ROW_MAJOR):
+                 block_num=0, layout_a=ROW_MAJOR, scale_type=DTYPE_F32, d_type=DTYPE_BF16, static_weights=False):
     """Enqueue the dense W8A8 dequant matmul. Arguments are torch CUDA tensors used as raw buffers."""
     args = QuantMatmulArgs(m=m, n=n, k=k, layout_a=layout_a, layout_b=layout_b, a=_p(a), b=_p(b),
                            scale=_p(scale), per_token_scale=_p(per_token), d=_p(d), acc=_p(acc),
-                           workspace=None, workspace_bytes=0, block_num=block_num, reserved=0)
+                           workspace=None, workspace_bytes=0, block_num=block_num,
+                           flags=FLAG_STATIC_WEIGHTS if static_weights else 0, scale_type=scale_type, d_type=d_type)
     _check("cb200_quant_matmul", load().cb200_quant_matmul(ctypes.byref(args), _stream(stream)))
 
 
 def grouped_quant_matmul(a, b, group_list, scale, per_token, d, m, n, k, group_count, layout_b=ROW_MAJOR,
-                         acc=None, stream=None, block_num=0, group_list_type=GROUP_LIST_INT64):
+                         acc=None, stream=None, block_num=0, group_list_type=GROUP_LIST_INT64,
+                         scale_type=DTYPE_F32, d_type=DTYPE_BF16):
     args = GroupedQuantMatmulArgs(m=m, n=n, k=k, group_count=group_count, layout_b=layout_b,
                                   group_list_type=group_list_type, a=_p(a), b=_p(b),
                                   group_list=_p(group_list), scale=_p(scale), per_token_scale=_p(per_token),
                                   d=_p(d), acc=_p(acc), workspace=None, workspace_bytes=0,
-                                  block_num=block_num, reserved=0)
+                                  block_num=block_num, flags=0, scale_type=scale_type, d_type=d_type)
     _check("cb200_grouped_quant_matmul_slice_m",
            load().cb200_grouped_quant_matmul_slice_m(ctypes.byref(args), _stream(stream)))
+
+
+def grouped_fixpipe_dequant(a, b, group_list, d, m, n, k, group_count, quant_mode, scale_per_tensor=1.0,
+                            per_channel_scale=None, per_channel_scale_type=DTYPE_F32, layout_b=ROW_MAJOR,
+                            d_type=DTYPE_F16, acc=None, stream=None, group_list_type=GROUP_LIST_INT64):
+    """Grouped slice-M W8A8 with per-tensor (quant_mode 0) or per-channel (1) dequant, no per-token factor."""
+    args = GroupedFixpipeDequantArgs(m=m, n=n, k=k, group_count=group_count, layout_b=layout_b,
+                                     group_list_type=group_list_type, quant_mode=quant_mode,
+                                     scale_per_tensor=scale_per_tensor, a=_p(a), b=_p(b), group_list=_p(group_list),
+                                     per_channel_scale=_p(per_channel_scale), d=_p(d), acc=_p(acc), workspace=None,
+                                     workspace_bytes=0, block_num=0, per_channel_scale_type=per_channel_scale_type,
+                                     d_type=d_type, flags=0)
+    _check("cb200_grouped_matmul_slice_m_fixpipe_dequant",
+           load().cb200_grouped_matmul_slice_m_fixpipe_dequant(ctypes.byref(args), _stream(stream)))
 
 
 W4A8_SPLIT_K = 1  # flags: split the K range over a CTA cluster (faster, fp32 sums reassociated)
 
 
-def w4a8_matmul(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, stream=None, split_k=False):
+def w4a8_matmul(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, stream=None, split_k=False,
+                static_weights=False, d_type=DTYPE_BF16):
+    flags = (W4A8_SPLIT_K if split_k else 0) | (FLAG_STATIC_WEIGHTS if static_weights else 0)
     args = W4A8MatmulArgs(m=m, n=n, k=k, group_size=group_size, a=_p(a), w_packed=_p(w_packed),
                           weight_scale=_p(weight_scale), per_token_scale=_p(per_token), d=_p(d), workspace=None,
-                          workspace_bytes=0, block_num=0, reserved=W4A8_SPLIT_K if split_k else 0)
+                          workspace_bytes=0, block_num=0, flags=flags, d_type=d_type, reserved=0)
     _check("cb200_w4a8_matmul", load().cb200_w4a8_matmul(ctypes.byref(args), _stream(stream)))
 
 

@@ -19,28 +19,100 @@ using namespace cb200::host;
 
 namespace {
 
+// Tuning hooks for sweeps.  They exist only in builds made with -DCB200_DEVELOPER_KNOBS (never the shipped
+// library): there `dev_knob` reads an environment variable, here it is the constant default, so nothing in the
+// environment can change what the library does.
+#ifdef CB200_DEVELOPER_KNOBS
+inline long dev_knob(const char* name, long dflt)
+{
+    const char* e = getenv(name);
+    return e == nullptr ? dflt : atol(e);
+}
+#else
+constexpr long dev_knob(const char*, long dflt)
+{
+    return dflt;
+}
+#endif
+
+// One-time per-device set-up of a launcher (function attributes, occupancy queries), safe from several host
+// threads: the flag is published after the set-up ran, under the mutex.
+struct PerDeviceOnce {
+    std::mutex mu;
+    std::atomic<bool> done[kMaxDevices];
+    PerDeviceOnce()
+    {
+        for (auto& d : done) {
+            d.store(false, std::memory_order_relaxed);
+        }
+    }
+    template <class F>
+    int run(int dev, F&& f)
+    {
+        if (done[dev].load(std::memory_order_acquire)) {
+            return CB200_SUCCESS;
+        }
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[dev].load(std::memory_order_relaxed)) {
+            const int rc = f();
+            if (rc != CB200_SUCCESS) {
+                return rc;
+            }
+            done[dev].store(true, std::memory_order_release);
+        }
+        return CB200_SUCCESS;
+    }
+};
+
+int current_device(int* dev)
+{
+    CB200_CUDA_TRY(cudaGetDevice(dev));
+    return (*dev < 0 || *dev >= kMaxDevices) ? CB200_INVALID : CB200_SUCCESS;
+}
+
 struct W8A8Problem {
     uint32_t m, n, k;
     uint32_t group_count;  // 0 = dense
     uint32_t group_list_type;
+    uint32_t layout_a;
     uint32_t layout_b;
     const void* a;
     const void* b;
     const void* group_list;
-    const float* scale;
-    const float* per_token;
+    const void* scale;      // null in scalar mode
+    const void* per_token;  // null when the operator has no per-token factor
     void* d;
     int32_t* acc;
     uint32_t block_num;
+    uint32_t scale_type = CB200_DTYPE_F32;
+    uint32_t d_type = CB200_DTYPE_BF16;
+    uint32_t scale_stride = 0;   // elements between the channel-scale vectors of two groups
+    bool has_per_token = true;
+    bool scalar_mode = false;
+    float scalar_scale = 0.0f;
+    bool static_weights = false;
 };
 
-int check_w8a8(const W8A8Problem& q, uint32_t layout_a)
+uint32_t scale_elem_bytes(uint32_t type)
 {
-    if (q.a == nullptr || q.b == nullptr || q.scale == nullptr || q.per_token == nullptr || q.d == nullptr) {
+    return type == CB200_DTYPE_F32 ? 4u : (type == CB200_DTYPE_F32_IN_U64 ? 8u : 2u);
+}
+
+int check_w8a8(const W8A8Problem& q)
+{
+    if (q.scale_type > CB200_DTYPE_F32_IN_U64 || (q.d_type != 0 && q.d_type != CB200_DTYPE_BF16 &&
+                                                  q.d_type != CB200_DTYPE_F16)) {
+        return CB200_INVALID;
+    }
+    if (q.a == nullptr || q.b == nullptr || (!q.scalar_mode && q.scale == nullptr) ||
+        (q.has_per_token && q.per_token == nullptr) || q.d == nullptr) {
         return (q.m == 0 || q.n == 0) ? CB200_SUCCESS : CB200_INVALID;
     }
-    if (layout_a != CB200_ROW_MAJOR) {
+    if (q.layout_a != CB200_ROW_MAJOR && q.layout_a != CB200_COLUMN_MAJOR) {
         return CB200_INVALID;
+    }
+    if (q.layout_a == CB200_COLUMN_MAJOR && q.group_count != 0) {
+        return CB200_INVALID;  // slice-M groups cut A by rows: the reference's grouped kernels take row-major A
     }
     if (q.layout_b != CB200_ROW_MAJOR && q.layout_b != CB200_COLUMN_MAJOR && q.layout_b != CB200_ZN) {
         return CB200_INVALID;
@@ -62,21 +134,51 @@ int check_w8a8(const W8A8Problem& q, uint32_t layout_a)
         return CB200_INVALID;
     }
     if (q.k != 0) {
-        if ((q.k & 15u) != 0) {
-            return CB200_INVALID;  // A rows (and column-major B columns) are k bytes apart
+        if (q.layout_a == CB200_ROW_MAJOR && (q.k & 15u) != 0) {
+            return CB200_INVALID;  // A rows are k bytes apart
+        }
+        if (q.layout_a == CB200_COLUMN_MAJOR && (q.m & 15u) != 0) {
+            return CB200_INVALID;  // A columns are m bytes apart
+        }
+        if (q.layout_b == CB200_COLUMN_MAJOR && (q.k & 15u) != 0) {
+            return CB200_INVALID;  // B columns are k bytes apart
         }
         if (q.layout_b == CB200_ROW_MAJOR && (q.n & 15u) != 0) {
             return CB200_INVALID;  // row-major B rows are n bytes apart
         }
     }
-    if ((reinterpret_cast<uintptr_t>(q.d) & 1u) != 0 || (reinterpret_cast<uintptr_t>(q.scale) & 3u) != 0 ||
-        (reinterpret_cast<uintptr_t>(q.per_token) & 3u) != 0) {
+    const uintptr_t scale_mask = scale_elem_bytes(q.scale_type) - 1u;
+    if ((reinterpret_cast<uintptr_t>(q.d) & 1u) != 0 || (reinterpret_cast<uintptr_t>(q.scale) & scale_mask) != 0 ||
+        (reinterpret_cast<uintptr_t>(q.per_token) & scale_mask) != 0) {
         return CB200_INVALID;
     }
     if ((q.n & 7u) == 0 && !aligned16(q.d)) {
-        return CB200_INVALID;  // vector stores of 8 bf16
+        return CB200_INVALID;  // vector stores of 8 outputs
     }
     return CB200_SUCCESS;
+}
+
+void fill_params(W8A8Params& p, const W8A8Problem& q, const DeviceState& dev)
+{
+    p.tma_store = 0;
+    p.m = q.m;
+    p.n = q.n;
+    p.k = q.k;
+    p.group_count = q.group_count;
+    p.group_list_is_i32 = q.group_list_type == CB200_GROUP_LIST_INT32 ? 1u : 0u;
+    p.num_k_blocks = (q.k + kBlockKBytes - 1) / kBlockKBytes;
+    p.group_list = q.group_list;
+    p.scale = q.scale;
+    p.per_token = q.has_per_token ? q.per_token : nullptr;
+    p.d = static_cast<uint16_t*>(q.d);
+    p.acc = q.acc;
+    p.status = dev.status;
+    p.scale_type = q.scale_type;
+    p.scale_stride = q.scale_stride;
+    p.scalar_mode = q.scalar_mode ? 1u : 0u;
+    p.scalar_scale = q.scalar_scale;
+    p.out_f16 = q.d_type == CB200_DTYPE_F16 ? 1u : 0u;
+    p.static_weights = q.static_weights ? 1u : 0u;
 }
 
 template <int BN, bool kBMn>
@@ -114,27 +216,21 @@ int launch_w8a8(const W8A8Problem& q, const DeviceState& dev, cudaStream_t strea
     }
 
     W8A8Params p;
-    p.tma_store = 0;
-    p.m = q.m;
-    p.n = q.n;
-    p.k = q.k;
-    p.group_count = q.group_count;
-    p.group_list_is_i32 = q.group_list_type == CB200_GROUP_LIST_INT32 ? 1u : 0u;
-    p.num_k_blocks = (q.k + kBlockKBytes - 1) / kBlockKBytes;
-    p.group_list = q.group_list;
-    p.scale = q.scale;
-    p.per_token = q.per_token;
-    p.d = static_cast<__nv_bfloat16*>(q.d);
-    p.acc = q.acc;
-    p.status = dev.status;
+    fill_params(p, q, dev);
 
     auto kernel = w8a8_gemm_kernel<BN, kBMn>;
-    static bool attr_set[kMaxDevices] = {};
+    static PerDeviceOnce once;
     int devid = 0;
-    CB200_CUDA_TRY(cudaGetDevice(&devid));
-    if (!attr_set[devid]) {
+    int rc_dev = current_device(&devid);
+    if (rc_dev != CB200_SUCCESS) {
+        return rc_dev;
+    }
+    rc_dev = once.run(devid, [&]() -> int {
         CB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotalBytes));
-        attr_set[devid] = true;
+        return CB200_SUCCESS;
+    });
+    if (rc_dev != CB200_SUCCESS) {
+        return rc_dev;
     }
     // upper bound of the tile count: every group may add one partial row tile
     const uint64_t n_tiles = (q.n + BN - 1) / BN;
@@ -156,7 +252,7 @@ int launch_w8a8(const W8A8Problem& q, const DeviceState& dev, cudaStream_t strea
 }
 
 // 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2): the default for problems with more than 128 columns.
-template <BLayout kB>
+template <BLayout kB, bool kAMn>
 int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t stream)
 {
     constexpr bool kBMn = kB == BLayout::kRowMajor;
@@ -165,10 +261,12 @@ int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t 
     CUtensorMap tmap_a, tmap_b;
     const uint32_t groups = q.group_count == 0 ? 1u : q.group_count;
     {
-        const uint64_t dims[2] = {q.k, q.m};
-        const uint64_t strides[1] = {q.k};
-        const uint32_t box[2] = {kBlockKBytes, kBlockM};
-        int rc = encode_tmap_u8(&tmap_a, q.a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        // row-major A: rows of k bytes; column-major A: k rows of m bytes (a tile is 128 bytes of M x 128 rows of K)
+        const uint64_t dims_k[2] = {q.k, q.m};
+        const uint64_t dims_m[2] = {q.m, q.k};
+        const uint64_t strides[1] = {kAMn ? q.m : q.k};
+        const uint32_t box[2] = {128, 128};
+        int rc = encode_tmap_u8(&tmap_a, q.a, 2, kAMn ? dims_m : dims_k, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != CB200_SUCCESS) {
             return rc;
         }
@@ -196,29 +294,12 @@ int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t 
         }
     }
     W8A8Params p;
-    p.tma_store = 0;
-    p.m = q.m;
-    p.n = q.n;
-    p.k = q.k;
-    p.group_count = q.group_count;
-    p.group_list_is_i32 = q.group_list_type == CB200_GROUP_LIST_INT32 ? 1u : 0u;
-    p.num_k_blocks = (q.k + kBlockKBytes - 1) / kBlockKBytes;
-    p.group_list = q.group_list;
-    p.scale = q.scale;
-    p.per_token = q.per_token;
-    p.d = static_cast<__nv_bfloat16*>(q.d);
-    p.acc = q.acc;
-    p.status = dev.status;
+    fill_params(p, q, dev);
     // D as a byte tensor [m][2n] for the epilogue's TMA stores (32 rows x 64 bytes per store): possible when the
     // row pitch is a multiple of 16 bytes; otherwise every row is stored by its thread
     CUtensorMap tmap_d;
     memset(&tmap_d, 0, sizeof(tmap_d));
-    p.tma_store = 0;
-    static const bool allow_tma_store = [] {
-        const char* e = getenv("CB200_W8A8_TMA_STORE");  // developer knob: 0 = per-thread stores only
-        return e == nullptr || atoi(e) != 0;
-    }();
-    if (allow_tma_store && (q.n & 7u) == 0 && aligned16(q.d)) {
+    if (dev_knob("CB200_W8A8_TMA_STORE", 1) != 0 && (q.n & 7u) == 0 && aligned16(q.d)) {
         const uint64_t dims[2] = {static_cast<uint64_t>(q.n) * 2u, q.m};
         const uint64_t strides[1] = {static_cast<uint64_t>(q.n) * 2u};
         const uint32_t box[2] = {64, 32};
@@ -229,13 +310,19 @@ int launch_w8a8_pair(const W8A8Problem& q, const DeviceState& dev, cudaStream_t 
         p.tma_store = 1;
     }
 
-    auto kernel = w8a8_pair_kernel<kB>;
-    static bool attr_set[kMaxDevices] = {};
+    auto kernel = w8a8_pair_kernel<kB, kAMn>;
+    static PerDeviceOnce once;
     int devid = 0;
-    CB200_CUDA_TRY(cudaGetDevice(&devid));
-    if (!attr_set[devid]) {
+    int rc = current_device(&devid);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    rc = once.run(devid, [&]() -> int {
         CB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotalBytes));
-        attr_set[devid] = true;
+        return CB200_SUCCESS;
+    });
+    if (rc != CB200_SUCCESS) {
+        return rc;
     }
     const uint64_t n_tiles = (q.n + kPairBN - 1) / kPairBN;
     const uint64_t max_tiles = (static_cast<uint64_t>((q.m + kPairTileM - 1) / kPairTileM) + groups) * n_tiles;
@@ -272,11 +359,14 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
     const uint32_t max_by_partials = 1u + (96u * 1024u) / (kSmallMTileN * p.mt * 4u);
     uint32_t splits = 1, tile_rows = kSmallMTileN;
     auto kernel = w8a8_smallm_kernel<kWMn>;
-    static bool attr_set[kMaxDevices] = {};
+    static PerDeviceOnce once;
     static int resident_ctas[kMaxDevices][4] = {};  // co-resident CTAs for cluster sizes 1, 2, 4, 8
     int devid = 0;
-    CB200_CUDA_TRY(cudaGetDevice(&devid));
-    if (!attr_set[devid]) {
+    int rc_dev = current_device(&devid);
+    if (rc_dev != CB200_SUCCESS) {
+        return rc_dev;
+    }
+    rc_dev = once.run(devid, [&]() -> int {
         CB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         // clusters must sit inside one GPC, so fewer CTAs than SMs may be resident at once: ask the runtime
         for (int i = 0; i < 4; ++i) {
@@ -298,7 +388,10 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
             }
             resident_ctas[devid][i] = clusters << i;
         }
-        attr_set[devid] = true;
+        return CB200_SUCCESS;
+    });
+    if (rc_dev != CB200_SUCCESS) {
+        return rc_dev;
     }
     {
         const double sm_all = static_cast<double>(dev.sm_count);
@@ -331,54 +424,43 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
     }
     p.tile_rows = tile_rows;
     // a ring stage holds 4 neighbouring K blocks: 512 contiguous bytes per weight row are requested together
-    uint32_t kbs = 4;
-    if (const char* e = getenv("CB200_SMALLM_KBS")) {
-        const uint32_t v = static_cast<uint32_t>(atoi(e));
-        if (v >= 1 && v <= 8) {
-            kbs = v;
-        }
-    }
-    // ring budget per CTA (developer knob CB200_SMALLM_RING_KB)
-    uint32_t ring_budget = 216u * 1024u;
-    if (const char* e = getenv("CB200_SMALLM_RING_KB")) {
-        const uint32_t v = static_cast<uint32_t>(atoi(e));
-        if (v >= 36 && v <= 216) {
-            ring_budget = v * 1024u;
-        }
-    }
+    uint32_t kbs = static_cast<uint32_t>(dev_knob("CB200_SMALLM_KBS", 4));
+    kbs = (kbs >= 1 && kbs <= 8) ? kbs : 4;
+    uint32_t ring_budget = static_cast<uint32_t>(dev_knob("CB200_SMALLM_RING_KB", 216));
+    ring_budget = (ring_budget >= 36 && ring_budget <= 216 ? ring_budget : 216u) * 1024u;
     while (kbs > 1 && 2 * smallm_stage_bytes(p.mt, kbs) > ring_budget) {
         kbs /= 2;  // wide token panels: keep at least two stages
     }
     p.kbs = kbs;
     const uint32_t stage_bytes = smallm_stage_bytes(p.mt, kbs);
     uint32_t stages = ring_budget / stage_bytes;
-    // developer knobs for tuning runs: CB200_SMALLM_SPLITS / CB200_SMALLM_STAGES override the heuristic
-    if (const char* e = getenv("CB200_SMALLM_SPLITS")) {
-        const uint32_t v = static_cast<uint32_t>(atoi(e));
+    {
+        const uint32_t v = static_cast<uint32_t>(dev_knob("CB200_SMALLM_SPLITS", 0));
         if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= max_by_partials && v <= p.num_k_blocks) {
             splits = v;
         }
-    }
-    if (const char* e = getenv("CB200_SMALLM_ROWS")) {
-        const uint32_t v = static_cast<uint32_t>(atoi(e));
-        if (!kWMn && v >= 8 && v <= 128 && v % 8 == 0) {
-            p.tile_rows = v;
+        const uint32_t r = static_cast<uint32_t>(dev_knob("CB200_SMALLM_ROWS", 0));
+        if (!kWMn && r >= 8 && r <= 128 && r % 8 == 0) {
+            p.tile_rows = r;
         }
-    }
-    if (const char* e = getenv("CB200_SMALLM_STAGES")) {
-        const uint32_t v = static_cast<uint32_t>(atoi(e));
-        if (v >= 2 && v * stage_bytes <= 216u * 1024u) {
-            stages = v;
+        const uint32_t st = static_cast<uint32_t>(dev_knob("CB200_SMALLM_STAGES", 0));
+        if (st >= 2 && st * stage_bytes <= 216u * 1024u) {
+            stages = st;
         }
     }
     p.splits = splits;
     stages = stages > static_cast<uint32_t>(kSmallMMaxStages) ? kSmallMMaxStages : (stages < 2 ? 2 : stages);
     p.stages = stages;
     p.scale = q.scale;
-    p.per_token = q.per_token;
-    p.d = static_cast<__nv_bfloat16*>(q.d);
+    p.per_token = q.has_per_token ? q.per_token : nullptr;
+    p.d = static_cast<uint16_t*>(q.d);
     p.acc = q.acc;
     p.status = dev.status;
+    p.scale_type = q.scale_type;
+    p.scalar_mode = q.scalar_mode ? 1u : 0u;
+    p.scalar_scale = q.scalar_scale;
+    p.out_f16 = q.d_type == CB200_DTYPE_F16 ? 1u : 0u;
+    p.static_weights = q.static_weights ? 1u : 0u;
 
     CUtensorMap tmap_w, tmap_x;
     {
@@ -412,24 +494,21 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
     attr[0].val.clusterDim.x = p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    // programmatic dependent launch: this kernel's set-up and first weight loads may overlap the tail of the
-    // kernel before it on the stream; it waits (griddepcontrol.wait) before it reads activations or writes D
+    // programmatic dependent launch: this kernel's set-up (and, for static weights, its first weight loads) may
+    // overlap the tail of the kernel before it on the stream; it waits (griddepcontrol.wait) before it reads
+    // anything else from global memory or writes D
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    static const bool use_pdl = [] {
-        const char* e = getenv("CB200_SMALLM_PDL");
-        return e == nullptr || atoi(e) != 0;
-    }();
-    cfg.numAttrs = use_pdl ? 2 : 1;
+    cfg.numAttrs = dev_knob("CB200_SMALLM_PDL", 1) != 0 ? 2 : 1;
     CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, tmap_w, tmap_x, p));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return CB200_SUCCESS;
 }
 
-int run_w8a8(const W8A8Problem& q, uint32_t layout_a, void* stream_v)
+int run_w8a8(const W8A8Problem& q, void* stream_v)
 {
-    int rc = check_w8a8(q, layout_a);
+    int rc = check_w8a8(q);
     if (rc != CB200_SUCCESS) {
         return rc;
     }
@@ -443,29 +522,31 @@ int run_w8a8(const W8A8Problem& q, uint32_t layout_a, void* stream_v)
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     if (q.k == 0) {
-        zero_rows_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(q.d), q.group_list,
+        zero_rows_kernel<<<dev->sm_count * 4, 256, 0, stream>>>(static_cast<uint16_t*>(q.d), q.group_list,
                                                                 q.group_list_type == CB200_GROUP_LIST_INT32,
                                                                 q.group_count, q.m, q.n);
         CB200_CUDA_TRY(cudaGetLastError());
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return CB200_SUCCESS;
     }
+    if (q.layout_a == CB200_COLUMN_MAJOR) {  // MN-major A tiles: the pair kernel, whatever the shape
+        switch (q.layout_b) {
+            case CB200_ZN: return launch_w8a8_pair<BLayout::kZN, true>(q, *dev, stream);
+            case CB200_ROW_MAJOR: return launch_w8a8_pair<BLayout::kRowMajor, true>(q, *dev, stream);
+            default: return launch_w8a8_pair<BLayout::kColumnMajor, true>(q, *dev, stream);
+        }
+    }
     if (q.layout_b == CB200_ZN) {
-        return launch_w8a8_pair<BLayout::kZN>(q, *dev, stream);  // fractal weights: always the pair kernel
+        return launch_w8a8_pair<BLayout::kZN, false>(q, *dev, stream);  // fractal weights: always the pair kernel
     }
     const bool b_mn = q.layout_b == CB200_ROW_MAJOR;
     if (q.group_count == 0 && q.m <= 128) {
         return b_mn ? launch_smallm<true>(q, *dev, stream) : launch_smallm<false>(q, *dev, stream);
     }
     if (q.n > 128) {
-        // CB200_W8A8_PAIR=0 selects the single-CTA 128 x 256 kernel (developer knob for comparisons)
-        static const bool use_pair = [] {
-            const char* e = getenv("CB200_W8A8_PAIR");
-            return e == nullptr || atoi(e) != 0;
-        }();
-        if (use_pair) {
-            return b_mn ? launch_w8a8_pair<BLayout::kRowMajor>(q, *dev, stream)
-                        : launch_w8a8_pair<BLayout::kColumnMajor>(q, *dev, stream);
+        if (dev_knob("CB200_W8A8_PAIR", 1) != 0) {  // 0: the single-CTA 128 x 256 kernel, for comparisons
+            return b_mn ? launch_w8a8_pair<BLayout::kRowMajor, false>(q, *dev, stream)
+                        : launch_w8a8_pair<BLayout::kColumnMajor, false>(q, *dev, stream);
         }
         return b_mn ? launch_w8a8<256, true>(q, *dev, stream) : launch_w8a8<256, false>(q, *dev, stream);
     }
@@ -492,6 +573,9 @@ int check_w4a8(const cb200_w4a8_matmul_args* a)
         return CB200_INVALID;
     }
     if (a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u) {
+        return CB200_INVALID;
+    }
+    if (a->d_type != 0 && a->d_type != CB200_DTYPE_BF16 && a->d_type != CB200_DTYPE_F16) {
         return CB200_INVALID;
     }
     if (!aligned16(a->a) || !aligned16(a->w_packed) || (reinterpret_cast<uintptr_t>(a->d) & 1u) != 0 ||
@@ -562,8 +646,8 @@ int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStre
     // stay in L2 while the band's columns go by
     p.band_rows = (32u << 20) / (128u * (row_bytes > 0 ? row_bytes : 1u));
     p.band_rows = p.band_rows < 4u ? 4u : (p.band_rows > 64u ? 64u : p.band_rows);
-    if (const char* e = getenv("CB200_MX_BAND")) {  // developer knob
-        const uint32_t v = static_cast<uint32_t>(atoi(e));
+    {
+        const uint32_t v = static_cast<uint32_t>(dev_knob("CB200_MX_BAND", 0));
         if (v >= 1 && v <= 4096) {
             p.band_rows = v;
         }
@@ -604,12 +688,18 @@ int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStre
         }
     }
     auto kernel = mx_gemm_kernel<kFp4>;
-    static bool attr_set[kMaxDevices] = {};
+    static PerDeviceOnce once;
     int devid = 0;
-    CB200_CUDA_TRY(cudaGetDevice(&devid));
-    if (!attr_set[devid]) {
+    int rc_dev = current_device(&devid);
+    if (rc_dev != CB200_SUCCESS) {
+        return rc_dev;
+    }
+    rc_dev = once.run(devid, [&]() -> int {
         CB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem::kTotalBytes));
-        attr_set[devid] = true;
+        return CB200_SUCCESS;
+    });
+    if (rc_dev != CB200_SUCCESS) {
+        return rc_dev;
     }
     const uint64_t tiles = static_cast<uint64_t>((args->m + kBlockM - 1) / kBlockM) * ((args->n + kMxBlockN - 1) / kMxBlockN);
     uint32_t grid = static_cast<uint32_t>(dev.sm_count);
@@ -697,15 +787,9 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     if (args->m > 64u && tiles_n * ((args->m + 63u) / 64u) <= static_cast<uint32_t>(dev->sm_count)) {
         p.tile_m = 64;
     }
-    // Opt-in (flags bit 0, or the developer knob CB200_W4A8_SPLITS=2|4): the K range split over the CTAs of a
-    // cluster, as many as still fit the SMs in one wave; fp32 partial sums are then added at the end.
-    uint32_t want_splits = (args->reserved & CB200_W4A8_SPLIT_K) ? static_cast<uint32_t>(kW4MaxSplits) : 1u;
-    if (const char* e = getenv("CB200_W4A8_SPLITS")) {
-        const uint32_t v = static_cast<uint32_t>(atoi(e));
-        if (v == 1 || v == 2 || v == 4) {
-            want_splits = v;
-        }
-    }
+    // Opt-in (flags bit 0): the K range split over the CTAs of a cluster, as many as still fit the SMs in one
+    // wave; fp32 partial sums are then added at the end.
+    const uint32_t want_splits = (args->flags & CB200_W4A8_SPLIT_K) ? static_cast<uint32_t>(kW4MaxSplits) : 1u;
     if (want_splits > 1) {
         const uint32_t tiles = tiles_n * ((args->m + kW4Tokens - 1) / kW4Tokens);
         while (p.splits < want_splits && tiles * p.splits * 2 <= static_cast<uint32_t>(dev->sm_count) &&
@@ -716,8 +800,8 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
             p.tile_m = kW4Tokens;
         }
     }
-    if (const char* e = getenv("CB200_W4A8_TILE_M")) {  // developer knob
-        const uint32_t v = static_cast<uint32_t>(atoi(e));
+    {
+        const uint32_t v = static_cast<uint32_t>(dev_knob("CB200_W4A8_TILE_M", 0));
         if ((v == 64 || v == 128) && p.splits == 1) {
             p.tile_m = v;
         }
@@ -725,8 +809,10 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     p.mt = args->m >= p.tile_m ? p.tile_m : ((args->m + 15u) & ~15u);
     p.sw = args->weight_scale;
     p.sa = args->per_token_scale;
-    p.d = static_cast<__nv_bfloat16*>(args->d);
+    p.d = static_cast<uint16_t*>(args->d);
     p.status = dev->status;
+    p.out_f16 = args->d_type == CB200_DTYPE_F16 ? 1u : 0u;
+    p.static_weights = (args->flags & CB200_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
     CUtensorMap tmap_w, tmap_x;
     {
         // packed weights as (64 bytes of a K block, channel, K block): a box is kW4Load consecutive blocks
@@ -748,15 +834,21 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
             return rc;
         }
     }
-    static bool attr_set[kMaxDevices] = {};
+    static PerDeviceOnce once;
     int devid = 0;
-    CB200_CUDA_TRY(cudaGetDevice(&devid));
-    if (!attr_set[devid]) {
+    rc = current_device(&devid);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    rc = once.run(devid, [&]() -> int {
         CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             W4A8Smem::kTotalBytes));
         CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             W4A8Smem::kTotalBytes));
-        attr_set[devid] = true;
+        return CB200_SUCCESS;
+    });
+    if (rc != CB200_SUCCESS) {
+        return rc;
     }
     const dim3 grid(tiles_n * p.splits, (args->m + p.tile_m - 1) / p.tile_m, 1);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -770,16 +862,13 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     attr[0].val.clusterDim.x = p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    // programmatic dependent launch: set-up and the first weight loads may overlap the tail of the kernel before
-    // this one on the stream; the kernel waits (griddepcontrol.wait) before it reads tokens or writes D
+    // programmatic dependent launch: set-up (and, for static weights, the first weight loads) may overlap the
+    // tail of the kernel before this one on the stream; the kernel waits (griddepcontrol.wait) before it reads
+    // anything else from global memory or writes D
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    static const bool use_pdl = [] {
-        const char* e = getenv("CB200_W4A8_PDL");
-        return e == nullptr || atoi(e) != 0;
-    }();
-    cfg.numAttrs = use_pdl ? 2 : 1;
+    cfg.numAttrs = dev_knob("CB200_W4A8_PDL", 1) != 0 ? 2 : 1;
     if (args->group_size == 128) {
         CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a8_gemm_kernel<true>, tmap_w, tmap_x, p));
     } else {
@@ -790,14 +879,105 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     return CB200_SUCCESS;
 }
 
+}  // extern "C"
+
+namespace {
+
+W8A8Problem dense_problem(const cb200_quant_matmul_args* args)
+{
+    W8A8Problem q{};
+    q.m = args->m;
+    q.n = args->n;
+    q.k = args->k;
+    q.group_count = 0;
+    q.group_list_type = CB200_GROUP_LIST_INT64;
+    q.layout_a = args->layout_a;
+    q.layout_b = args->layout_b;
+    q.a = args->a;
+    q.b = args->b;
+    q.group_list = nullptr;
+    q.scale = args->scale;
+    q.per_token = args->per_token_scale;
+    q.d = args->d;
+    q.acc = args->acc;
+    q.block_num = args->block_num;
+    q.scale_type = args->scale_type;
+    q.d_type = args->d_type;
+    q.scale_stride = 0;
+    q.static_weights = (args->flags & CB200_FLAG_STATIC_WEIGHTS) != 0;
+    return q;
+}
+
+W8A8Problem grouped_problem(const cb200_grouped_quant_matmul_args* args)
+{
+    W8A8Problem q{};
+    q.m = args->m;
+    q.n = args->n;
+    q.k = args->k;
+    q.group_count = args->group_count;
+    q.group_list_type = args->group_list_type;
+    q.layout_a = CB200_ROW_MAJOR;
+    q.layout_b = args->layout_b;
+    q.a = args->a;
+    q.b = args->b;
+    q.group_list = args->group_list;
+    q.scale = args->scale;
+    q.per_token = args->per_token_scale;
+    q.d = args->d;
+    q.acc = args->acc;
+    q.block_num = args->block_num;
+    q.scale_type = args->scale_type;
+    q.d_type = args->d_type;
+    q.scale_stride = args->n;
+    return q;
+}
+
+// Per-tensor / per-channel dequant: the grouped kernel with one scale vector (or one scalar) for all groups and no
+// per-token factor.  (x * 1.0f is exact, so the epilogue's second multiply changes nothing.)
+W8A8Problem fixpipe_problem(const cb200_grouped_fixpipe_dequant_args* args)
+{
+    W8A8Problem q{};
+    q.m = args->m;
+    q.n = args->n;
+    q.k = args->k;
+    q.group_count = args->group_count;
+    q.group_list_type = args->group_list_type;
+    q.layout_a = CB200_ROW_MAJOR;
+    q.layout_b = args->layout_b;
+    q.a = args->a;
+    q.b = args->b;
+    q.group_list = args->group_list;
+    q.scale = args->per_channel_scale;
+    q.per_token = nullptr;
+    q.has_per_token = false;
+    q.d = args->d;
+    q.acc = args->acc;
+    q.block_num = args->block_num;
+    q.scale_type = args->per_channel_scale_type;
+    q.d_type = args->d_type;
+    q.scale_stride = 0;
+    q.scalar_mode = args->quant_mode == CB200_QUANT_PER_TENSOR;
+    q.scalar_scale = args->scale_per_tensor;
+    return q;
+}
+
+bool fixpipe_args_ok(const cb200_grouped_fixpipe_dequant_args* args)
+{
+    return args != nullptr && args->group_count != 0 &&
+           (args->quant_mode == CB200_QUANT_PER_TENSOR || args->quant_mode == CB200_QUANT_PER_CHANNEL) &&
+           (args->per_channel_scale_type == CB200_DTYPE_F32 || args->per_channel_scale_type == CB200_DTYPE_F32_IN_U64);
+}
+
+}  // namespace
+
+extern "C" {
+
 int cb200_quant_matmul_can_implement(const cb200_quant_matmul_args* args)
 {
     if (args == nullptr) {
         return CB200_INVALID;
     }
-    W8A8Problem q{args->m, args->n, args->k, 0, CB200_GROUP_LIST_INT64, args->layout_b, args->a, args->b, nullptr,
-                  args->scale, args->per_token_scale, args->d, args->acc, args->block_num};
-    return check_w8a8(q, args->layout_a);
+    return check_w8a8(dense_problem(args));
 }
 
 uint64_t cb200_quant_matmul_workspace_size(const cb200_quant_matmul_args* args)
@@ -811,9 +991,7 @@ int cb200_quant_matmul(const cb200_quant_matmul_args* args, void* stream)
     if (args == nullptr) {
         return CB200_INVALID;
     }
-    W8A8Problem q{args->m, args->n, args->k, 0, CB200_GROUP_LIST_INT64, args->layout_b, args->a, args->b, nullptr,
-                  args->scale, args->per_token_scale, args->d, args->acc, args->block_num};
-    return run_w8a8(q, args->layout_a, stream);
+    return run_w8a8(dense_problem(args), stream);
 }
 
 int cb200_grouped_quant_matmul_slice_m_can_implement(const cb200_grouped_quant_matmul_args* args)
@@ -821,10 +999,7 @@ int cb200_grouped_quant_matmul_slice_m_can_implement(const cb200_grouped_quant_m
     if (args == nullptr || args->group_count == 0) {
         return CB200_INVALID;
     }
-    W8A8Problem q{args->m, args->n, args->k, args->group_count, args->group_list_type, args->layout_b, args->a,
-                  args->b, args->group_list, args->scale, args->per_token_scale, args->d, args->acc,
-                  args->block_num};
-    return check_w8a8(q, CB200_ROW_MAJOR);
+    return check_w8a8(grouped_problem(args));
 }
 
 uint64_t cb200_grouped_quant_matmul_slice_m_workspace_size(const cb200_grouped_quant_matmul_args* args)
@@ -838,10 +1013,29 @@ int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args* ar
     if (args == nullptr || args->group_count == 0) {
         return CB200_INVALID;
     }
-    W8A8Problem q{args->m, args->n, args->k, args->group_count, args->group_list_type, args->layout_b, args->a,
-                  args->b, args->group_list, args->scale, args->per_token_scale, args->d, args->acc,
-                  args->block_num};
-    return run_w8a8(q, CB200_ROW_MAJOR, stream);
+    return run_w8a8(grouped_problem(args), stream);
+}
+
+int cb200_grouped_matmul_slice_m_fixpipe_dequant_can_implement(const cb200_grouped_fixpipe_dequant_args* args)
+{
+    if (!fixpipe_args_ok(args)) {
+        return CB200_INVALID;
+    }
+    return check_w8a8(fixpipe_problem(args));
+}
+
+uint64_t cb200_grouped_matmul_slice_m_fixpipe_dequant_workspace_size(const cb200_grouped_fixpipe_dequant_args* args)
+{
+    (void)args;
+    return 0;
+}
+
+int cb200_grouped_matmul_slice_m_fixpipe_dequant(const cb200_grouped_fixpipe_dequant_args* args, void* stream)
+{
+    if (!fixpipe_args_ok(args)) {
+        return CB200_INVALID;
+    }
+    return run_w8a8(fixpipe_problem(args), stream);
 }
 
 }  // extern "C"
@@ -854,6 +1048,7 @@ constexpr uint32_t kHostDefaultChunks = 16;  // measured on the MoE workload: 4:
 constexpr uint32_t kHostMaxChunks = 64;
 
 struct HostPipe {
+    std::mutex mu;  // held for the whole of a host-buffer call: the streams, events and lists_host are shared
     bool ready = false;
     cudaStream_t in = nullptr, out = nullptr;
     cudaEvent_t start = nullptr, lists_copied = nullptr, all_out = nullptr;
@@ -890,15 +1085,17 @@ uint32_t host_chunks(const cb200_grouped_quant_matmul_host_args* a)
     return c > tiles ? (tiles == 0 ? 1u : tiles) : c;
 }
 
-int host_pipe(HostPipe** out, size_t lists_needed)
+// The pipe of the current device, created on first use.
+int host_pipe(HostPipe** out)
 {
     static HostPipe pipes[kMaxDevices];
     int dev = 0;
-    CB200_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices) {
-        return CB200_INVALID;
+    int rc = current_device(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
     }
     HostPipe& hp = pipes[dev];
+    std::lock_guard<std::mutex> lock(hp.mu);
     if (!hp.ready) {
         CB200_CUDA_TRY(cudaStreamCreateWithFlags(&hp.in, cudaStreamNonBlocking));
         CB200_CUDA_TRY(cudaStreamCreateWithFlags(&hp.out, cudaStreamNonBlocking));
@@ -911,16 +1108,23 @@ int host_pipe(HostPipe** out, size_t lists_needed)
         }
         hp.ready = true;
     }
-    if (hp.lists_capacity < lists_needed) {
-        if (hp.lists_host != nullptr) {
-            CB200_CUDA_TRY(cudaEventSynchronize(hp.lists_copied));
-            CB200_CUDA_TRY(cudaFreeHost(hp.lists_host));
-            hp.lists_host = nullptr;
-        }
-        CB200_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&hp.lists_host), lists_needed, cudaHostAllocDefault));
-        hp.lists_capacity = lists_needed;
-    }
     *out = &hp;
+    return CB200_SUCCESS;
+}
+
+// Grows the pinned staging buffer of the group lists; the caller holds the pipe's mutex.
+int host_pipe_lists(HostPipe* hp, size_t lists_needed)
+{
+    if (hp->lists_capacity < lists_needed) {
+        if (hp->lists_host != nullptr) {
+            CB200_CUDA_TRY(cudaEventSynchronize(hp->lists_copied));
+            CB200_CUDA_TRY(cudaFreeHost(hp->lists_host));
+            hp->lists_host = nullptr;
+            hp->lists_capacity = 0;
+        }
+        CB200_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&hp->lists_host), lists_needed, cudaHostAllocDefault));
+        hp->lists_capacity = lists_needed;
+    }
     return CB200_SUCCESS;
 }
 
@@ -955,20 +1159,42 @@ int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_matmul_hos
     uint8_t* ws = static_cast<uint8_t*>(args->workspace);
     int8_t* a_dev = reinterpret_cast<int8_t*>(ws + lay.a);
     float* pt_dev = reinterpret_cast<float*>(ws + lay.pt);
-    __nv_bfloat16* d_dev = reinterpret_cast<__nv_bfloat16*>(ws + lay.d);
+    uint16_t* d_dev = reinterpret_cast<uint16_t*>(ws + lay.d);
     int64_t* lists_dev = reinterpret_cast<int64_t*>(ws + lay.lists);
+    const uint32_t G = args->group_count;
+    // the chunk launches differ only in their row range
+    auto chunk_problem = [&](uint32_t rows, int64_t r0, uint32_t c) {
+        W8A8Problem q{};
+        q.m = rows;
+        q.n = args->n;
+        q.k = args->k;
+        q.group_count = G;
+        q.group_list_type = CB200_GROUP_LIST_INT64;
+        q.layout_a = CB200_ROW_MAJOR;
+        q.layout_b = args->layout_b;
+        q.a = a_dev + r0 * args->k;
+        q.b = args->b;
+        q.group_list = lists_dev + static_cast<size_t>(c) * G;
+        q.scale = args->scale;
+        q.per_token = pt_dev + r0;
+        q.d = d_dev + r0 * args->n;
+        q.acc = nullptr;
+        q.block_num = 0;
+        q.scale_stride = args->n;
+        return q;
+    };
     // validate once with the whole problem (alignment, layouts, sizes)
-    {
-        W8A8Problem q{args->m, args->n, args->k, args->group_count, CB200_GROUP_LIST_INT64, args->layout_b, a_dev,
-                      args->b, lists_dev, args->scale, pt_dev, d_dev, nullptr, 0};
-        int rc = check_w8a8(q, CB200_ROW_MAJOR);
-        if (rc != CB200_SUCCESS) {
-            return rc;
-        }
+    int rc = check_w8a8(chunk_problem(args->m, 0, 0));
+    if (rc != CB200_SUCCESS) {
+        return rc;
     }
     HostPipe* hp = nullptr;
-    const uint32_t G = args->group_count;
-    int rc = host_pipe(&hp, static_cast<size_t>(chunks) * G * 8u);
+    rc = host_pipe(&hp);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    std::lock_guard<std::mutex> pipe_lock(hp->mu);
+    rc = host_pipe_lists(hp, static_cast<size_t>(chunks) * G * 8u);
     if (rc != CB200_SUCCESS) {
         return rc;
     }
@@ -1011,10 +1237,7 @@ int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_matmul_hos
                                        cudaMemcpyHostToDevice, hp->in));
         CB200_CUDA_TRY(cudaEventRecord(hp->chunk_in[c], hp->in));
         CB200_CUDA_TRY(cudaStreamWaitEvent(stream, hp->chunk_in[c], 0));
-        W8A8Problem q{static_cast<uint32_t>(cr), args->n, args->k, G, CB200_GROUP_LIST_INT64, args->layout_b,
-                      a_dev + r0 * args->k, args->b, lists_dev + static_cast<size_t>(c) * G, args->scale,
-                      pt_dev + r0, d_dev + r0 * args->n, nullptr, 0};
-        rc = run_w8a8(q, CB200_ROW_MAJOR, stream);
+        rc = run_w8a8(chunk_problem(static_cast<uint32_t>(cr), r0, c), stream);
         if (rc != CB200_SUCCESS) {
             return rc;
         }

@@ -72,8 +72,10 @@ struct W4A8Params {
     uint32_t splits;            // cluster size along K: 1, 2 or 4
     const float* sw;            // [k / group_size][n]
     const float* sa;            // [m]
-    __nv_bfloat16* d;           // [m][n]
+    uint16_t* d;                // [m][n] bf16 or fp16 bit patterns
     unsigned* status;
+    uint32_t out_f16;
+    uint32_t static_weights;    // weights and their scales may be read before the stream dependency resolves
 };
 
 struct W4A8Smem {
@@ -159,15 +161,7 @@ __device__ __forceinline__ void accumulate16(unsigned long long (&y2)[32], const
 #pragma unroll
     for (int v = 0; v < 8; ++v) {
         if constexpr (kMagic) {
-#ifdef CB200_W4A8_SCALAR_MATH
-            float lo, hi;
-            unpack_pair(y2[kOff + v], lo, hi);
-            lo = __fmaf_rn(__fsub_rn(__uint_as_float(r[2 * v] + 0x49400000u), 786432.0f), s, lo);
-            hi = __fmaf_rn(__fsub_rn(__uint_as_float(r[2 * v + 1] + 0x49400000u), 786432.0f), s, hi);
-            y2[kOff + v] = pack_pair(lo, hi);
-#else
             scaled_accumulate_pair(y2[kOff + v], r[2 * v], r[2 * v + 1], s2);
-#endif
         } else {
             // the sums are multiples of 16 below 2^28: the conversion and the scaling by 1/16 are exact
             fma_pair(y2[kOff + v], __int2float_rn(static_cast<int32_t>(r[2 * v])) * 0.0625f,
@@ -264,6 +258,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // (Weights and tokens each have a producer thread of their own: the deep weight ring keeps running ahead
         // while the token thread waits for a tile slot.)
         if (lane == 0) {
+            if (!p.static_weights) {
+                grid_dependency_wait();  // plain stream order: the weights may come from the kernel before this one
+            }
             bool ok = true;
             const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
             for (uint32_t l = 0; ok && l < loads; ++l) {
@@ -283,10 +280,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         __syncwarp();
     } else if (warp == 15) {
         // ------------------------------------------------------- token producer
-        // Weights and their scales never depend on the kernel launched before this one on the stream; the
-        // tokens may.  Under programmatic dependent launch this thread therefore waits for that kernel before
-        // its first load, while the weight ring is already filling.  Everything that reads token-dependent data
-        // or writes the output happens after a token tile has landed.
+        // The tokens may depend on the kernel launched before this one on the stream: under programmatic
+        // dependent launch this thread waits for that kernel before its first load.  (When the caller declares
+        // the weights static, the weight ring is already filling meanwhile.)  Everything that reads
+        // token-dependent data or writes the output happens after a token tile has landed.
         if (lane == 0) {
             grid_dependency_wait();
             bool ok = true;
@@ -439,15 +436,18 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // held in registers, so that the latency never sits on the per-group critical path.
         const uint32_t scol = static_cast<uint32_t>(n0) + quad * 32 + lane;
         const float* sw_col = p.sw + static_cast<size_t>(g_begin) * p.n + (scol < p.n ? scol : 0);
-        auto load_scale = [&](uint32_t j) -> float {
+        if (!p.static_weights) {
+            grid_dependency_wait();  // the weight scales may come from the kernel before this one
+        }
+        auto load_sw = [&](uint32_t j) -> float {
             return j < my_groups ? __ldg(sw_col + static_cast<size_t>(j) * p.n) : 0.0f;
         };
-        float s_now = load_scale(0), s_next1 = load_scale(1), s_next2 = load_scale(2);
+        float s_now = load_sw(0), s_next1 = load_sw(1), s_next2 = load_sw(2);
         auto scale_of = [&](uint32_t j) -> float {
             const float s = s_now;
             s_now = s_next1;
             s_next1 = s_next2;
-            s_next2 = load_scale(j + 3);
+            s_next2 = load_sw(j + 3);
             return s;
         };
         auto acquire = [&](uint32_t pair) -> bool {
@@ -596,19 +596,18 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             }
             const float sa = __ldg(p.sa + mrow);
             const float y[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            __nv_bfloat16* drow = p.d + static_cast<size_t>(mrow) * p.n + ncol;
+            uint16_t* drow = p.d + static_cast<size_t>(mrow) * p.n + ncol;
+            const bool f16 = p.out_f16 != 0;
             if (vec_ok && ncol + 8 <= p.n) {
                 uint32_t packed[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const __nv_bfloat162 h =
-                        __floats2bfloat162_rn(__fmul_rn(y[2 * e], sa), __fmul_rn(y[2 * e + 1], sa));
-                    packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    packed[e] = pack_out2(__fmul_rn(y[2 * e], sa), __fmul_rn(y[2 * e + 1], sa), f16);
                 }
                 *reinterpret_cast<uint4*>(drow) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             } else {
                 for (uint32_t e = 0; e < 8 && ncol + e < p.n; ++e) {
-                    drow[e] = __float2bfloat16_rn(__fmul_rn(y[e], sa));
+                    drow[e] = pack_out1(__fmul_rn(y[e], sa), f16);
                 }
             }
         }

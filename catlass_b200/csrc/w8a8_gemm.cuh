@@ -19,6 +19,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "ptx.cuh"
 
@@ -38,6 +39,14 @@ enum class BLayout : int {
 constexpr int kGemmThreads = 192;
 constexpr int kEpilogueThreads = 128;
 
+// Element types of the scale vectors (converted to fp32 when loaded, which is what the goldens do with
+// static_cast<float>) and of D.
+constexpr uint32_t kTypeF32 = 0;
+constexpr uint32_t kTypeBf16 = 1;
+constexpr uint32_t kTypeF16 = 2;
+constexpr uint32_t kTypeF32InU64 = 3;  // fp32 bit pattern in the low half of a 64-bit word (the reference's
+                                       // fixpipe scale format, example 48)
+
 struct W8A8Params {
     uint32_t m;                // row capacity of A / D (dense: M)
     uint32_t n;
@@ -46,13 +55,76 @@ struct W8A8Params {
     uint32_t group_list_is_i32;
     uint32_t num_k_blocks;     // ceil(k / 128)
     const void* group_list;    // device: ascending prefix sums of rows
-    const float* scale;        // [max(group_count,1)][n]
-    const float* per_token;    // [m]
-    __nv_bfloat16* d;          // [m][n]
+    const void* scale;         // channel scales, scale_type elements; group g uses scale + g * scale_stride
+    const void* per_token;     // [m] scale_type elements, or null: no per-token factor
+    uint16_t* d;               // [m][n] bf16 or fp16 bit patterns
     int32_t* acc;              // optional raw accumulators [m][n]
     unsigned* status;          // device status word
     uint32_t tma_store;        // pair kernel: D has a tensor map, full 32-row slabs leave through TMA stores
+    uint32_t scale_type;       // kTypeF32 / kTypeBf16 / kTypeF16 / kTypeF32InU64
+    uint32_t scale_stride;     // elements between the scale vectors of two groups (0: one vector for all groups)
+    uint32_t scalar_mode;      // 1: every channel uses scalar_scale (per-tensor dequant), `scale` is not read
+    float scalar_scale;
+    uint32_t out_f16;          // D holds fp16 instead of bf16
+    uint32_t static_weights;   // weights and channel scales may be read before the stream dependency resolves
 };
+
+// One element of a scale vector as fp32.
+__device__ __forceinline__ float load_scale(const void* base, size_t i, uint32_t type)
+{
+    if (type == kTypeF32) {
+        return __ldg(static_cast<const float*>(base) + i);
+    }
+    if (type == kTypeF32InU64) {
+        return __ldg(static_cast<const float*>(base) + 2 * i);
+    }
+    const uint32_t v = __ldg(static_cast<const unsigned short*>(base) + i);
+    if (type == kTypeBf16) {
+        return __uint_as_float(v << 16);
+    }
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(v)));
+}
+
+// The dequant step of the goldens: (float(acc) * scale) * per_token, two separately rounded fp32 multiplies
+// (examples/common/golden/matmul.hpp:320-321); per_token = 1 where the operator has no per-token factor.
+__device__ __forceinline__ float dequant(uint32_t acc, float scale, float per_token)
+{
+    return __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(acc)), scale), per_token);
+}
+
+// Two / one fp32 values rounded to nearest even into bf16 or fp16 bit patterns.
+__device__ __forceinline__ uint32_t pack_out2(float x0, float x1, bool f16)
+{
+    if (f16) {
+        const __half2 h = __floats2half2_rn(x0, x1);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__device__ __forceinline__ uint16_t pack_out1(float x, bool f16)
+{
+    if (f16) {
+        return __half_as_ushort(__float2half_rn(x));
+    }
+    return __bfloat16_as_ushort(__float2bfloat16_rn(x));
+}
+
+// This warp's private copy of a tile's channel scales (columns n0 .. n0 + count), zero past column n.
+__device__ __forceinline__ void stage_tile_scales(float* sc, const W8A8Params& p, uint32_t group, uint32_t n0,
+                                                  uint32_t count, uint32_t lane)
+{
+    const size_t base = static_cast<size_t>(p.group_count == 0 ? 0 : group) * p.scale_stride;
+    for (uint32_t i = lane; i < count; i += 32) {
+        const uint32_t col = n0 + i;
+        float v = 0.0f;
+        if (col < p.n) {
+            v = p.scalar_mode ? p.scalar_scale : load_scale(p.scale, base + col, p.scale_type);
+        }
+        sc[i] = v;
+    }
+}
 
 template <int BN>
 struct W8A8Smem {
@@ -283,6 +355,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // ---------------------------------------------------------------- epilogue warps 2..5
         const uint32_t quad = warp & 3;             // the 32-lane quarter of TMEM this warp can read
         const bool vec_ok = (p.n & 7u) == 0;
+        const bool f16 = p.out_f16 != 0;
         TileScheduler sched{s_row_begin, s_row_end, s_tile_begin, n_tiles, 0};
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
@@ -291,12 +364,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             sched.get<BN>(idx, t);
             // channel scales of this tile -> this warp's private smem copy (no cross-warp barrier needed)
             float* sc = s_scale + (warp - 2) * BN;
-            const float* gscale = p.scale + static_cast<size_t>(p.group_count == 0 ? 0 : t.group) * p.n;
             __syncwarp();
-            for (uint32_t i = lane; i < BN; i += 32) {
-                const uint32_t col = t.n0 + i;
-                sc[i] = col < p.n ? __ldg(gscale + col) : 0.0f;
-            }
+            stage_tile_scales(sc, p, t.group, static_cast<uint32_t>(t.n0), BN, lane);
             __syncwarp();
 
             ok = mbar_wait(bar_tmem_full + acc * 8, acc_phase, s_abort, p.status, kDevTimeoutEpilogue);
@@ -308,9 +377,9 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
             const int32_t row = t.row0 + static_cast<int32_t>(quad * 32 + lane);
             const bool row_ok = row < t.row_end;
-            const float pt = row_ok ? __ldg(p.per_token + row) : 0.0f;
+            const float pt = !row_ok ? 0.0f : (p.per_token ? load_scale(p.per_token, row, p.scale_type) : 1.0f);
             const uint32_t taddr = tmem_base + acc * BN + ((quad * 32u) << 16);
-            __nv_bfloat16* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
+            uint16_t* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
             int32_t* arow = p.acc ? p.acc + static_cast<size_t>(row_ok ? row : 0) * p.n : nullptr;
 
 #pragma unroll 1
@@ -328,12 +397,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const int j = v * 8 + e * 2;
-                                const float x0 =
-                                    __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), scc[j]), pt);
-                                const float x1 = __fmul_rn(
-                                    __fmul_rn(__int2float_rn(static_cast<int>(r[j + 1])), scc[j + 1]), pt);
-                                const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                                packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+                                packed[e] = pack_out2(dequant(r[j], scc[j], pt), dequant(r[j + 1], scc[j + 1], pt), f16);
                             }
                             *reinterpret_cast<uint4*>(drow + col0 + v * 8) =
                                 make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -341,9 +405,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     } else {
                         for (int j = 0; j < 32; ++j) {
                             if (col0 + j < p.n) {
-                                const float x =
-                                    __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), scc[j]), pt);
-                                drow[col0 + j] = __float2bfloat16_rn(x);
+                                drow[col0 + j] = pack_out1(dequant(r[j], scc[j], pt), f16);
                             }
                         }
                     }
@@ -382,7 +444,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
 // D rows [0, rows) := 0 for a problem with k == 0 (the reference epilogue writes zeros then:
 // include/catlass/epilogue/block/block_epilogue_per_token_dequant.hpp:500-527).
-__global__ void zero_rows_kernel(__nv_bfloat16* d, const void* group_list, uint32_t group_list_is_i32,
+__global__ void zero_rows_kernel(uint16_t* d, const void* group_list, uint32_t group_list_is_i32,
                                  uint32_t group_count, uint32_t m, uint32_t n)
 {
     long long rows = m;
@@ -394,7 +456,7 @@ __global__ void zero_rows_kernel(__nv_bfloat16* d, const void* group_list, uint3
     const size_t total = static_cast<size_t>(rows) * n;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        d[i] = __float2bfloat16_rn(0.0f);
+        d[i] = 0;  // +0.0 in bf16 and in fp16
     }
 }
 

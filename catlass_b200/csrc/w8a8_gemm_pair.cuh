@@ -49,7 +49,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
     return remote;
 }
 
-template <BLayout kB>
+// kAMn: A is column-major ([k][m], m contiguous; dense problems only): its tiles are loaded as MN-major
+// operand panels, 128 rows of K x 128 bytes of M, exactly as a row-major B is.
+template <BLayout kB, bool kAMn>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const W8A8Params p)
@@ -166,7 +168,11 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         mbar_expect_tx(bar_full + stage * 8, 2 * S::kStageBytes);  // both CTAs' operands
                     }
                     const uint32_t full = map_to_cta(bar_full + stage * 8, 0);    // the leader's barrier
-                    tma_load_2d_pair(sa, &tmap_a, full, k0, row0);
+                    if constexpr (kAMn) {
+                        tma_load_2d_pair(sa, &tmap_a, full, row0, k0);  // 128 rows of K x 128 bytes of M
+                    } else {
+                        tma_load_2d_pair(sa, &tmap_a, full, k0, row0);  // 128 rows of M x 128 bytes of K
+                    }
                     if constexpr (kB == BLayout::kRowMajor) {
                         tma_load_3d_pair(sb, &tmap_b, full, ncol0, k0, bz);  // 128 rows of K x 128 bytes of N
                     } else if constexpr (kB == BLayout::kZN) {
@@ -187,7 +193,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // ---------------------------------------------------------------- MMA issuer (leader CTA only)
         if (lane == 0 && cta_rank == 0) {
             constexpr uint32_t idesc =
-                make_idesc(kAccS32, kFmtS8, kFmtS8, false, kB != BLayout::kColumnMajor, kPairTileM, BN);
+                make_idesc(kAccS32, kFmtS8, kFmtS8, kAMn, kB != BLayout::kColumnMajor, kPairTileM, BN);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
@@ -208,8 +214,13 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                     for (int j = 0; j < kBlockKBytes / kUmmaK; ++j) {
                         // the descriptors name this CTA's tiles; the peer's tiles sit at the same offsets
-                        const uint64_t da = make_smem_desc_sw128(sa + j * kUmmaK, 16, 1024);
-                        uint64_t db;
+                        uint64_t da, db;
+                        if constexpr (kAMn) {
+                            // one 128-byte panel of M per CTA; 32 rows of K further down per MMA
+                            da = make_smem_desc_sw128(sa + j * (kUmmaK * 128), kBlockKBytes * 128, 1024);
+                        } else {
+                            da = make_smem_desc_sw128(sa + j * kUmmaK, 16, 1024);
+                        }
                         if constexpr (kB == BLayout::kRowMajor) {
                             db = make_smem_desc_sw128(sb + j * (kUmmaK * 128), kBlockKBytes * 128, 1024);
                         } else if constexpr (kB == BLayout::kZN) {
@@ -242,19 +253,17 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // ---------------------------------------------------------------- epilogue warps 2..5 (both CTAs)
         const uint32_t quad = warp & 3;
         const bool vec_ok = (p.n & 7u) == 0;
+        const bool f16 = p.out_f16 != 0;
         TileScheduler sched{s_row_begin, s_row_end, s_tile_begin, n_tiles, 0};
         uint32_t acc = 0, acc_phase = 0;
+        uint32_t slab_stores = 0;  // TMA stores this warp has issued: picks the staging slab, across tiles too
         bool ok = true;
         for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
             TileScheduler::Tile t;
             sched.get<BN, kPairTileM>(idx, t);
             float* sc = s_scale + (warp - 2) * BN;
-            const float* gscale = p.scale + static_cast<size_t>(p.group_count == 0 ? 0 : t.group) * p.n;
             __syncwarp();
-            for (uint32_t i = lane; i < BN; i += 32) {
-                const uint32_t col = t.n0 + i;
-                sc[i] = col < p.n ? __ldg(gscale + col) : 0.0f;
-            }
+            stage_tile_scales(sc, p, t.group, static_cast<uint32_t>(t.n0), BN, lane);
             __syncwarp();
 
             ok = mbar_wait(bar_tmem_full + acc * 8, acc_phase, s_abort, p.status, kDevTimeoutEpilogue);
@@ -266,9 +275,9 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
             const int32_t row = t.row0 + static_cast<int32_t>(cta_rank * kBlockM + quad * 32 + lane);
             const bool row_ok = row < t.row_end;
-            const float pt = row_ok ? __ldg(p.per_token + row) : 0.0f;
+            const float pt = !row_ok ? 0.0f : (p.per_token ? load_scale(p.per_token, row, p.scale_type) : 1.0f);
             const uint32_t taddr = tmem_base + acc * BN + ((quad * 32u) << 16);
-            __nv_bfloat16* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
+            uint16_t* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
             int32_t* arow = p.acc ? p.acc + static_cast<size_t>(row_ok ? row : 0) * p.n : nullptr;
             // a whole warp without valid rows (ragged tail of a group) skips the drain
             const int32_t warp_row0 = t.row0 + static_cast<int32_t>(cta_rank * kBlockM + quad * 32);
@@ -286,9 +295,12 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const uint32_t col0 = t.n0 + c * 32;
                 if (slab_store && col0 < p.n) {
                     const float* scc = sc + c * 32;
-                    uint8_t* slab = s_store + ((warp - 2) * 2 + (c & 1)) * S::kStoreSlabBytes;
+                    // the two slabs strictly alternate over the warp's stores (a tile may issue an odd number), so
+                    // "at most one store still reading" means the store that last read THIS slab has finished
+                    uint8_t* slab = s_store + ((warp - 2) * 2 + (slab_stores & 1)) * S::kStoreSlabBytes;
+                    ++slab_stores;
                     if (lane == 0) {
-                        tma_store_wait_read<1>();  // the store that read this slab two chunks ago has done so
+                        tma_store_wait_read<1>();
                     }
                     __syncwarp();
 #pragma unroll
@@ -297,11 +309,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int j = v * 8 + e * 2;
-                            const float x0 = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), scc[j]), pt);
-                            const float x1 =
-                                __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j + 1])), scc[j + 1]), pt);
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                            packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            packed[e] = pack_out2(dequant(r[j], scc[j], pt), dequant(r[j + 1], scc[j + 1], pt), f16);
                         }
                         // row = lane, 16-byte chunk v at v ^ ((row >> 1) & 3): the 64-byte swizzle of the map
                         *reinterpret_cast<uint4*>(slab + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) =
@@ -329,12 +337,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const int j = v * 8 + e * 2;
-                                const float x0 =
-                                    __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), scc[j]), pt);
-                                const float x1 = __fmul_rn(
-                                    __fmul_rn(__int2float_rn(static_cast<int>(r[j + 1])), scc[j + 1]), pt);
-                                const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                                packed[e] = *reinterpret_cast<const uint32_t*>(&h);
+                                packed[e] = pack_out2(dequant(r[j], scc[j], pt), dequant(r[j + 1], scc[j + 1], pt), f16);
                             }
                             *reinterpret_cast<uint4*>(drow + col0 + v * 8) =
                                 make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -342,9 +345,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     } else {
                         for (int j = 0; j < 32; ++j) {
                             if (col0 + j < p.n) {
-                                const float x =
-                                    __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[j])), scc[j]), pt);
-                                drow[col0 + j] = __float2bfloat16_rn(x);
+                                drow[col0 + j] = pack_out1(dequant(r[j], scc[j], pt), f16);
                             }
                         }
                     }

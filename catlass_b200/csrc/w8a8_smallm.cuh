@@ -33,11 +33,16 @@ struct SmallMParams {
     uint32_t stages;        // ring depth (fits the dynamic smem given at launch)
     uint32_t kbs;           // 128-byte K blocks per ring stage: one stage = kbs*128 contiguous bytes per weight row
     uint32_t tile_rows;     // weight rows a CTA owns (<= 128, multiple of 8): chosen so the tiles fill the SMs
-    const float* scale;     // [n]
-    const float* per_token; // [m]
-    __nv_bfloat16* d;       // [m][n]
+    const void* scale;      // [n] scale_type elements (not read in scalar mode)
+    const void* per_token;  // [m] scale_type elements, or null: no per-token factor
+    uint16_t* d;            // [m][n] bf16 or fp16 bit patterns
     int32_t* acc;           // optional [m][n]
     unsigned* status;
+    uint32_t scale_type;
+    uint32_t scalar_mode;
+    float scalar_scale;
+    uint32_t out_f16;
+    uint32_t static_weights;  // weights and channel scales may be read before the stream dependency resolves
 };
 
 // dynamic smem: [1024 align pad][stages x (16 KB W + mt*128 B X)][(splits-1) x 128 x mt x 4 B partials,
@@ -122,9 +127,11 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            // Weights never depend on the kernel launched before this one, activations may: when launched with
-            // programmatic dependent launch, the first ring fill of WEIGHT tiles is issued before
-            // griddepcontrol.wait, the activation tiles (and, transitively, every store to D) after it.
+            // The kernel is launched with programmatic dependent launch: its set-up overlaps the tail of the kernel
+            // before it on the stream.  By default nothing is read from global memory before griddepcontrol.wait
+            // (plain stream order).  When the caller declares the weights static (not written by earlier work on
+            // this stream), the first ring fill of WEIGHT tiles is issued before the wait; the activation tiles
+            // (and, transitively, every store to D) always come after it.
             auto load_w = [&](uint32_t stage, uint32_t kb, uint32_t nsub) {
                 const uint32_t full = bar_full + stage * 8;
                 // the W box holds tile_rows rows; the UMMA still reads 128: the rows behind are never stored
@@ -150,6 +157,9 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             };
             const uint32_t iters = (my_kb + p.kbs - 1) / p.kbs;
             const uint32_t pre = iters < p.stages ? iters : p.stages;  // the ring is empty: no waits needed
+            if (!p.static_weights) {
+                grid_dependency_wait();
+            }
             for (uint32_t i = 0; i < pre; ++i) {
                 const uint32_t kb = kb_begin + i * p.kbs;
                 load_w(i, kb, kb_end - kb < p.kbs ? kb_end - kb : p.kbs);
@@ -229,14 +239,17 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     float tok[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (epi && split == 0) {
         const uint32_t ncol_early = static_cast<uint32_t>(n0) + row;
-        if (ncol_early < p.n && row < p.tile_rows) {
-            sc = __ldg(p.scale + ncol_early);  // weights' scales do not depend on the previous kernel
+        if (!p.static_weights) {
+            grid_dependency_wait();
         }
-        grid_dependency_wait();                // the per-token scales may
+        if (ncol_early < p.n && row < p.tile_rows) {
+            sc = p.scalar_mode ? p.scalar_scale : load_scale(p.scale, ncol_early, p.scale_type);
+        }
+        grid_dependency_wait();                // the per-token scales may depend on the previous kernel
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const uint32_t t = q * 32 + lane;
-            tok[q] = t < p.m ? __ldg(p.per_token + t) : 0.0f;
+            tok[q] = t >= p.m ? 0.0f : (p.per_token ? load_scale(p.per_token, t, p.scale_type) : 1.0f);
         }
     }
     if (epi && my_kb != 0) {
@@ -313,8 +326,7 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 const uint32_t mrow = c * 16 + i;
                 const float st = __shfl_sync(0xffffffffu, tq, (c & 1) * 16 + i);
                 if (n_ok && mrow < p.m) {
-                    const float x = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(r[i])), sc), st);
-                    p.d[static_cast<size_t>(mrow) * p.n + ncol] = __float2bfloat16_rn(x);
+                    p.d[static_cast<size_t>(mrow) * p.n + ncol] = pack_out1(dequant(r[i], sc, st), p.out_f16 != 0);
                     if (p.acc != nullptr) {
                         p.acc[static_cast<size_t>(mrow) * p.n + ncol] = static_cast<int32_t>(r[i]);
                     }

@@ -5,15 +5,34 @@ each rank receives whole experts, or row slices of a hot expert together with a 
 weights, and computes its own rows.  Nothing here runs on the GPU; it only decides who computes what.
 
 Two placements are offered:
-  "whole"  every expert lives on exactly one rank (speed-up limited by the largest expert),
-  "split"  experts larger than a chunk are cut into row chunks (multiples of the 128-row tile) that are
-           placed independently; weights of a cut expert are replicated on the ranks that hold a chunk.
-Both use longest-processing-time-first bin packing on the row counts.
+  "whole"  every expert lives on exactly one rank (speed-up limited by the largest expert); longest-processing-
+           time-first bin packing on the tile cost,
+  "split"  the experts' row tiles are laid on a line, expert after expert, and the line is cut into world_size
+           contiguous stretches of equal cost: a rank holds whole experts plus at most two partial ones, cuts fall
+           on multiples of the kernel's 256-row tile, and an expert's weights are replicated only on the ranks
+           its rows span (a hot expert with a quarter of all rows spans three of eight ranks).
+What is balanced is the kernel's cost, not the row count: the grouped kernel works in 256-row tiles per expert,
+so an expert costs its full tiles plus one (cheaper, when the kernel narrows it) partial tile.
 """
 from dataclasses import dataclass
 from typing import List
 
-ROW_TILE = 128
+ROW_TILE = 256          # the pair kernel's row tile (kPairTileM): shard cuts fall on its multiples
+TAIL_GRANULE = 32       # a group's last, partial tile is issued in steps of this many rows ...
+TAIL_FIXED_COST = 0.15  # ... and costs this fraction of a full tile on top (pipeline fill and drain)
+NARROW_TAILS = False    # whether the kernel narrows partial tiles (else a partial tile costs a full one)
+
+
+def tile_cost(rows):
+    """Cost of `rows` rows of one expert on one rank, in full 256-row tiles."""
+    rows = int(rows)
+    full, rem = divmod(rows, ROW_TILE)
+    if rem == 0:
+        return float(full)
+    if not NARROW_TAILS:
+        return float(full + 1)
+    issued = (rem + TAIL_GRANULE - 1) // TAIL_GRANULE * TAIL_GRANULE
+    return full + min(1.0, TAIL_FIXED_COST + (1.0 - TAIL_FIXED_COST) * issued / ROW_TILE)
 
 
 @dataclass(frozen=True)
@@ -31,6 +50,11 @@ class RankShard:
     @property
     def rows(self):
         return sum(p.rows for p in self.pieces)
+
+    @property
+    def cost(self):
+        """Kernel cost of this rank's launch in full tiles (pieces of one expert form one group)."""
+        return sum(tile_cost(r) for _, r in self.local_groups())
 
     def group_list(self):
         """Local prefix sums, one entry per piece (the group list of the rank's own grouped matmul)."""
@@ -57,7 +81,8 @@ class RankShard:
 
 
 def plan(group_sizes, world_size, mode="split", chunk_rows=None):
-    """Returns one RankShard per rank. group_sizes: rows per expert. Every row is placed exactly once."""
+    """Returns one RankShard per rank. group_sizes: rows per expert. Every row is placed exactly once.
+    chunk_rows (split mode): granularity of the cuts, a multiple of ROW_TILE (default: ROW_TILE)."""
     if world_size < 1:
         raise ValueError("world_size must be >= 1")
     if mode not in ("whole", "split"):
@@ -65,29 +90,34 @@ def plan(group_sizes, world_size, mode="split", chunk_rows=None):
     sizes = [int(s) for s in group_sizes]
     if any(s < 0 for s in sizes):
         raise ValueError("negative group size")
-    total = sum(sizes)
-    units: List[Piece] = []
+    if chunk_rows is None:
+        chunk_rows = ROW_TILE
+    if chunk_rows <= 0 or chunk_rows % ROW_TILE:
+        raise ValueError(f"chunk_rows must be a multiple of the {ROW_TILE}-row tile")
+    bins: List[List[Piece]] = [[] for _ in range(world_size)]
     if mode == "whole" or world_size == 1:
+        loads = [0.0] * world_size
         units = [Piece(e, 0, s) for e, s in enumerate(sizes) if s > 0]
+        for u in sorted(units, key=lambda p: (-p.rows, p.expert)):
+            r = min(range(world_size), key=lambda i: (loads[i], i))
+            bins[r].append(u)
+            loads[r] += tile_cost(u.rows)
     else:
-        if chunk_rows is None:
-            # small enough that the packing error is a few percent of a rank's load
-            target = max(total // (world_size * 16), ROW_TILE)
-            chunk_rows = max(ROW_TILE, (target // ROW_TILE) * ROW_TILE)
-        if chunk_rows % ROW_TILE:
-            raise ValueError("chunk_rows must be a multiple of the 128-row tile")
+        # units of chunk_rows rows in expert order, each with the cost it adds to its expert
+        units = []
         for e, s in enumerate(sizes):
             r = 0
             while r < s:
                 take = min(chunk_rows, s - r)
-                units.append(Piece(e, r, take))
+                units.append((Piece(e, r, take), tile_cost(take)))
                 r += take
-    loads = [0] * world_size
-    bins: List[List[Piece]] = [[] for _ in range(world_size)]
-    for u in sorted(units, key=lambda p: (-p.rows, p.expert, p.row_begin)):
-        r = min(range(world_size), key=lambda i: (loads[i], i))
-        bins[r].append(u)
-        loads[r] += u.rows
+        total = sum(c for _, c in units)
+        done = 0.0
+        for piece, c in units:
+            # the unit goes to the rank whose equal share of the line holds the unit's midpoint
+            r = min(world_size - 1, int((done + 0.5 * c) * world_size / total)) if total > 0 else 0
+            bins[r].append(piece)
+            done += c
     shards = []
     for r in range(world_size):
         pieces = sorted(bins[r], key=lambda p: (p.expert, p.row_begin))

@@ -45,6 +45,24 @@ extern "C" {
 #define CB200_GROUP_LIST_INT64 0
 #define CB200_GROUP_LIST_INT32 1
 
+/* ---- element types of scale vectors and of the output D ----
+ * The reference instantiates its W8A8 kernels with fp32, bf16 or half scales and bf16 or half outputs
+ * (examples 12: half/half, 07: float/half, 10: bf16/bf16); the goldens convert a scale to float before they
+ * use it (examples/common/golden/matmul.hpp:296-298), so do the kernels here. */
+#define CB200_DTYPE_F32 0
+#define CB200_DTYPE_BF16 1
+#define CB200_DTYPE_F16 2
+#define CB200_DTYPE_F32_IN_U64 3 /* fp32 bit pattern in the low half of a uint64: the reference's fixpipe scales */
+
+/* ---- flags ----
+ * CB200_FLAG_STATIC_WEIGHTS: the weight matrix and the weight/channel scales of this call are not written by
+ * any work enqueued earlier on the same stream (the usual case: parameters loaded once).  The few-token (m <= 128)
+ * W8A8 kernel and the W4A8 kernel are launched with programmatic dependent launch; with this flag they start
+ * streaming weights while the kernel before them on the stream is still finishing.  Without it every read of
+ * global memory waits for that kernel (plain stream order).  Activations, per-token scales and the output are
+ * always ordered after it. */
+#define CB200_FLAG_STATIC_WEIGHTS 2u
+
 /*
  * Dense W8A8 matmul with per-token / per-channel dequant:
  *     D[i,j] = bf16_rne( (float(sum_k A[i,k]*B[k,j]) * scale[j]) * per_token_scale[i] )
@@ -53,23 +71,28 @@ extern "C" {
  *         (include/catlass/gemm/kernel/quant_matmul_multistage_workspace.hpp:92-100),
  *     operand order of tests/optest/kernels/12_quant_matmul/quant_matmul_impl.cpp:103-105
  *         (inputs A, B, scale, perTokenScale; output D).
- * A: int8 m x k row-major; B: int8 k x n row-major, column-major (densely packed) or in the reference's zN
- * fractal format (k padded to 16, n to 32: layout::zN::MakeLayout<int8_t>(k, n)); D: bf16 m x n row-major.
+ * A: int8 m x k row-major or column-major (the four layout pairs of example 103,
+ * examples/103_dynamic_optimized_quant_matmul_per_token_basic/include/do_tiling_b8.h:24,62,117,166; column-major A
+ * needs m % 16 == 0); B: int8 k x n row-major, column-major (densely packed) or in the reference's zN
+ * fractal format (k padded to 16, n to 32: layout::zN::MakeLayout<int8_t>(k, n)); D: m x n row-major.
+ * Thread safety: any number of host threads may call concurrently, on any streams.
  */
 typedef struct cb200_quant_matmul_args {
     uint32_t m, n, k;
-    uint32_t layout_a;            /* CB200_ROW_MAJOR only */
+    uint32_t layout_a;            /* CB200_ROW_MAJOR or CB200_COLUMN_MAJOR */
     uint32_t layout_b;            /* CB200_ROW_MAJOR, CB200_COLUMN_MAJOR or CB200_ZN */
     const void *a;                /* int8 */
     const void *b;                /* int8 */
-    const float *scale;           /* n per-channel scales */
-    const float *per_token_scale; /* m per-token scales */
-    void *d;                      /* bf16 out */
+    const void *scale;            /* n per-channel scales, scale_type elements */
+    const void *per_token_scale;  /* m per-token scales, scale_type elements */
+    void *d;                      /* out, d_type elements */
     int32_t *acc;                 /* optional: raw int32 accumulators, m x n row-major (NULL = off) */
     void *workspace;
     uint64_t workspace_bytes;
     uint32_t block_num;           /* upper bound on the CTAs launched; 0 = one per SM */
-    uint32_t reserved;
+    uint32_t flags;               /* 0, or CB200_FLAG_STATIC_WEIGHTS */
+    uint32_t scale_type;          /* CB200_DTYPE_F32 (0, default), _BF16 or _F16: type of both scale vectors */
+    uint32_t d_type;              /* CB200_DTYPE_BF16 (default; 0 is accepted as bf16) or CB200_DTYPE_F16 */
 } cb200_quant_matmul_args;
 
 CB200_API int cb200_quant_matmul_can_implement(const cb200_quant_matmul_args *args);
@@ -87,6 +110,7 @@ CB200_API int cb200_quant_matmul(const cb200_quant_matmul_args *args, void *stre
  *         grouped_matmul_slice_m_per_token_dequant_moe_impl.cpp:98-102
  *         (inputs A, B, groupList, scale, perTokenScale; batch = group count).
  * m is the row capacity of A / D / per_token_scale (group_list entries are clamped to it).
+ * Thread safety: any number of host threads may call concurrently, on any streams.
  */
 typedef struct cb200_grouped_quant_matmul_args {
     uint32_t m, n, k;
@@ -97,19 +121,65 @@ typedef struct cb200_grouped_quant_matmul_args {
     const void *a;                /* int8 m x k row-major */
     const void *b;                /* int8 [group_count][k x n] */
     const void *group_list;       /* device pointer */
-    const float *scale;           /* [group_count][n] */
-    const float *per_token_scale; /* [m] */
-    void *d;                      /* bf16 m x n row-major */
+    const void *scale;            /* [group_count][n], scale_type elements */
+    const void *per_token_scale;  /* [m], scale_type elements */
+    void *d;                      /* m x n row-major, d_type elements */
     int32_t *acc;                 /* optional raw accumulators */
     void *workspace;
     uint64_t workspace_bytes;
     uint32_t block_num;
-    uint32_t reserved;
+    uint32_t flags;               /* 0 */
+    uint32_t scale_type;          /* CB200_DTYPE_F32 (0, default), _BF16 or _F16 */
+    uint32_t d_type;              /* CB200_DTYPE_BF16 (default; 0 is accepted as bf16) or CB200_DTYPE_F16 */
 } cb200_grouped_quant_matmul_args;
 
 CB200_API int cb200_grouped_quant_matmul_slice_m_can_implement(const cb200_grouped_quant_matmul_args *args);
 CB200_API uint64_t cb200_grouped_quant_matmul_slice_m_workspace_size(const cb200_grouped_quant_matmul_args *args);
 CB200_API int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args *args, void *stream);
+
+/*
+ * Grouped slice-M W8A8 matmul with per-tensor or per-channel dequant and no per-token factor:
+ *     quant_mode 0:  D[i,j] = round( float(acc[i,j]) * scale_per_tensor )
+ *     quant_mode 1:  D[i,j] = round( float(acc[i,j]) * per_channel_scale[j] )     one [n] vector for all groups
+ * Groups, group_list and B as in cb200_grouped_quant_matmul_slice_m.  Replaces the kernel behind example 48:
+ *     Gemm::Kernel::GroupedMatmulSliceMFixpipeDequantTla::Arguments (problemShape, problemCount, ptrGroupList,
+ *     ptrA, layoutA, ptrB, layoutB, ptrC, layoutC, scalePerTensor, ptrPerChannelScale:
+ *     examples/48_ascend950_grouped_matmul_slice_m_per_tensor_per_channel_dequant/
+ *     grouped_matmul_slice_m_per_tensor_per_channel_dequant.cpp:173-185), golden
+ *     golden::ComputeGroupedMatmulFixpipeDequant (examples/common/golden/matmul.hpp:234-269).
+ * The reference hands the per-channel scales over as 64-bit words with the fp32 bits in the low half
+ * (same file :103-107): pass them unchanged with per_channel_scale_type = CB200_DTYPE_F32_IN_U64, or a plain
+ * float array with CB200_DTYPE_F32.  The reference writes half: d_type = CB200_DTYPE_F16.
+ */
+#define CB200_QUANT_PER_TENSOR 0
+#define CB200_QUANT_PER_CHANNEL 1
+typedef struct cb200_grouped_fixpipe_dequant_args {
+    uint32_t m, n, k;
+    uint32_t group_count;
+    uint32_t layout_b;
+    uint32_t group_list_type;
+    uint32_t quant_mode;              /* CB200_QUANT_PER_TENSOR / CB200_QUANT_PER_CHANNEL */
+    float scale_per_tensor;
+    const void *a;                    /* int8 m x k row-major */
+    const void *b;                    /* int8 [group_count][k x n] */
+    const void *group_list;
+    const void *per_channel_scale;    /* [n]; read in per-channel mode only */
+    void *d;                          /* m x n row-major, d_type elements */
+    int32_t *acc;                     /* optional raw accumulators */
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t per_channel_scale_type;  /* CB200_DTYPE_F32 or CB200_DTYPE_F32_IN_U64 */
+    uint32_t d_type;                  /* CB200_DTYPE_BF16 (0 accepted) or CB200_DTYPE_F16 */
+    uint32_t flags;                   /* 0 */
+} cb200_grouped_fixpipe_dequant_args;
+
+CB200_API int cb200_grouped_matmul_slice_m_fixpipe_dequant_can_implement(
+    const cb200_grouped_fixpipe_dequant_args *args);
+CB200_API uint64_t cb200_grouped_matmul_slice_m_fixpipe_dequant_workspace_size(
+    const cb200_grouped_fixpipe_dequant_args *args);
+CB200_API int cb200_grouped_matmul_slice_m_fixpipe_dequant(const cb200_grouped_fixpipe_dequant_args *args,
+                                                           void *stream);
 
 /*
  * The grouped matmul for HOST-resident activations and output: what the reference's example mains do around
@@ -122,6 +192,8 @@ CB200_API int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmu
  * b and scale (the expert weights) stay on the device.  The device workspace
  * (cb200_grouped_quant_matmul_slice_m_host_workspace_size bytes) stages A, the per-token scales, D and the
  * per-chunk group lists.  On return all work is enqueued; d_host is complete once `stream` has caught up.
+ * Thread safety: calls on one device are serialised inside the library (they share its copy streams and a
+ * pinned staging buffer for the group lists); calls on different devices run concurrently.
  */
 typedef struct cb200_grouped_quant_matmul_host_args {
     uint32_t m, n, k;
@@ -146,21 +218,32 @@ CB200_API int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_
 /*
  * W4A8 matmul with per-group weight scales:
  *     acc_g[i,j] = sum_{k in group g} A[i,k] * W[k,j]                       (int32)
- *     y[i,j]     = fma(float(acc_g), weight_scale[g,j], y), g ascending     (fp32)
- *     D[i,j]     = bf16_rne(y * per_token_scale[i])
+ *     y[i,j]     = fma(float(acc_g), weight_scale[g,j], y), g ascending     (fp32, y starts at 0)
+ *     D[i,j]     = round(y * per_token_scale[i])
  * W holds signed 4-bit values, two per byte along K (even k in bits 0-3, odd k in bits 4-7), column after
- * column (k/2 bytes each): the packing of the reference's example 32 for a column-major B
+ * column (ceil(k/2) bytes each): the packing of the reference's example 32 for a column-major B
  * (examples/32_w4a8_matmul/gen_data.py:77-105).  Replaces Gemm::Kernel::W4A8Matmul::Arguments
  * (include/catlass/gemm/kernel/w4a8_matmul.hpp:83-93; operand order A, packed B of
  * tests/optest/kernels/32_w4a8_matmul/w4a8_matmul_impl.cpp:101-103).  The reference's own kernel applies one
- * per-tensor scalar; that case is group_size = k with weight_scale all ones and per_token_scale = scalar.
- * Requirements: k and group_size multiples of 128, group_size divides k, group_size <= 16384.
+ * per-tensor scalar and writes half; that case is group_size = k with weight_scale all ones,
+ * per_token_scale = the scalar and d_type = CB200_DTYPE_F16.
+ *
+ * Which fp32 reading of "rescale each group and sum in fp32" this is: ONE rounding per group (a fused
+ * multiply-add), groups in ascending order.  The reference holds no per-group golden to settle the choice; the
+ * fused form is the more accurate of the two natural readings (the unfused one rounds the product first) and
+ * is what the hardware does at full rate.  Both readings, and any other summation order, agree with the exact
+ * sum to within 2^-22 x sum_g |acc_g * weight_scale[g,j]| x per_token_scale[i] (64 groups, one ulp of the
+ * running sum each at most), plus the final rounding of D; the GPU tests check the output against the exact
+ * (float64) sum with that bound, and bit for bit against the fused definition.
+ *
+ * Requirements: group_size a multiple of 128 that divides round_up(k, 128), or group_size = k (one group);
+ * k % 32 == 0 (the packed rows must be 16-byte multiples for the bulk copies); group_size <= 16384.
  * Summation order: by default the groups are summed in ascending order, exactly as written above (D is
  * bit-exact against that definition).  With CB200_W4A8_SPLIT_K in `flags`, shapes with few 128-channel tiles
- * split the groups over the 2 or 4 CTAs of a cluster and add the fp32 partial sums at the end: faster (M=128,
- * N=K=8192: 25 us instead of 33 us), but an output whose partial sums nearly cancel can then differ
- * from the definition by more than one bf16 ulp of its small value; the absolute difference stays below
- * 2^-20 x the sum of the absolute group terms.
+ * split the groups over the 2 or 4 CTAs of a cluster and add the fp32 partial sums at the end: faster, but an
+ * output whose partial sums nearly cancel can then differ from the definition by more than one ulp of its small
+ * value; the absolute difference stays inside the bound above.
+ * Thread safety: any number of host threads may call concurrently, on any streams.
  */
 #define CB200_W4A8_SPLIT_K 1u
 typedef struct cb200_w4a8_matmul_args {
@@ -168,13 +251,15 @@ typedef struct cb200_w4a8_matmul_args {
     uint32_t group_size;
     const void *a;                /* int8 m x k row-major */
     const void *w_packed;         /* n columns of k/2 bytes */
-    const float *weight_scale;    /* [k / group_size][n] */
+    const float *weight_scale;    /* [ceil(k / group_size)][n] */
     const float *per_token_scale; /* [m] */
-    void *d;                      /* bf16 m x n row-major */
+    void *d;                      /* m x n row-major, d_type elements */
     void *workspace;
     uint64_t workspace_bytes;
     uint32_t block_num;
-    uint32_t reserved;            /* flags: 0, or CB200_W4A8_SPLIT_K */
+    uint32_t flags;               /* 0, CB200_W4A8_SPLIT_K and/or CB200_FLAG_STATIC_WEIGHTS */
+    uint32_t d_type;              /* CB200_DTYPE_BF16 (0 accepted) or CB200_DTYPE_F16 */
+    uint32_t reserved;
 } cb200_w4a8_matmul_args;
 
 CB200_API int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args *args);

@@ -52,6 +52,9 @@ struct QuantMatmul {
         uint8_t* ptrScale = nullptr;
         uint8_t* ptrPerTokenScale = nullptr;
         uint8_t* ptrD = nullptr;
+        uint32_t scaleType = CB200_DTYPE_F32;  // element type of both scale vectors (the reference's ElementScale)
+        uint32_t dType = CB200_DTYPE_BF16;     // element type of D (the reference's ElementD: bf16 or half)
+        uint32_t flags = 0;                    // CB200_FLAG_STATIC_WEIGHTS
     };
     using CArgs = cb200_quant_matmul_args;
     static CArgs ToUnderlyingArguments(Arguments const& a, void* workspace, size_t workspaceBytes)
@@ -64,12 +67,15 @@ struct QuantMatmul {
         c.layout_b = detail::LayoutTag<LayoutB>::value;
         c.a = a.ptrA;
         c.b = a.ptrB;
-        c.scale = reinterpret_cast<const float*>(a.ptrScale);
-        c.per_token_scale = reinterpret_cast<const float*>(a.ptrPerTokenScale);
+        c.scale = a.ptrScale;
+        c.per_token_scale = a.ptrPerTokenScale;
         c.d = a.ptrD;
         c.workspace = workspace;
         c.workspace_bytes = workspaceBytes;
         c.block_num = a.aicCoreNum;
+        c.flags = a.flags;
+        c.scale_type = a.scaleType;
+        c.d_type = a.dType;
         return c;
     }
     static int CanImplement(CArgs const* c) { return cb200_quant_matmul_can_implement(c); }
@@ -91,6 +97,8 @@ struct GroupedMatmulSliceMPerTokenDequant {
         uint8_t* ptrPerTokenScale = nullptr;
         uint8_t* ptrD = nullptr;
         uint32_t aicCoreNum = 0;
+        uint32_t scaleType = CB200_DTYPE_F32;
+        uint32_t dType = CB200_DTYPE_BF16;
     };
     using CArgs = cb200_grouped_quant_matmul_args;
     static CArgs ToUnderlyingArguments(Arguments const& a, void* workspace, size_t workspaceBytes)
@@ -106,17 +114,68 @@ struct GroupedMatmulSliceMPerTokenDequant {
         c.a = a.ptrA;
         c.b = a.ptrB;
         c.group_list = a.ptrGroupList;
-        c.scale = reinterpret_cast<const float*>(a.ptrScale);
-        c.per_token_scale = reinterpret_cast<const float*>(a.ptrPerTokenScale);
+        c.scale = a.ptrScale;
+        c.per_token_scale = a.ptrPerTokenScale;
         c.d = a.ptrD;
         c.workspace = workspace;
         c.workspace_bytes = workspaceBytes;
         c.block_num = a.aicCoreNum;
+        c.scale_type = a.scaleType;
+        c.d_type = a.dType;
         return c;
     }
     static int CanImplement(CArgs const* c) { return cb200_grouped_quant_matmul_slice_m_can_implement(c); }
     static uint64_t WorkspaceSize(CArgs const* c) { return cb200_grouped_quant_matmul_slice_m_workspace_size(c); }
     static int Run(CArgs const* c, void* stream) { return cb200_grouped_quant_matmul_slice_m(c, stream); }
+};
+
+/// Grouped slice-M W8A8 with per-tensor or per-channel dequant (no per-token factor).  Arguments as
+/// GroupedMatmulSliceMFixpipeDequantTla::Arguments (example 48: problemShape, problemCount, ptrGroupList, ptrA,
+/// ptrB, ptrC, scalePerTensor, ptrPerChannelScale).  kPerChannel is the reference's ScaleGranularity template
+/// argument; the per-channel scales are the reference's 64-bit words (fp32 bits in the low half).
+template <bool kPerChannel, class LayoutB = layout::RowMajor, class ElementGroupList = int64_t>
+struct GroupedMatmulSliceMFixpipeDequant {
+    struct Arguments {
+        GemmCoord problemShape;
+        uint32_t problemCount = 0;
+        uint8_t* ptrGroupList = nullptr;
+        uint8_t* ptrA = nullptr;
+        uint8_t* ptrB = nullptr;
+        uint8_t* ptrC = nullptr;
+        float scalePerTensor = 1.0f;
+        uint8_t* ptrPerChannelScale = nullptr;
+        uint32_t perChannelScaleType = CB200_DTYPE_F32_IN_U64;
+        uint32_t dType = CB200_DTYPE_F16;  // the reference writes half
+    };
+    using CArgs = cb200_grouped_fixpipe_dequant_args;
+    static CArgs ToUnderlyingArguments(Arguments const& a, void* workspace, size_t workspaceBytes)
+    {
+        CArgs c{};
+        c.m = a.problemShape.m();
+        c.n = a.problemShape.n();
+        c.k = a.problemShape.k();
+        c.group_count = a.problemCount;
+        c.layout_b = detail::LayoutTag<LayoutB>::value;
+        c.group_list_type = sizeof(ElementGroupList) == 8 ? CB200_GROUP_LIST_INT64 : CB200_GROUP_LIST_INT32;
+        c.quant_mode = kPerChannel ? CB200_QUANT_PER_CHANNEL : CB200_QUANT_PER_TENSOR;
+        c.scale_per_tensor = a.scalePerTensor;
+        c.a = a.ptrA;
+        c.b = a.ptrB;
+        c.group_list = a.ptrGroupList;
+        c.per_channel_scale = a.ptrPerChannelScale;
+        c.d = a.ptrC;
+        c.workspace = workspace;
+        c.workspace_bytes = workspaceBytes;
+        c.per_channel_scale_type = a.perChannelScaleType;
+        c.d_type = a.dType;
+        return c;
+    }
+    static int CanImplement(CArgs const* c) { return cb200_grouped_matmul_slice_m_fixpipe_dequant_can_implement(c); }
+    static uint64_t WorkspaceSize(CArgs const* c)
+    {
+        return cb200_grouped_matmul_slice_m_fixpipe_dequant_workspace_size(c);
+    }
+    static int Run(CArgs const* c, void* stream) { return cb200_grouped_matmul_slice_m_fixpipe_dequant(c, stream); }
 };
 
 /// W4A8 with per-group weight scales (W4A8Matmul::Arguments, w4a8_matmul.hpp:83-93, plus the scale arrays).
@@ -129,6 +188,8 @@ struct W4A8Matmul {
         uint8_t* ptrWeightScale = nullptr;
         uint8_t* ptrPerTokenScale = nullptr;
         uint8_t* ptrC = nullptr;
+        uint32_t dType = CB200_DTYPE_BF16;
+        uint32_t flags = 0;  // CB200_W4A8_SPLIT_K, CB200_FLAG_STATIC_WEIGHTS
     };
     using CArgs = cb200_w4a8_matmul_args;
     static CArgs ToUnderlyingArguments(Arguments const& a, void* workspace, size_t workspaceBytes)
@@ -145,6 +206,8 @@ struct W4A8Matmul {
         c.d = a.ptrC;
         c.workspace = workspace;
         c.workspace_bytes = workspaceBytes;
+        c.flags = a.flags;
+        c.d_type = a.dType;
         return c;
     }
     static int CanImplement(CArgs const* c) { return cb200_w4a8_matmul_can_implement(c); }

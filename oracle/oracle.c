@@ -116,14 +116,149 @@ void orc_grouped_quant_matmul_slice_m(uint32_t m, uint32_t n, uint32_t k, uint32
     free(row_acc);
 }
 
+void orc_grouped_matmul_fixpipe_dequant(uint32_t m, uint32_t n, uint32_t k, uint32_t group_count,
+                                        const int64_t *group_list, const int8_t *a, const int8_t *b,
+                                        int layout_b, int quant_mode, float scale_per_tensor,
+                                        const float *per_channel_scale, float *out, int32_t *acc)
+{
+    (void)m;
+    int32_t *row_acc = (int32_t *)malloc(sizeof(int32_t) * (n ? n : 1));
+    int64_t start_row = 0;
+    for (uint32_t g = 0; g < group_count; ++g) {
+        const int8_t *bg = b + (size_t)g * k * n;
+        for (int64_t i = start_row; i < group_list[g]; ++i) {
+            int8_row_times_matrix(n, k, a + (size_t)i * k, 1, bg, layout_b, row_acc);
+            for (uint32_t j = 0; j < n; ++j) {
+                float s = quant_mode == 0 ? scale_per_tensor : per_channel_scale[j];
+                out[(size_t)i * n + j] = (float)row_acc[j] * s;
+            }
+            if (acc) {
+                memcpy(acc + (size_t)i * n, row_acc, sizeof(int32_t) * n);
+            }
+        }
+        start_row = group_list[g];
+    }
+    free(row_acc);
+}
+
+void orc_grouped_quant_matmul_slice_k(uint32_t m, uint32_t n, uint32_t k, uint32_t group_count,
+                                      const int64_t *group_list, const int8_t *a, const int8_t *b,
+                                      const float *scale, const float *per_token, float *out, int32_t *acc)
+{
+    (void)k;
+    int32_t *row_acc = (int32_t *)malloc(sizeof(int32_t) * (n ? n : 1));
+    int64_t start = 0;
+    for (uint32_t g = 0; g < group_count; ++g) {
+        int64_t end = group_list[g];
+        uint32_t kg = end > start ? (uint32_t)(end - start) : 0;
+        float *og = out + (size_t)g * m * n;
+        for (uint32_t i = 0; i < m; ++i) {
+            /* A is column-major: element (i, kk) at a[kk * m + i]; B row-major: row kk at b + kk * n */
+            int8_row_times_matrix(n, kg, a + (size_t)start * m + i, m, b + (size_t)start * n, ORC_ROW_MAJOR, row_acc);
+            for (uint32_t j = 0; j < n; ++j) {
+                float t = (float)row_acc[j] * scale[(size_t)g * n + j];
+                og[(size_t)i * n + j] = t * per_token[(size_t)g * m + i];
+            }
+            if (acc) {
+                memcpy(acc + ((size_t)g * m + i) * n, row_acc, sizeof(int32_t) * n);
+            }
+        }
+        start = end;
+    }
+    free(row_acc);
+}
+
+/* ------------------------------------------------------------------ fp16 */
+
+uint16_t orc_f16_rne(float x)
+{
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    uint32_t sign = (u >> 16) & 0x8000u;
+    uint32_t abs = u & 0x7fffffffu;
+    if (abs > 0x7f800000u) {
+        return (uint16_t)(sign | 0x7e00u); /* NaN */
+    }
+    if (abs >= 0x477ff000u) { /* >= 65520: rounds to infinity */
+        return (uint16_t)(sign | 0x7c00u);
+    }
+    if (abs < 0x33000001u) { /* <= 2^-25: rounds to zero (the tie 2^-25 goes to even = 0) */
+        return (uint16_t)sign;
+    }
+    int32_t e = (int32_t)(abs >> 23) - 127;
+    uint32_t mant = (abs & 0x7fffffu) | 0x800000u; /* 24 bits */
+    uint32_t shift = e < -14 ? (uint32_t)(13 + (-14 - e)) : 13u; /* bits dropped */
+    uint32_t kept = mant >> shift;
+    uint32_t rem = mant & ((1u << shift) - 1u);
+    uint32_t half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (kept & 1u))) {
+        ++kept;
+    }
+    uint32_t r;
+    if (e < -14) {
+        r = kept; /* subnormal (a carry into 0x400 is the smallest normal, correctly encoded) */
+    } else {
+        r = ((uint32_t)(e + 15) << 10) + (kept - 0x400u); /* a mantissa carry bumps the exponent */
+    }
+    return (uint16_t)(sign | r);
+}
+
+void orc_f16_rne_array(const float *x, uint16_t *y, size_t count)
+{
+    for (size_t i = 0; i < count; ++i) {
+        y[i] = orc_f16_rne(x[i]);
+    }
+}
+
 /* ------------------------------------------------------------------ W4A8 */
+
+void orc_w4a8_matmul_per_group_readings(uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
+                                        const int8_t *a, const uint8_t *w_packed, const float *sw,
+                                        const float *sa, float *out_unfused, double *out_exact,
+                                        double *abs_terms)
+{
+    uint32_t groups = (k + group_size - 1) / group_size;
+    size_t col_bytes = (k + 1) / 2;
+    for (uint32_t i = 0; i < m; ++i) {
+        const int8_t *a_row = a + (size_t)i * k;
+        for (uint32_t j = 0; j < n; ++j) {
+            const uint8_t *col = w_packed + (size_t)j * col_bytes;
+            float y = 0.0f;
+            double y64 = 0.0, mag = 0.0;
+            for (uint32_t g = 0; g < groups; ++g) {
+                int32_t s = 0;
+                uint32_t k0 = g * group_size;
+                uint32_t k1 = k0 + group_size < k ? k0 + group_size : k;
+                for (uint32_t kk = k0; kk < k1; ++kk) {
+                    uint8_t byte = col[kk >> 1];
+                    int w = (kk & 1) ? orc_int4(byte >> 4) : orc_int4(byte & 0xF);
+                    s += (int32_t)a_row[kk] * w;
+                }
+                float scale = sw[(size_t)g * n + j];
+                float prod = (float)s * scale; /* rounded product: the unfused reading */
+                y = y + prod;
+                y64 += (double)s * (double)scale;
+                mag += fabs((double)s * (double)scale);
+            }
+            if (out_unfused) {
+                out_unfused[(size_t)i * n + j] = y * sa[i];
+            }
+            if (out_exact) {
+                out_exact[(size_t)i * n + j] = y64 * (double)sa[i];
+            }
+            if (abs_terms) {
+                abs_terms[(size_t)i * n + j] = mag * fabs((double)sa[i]);
+            }
+        }
+    }
+}
 
 void orc_w4a8_matmul_per_group(uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
                                const int8_t *a, const uint8_t *w_packed, const float *sw,
                                const float *sa, float *out)
 {
-    uint32_t groups = k / group_size;
-    size_t col_bytes = k / 2;
+    uint32_t groups = (k + group_size - 1) / group_size; /* the last group may be shorter */
+    size_t col_bytes = (k + 1) / 2;
     for (uint32_t i = 0; i < m; ++i) {
         const int8_t *a_row = a + (size_t)i * k;
         for (uint32_t j = 0; j < n; ++j) {
@@ -132,10 +267,11 @@ void orc_w4a8_matmul_per_group(uint32_t m, uint32_t n, uint32_t k, uint32_t grou
             for (uint32_t g = 0; g < groups; ++g) {
                 int32_t s = 0;
                 uint32_t k0 = g * group_size;
-                for (uint32_t kk = k0; kk < k0 + group_size; kk += 2) {
+                uint32_t k1 = k0 + group_size < k ? k0 + group_size : k;
+                for (uint32_t kk = k0; kk < k1; ++kk) {
                     uint8_t byte = col[kk >> 1];
-                    s += (int32_t)a_row[kk] * orc_int4(byte & 0xF);
-                    s += (int32_t)a_row[kk + 1] * orc_int4(byte >> 4);
+                    int w = (kk & 1) ? orc_int4(byte >> 4) : orc_int4(byte & 0xF);
+                    s += (int32_t)a_row[kk] * w;
                 }
                 y = fmaf((float)s, sw[(size_t)g * n + j], y);
             }

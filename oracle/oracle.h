@@ -53,6 +53,28 @@ void orc_grouped_quant_matmul_slice_m(uint32_t m, uint32_t n, uint32_t k, uint32
                                       const float *per_token, float *out, int32_t *acc);
 
 /*
+ * Grouped slice-M W8A8 with per-tensor / per-channel dequant. [pinned: reference golden]
+ * Follows golden::ComputeGroupedMatmulFixpipeDequant, examples/common/golden/matmul.hpp:234-269:
+ *   quant_mode 0: out = float(acc) * scale_per_tensor;  quant_mode 1: out = float(acc) * per_channel_scale[j]
+ * (one [n] vector shared by every group; no per-token factor).
+ */
+void orc_grouped_matmul_fixpipe_dequant(uint32_t m, uint32_t n, uint32_t k, uint32_t group_count,
+                                        const int64_t *group_list, const int8_t *a, const int8_t *b,
+                                        int layout_b, int quant_mode, float scale_per_tensor,
+                                        const float *per_channel_scale, float *out, int32_t *acc);
+
+/*
+ * Grouped slice-K W8A8 with per-token dequant.                [pinned: reference golden]
+ * Follows golden::ComputeGroupedMatmulSliceKPerTokenDequant, examples/common/golden/matmul.hpp:326-359:
+ * group_list holds ascending prefix sums over K; group g multiplies A[:, k_{g-1}:k_g] (A column-major m x k)
+ * with B[k_{g-1}:k_g, :] (row-major k x n) into its own m x n output block out + g*m*n, scaled by
+ * scale[g*n + j] and per_token[g*m + i].
+ */
+void orc_grouped_quant_matmul_slice_k(uint32_t m, uint32_t n, uint32_t k, uint32_t group_count,
+                                      const int64_t *group_list, const int8_t *a, const int8_t *b,
+                                      const float *scale, const float *per_token, float *out, int32_t *acc);
+
+/*
  * W4A8 with per-group weight scales.                          [parity unpinned]
  * The reference holds a per-TENSOR W4A8 golden only (examples/32_w4a8_matmul/gen_data.py:111-131,
  * out = 1.5 * (A @ B)); the per-group formula restated here is:
@@ -61,11 +83,24 @@ void orc_grouped_quant_matmul_slice_m(uint32_t m, uint32_t n, uint32_t k, uint32
  *   out[i,j]   = y * sa[i]
  * Weights are signed 4-bit, packed two per byte along K: byte t of column j holds W[2t,j] in bits 0-3
  * and W[2t+1,j] in bits 4-7 (nibble order of examples/32_w4a8_matmul/gen_data.py:102-105), columns
- * stored one after another (column-major B, k/2 bytes per column).  k must be even; group_size divides k.
+ * stored one after another (column-major B, ceil(k/2) bytes per column).  The last group is shorter when
+ * group_size does not divide k.
+ *
+ * Which fp32 reading this is.  "Rescale each group's int32 sum and add in fp32" can be read fused (one rounding
+ * per group, as here) or unfused (round the product, then the sum).  Nothing in the reference decides between
+ * them; the fused form is the definition here because it is the more accurate one and what a GPU does at full
+ * rate.  So that parity does not rest on this choice alone, orc_w4a8_matmul_per_group_readings returns the
+ * UNFUSED fp32 result, the exact result in double, and sum_g |acc_g * sw| * |sa|: every fp32 evaluation in any
+ * order lies within (number of groups) * 2^-24 * that magnitude of the exact value.
  */
 void orc_w4a8_matmul_per_group(uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
                                const int8_t *a, const uint8_t *w_packed, const float *sw,
                                const float *sa, float *out);
+
+void orc_w4a8_matmul_per_group_readings(uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
+                                        const int8_t *a, const uint8_t *w_packed, const float *sw,
+                                        const float *sa, float *out_unfused, double *out_exact,
+                                        double *abs_terms);
 
 /*
  * W4A8 per-tensor (the reference's example 32).               [pinned: reference python]
@@ -109,6 +144,10 @@ void orc_mx_matmul(uint32_t m, uint32_t n, uint32_t k, int fmt, const uint8_t *a
 uint16_t orc_bf16_rne(float x);
 void orc_bf16_rne_array(const float *x, uint16_t *y, size_t count);
 float orc_bf16_to_float(uint16_t v);
+
+/* fp32 -> fp16 bits, round to nearest even (overflow to infinity, gradual underflow). */
+uint16_t orc_f16_rne(float x);
+void orc_f16_rne_array(const float *x, uint16_t *y, size_t count);
 
 #ifdef __cplusplus
 }

@@ -52,9 +52,54 @@ void RunGrouped(uint32_t m, uint32_t n, uint32_t k, uint32_t g, const int64_t *g
     golden::ComputeGroupedMatmulPerTokenDequant(shape, g, gl, va, la, vb, lb, vs, ls, vp, lp, vo, lo);
     std::memcpy(out, vo.data(), vo.size() * sizeof(float));
 }
+
+template <class LayoutB>
+void RunFixpipe(uint32_t m, uint32_t n, uint32_t k, uint32_t g, const int64_t *groupList, const int8_t *a,
+                const int8_t *b, int quantMode, float scalePerTensor, const float *perChannel, float *out)
+{
+    std::vector<int64_t> gl(groupList, groupList + g);
+    std::vector<int8_t> va(a, a + size_t(m) * k), vb(b, b + size_t(g) * k * n);
+    std::vector<float> vc(perChannel ? perChannel : nullptr, perChannel ? perChannel + n : nullptr);
+    std::vector<float> vo(out, out + size_t(m) * n);
+    GemmCoord shape{m, n, k};
+    layout::RowMajor la{m, k}, lo{m, n};
+    LayoutB lb{k, n};
+    golden::ComputeGroupedMatmulFixpipeDequant(shape, g, gl, va, la, vb, lb, vo, lo, quantMode, scalePerTensor, vc);
+    std::memcpy(out, vo.data(), vo.size() * sizeof(float));
+}
 } // namespace
 
 extern "C" {
+
+// golden::ComputeGroupedMatmulFixpipeDequant, examples/common/golden/matmul.hpp:234-269
+void ref_grouped_fixpipe_dequant(uint32_t m, uint32_t n, uint32_t k, uint32_t g, const int64_t *groupList,
+                                 const int8_t *a, const int8_t *b, int layoutB, int quantMode, float scalePerTensor,
+                                 const float *perChannel, float *out)
+{
+    if (layoutB == 1) {
+        RunFixpipe<layout::ColumnMajor>(m, n, k, g, groupList, a, b, quantMode, scalePerTensor, perChannel, out);
+    } else {
+        RunFixpipe<layout::RowMajor>(m, n, k, g, groupList, a, b, quantMode, scalePerTensor, perChannel, out);
+    }
+}
+
+// golden::ComputeGroupedMatmulSliceKPerTokenDequant, examples/common/golden/matmul.hpp:326-359
+// (A column-major m x k, B row-major k x n, groups along K, one m x n output block per group)
+void ref_grouped_quant_matmul_slice_k(uint32_t m, uint32_t n, uint32_t k, uint32_t g, const int64_t *groupList,
+                                      const int8_t *a, const int8_t *b, const float *scale, const float *perToken,
+                                      float *out)
+{
+    std::vector<int64_t> gl(groupList, groupList + g);
+    std::vector<int8_t> va(a, a + size_t(m) * k), vb(b, b + size_t(k) * n);
+    std::vector<float> vs(scale, scale + size_t(g) * n), vp(perToken, perToken + size_t(g) * m);
+    std::vector<float> vo(out, out + size_t(g) * m * n);
+    GemmCoord shape{m, n, k};
+    layout::VectorLayout ls{n}, lp{m};
+    layout::ColumnMajor la{m, k};
+    layout::RowMajor lb{k, n}, lo{m, n};
+    golden::ComputeGroupedMatmulSliceKPerTokenDequant(shape, g, gl, va, la, vb, lb, vs, ls, vp, lp, vo, lo);
+    std::memcpy(out, vo.data(), vo.size() * sizeof(float));
+}
 
 // golden::QuantMatmul, examples/common/golden/matmul.hpp:303-324
 void ref_quant_matmul(uint32_t m, uint32_t n, uint32_t k, const int8_t *a, int layoutA, const int8_t *b,

@@ -51,6 +51,21 @@ def w8a8(ref_lib):
     out.update(grp_shape=np.array([gm, gn, gk, gg]), grp_list=gl, grp_a=ga, grp_b=gb, grp_scale=gs, grp_pt=gp)
     for lb in (0, 1):
         out[f"grp_out_{lb}"] = O.ref_grouped_quant_matmul(ga, gb, gl, gs, gp, gm, gn, gk, lb)
+    # per-tensor / per-channel grouped dequant (example 48's golden) on the grouped inputs above, and slice-K
+    # (example 11's golden: A column-major, groups along K) on inputs of its own
+    pcs = rng.uniform(0, 1, gn).astype(np.float32)
+    out.update(fix_pcs=pcs, fix_scalar=np.float32(0.37))
+    for mode in (0, 1):
+        for lb in (0, 1):
+            out[f"fix_out_{mode}{lb}"] = O.ref_grouped_fixpipe_dequant(ga, gb, gl, mode, 0.37, pcs, gm, gn, gk, lb)
+    sm, sn, sk, sg = 16, 24, 80, 5
+    sgl = O.ref_generate_group_list(sk, sg)
+    sa_ = rng.integers(-16, 17, sm * sk, dtype=np.int8)
+    sb_ = rng.integers(-16, 17, sk * sn, dtype=np.int8)
+    ss_ = rng.uniform(0, 1, sg * sn).astype(np.float32)
+    sp_ = rng.uniform(0, 1, sg * sm).astype(np.float32)
+    out.update(slk_shape=np.array([sm, sn, sk, sg]), slk_list=sgl, slk_a=sa_, slk_b=sb_, slk_scale=ss_, slk_pt=sp_,
+               slk_out=O.ref_grouped_quant_matmul_slice_k(sa_, sb_, sgl, ss_, sp_, sm, sn, sk))
     # the runner's group list: examples 07/10/47 are run with 128 groups over m = 512
     out["group_list_512_128"] = O.ref_generate_group_list(512, 128)
     # layout offsets: (tag, elem_bytes, rows, cols) -> offsets of a fixed coordinate walk

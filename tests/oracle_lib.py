@@ -45,6 +45,8 @@ def lib():
         _lib = _load(path)
         _lib.orc_bf16_rne.restype = ctypes.c_uint16
         _lib.orc_bf16_rne.argtypes = [ctypes.c_float]
+        _lib.orc_f16_rne.restype = ctypes.c_uint16
+        _lib.orc_f16_rne.argtypes = [ctypes.c_float]
         for name in ("orc_e4m3_to_float", "orc_e2m1_to_float", "orc_e8m0_to_float"):
             getattr(_lib, name).restype = ctypes.c_float
             getattr(_lib, name).argtypes = [ctypes.c_uint8]
@@ -92,6 +94,45 @@ def grouped_quant_matmul(a, b, group_list, scale, per_token, m, n, k, layout_b=R
     return (out, acc) if want_acc else out
 
 
+def grouped_fixpipe_dequant(a, b, group_list, quant_mode, scale_per_tensor, per_channel_scale, m, n, k,
+                            layout_b=ROW_MAJOR, want_acc=False, out_init=None):
+    """Per-tensor (quant_mode 0) / per-channel (1) grouped dequant golden. Returns fp32 out [m, n]."""
+    a, b = _c(a, np.int8), _c(b, np.int8)
+    gl = _c(group_list, np.int64)
+    pcs = _c(per_channel_scale, np.float32) if per_channel_scale is not None else None
+    out = np.zeros((m, n), np.float32) if out_init is None else _c(out_init, np.float32).copy()
+    acc = np.zeros((m, n), np.int32) if want_acc else None
+    lib().orc_grouped_matmul_fixpipe_dequant(_c_u32(m), _c_u32(n), _c_u32(k), _c_u32(len(gl)), _ptr(gl), _ptr(a),
+                                             _ptr(b), layout_b, int(quant_mode), ctypes.c_float(scale_per_tensor),
+                                             _ptr(pcs), _ptr(out), _ptr(acc))
+    return (out, acc) if want_acc else out
+
+
+def grouped_quant_matmul_slice_k(a, b, group_list, scale, per_token, m, n, k, want_acc=False):
+    """a: column-major m x k ([k][m] bytes), b: row-major k x n; groups along K. Returns fp32 [G, m, n]."""
+    a, b = _c(a, np.int8), _c(b, np.int8)
+    gl = _c(group_list, np.int64)
+    scale, per_token = _c(scale, np.float32), _c(per_token, np.float32)
+    out = np.zeros((len(gl), m, n), np.float32)
+    acc = np.zeros((len(gl), m, n), np.int32) if want_acc else None
+    lib().orc_grouped_quant_matmul_slice_k(_c_u32(m), _c_u32(n), _c_u32(k), _c_u32(len(gl)), _ptr(gl), _ptr(a),
+                                           _ptr(b), _ptr(scale), _ptr(per_token), _ptr(out), _ptr(acc))
+    return (out, acc) if want_acc else out
+
+
+def w4a8_per_group_readings(a, w_packed, sw, sa, m, n, k, group_size):
+    """(unfused fp32 result, exact result in float64, sum of |group terms| * |sa|) of the per-group formula."""
+    a, w_packed = _c(a, np.int8), _c(w_packed, np.uint8)
+    sw, sa = _c(sw, np.float32), _c(sa, np.float32)
+    unfused = np.empty((m, n), np.float32)
+    exact = np.empty((m, n), np.float64)
+    mag = np.empty((m, n), np.float64)
+    lib().orc_w4a8_matmul_per_group_readings(_c_u32(m), _c_u32(n), _c_u32(k), _c_u32(group_size), _ptr(a),
+                                             _ptr(w_packed), _ptr(sw), _ptr(sa), _ptr(unfused), _ptr(exact),
+                                             _ptr(mag))
+    return unfused, exact, mag
+
+
 def w4a8_per_group(a, w_packed, sw, sa, m, n, k, group_size):
     a, w_packed = _c(a, np.int8), _c(w_packed, np.uint8)
     sw, sa = _c(sw, np.float32), _c(sa, np.float32)
@@ -135,14 +176,29 @@ def bf16_bits(x):
     return y
 
 
+def f16_bits(x):
+    x = _c(x, np.float32)
+    y = np.empty(x.shape, np.uint16)
+    lib().orc_f16_rne_array(_ptr(x), _ptr(y), ctypes.c_size_t(x.size))
+    return y
+
+
+def out_bits(x, f16=False):
+    """fp32 golden values rounded to the output element type (bf16, or fp16)."""
+    return f16_bits(x) if f16 else bf16_bits(x)
+
+
 def bf16_to_float(bits):
     return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
 def pack_int4_along_k(w):
-    """w: int8 [k, n] with values in [-8, 7] -> uint8 [n, k/2]; low nibble = even k, high nibble = odd k."""
+    """w: int8 [k, n] with values in [-8, 7] -> uint8 [n, ceil(k/2)]; low nibble = even k, high nibble = odd k
+    (an odd k leaves the last high nibble zero)."""
     k, n = w.shape
     wt = np.ascontiguousarray(w.T).astype(np.uint8) & 0xF  # [n, k]
+    if k & 1:
+        wt = np.concatenate([wt, np.zeros((n, 1), np.uint8)], axis=1)
     return (wt[:, 0::2] | (wt[:, 1::2] << 4)).astype(np.uint8)
 
 
@@ -165,6 +221,28 @@ def ref_grouped_quant_matmul(a, b, group_list, scale, per_token, m, n, k, layout
     ref().ref_grouped_quant_matmul_slice_m(_c_u32(m), _c_u32(n), _c_u32(k), _c_u32(len(gl)), _ptr(gl),
                                            _ptr(a), _ptr(b), layout_b, _ptr(scale), _ptr(per_token),
                                            _ptr(out))
+    return out
+
+
+def ref_grouped_fixpipe_dequant(a, b, group_list, quant_mode, scale_per_tensor, per_channel_scale, m, n, k,
+                                layout_b=ROW_MAJOR):
+    a, b = _c(a, np.int8), _c(b, np.int8)
+    gl = _c(group_list, np.int64)
+    pcs = _c(per_channel_scale, np.float32) if per_channel_scale is not None else None
+    out = np.zeros((m, n), np.float32)
+    ref().ref_grouped_fixpipe_dequant(_c_u32(m), _c_u32(n), _c_u32(k), _c_u32(len(gl)), _ptr(gl), _ptr(a), _ptr(b),
+                                      layout_b, int(quant_mode), ctypes.c_float(scale_per_tensor), _ptr(pcs),
+                                      _ptr(out))
+    return out
+
+
+def ref_grouped_quant_matmul_slice_k(a, b, group_list, scale, per_token, m, n, k):
+    a, b = _c(a, np.int8), _c(b, np.int8)
+    gl = _c(group_list, np.int64)
+    scale, per_token = _c(scale, np.float32), _c(per_token, np.float32)
+    out = np.zeros((len(gl), m, n), np.float32)
+    ref().ref_grouped_quant_matmul_slice_k(_c_u32(m), _c_u32(n), _c_u32(k), _c_u32(len(gl)), _ptr(gl), _ptr(a),
+                                           _ptr(b), _ptr(scale), _ptr(per_token), _ptr(out))
     return out
 
 

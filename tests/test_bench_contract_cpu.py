@@ -23,3 +23,21 @@ def test_reference_arm_prints_contract_line():
     assert line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert line["value"] > 0
+
+
+def test_reference_arm_config_equals_the_main_arm_config():
+    """Both arms describe the workload with the same `config` object (the reference arm adds one key)."""
+    import sys as _sys
+    _sys.path.insert(0, ROOT)
+    import bench
+    cfg = bench.moe_config(bench.MOE, "split", 1)
+    assert set(cfg) == {"workload", "placement", "rows_per_rank", "l2", "weights"}
+    assert cfg["rows_per_rank"] == [131072]
+    assert sum(bench.moe_config(bench.MOE, "split", 8)["rows_per_rank"]) == 131072
+
+
+def test_recorded_dram_traffic_matches_the_kernel_sources():
+    """The profiler figures the bench quotes name the tile constants they were captured with."""
+    from catlass_b200 import kernel_facts
+    assert kernel_facts.check() == []
+    assert kernel_facts.traffic("w8a8_pair_kernel/moe_small", 8.0) == 8 * 540.2e6

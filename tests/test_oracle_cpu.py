@@ -39,6 +39,46 @@ def test_grouped_matches_reference_golden_vectors(w8a8_golden):
         assert np.array_equal(bits(out), bits(g[f"grp_out_{lb}"])), lb
 
 
+def test_fixpipe_dequant_matches_reference_golden_vectors(w8a8_golden):
+    g = w8a8_golden
+    m, n, k, groups = (int(x) for x in g["grp_shape"])
+    for mode in (0, 1):
+        for lb in (0, 1):
+            out = O.grouped_fixpipe_dequant(g["grp_a"], g["grp_b"], g["grp_list"], mode, float(g["fix_scalar"]),
+                                            g["fix_pcs"], m, n, k, lb)
+            assert np.array_equal(bits(out), bits(g[f"fix_out_{mode}{lb}"])), (mode, lb)
+
+
+def test_slice_k_matches_reference_golden_vectors(w8a8_golden):
+    g = w8a8_golden
+    m, n, k, groups = (int(x) for x in g["slk_shape"])
+    out = O.grouped_quant_matmul_slice_k(g["slk_a"], g["slk_b"], g["slk_list"], g["slk_scale"], g["slk_pt"], m, n, k)
+    assert out.shape == (groups, m, n)
+    assert np.array_equal(bits(out), bits(g["slk_out"]))
+
+
+@pytest.mark.skipif(O.ref() is None, reason="reference golden (oracle/_ref) not built")
+def test_siblings_against_live_reference_golden():
+    rng = np.random.default_rng(48)
+    m, n, k, g = 70, 36, 64, 6
+    gl = O.ref_generate_group_list(m, g)
+    a = rng.integers(-128, 128, m * k, dtype=np.int8)
+    b = rng.integers(-128, 128, g * k * n, dtype=np.int8)
+    pcs = rng.uniform(0, 1, n).astype(np.float32)
+    for mode in (0, 1):
+        for lb in (0, 1):
+            assert np.array_equal(bits(O.grouped_fixpipe_dequant(a, b, gl, mode, 0.8125, pcs, m, n, k, lb)),
+                                  bits(O.ref_grouped_fixpipe_dequant(a, b, gl, mode, 0.8125, pcs, m, n, k, lb)))
+    kk = 150
+    glk = O.ref_generate_group_list(kk, g)
+    a2 = rng.integers(-128, 128, 24 * kk, dtype=np.int8)
+    b2 = rng.integers(-128, 128, kk * n, dtype=np.int8)
+    s2 = rng.uniform(1e-3, 1e-2, g * n).astype(np.float32)
+    p2 = rng.uniform(1e-3, 1e-2, g * 24).astype(np.float32)
+    assert np.array_equal(bits(O.grouped_quant_matmul_slice_k(a2, b2, glk, s2, p2, 24, n, kk)),
+                          bits(O.ref_grouped_quant_matmul_slice_k(a2, b2, glk, s2, p2, 24, n, kk)))
+
+
 def test_reference_group_list_fixture_is_a_prefix_sum_list(w8a8_golden):
     gl = w8a8_golden["group_list_512_128"]
     assert len(gl) == 128 and (np.diff(gl) >= 0).all() and 0 <= gl[0] and gl[-1] <= 512
@@ -91,6 +131,18 @@ def test_bf16_round_to_nearest_even():
     y = np.random.default_rng(1).standard_normal(4096).astype(np.float32) * 1e-3
     t = torch.from_numpy(y).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     assert np.array_equal(O.bf16_bits(y), t)
+
+
+def test_f16_round_to_nearest_even():
+    rng = np.random.default_rng(16)
+    x = np.concatenate([
+        rng.standard_normal(20000).astype(np.float32) * np.float32(10.0) ** rng.integers(-9, 6, 20000),
+        np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, 1e9, -1e9, 2.0 ** -24, 2.0 ** -25, 1.5 * 2.0 ** -25,
+                  2.0 ** -14, 2.0 ** -14 - 2.0 ** -25, 1.0 + 2.0 ** -11, 1.0 + 3 * 2.0 ** -11], np.float32)])
+    x = x.astype(np.float32)
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16).view(np.uint16)
+    assert np.array_equal(O.f16_bits(x), want)
 
 
 # ------------------------------------------------------------------ MX
@@ -177,6 +229,36 @@ def test_w4a8_per_group_formula():
     one = O.w4a8_per_group(a, O.pack_int4_along_k(w), np.ones((1, n), np.float32), np.ones(m, np.float32),
                            m, n, k, k)
     assert np.array_equal(bits(one), bits(O.w4a8_per_tensor(a, O.pack_int4_along_k(w), 1.0, m, n, k)))
+
+
+def test_w4a8_per_group_readings_bracket_the_definition():
+    """The fused definition, the unfused fp32 reading and the exact sum agree within the stated bound, and the
+    ragged forms (odd k, a shorter last group) reduce to the same integer sums."""
+    rng = np.random.default_rng(36)
+    m, n, k, gs = 7, 10, 640, 128
+    a = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    w = rng.integers(-8, 8, (k, n), dtype=np.int8)
+    sw = (rng.uniform(1e-3, 1e-2, (k // gs, n)) * rng.choice([-1.0, 1.0], (k // gs, n))).astype(np.float32)
+    sa = rng.uniform(1e-3, 1e-2, m).astype(np.float32)
+    wp = O.pack_int4_along_k(w)
+    fused = O.w4a8_per_group(a, wp, sw, sa, m, n, k, gs)
+    unfused, exact, mag = O.w4a8_per_group_readings(a, wp, sw, sa, m, n, k, gs)
+    groups = k // gs
+    bound = (groups + 2) * 2.0 ** -24 * mag + 2.0 ** -149
+    assert (np.abs(fused.astype(np.float64) - exact) <= bound).all()
+    assert (np.abs(unfused.astype(np.float64) - exact) <= bound).all()
+    want = (a.astype(np.int64) @ w.astype(np.int64)).astype(np.float64)
+    one = O.w4a8_per_group_readings(a, wp, np.ones((1, n), np.float32), np.ones(m, np.float32), m, n, k, k)[1]
+    assert np.array_equal(one, want)
+    # odd k and a last group of 37 elements
+    k2 = 293
+    a2, w2 = a[:, :k2], w[:k2]
+    exact2 = O.w4a8_per_group_readings(a2, O.pack_int4_along_k(w2), sw[:3], sa, m, n, k2, 128)[1]
+    ref2 = np.zeros((m, n))
+    for g in range(3):
+        ref2 += (a2[:, g * 128:(g + 1) * 128].astype(np.int64) @ w2[g * 128:(g + 1) * 128].astype(np.int64)) \
+            * sw[g].astype(np.float64)
+    assert np.allclose(exact2, ref2 * sa[:, None].astype(np.float64), rtol=1e-12, atol=0)
 
 
 def test_zn_storage_helper_matches_the_reference_layout(w8a8_golden):

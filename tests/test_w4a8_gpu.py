@@ -4,7 +4,12 @@ Default call: every CTA sums the scale groups in ascending order, exactly like t
 bit-identical.  With the CB200_W4A8_SPLIT_K flag the K range is split over a CTA cluster and fp32 partial sums
 are added at the end: the sum is reassociated, so the bar is |got - want| <= max(1 bf16 ulp of want,
 2^-20 x sa[m] x sum_g |acc_g| x sw[g,n]) -- one ulp wherever the terms do not cancel, the fp32 reassociation
-bound where they do -- and at most 1 % of the outputs may differ at all."""
+bound where they do -- and at most 1 % of the outputs may differ at all.
+
+So that parity does not hang on the oracle's choice of a fused multiply-add alone, every case (both modes) is
+also compared with two references that do not share it: the exact sum in float64 and the unfused fp32 reading
+(round the product, then the sum).  Bar for both: |got - ref| <= max(1 bf16 ulp of ref,
+2^-20 x sa[m] x sum_g |acc_g x sw[g,n]|)."""
 import numpy as np
 import pytest
 
@@ -53,6 +58,16 @@ def _check(got, want, exact, terms=None):
         assert not over.any(), f"{over.sum()} outputs beyond both bounds (max {dist[over].max()} bf16 ulp)"
 
 
+def _check_order_independent(got, a, packed, sw, sa, m, n, k, gs):
+    unfused, exact64, mag = O.w4a8_per_group_readings(a, packed, sw, sa, m, n, k, gs)
+    got64 = O.bf16_to_float(got).astype(np.float64)
+    for name, ref in (("exact float64 sum", exact64), ("unfused fp32 reading", unfused.astype(np.float64))):
+        ulp = np.spacing(np.abs(ref).astype(np.float32)).astype(np.float64) * 65536.0  # one bf16 step at ref
+        bound = np.maximum(ulp, mag * 2.0 ** -20)
+        over = np.abs(got64 - ref) > bound
+        assert not over.any(), f"{over.sum()} of {over.size} outputs beyond the bound against the {name}"
+
+
 @pytest.fixture(params=["default", "split_k"])
 def exact(request):
     """Runs a test twice: default call (bit-exact) and with the split-K flag (reassociation bound)."""
@@ -79,6 +94,20 @@ def test_w4a8_per_group_matches_oracle(cuda, exact, m, n, k, gs):
     got = _run(cuda, a, packed, sw, sa, m, n, k, gs, split_k=not exact)
     want = O.bf16_bits(O.w4a8_per_group(a, packed, sw, sa, m, n, k, gs))
     _check(got, want, exact, None if exact else _abs_terms(a, w, sw, sa, gs))
+    _check_order_independent(got, a, packed, sw, sa, m, n, k, gs)
+
+
+def test_w4a8_cancelling_groups_against_order_independent_references(cuda, exact):
+    """Scales of both signs: group terms that nearly cancel are where the fused and the unfused reading, and
+    any reordering, differ most."""
+    m, n, k, gs = 96, 384, 4096, 128
+    a, w, packed, sw, sa = _problem(m, n, k, gs, seed=99)
+    rng = np.random.default_rng(100)
+    sw = (sw * rng.choice([-1.0, 1.0], sw.shape)).astype(np.float32)
+    got = _run(cuda, a, packed, sw, sa, m, n, k, gs, split_k=not exact)
+    if exact:
+        _check(got, O.bf16_bits(O.w4a8_per_group(a, packed, sw, sa, m, n, k, gs)), True)
+    _check_order_independent(got, a, packed, sw, sa, m, n, k, gs)
 
 
 def test_w4a8_extreme_values(cuda, exact):
@@ -114,6 +143,8 @@ def test_w4a8_full_config_sampled_columns(cuda, exact):
     cols = np.unique(np.concatenate([[0, 127, 128, 255, 4095, 4096, 8191], rng.integers(0, n, 185)]))
     want = O.bf16_bits(O.w4a8_per_group(a, packed[cols], np.ascontiguousarray(sw[:, cols]), sa, m, len(cols), k, gs))
     _check(got[:, cols], want, exact, None if exact else _abs_terms(a, w[:, cols], sw[:, cols], sa, gs))
+    _check_order_independent(np.ascontiguousarray(got[:, cols]), a, packed[cols], np.ascontiguousarray(sw[:, cols]), sa,
+                             m, len(cols), k, gs)
 
 
 def test_w4a8_invalid_arguments(cuda):

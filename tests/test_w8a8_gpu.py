@@ -303,7 +303,11 @@ def test_invalid_arguments_are_rejected(cuda):
     with pytest.raises(capi.CallError):
         capi.quant_matmul(a[1:], b, s, p, d, m, n, k)  # misaligned A
     with pytest.raises(capi.CallError):
-        capi.quant_matmul(a, b, s, p, d, m, n, k, layout_a=capi.COLUMN_MAJOR)
+        capi.quant_matmul(a, b, s, p, d, m, n, k, layout_a=7)
+    with pytest.raises(capi.CallError):
+        capi.quant_matmul(a, b, s, p, d, 120, n, k, layout_a=capi.COLUMN_MAJOR)  # column-major A: m % 16
+    with pytest.raises(capi.CallError):
+        capi.quant_matmul(a, b, s, p, d, m, n, k, d_type=5)
     with pytest.raises(capi.CallError):
         capi.quant_matmul(a, b, s, p, d, m, n, k, layout_b=7)
     with pytest.raises(capi.CallError):
