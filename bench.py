@@ -508,12 +508,7 @@ def run_moe(args, rank, world, local, sampler):
     sustained_peak = peaks["bf16_tflops_sustained"] * INT8_PER_BF16
 
     # tile accounting of this rank's launch: issued MMA work over the work the rows need
-    tile_m = 256
-    local_sizes = [r for _, r in w["shards"][rank].local_groups()]
-    full = sum(s // tile_m for s in local_sizes)
-    tails = [s % tile_m for s in local_sizes if s % tile_m]
-    tail_rows_issued = sum((t + 31) // 32 * 32 for t in tails) if capi_has_narrow_tails() else len(tails) * tile_m
-    issued_over_needed = (full * tile_m + tail_rows_issued) / max(m, 1)
+    issued_over_needed = w["shards"][rank].cost * sharding.ROW_TILE / max(m, 1)
 
     # ---- end to end: host buffers in, host buffer out, through the same C-ABI call
     a_h = torch.empty_like(w["a"], device="cpu").pin_memory()
@@ -577,11 +572,6 @@ def run_moe(args, rank, world, local, sampler):
         result["ms_x_sm_mhz"] = ms_step * clocks["sm_mhz"]
     del a_h, d_h, ws
     return result, w
-
-
-def capi_has_narrow_tails():
-    from catlass_b200 import capi
-    return bool(getattr(capi, "NARROW_GROUP_TAILS", False))
 
 
 # ------------------------------------------------------------------------------------------ other workloads

@@ -60,7 +60,7 @@ class W4A8MatmulArgs(ctypes.Structure):
         ("m", _u32), ("n", _u32), ("k", _u32), ("group_size", _u32),
         ("a", _vp), ("w_packed", _vp), ("weight_scale", _vp), ("per_token_scale", _vp), ("d", _vp),
         ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("flags", _u32),
-        ("d_type", _u32), ("reserved", _u32),
+        ("d_type", _u32), ("pack_axis", _u32),
     ]
 
 
@@ -68,11 +68,13 @@ class MxMatmulArgs(ctypes.Structure):
     _fields_ = [
         ("m", _u32), ("n", _u32), ("k", _u32), ("format", _u32), ("layout_a", _u32), ("layout_b", _u32),
         ("a", _vp), ("b", _vp), ("scale_a", _vp), ("scale_b", _vp), ("d", _vp),
-        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("flags", _u32),
     ]
 
 
 MX_E4M3, MX_E2M1 = 0, 1
+MX_OUT_F32 = 1
+W4_PACKED_ALONG_K, W4_PACKED_ALONG_N = 0, 1
 
 _lib = None
 
@@ -193,36 +195,56 @@ def grouped_fixpipe_dequant(a, b, group_list, d, m, n, k, group_count, quant_mod
 W4A8_SPLIT_K = 1  # flags: split the K range over a CTA cluster (faster, fp32 sums reassociated)
 
 
+def _w4a8_args(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, flags, d_type, pack_axis, workspace):
+    return W4A8MatmulArgs(m=m, n=n, k=k, group_size=group_size, a=_p(a), w_packed=_p(w_packed),
+                          weight_scale=_p(weight_scale), per_token_scale=_p(per_token), d=_p(d),
+                          workspace=_p(workspace),
+                          workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(),
+                          block_num=0, flags=flags, d_type=d_type, pack_axis=pack_axis)
+
+
+def w4a8_matmul_workspace_size(m, n, k, group_size, pack_axis=W4_PACKED_ALONG_K, aligned=True):
+    """Bytes the call needs (0 on the fast path). `aligned`: the operand pointers are 16-byte aligned."""
+    ptr = 256 if aligned else 257
+    args = W4A8MatmulArgs(m=m, n=n, k=k, group_size=group_size, a=ptr, w_packed=ptr, weight_scale=256,
+                          per_token_scale=256, d=256, pack_axis=pack_axis)
+    return int(load().cb200_w4a8_matmul_workspace_size(ctypes.byref(args)))
+
+
 def w4a8_matmul(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, stream=None, split_k=False,
-                static_weights=False, d_type=DTYPE_BF16):
+                static_weights=False, d_type=DTYPE_BF16, pack_axis=W4_PACKED_ALONG_K, workspace=None):
     flags = (W4A8_SPLIT_K if split_k else 0) | (FLAG_STATIC_WEIGHTS if static_weights else 0)
-    args = W4A8MatmulArgs(m=m, n=n, k=k, group_size=group_size, a=_p(a), w_packed=_p(w_packed),
-                          weight_scale=_p(weight_scale), per_token_scale=_p(per_token), d=_p(d), workspace=None,
-                          workspace_bytes=0, block_num=0, flags=flags, d_type=d_type, reserved=0)
+    args = _w4a8_args(a, w_packed, weight_scale, per_token, d, m, n, k, group_size, flags, d_type, pack_axis, workspace)
     _check("cb200_w4a8_matmul", load().cb200_w4a8_matmul(ctypes.byref(args), _stream(stream)))
 
 
-def mx_matmul_workspace_size(m, n, k, fmt):
-    args = MxMatmulArgs(m=m, n=n, k=k, format=fmt, layout_a=ROW_MAJOR, layout_b=COLUMN_MAJOR, a=256, b=256,
+def _mx_args(a, b, scale_a, scale_b, d, m, n, k, fmt, workspace, layout_a, layout_b, out_f32):
+    return MxMatmulArgs(m=m, n=n, k=k, format=fmt, layout_a=layout_a, layout_b=layout_b, a=_p(a), b=_p(b),
+                        scale_a=_p(scale_a), scale_b=_p(scale_b), d=_p(d), workspace=_p(workspace),
+                        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(),
+                        block_num=0, flags=MX_OUT_F32 if out_f32 else 0)
+
+
+def mx_matmul_workspace_size(m, n, k, fmt, layout_a=ROW_MAJOR, layout_b=COLUMN_MAJOR):
+    args = MxMatmulArgs(m=m, n=n, k=k, format=fmt, layout_a=layout_a, layout_b=layout_b, a=256, b=256,
                         scale_a=256, scale_b=256, d=256)
     return int(load().cb200_mx_matmul_workspace_size(ctypes.byref(args)))
 
 
-def mx_matmul(a, b, scale_a, scale_b, d, m, n, k, fmt, workspace, stream=None):
-    """a: [m][k] elements (E2M1: k/2 bytes per row), b: [n][k] (column-major B); scales [rows][k/32] bytes.
+def mx_matmul(a, b, scale_a, scale_b, d, m, n, k, fmt, workspace, stream=None, layout_a=ROW_MAJOR,
+              layout_b=COLUMN_MAJOR, out_f32=False):
+    """a: [m][k] elements, or [k][m] with layout_a = COLUMN_MAJOR; b: [n][k] (column-major B), or [k][n] with
+    layout_b = ROW_MAJOR; E2M1: two elements per byte along the contiguous axis.  Scales follow the operand:
+    [rows][KS] bytes, or [KS/2][rows][2] for an operand stored with k first (KS = even number of 32-blocks).
     workspace: a CUDA byte tensor of at least mx_matmul_workspace_size bytes."""
-    args = MxMatmulArgs(m=m, n=n, k=k, format=fmt, layout_a=ROW_MAJOR, layout_b=COLUMN_MAJOR, a=_p(a), b=_p(b),
-                        scale_a=_p(scale_a), scale_b=_p(scale_b), d=_p(d), workspace=_p(workspace),
-                        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(),
-                        block_num=0, reserved=0)
+    args = _mx_args(a, b, scale_a, scale_b, d, m, n, k, fmt, workspace, layout_a, layout_b, out_f32)
     _check("cb200_mx_matmul", load().cb200_mx_matmul(ctypes.byref(args), _stream(stream)))
 
 
-def mx_matmul_static(a, b, scale_a, scale_b, d, m, n, k, fmt, stream=None):
-    """cb200_mx_matmul_static: as mx_matmul, scale scratch inside the library image, no workspace argument."""
-    args = MxMatmulArgs(m=m, n=n, k=k, format=fmt, layout_a=ROW_MAJOR, layout_b=COLUMN_MAJOR, a=_p(a), b=_p(b),
-                        scale_a=_p(scale_a), scale_b=_p(scale_b), d=_p(d), workspace=None, workspace_bytes=0,
-                        block_num=0, reserved=0)
+def mx_matmul_static(a, b, scale_a, scale_b, d, m, n, k, fmt, stream=None, layout_a=ROW_MAJOR,
+                     layout_b=COLUMN_MAJOR, out_f32=False):
+    """cb200_mx_matmul_static: as mx_matmul, scratch inside the library image, no workspace argument."""
+    args = _mx_args(a, b, scale_a, scale_b, d, m, n, k, fmt, None, layout_a, layout_b, out_f32)
     _check("cb200_mx_matmul_static", load().cb200_mx_matmul_static(ctypes.byref(args), _stream(stream)))
 
 

@@ -13,6 +13,7 @@
 #include "w8a8_smallm.cuh"
 #include "w4a8_gemm.cuh"
 #include "mx_gemm.cuh"
+#include "ingest.cuh"
 
 using namespace cb200;
 using namespace cb200::host;
@@ -553,23 +554,42 @@ int run_w8a8(const W8A8Problem& q, void* stream_v)
     return b_mn ? launch_w8a8<128, true>(q, *dev, stream) : launch_w8a8<128, false>(q, *dev, stream);
 }
 
-int check_w4a8(const cb200_w4a8_matmul_args* a)
+inline uint64_t align256(uint64_t v)
+{
+    return (v + 255u) & ~static_cast<uint64_t>(255u);
+}
+
+// How a W4A8 call is served: in place (fast path), or through the ingestion pre-pass that writes K-padded,
+// K-packed copies of both operands into the workspace.
+struct W4Plan {
+    bool ingest;
+    uint32_t k_padded;    // K the kernel runs on: a whole number of scale groups of 128-element blocks
+    uint32_t group_size;  // scale group the kernel runs with
+    uint64_t a_bytes, w_bytes;
+};
+
+int plan_w4a8(const cb200_w4a8_matmul_args* a, W4Plan* plan)
 {
     if (a == nullptr) {
         return CB200_INVALID;
     }
     if (a->m == 0 || a->n == 0) {
+        plan->ingest = false;
         return CB200_SUCCESS;
     }
     if (a->a == nullptr || a->w_packed == nullptr || a->weight_scale == nullptr || a->per_token_scale == nullptr ||
         a->d == nullptr) {
         return CB200_INVALID;
     }
-    if (a->k == 0 || a->group_size == 0 || (a->k % 128u) != 0 || (a->group_size % 128u) != 0 ||
-        (a->k % a->group_size) != 0) {
+    if (a->k == 0 || a->group_size == 0 || a->pack_axis > CB200_W4_PACKED_ALONG_N) {
         return CB200_INVALID;
     }
-    if (a->group_size > 16384u) {  // 16 x the int32 sum of a group must stay exactly convertible to fp32
+    const bool one_group = a->group_size >= a->k;
+    if (!one_group && (a->group_size % 128u) != 0) {
+        return CB200_INVALID;
+    }
+    // 16 x the int32 sum of a group must stay exactly convertible to fp32: at most 16384 elements per group
+    if ((one_group ? a->k : a->group_size) > 16384u) {
         return CB200_INVALID;
     }
     if (a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u) {
@@ -578,29 +598,40 @@ int check_w4a8(const cb200_w4a8_matmul_args* a)
     if (a->d_type != 0 && a->d_type != CB200_DTYPE_BF16 && a->d_type != CB200_DTYPE_F16) {
         return CB200_INVALID;
     }
-    if (!aligned16(a->a) || !aligned16(a->w_packed) || (reinterpret_cast<uintptr_t>(a->d) & 1u) != 0 ||
-        (reinterpret_cast<uintptr_t>(a->weight_scale) & 3u) != 0 ||
+    if ((reinterpret_cast<uintptr_t>(a->d) & 1u) != 0 || (reinterpret_cast<uintptr_t>(a->weight_scale) & 3u) != 0 ||
         (reinterpret_cast<uintptr_t>(a->per_token_scale) & 3u) != 0) {
         return CB200_INVALID;
     }
     if ((a->n & 7u) == 0 && !aligned16(a->d)) {
-        return CB200_INVALID;  // vector stores of 8 bf16
+        return CB200_INVALID;  // vector stores of 8 outputs
     }
+    const uint32_t unit = one_group ? 128u : a->group_size;
+    plan->k_padded = (a->k + unit - 1u) / unit * unit;
+    plan->group_size = one_group ? plan->k_padded : a->group_size;
+    plan->ingest = a->pack_axis != CB200_W4_PACKED_ALONG_K || plan->k_padded != a->k || !aligned16(a->a) ||
+                   !aligned16(a->w_packed);
+    plan->a_bytes = align256(static_cast<uint64_t>(a->m) * plan->k_padded);
+    plan->w_bytes = align256(static_cast<uint64_t>(a->n) * (plan->k_padded / 2u));
     return CB200_SUCCESS;
 }
 
-uint64_t mx_workspace_bytes(const cb200_mx_matmul_args* a)
-{
-    const uint64_t kq = a->k / 128u;
-    // scale blocks of 128 rows; B's are padded to whole 256-column tiles
-    return (static_cast<uint64_t>((a->m + 127u) / 128u) + 2u * ((a->n + 255u) / 256u)) * kq * 512u;
-}
+// How an MX call is served.  The kernel wants both operands with rows along K, padded to whole K stages
+// (128 E4M3 / 256 E2M1 elements) and 16-byte aligned; an operand that is not is rewritten by the ingestion
+// pre-pass into the workspace, behind the re-tiled scales.
+struct MxPlan {
+    uint32_t k_padded;
+    uint32_t row_bytes;     // bytes of one padded operand row
+    bool ingest_a, ingest_b;
+    uint64_t sf_bytes, a_bytes, b_bytes;
+    uint64_t total() const { return sf_bytes + (ingest_a ? a_bytes : 0) + (ingest_b ? b_bytes : 0); }
+};
 
-int check_mx(const cb200_mx_matmul_args* a)
+int plan_mx(const cb200_mx_matmul_args* a, MxPlan* plan)
 {
     if (a == nullptr) {
         return CB200_INVALID;
     }
+    *plan = MxPlan{};
     if (a->m == 0 || a->n == 0) {
         return CB200_SUCCESS;
     }
@@ -610,38 +641,84 @@ int check_mx(const cb200_mx_matmul_args* a)
     if (a->format != CB200_MX_E4M3 && a->format != CB200_MX_E2M1) {
         return CB200_INVALID;
     }
-    if (a->layout_a != CB200_ROW_MAJOR || a->layout_b != CB200_COLUMN_MAJOR) {
-        return CB200_INVALID;  // both operands K-contiguous, as the block scales run along K
-    }
-    const uint32_t kmul = a->format == CB200_MX_E2M1 ? 256u : 128u;
-    if (a->k == 0 || (a->k % kmul) != 0) {
+    if ((a->layout_a != CB200_ROW_MAJOR && a->layout_a != CB200_COLUMN_MAJOR) ||
+        (a->layout_b != CB200_ROW_MAJOR && a->layout_b != CB200_COLUMN_MAJOR)) {
         return CB200_INVALID;
     }
-    if (a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u) {
+    if ((a->flags & ~CB200_MX_OUT_F32) != 0) {
         return CB200_INVALID;
     }
-    if (!aligned16(a->a) || !aligned16(a->b) || (reinterpret_cast<uintptr_t>(a->scale_a) & 3u) != 0 ||
-        (reinterpret_cast<uintptr_t>(a->scale_b) & 3u) != 0 || (reinterpret_cast<uintptr_t>(a->d) & 1u) != 0) {
+    if (a->k == 0 || a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u) {
         return CB200_INVALID;
     }
-    if ((a->n & 7u) == 0 && !aligned16(a->d)) {
+    const bool f32 = (a->flags & CB200_MX_OUT_F32) != 0;
+    if ((reinterpret_cast<uintptr_t>(a->d) & (f32 ? 3u : 1u)) != 0) {
         return CB200_INVALID;
     }
+    if (((a->n & (f32 ? 3u : 7u)) == 0) && !aligned16(a->d)) {
+        return CB200_INVALID;  // 16-byte vector stores
+    }
+    const bool fp4 = a->format == CB200_MX_E2M1;
+    const uint32_t kmul = fp4 ? 256u : 128u;
+    plan->k_padded = (a->k + kmul - 1u) / kmul * kmul;
+    plan->row_bytes = fp4 ? plan->k_padded / 2u : plan->k_padded;
+    plan->ingest_a = a->layout_a != CB200_ROW_MAJOR || plan->k_padded != a->k || !aligned16(a->a);
+    plan->ingest_b = a->layout_b != CB200_COLUMN_MAJOR || plan->k_padded != a->k || !aligned16(a->b);
+    const uint64_t kq = plan->k_padded / 128u;
+    // scale blocks of 128 rows; B's are padded to whole 256-column tiles
+    plan->sf_bytes = (static_cast<uint64_t>((a->m + 127u) / 128u) + 2u * ((a->n + 255u) / 256u)) * kq * 512u;
+    plan->a_bytes = align256(static_cast<uint64_t>(a->m) * plan->row_bytes);
+    plan->b_bytes = align256(static_cast<uint64_t>(a->n) * plan->row_bytes);
     return CB200_SUCCESS;
 }
 
-template <bool kFp4>
-int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStream_t stream)
+// One operand into its canonical form: `rows` rows of row_bytes bytes along K.
+// stored_k_major: the caller's array is [k][rows] (elements, packed two per byte along `rows` for E2M1).
+void ingest_mx_operand(const void* src, uint8_t* dst, uint32_t rows, uint32_t k, bool fp4, bool stored_k_major,
+                       uint32_t row_bytes, int sm_count, cudaStream_t stream)
 {
-    const uint32_t row_bytes = kFp4 ? args->k / 2u : args->k;
+    const uint8_t* s = static_cast<const uint8_t*>(src);
+    const uint32_t blocks = static_cast<uint32_t>(sm_count) * 8u;
+    if (!stored_k_major) {
+        const uint32_t valid = fp4 ? (k + 1u) / 2u : k;
+        pad_rows_kernel<<<blocks, 256, 0, stream>>>(s, dst, rows, valid, row_bytes, valid, fp4 ? (k & 1u) : 0u);
+    } else if (fp4) {
+        transpose_nibbles_kernel<<<blocks, 256, 0, stream>>>(s, dst, rows, k, (rows + 1u) / 2u, row_bytes);
+    } else {
+        transpose_bytes_kernel<<<blocks, dim3(32, 8), 0, stream>>>(s, dst, rows, k, rows, row_bytes);
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+template <bool kFp4>
+int launch_mx(const cb200_mx_matmul_args* args, const MxPlan& plan, const DeviceState& dev, cudaStream_t stream)
+{
+    uint8_t* ws = static_cast<uint8_t*>(args->workspace);
+    const void* a_ptr = args->a;
+    const void* b_ptr = args->b;
+    {
+        uint8_t* next = ws + plan.sf_bytes;
+        if (plan.ingest_a) {
+            ingest_mx_operand(args->a, next, args->m, args->k, kFp4, args->layout_a == CB200_COLUMN_MAJOR,
+                              plan.row_bytes, dev.sm_count, stream);
+            a_ptr = next;
+            next += plan.a_bytes;
+        }
+        if (plan.ingest_b) {
+            ingest_mx_operand(args->b, next, args->n, args->k, kFp4, args->layout_b == CB200_ROW_MAJOR, plan.row_bytes,
+                              dev.sm_count, stream);
+            b_ptr = next;
+        }
+    }
+    const uint32_t row_bytes = plan.row_bytes;
     MxParams p;
     p.m = args->m;
     p.n = args->n;
-    p.k = args->k;
+    p.k = plan.k_padded;
     p.fp4 = kFp4 ? 1u : 0u;
     p.num_k_blocks = row_bytes / 128u;
     p.words_per_stage = kFp4 ? 2u : 1u;
-    p.kq_total = args->k / 128u;
+    p.kq_total = plan.k_padded / 128u;
     // a band of the tile order holds ~32 MB of A (measured best at 8192^3: 32 row panels for fp8): its row panels
     // stay in L2 while the band's columns go by
     p.band_rows = (32u << 20) / (128u * (row_bytes > 0 ? row_bytes : 1u));
@@ -652,19 +729,23 @@ int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStre
             p.band_rows = v;
         }
     }
-    uint8_t* ws = static_cast<uint8_t*>(args->workspace);
     const uint64_t sfa_bytes = static_cast<uint64_t>((args->m + 127u) / 128u) * p.kq_total * 512u;
     p.sfa = ws;
     p.sfb = ws + sfa_bytes;
-    p.d = static_cast<__nv_bfloat16*>(args->d);
+    p.d = args->d;
     p.status = dev.status;
+    p.out_f32 = (args->flags & CB200_MX_OUT_F32) ? 1u : 0u;
 
-    const uint32_t kblocks = args->k / 32u;
-    mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(static_cast<const uint8_t*>(args->scale_a), ws,
-                                                                args->m, kblocks, (args->m + 127u) / 128u);
-    mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(static_cast<const uint8_t*>(args->scale_b),
-                                                                ws + sfa_bytes, args->n, kblocks,
-                                                                2u * ((args->n + 255u) / 256u));
+    // the caller's scale arrays: ceil(k/32) blocks per row, held in an even number of columns; stored along the
+    // operand's rows, or K-major when the operand itself is stored K-major
+    const uint32_t kblocks = (args->k + 31u) / 32u;
+    const uint32_t ks_pitch = (kblocks + 1u) & ~1u;
+    mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(
+        static_cast<const uint8_t*>(args->scale_a), ws, args->m, kblocks, ks_pitch, p.kq_total, (args->m + 127u) / 128u,
+        args->layout_a == CB200_COLUMN_MAJOR ? 1u : 0u);
+    mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(
+        static_cast<const uint8_t*>(args->scale_b), ws + sfa_bytes, args->n, kblocks, ks_pitch, p.kq_total,
+        2u * ((args->n + 255u) / 256u), args->layout_b == CB200_ROW_MAJOR ? 1u : 0u);
     CB200_CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(2, std::memory_order_relaxed);
 
@@ -673,7 +754,7 @@ int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStre
         const uint64_t dims[2] = {row_bytes, args->m};
         const uint64_t strides[1] = {row_bytes};
         const uint32_t box[2] = {kBlockKBytes, kBlockM};
-        int rc = encode_tmap_u8(&tmap_a, args->a, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        int rc = encode_tmap_u8(&tmap_a, a_ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != CB200_SUCCESS) {
             return rc;
         }
@@ -682,7 +763,7 @@ int launch_mx(const cb200_mx_matmul_args* args, const DeviceState& dev, cudaStre
         const uint64_t dims[2] = {row_bytes, args->n};
         const uint64_t strides[1] = {row_bytes};
         const uint32_t box[2] = {kBlockKBytes, kMxBlockN};
-        int rc = encode_tmap_u8(&tmap_b, args->b, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        int rc = encode_tmap_u8(&tmap_b, b_ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != CB200_SUCCESS) {
             return rc;
         }
@@ -721,24 +802,27 @@ extern "C" {
 
 int cb200_mx_matmul_can_implement(const cb200_mx_matmul_args* args)
 {
-    return check_mx(args);
+    MxPlan plan;
+    return plan_mx(args, &plan);
 }
 
 uint64_t cb200_mx_matmul_workspace_size(const cb200_mx_matmul_args* args)
 {
-    if (args == nullptr || check_mx(args) != CB200_SUCCESS) {
+    MxPlan plan;
+    if (plan_mx(args, &plan) != CB200_SUCCESS) {
         return 0;
     }
-    return mx_workspace_bytes(args);
+    return plan.total();
 }
 
 int cb200_mx_matmul(const cb200_mx_matmul_args* args, void* stream_v)
 {
-    int rc = check_mx(args);
+    MxPlan plan;
+    int rc = plan_mx(args, &plan);
     if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
         return rc;
     }
-    if (args->workspace == nullptr || args->workspace_bytes < mx_workspace_bytes(args) ||
+    if (args->workspace == nullptr || args->workspace_bytes < plan.total() ||
         (reinterpret_cast<uintptr_t>(args->workspace) & 255u) != 0) {
         return CB200_INVALID;
     }
@@ -748,24 +832,33 @@ int cb200_mx_matmul(const cb200_mx_matmul_args* args, void* stream_v)
         return rc;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    return args->format == CB200_MX_E2M1 ? launch_mx<true>(args, *dev, stream) : launch_mx<false>(args, *dev, stream);
+    return args->format == CB200_MX_E2M1 ? launch_mx<true>(args, plan, *dev, stream)
+                                         : launch_mx<false>(args, plan, *dev, stream);
 }
 
 int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args* args)
 {
-    return check_w4a8(args);
+    W4Plan plan;
+    return plan_w4a8(args, &plan);
 }
 
 uint64_t cb200_w4a8_matmul_workspace_size(const cb200_w4a8_matmul_args* args)
 {
-    (void)args;
-    return 0;  // weights are unpacked between two shared-memory buffers, never through global memory
+    // Fast path (weights packed along K, K a whole number of 128-element blocks, 16-byte aligned operands): the
+    // weights are unpacked between two shared-memory buffers and nothing goes through global memory.  Otherwise
+    // the ingestion pre-pass needs room for the K-padded copies of A and W.
+    W4Plan plan;
+    if (plan_w4a8(args, &plan) != CB200_SUCCESS || args->m == 0 || args->n == 0 || !plan.ingest) {
+        return 0;
+    }
+    return plan.a_bytes + plan.w_bytes;
 }
 
-int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
+int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args_in, void* stream_v)
 {
-    int rc = check_w4a8(args);
-    if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
+    W4Plan plan;
+    int rc = plan_w4a8(args_in, &plan);
+    if (rc != CB200_SUCCESS || args_in->m == 0 || args_in->n == 0) {
         return rc;
     }
     DeviceState* dev = nullptr;
@@ -773,6 +866,36 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
     if (rc != CB200_SUCCESS) {
         return rc;
     }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    cb200_w4a8_matmul_args local = *args_in;
+    const cb200_w4a8_matmul_args* args = &local;
+    if (plan.ingest) {
+        if (args_in->workspace == nullptr || args_in->workspace_bytes < plan.a_bytes + plan.w_bytes ||
+            (reinterpret_cast<uintptr_t>(args_in->workspace) & 255u) != 0) {
+            return CB200_INVALID;
+        }
+        uint8_t* a_pad = static_cast<uint8_t*>(args_in->workspace);
+        uint8_t* w_pad = a_pad + plan.a_bytes;
+        const uint32_t blocks = static_cast<uint32_t>(dev->sm_count) * 8u;
+        pad_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(args_in->a), a_pad, args_in->m,
+                                                    args_in->k, plan.k_padded, args_in->k, 0);
+        if (args_in->pack_axis == CB200_W4_PACKED_ALONG_K) {
+            pad_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(args_in->w_packed), w_pad,
+                                                        args_in->n, (args_in->k + 1u) / 2u, plan.k_padded / 2u,
+                                                        (args_in->k + 1u) / 2u, args_in->k & 1u);
+        } else {
+            transpose_nibbles_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(args_in->w_packed), w_pad,
+                                                                 args_in->n, args_in->k, (args_in->n + 1u) / 2u,
+                                                                 plan.k_padded / 2u);
+        }
+        CB200_CUDA_TRY(cudaGetLastError());
+        g_launches.fetch_add(2, std::memory_order_relaxed);
+        local.a = a_pad;
+        local.w_packed = w_pad;
+        local.k = plan.k_padded;
+        local.flags &= ~CB200_FLAG_STATIC_WEIGHTS;  // the kernel's weights now come from the pre-pass on this stream
+    }
+    local.group_size = plan.group_size;
     W4A8Params p;
     p.m = args->m;
     p.n = args->n;
@@ -851,7 +974,6 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args, void* stream_v)
         return rc;
     }
     const dim3 grid(tiles_n * p.splits, (args->m + p.tile_m - 1) / p.tile_m, 1);
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kW4Threads, 1, 1);
@@ -1056,11 +1178,6 @@ struct HostPipe {
     int64_t* lists_host = nullptr;  // pinned: [chunks][group_count] chunk-local prefix sums
     size_t lists_capacity = 0;
 };
-
-inline uint64_t align256(uint64_t v)
-{
-    return (v + 255u) & ~static_cast<uint64_t>(255u);
-}
 
 struct HostLayout {
     uint64_t a, pt, d, lists, total;
@@ -1298,11 +1415,12 @@ uint64_t cb200_mx_matmul_static_scratch_bytes(void)
 // Allocates nothing.  The first call on a device performs the address look-up above.
 int cb200_mx_matmul_static(const cb200_mx_matmul_args* args, void* stream_v)
 {
-    int rc = check_mx(args);
+    MxPlan plan;
+    int rc = plan_mx(args, &plan);
     if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
         return rc;
     }
-    if (mx_workspace_bytes(args) > kMxStaticScratchBytes) {
+    if (plan.total() > kMxStaticScratchBytes) {
         return CB200_SCRATCH_TOO_SMALL;
     }
     DeviceState* dev = nullptr;
@@ -1319,11 +1437,23 @@ int cb200_mx_matmul_static(const cb200_mx_matmul_args* args, void* stream_v)
     with_scratch.workspace = scratch;
     with_scratch.workspace_bytes = kMxStaticScratchBytes;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    return args->format == CB200_MX_E2M1 ? launch_mx<true>(&with_scratch, *dev, stream)
-                                         : launch_mx<false>(&with_scratch, *dev, stream);
+    return args->format == CB200_MX_E2M1 ? launch_mx<true>(&with_scratch, plan, *dev, stream)
+                                         : launch_mx<false>(&with_scratch, plan, *dev, stream);
 }
 
 }  // extern "C"
+
+#ifdef CB200_DEVELOPER_KNOBS
+// Developer builds only: reads and clears the W4A8 kernel's per-role cycle counters.
+extern "C" CB200_API int cb200_dev_w4a8_probe(unsigned long long* out)
+{
+    CB200_CUDA_TRY(cudaDeviceSynchronize());
+    CB200_CUDA_TRY(cudaMemcpyFromSymbol(out, cb200::g_w4a8_probe, 64 * sizeof(unsigned long long)));
+    unsigned long long zero[64] = {};
+    CB200_CUDA_TRY(cudaMemcpyToSymbol(cb200::g_w4a8_probe, zero, sizeof(zero)));
+    return CB200_SUCCESS;
+}
+#endif
 
 namespace {
 // One thread waits on an mbarrier that nobody will ever arrive on, with a short limit: exercises exactly the

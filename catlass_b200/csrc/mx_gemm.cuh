@@ -13,12 +13,14 @@
 //                          into the tile order the tensor core's scale copy wants: per 128 rows x 4 scale
 //                          blocks a 512-byte block [row % 32][row / 32][4 bytes].  Output goes to the
 //                          caller-provided workspace; B's blocks are padded to a whole number of 256-wide tiles.
-//   mx_gemm_kernel         persistent, warp-specialised like the W8A8 kernel: TMA producer (operand tiles +
-//                          packed scale blocks), one MMA thread (tcgen05.cp scale blocks smem -> TMEM, then the
-//                          block-scaled MMAs), four epilogue warps (fp32 -> bf16).  Tile 128 x 256 with ONE
+//   mx_gemm_kernel         persistent, warp-specialised like the W8A8 kernel, twelve warps: TMA producer (operand
+//                          tiles + packed scale blocks), MMA issuer (the block-scaled MMAs), two scale copier
+//                          threads (tcgen05.cp scale blocks smem -> TMEM, off the MMA thread), eight epilogue warps
+//                          (two per TMEM lane quarter; fp32 -> bf16, or fp32 as it is).  Tile 128 x 256 with ONE
 //                          accumulator: a 128 x 128 MMA would run shorter than issuing it takes (~70 ns), which
 //                          capped 128-wide tiles at half the tensor rate; 256 columns plus the scale columns do
-//                          not leave room for a second accumulator, so the short epilogue is not overlapped.
+//                          not leave room for a second accumulator, so the epilogue pulls its columns out of TMEM
+//                          first, hands the accumulator back, and stores afterwards.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -42,8 +44,9 @@ struct MxParams {
     uint32_t band_rows;        // tile rows per band of the tile order (see mx_tile_coords)
     const uint8_t* sfa;        // packed scales of A: [ceil(m/128)][kq_total][512]
     const uint8_t* sfb;        // packed scales of B: [ceil(n/128)][kq_total][512]
-    __nv_bfloat16* d;
+    void* d;                   // [m][n] bf16, or fp32 when out_f32
     unsigned* status;
+    uint32_t out_f32;
 };
 
 struct MxSmem {
@@ -57,13 +60,19 @@ struct MxSmem {
     static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
 };
 
-// in : [rows][kblocks] bytes (kblocks = K/32), out: [ceil(rows/128)][kblocks/4][512]
-// Rows past the end get the neutral scale 2^0.
+// Re-tiles one operand's scale bytes: out is [row_blocks][kq_total][512], one 512-byte block per 128 rows x 4 scale
+// blocks, laid out [row % 32][row / 32][4 bytes].  The input is either
+//   rows-major  [rows][ks_pitch] bytes (the operand's rows run along K: A row-major, B column-major), or
+//   k-major     [ks_pitch / 2][rows][2] bytes (the operand is stored the other way round),
+// the reference's two scale layouts (tests/optest/tests/mx_golden.py:253-266), with ks_pitch = the even number of
+// scale blocks per row the caller's array holds.  Blocks at or beyond `kblocks_valid` = ceil(K / 32), and rows
+// past the end, get the neutral scale 2^0 (their elements are zero).
 __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t rows,
-                                      uint32_t kblocks, uint32_t row_blocks)
+                                      uint32_t kblocks_valid, uint32_t ks_pitch, uint32_t kq_total,
+                                      uint32_t row_blocks, uint32_t k_major)
 {
-    const uint32_t kq_total = kblocks / 4;
     const size_t words = static_cast<size_t>(row_blocks) * kq_total * 128;
+    const bool word_loads = !k_major && (ks_pitch & 3u) == 0 && (reinterpret_cast<uintptr_t>(in) & 3u) == 0;
     for (size_t w = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; w < words;
          w += static_cast<size_t>(gridDim.x) * blockDim.x) {
         // consecutive threads walk consecutive scale words of one row: coalesced reads
@@ -71,7 +80,21 @@ __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* _
         const uint32_t row = static_cast<uint32_t>(w / kq_total);  // padded row index
         uint32_t v = 0x7F7F7F7Fu;
         if (row < rows) {
-            v = *reinterpret_cast<const uint32_t*>(in + static_cast<size_t>(row) * kblocks + kq * 4);
+            if (word_loads && kq * 4 + 4 <= kblocks_valid) {
+                v = *reinterpret_cast<const uint32_t*>(in + static_cast<size_t>(row) * ks_pitch + kq * 4);
+            } else {
+                v = 0;
+#pragma unroll
+                for (uint32_t b = 0; b < 4; ++b) {
+                    const uint32_t kb = kq * 4 + b;
+                    uint32_t byte = 0x7Fu;
+                    if (kb < kblocks_valid) {
+                        byte = k_major ? in[(static_cast<size_t>(kb >> 1) * rows + row) * 2 + (kb & 1u)]
+                                       : in[static_cast<size_t>(row) * ks_pitch + kb];
+                    }
+                    v |= byte << (8 * b);
+                }
+            }
         }
         const uint32_t rb = row / 128, r = row % 128;
         uint8_t* dst = out + (static_cast<size_t>(rb) * kq_total + kq) * 512 + (r % 32) * 16 + (r / 32) * 4;
@@ -310,7 +333,46 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t row = mt * kBlockM + quad * 32 + lane;
             const bool row_ok = row < p.m;
             const uint32_t taddr = tmem_base + acc * kMxBlockN + half * 128 + ((quad * 32u) << 16);
-            __nv_bfloat16* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
+            if (p.out_f32) {
+                // fp32 output (what the reference's MX kernels write): the accumulator goes out as it is, 32 columns
+                // at a time, before the accumulator is handed back (nothing to round, nothing to keep in registers)
+                float* frow = static_cast<float*>(p.d) + static_cast<size_t>(row_ok ? row : 0) * p.n;
+                const uint32_t col_base = nt * kMxBlockN + half * 128;
+                const bool vec4 = (p.n & 3u) == 0;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                    const uint32_t col0 = col_base + c * 32;
+                    if (row_ok && col0 < p.n) {
+                        if (vec4 && col0 + 32 <= p.n) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v) {
+                                *reinterpret_cast<uint4*>(frow + col0 + v * 4) =
+                                    make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j) {
+                                if (col0 + j < p.n) {
+                                    frow[col0 + j] = __uint_as_float(r[j]);
+                                }
+                            }
+                        }
+                    }
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_tmem_empty + acc * 8);
+                }
+                if (++acc == kMxAccs) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+                continue;
+            }
+            __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + static_cast<size_t>(row_ok ? row : 0) * p.n;
             uint32_t packed[64];  // bf16 pairs: columns 2i, 2i+1 of this warp's 128
 #pragma unroll
             for (int c = 0; c < 4; ++c) {

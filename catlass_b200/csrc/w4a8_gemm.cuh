@@ -27,12 +27,13 @@
 //
 // Warp roles (16 warps):
 //   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 12 in flight: they come from HBM) and token
-//               tiles (mt x 128 B, 4 in flight: they come from L2), one thread and one ring each, two
-//               consecutive K blocks per load (3-D boxes)
+//               tiles (mt x 128 B, as many as fit 64 KB: 8 for 64 tokens; they come from L2), one thread and one
+//               ring each, two consecutive K blocks per load (3-D boxes)
 //   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x mt x 32); one-block scale groups alternate between them
 //               (issuing an MMA costs its thread ~70 ns), longer groups are all issued by warp 1.  A group
-//               accumulates into one of four int32 accumulators in TMEM.  Per K block one commit frees
-//               the token tile and the unpacked tile; per group one more hands the accumulator to the epilogue.
+//               accumulates into one of four int32 accumulators in TMEM.  Per K block one commit frees the
+//               unpacked tile and one its half of the token load; per group one more hands the accumulator to the
+//               epilogue.
 //   warps 2-5   unpack: nibble -> int8 holding 16*w (the nibble moved to the high half of the byte: no sign
 //               fix-up needed), written in the 128B-swizzled K-major operand layout, then handed to the MMA
 //               through a proxy fence + mbarrier.  The factor 16 is removed again, exactly, when the epilogue
@@ -61,7 +62,22 @@ constexpr int kW4PackedSlots = 12;  // packed-weight tiles in flight (8 KB each)
 constexpr int kW4MaxSplits = 4;     // CTAs of a cluster sharing one channel tile along K
 constexpr int kW4Load = 2;          // K blocks per TMA load (3-D boxes): half the loads and barrier round trips
 constexpr int kW4PackedLoads = kW4PackedSlots / kW4Load;  // load slots of the packed-weight ring
-constexpr int kW4TokenLoads = kW4Tiles / kW4Load;         // load slots of the token ring
+constexpr int kW4MaxTokenLoads = 8;                       // load slots of the token ring at most (see x_loads)
+
+#ifdef CB200_DEVELOPER_KNOBS
+// Developer builds only: per-role cycle counters of CTA 0 (where each role of the pipeline spends its time).
+__device__ unsigned long long g_w4a8_probe[64];
+#define W4_PROBE_BEGIN() const long long probe_t0__ = clock64()
+#define W4_PROBE_END(slot)                                                                    \
+    do {                                                                                      \
+        if (blockIdx.x == 0 && blockIdx.y == 0) {                                             \
+            atomicAdd(&g_w4a8_probe[slot], static_cast<unsigned long long>(clock64() - probe_t0__)); \
+        }                                                                                     \
+    } while (0)
+#else
+#define W4_PROBE_BEGIN() do { } while (0)
+#define W4_PROBE_END(slot) do { } while (0)
+#endif
 
 struct W4A8Params {
     uint32_t m, n, k;
@@ -90,9 +106,9 @@ struct W4A8Smem {
     // partial sums: (splits - 1) x (128 / splits) token columns x 128 channels x fp32 <= 48 KB
     static constexpr int kLandingBytes =
         kW4Tokens * kW4Channels * 4 + (kW4MaxSplits - 1) * (kW4Tokens / kW4MaxSplits) * kW4Channels * 4;
-    // p_full, p_empty [packed loads]; x_full [token loads]; c_full, tiles_free [tiles]; acc_full, acc_empty
-    // [accumulator pairs]
-    static constexpr int kBarriers = 2 * kW4PackedLoads + kW4TokenLoads + 2 * kW4Tiles + 2 * kW4AccPairs;
+    // p_full, p_empty [packed loads]; x_full, x_free [token loads]; c_full, tiles_free [tiles]; acc_full,
+    // acc_empty [accumulator pairs]
+    static constexpr int kBarriers = 2 * kW4PackedLoads + 2 * kW4MaxTokenLoads + 2 * kW4Tiles + 2 * kW4AccPairs;
     static constexpr int kBarrierBytes = kBarriers * 8 + 16;
     static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
 };
@@ -188,8 +204,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t bar_p_full = smem_u32(s_bars);                    // packed tile landed (TMA bytes)
     const uint32_t bar_p_empty = bar_p_full + kW4PackedLoads * 8;    // the unpack warps have read both tiles
     const uint32_t bar_x_full = bar_p_empty + kW4PackedLoads * 8;    // a pair of token tiles landed
-    const uint32_t bar_c_full = bar_x_full + kW4TokenLoads * 8;      // unpacked tile written
-    const uint32_t bar_tiles_free = bar_c_full + kW4Tiles * 8;       // the MMAs that read both tiles completed
+    const uint32_t bar_x_free = bar_x_full + kW4MaxTokenLoads * 8;   // the MMAs that read the pair completed
+    const uint32_t bar_c_full = bar_x_free + kW4MaxTokenLoads * 8;   // unpacked tile written
+    const uint32_t bar_tiles_free = bar_c_full + kW4Tiles * 8;       // the MMAs that read the unpacked tile completed
     const uint32_t bar_acc_full = bar_tiles_free + kW4Tiles * 8;     // all MMAs of a pair of scale groups completed
     const uint32_t bar_acc_empty = bar_acc_full + kW4AccPairs * 8;   // the epilogue has read the pair's accumulators
     uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + S::kBarriers);
@@ -210,6 +227,12 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t kb_begin = g_begin * bpg;
     const uint32_t my_kb = my_groups * bpg;
     constexpr uint32_t kTmemCols = 512;
+    // The token ring (64 KB) holds as many K blocks of mt x 128 bytes as fit: 4 blocks of 128 tokens, 8 of 64, 16 of
+    // fewer.  Token tiles come from L2 with ~1-2 us of latency while every CTA of the grid asks for the same lines,
+    // so the bytes in flight decide the rate; the ring is independent of the four unpacked-tile slots.
+    const uint32_t x_load_bytes = kW4Load * p.mt * 128;
+    const uint32_t x_loads_fit = (kW4Tiles * S::kTokenBytes) / x_load_bytes;
+    const uint32_t x_loads = x_loads_fit < static_cast<uint32_t>(kW4MaxTokenLoads) ? x_loads_fit : kW4MaxTokenLoads;
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
@@ -217,8 +240,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             mbar_init(bar_p_full + i * 8, 1);
             mbar_init(bar_p_empty + i * 8, kW4Load);  // one arrival per tile of the load
         }
-        for (int i = 0; i < kW4TokenLoads; ++i) {
+        for (int i = 0; i < kW4MaxTokenLoads; ++i) {
             mbar_init(bar_x_full + i * 8, 1);
+            mbar_init(bar_x_free + i * 8, kW4Load);  // one commit per K block of the load
         }
         for (int i = 0; i < kW4Tiles; ++i) {
             mbar_init(bar_c_full + i * 8, 1);
@@ -265,8 +289,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
             for (uint32_t l = 0; ok && l < loads; ++l) {
                 const uint32_t slot = l % kW4PackedLoads;
+                W4_PROBE_BEGIN();
                 ok = mbar_wait(bar_p_empty + slot * 8, ((l / kW4PackedLoads) & 1) ^ 1, s_abort, p.status,
                                kDevTimeoutProducer);
+                W4_PROBE_END(0);
                 if (ok) {
                     // kW4Load consecutive K blocks, one 128 x 64 B tile each (a last, odd block brings the
                     // neighbouring block or zeros along: the transaction count is always that of a full box)
@@ -289,18 +315,17 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             bool ok = true;
             const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
             for (uint32_t l = 0; ok && l < loads; ++l) {
-                const uint32_t slot = l % kW4TokenLoads;
-                const uint32_t parity = ((l / kW4TokenLoads) & 1) ^ 1;
-                for (uint32_t h = 0; ok && h < kW4Load; ++h) {  // both tile slots of the load must be free
-                    ok = mbar_wait(bar_tiles_free + (slot * kW4Load + h) * 8, parity, s_abort, p.status,
-                                   kDevTimeoutProducer);
-                }
+                const uint32_t slot = l % x_loads;
+                const uint32_t parity = ((l / x_loads) & 1) ^ 1;
+                W4_PROBE_BEGIN();
+                ok = mbar_wait(bar_x_free + slot * 8, parity, s_abort, p.status, kDevTimeoutProducer);
+                W4_PROBE_END(1);
                 if (ok) {
                     // kW4Load consecutive K blocks of the mt token rows (rows past m read as zeros): the tiles of
                     // a load land back to back, mt * 128 bytes apart
                     const uint32_t full = bar_x_full + slot * 8;
-                    mbar_expect_tx(full, kW4Load * p.mt * 128);
-                    tma_load_3d(ring + S::kTokenRing + slot * (kW4Load * S::kTokenBytes), &tmap_x, full, 0, m0,
+                    mbar_expect_tx(full, x_load_bytes);
+                    tma_load_3d(ring + S::kTokenRing + slot * x_load_bytes, &tmap_x, full, 0, m0,
                                 static_cast<int32_t>(kb_begin + l * kW4Load));
                 }
             }
@@ -319,8 +344,12 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             for (uint32_t j = (warp == 1 ? 0 : 1); ok && j < my_groups; j += kIssuers) {
                 const uint32_t acc = j % kW4Accs;
                 const uint32_t pair = j >> 1, pslot = pair % kW4AccPairs;
-                ok = mbar_wait(bar_acc_empty + pslot * 8, ((pair / kW4AccPairs) & 1) ^ 1, s_abort, p.status,
-                               kDevTimeoutMmaTmem);
+                {
+                    W4_PROBE_BEGIN();
+                    ok = mbar_wait(bar_acc_empty + pslot * 8, ((pair / kW4AccPairs) & 1) ^ 1, s_abort, p.status,
+                                   kDevTimeoutMmaTmem);
+                    W4_PROBE_END(warp == 1 ? 2 : 3);
+                }
                 if (!ok) {
                     break;
                 }
@@ -330,22 +359,35 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     const uint32_t i = j * bpg + b;
                     const uint32_t slot = i % kW4Tiles;
                     const uint32_t ph = (i / kW4Tiles) & 1;
-                    ok = mbar_wait(bar_x_full + (slot / kW4Load) * 8, ph, s_abort, p.status, kDevTimeoutMma) &&
-                         mbar_wait(bar_c_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma);
+                    const uint32_t xl = i / kW4Load;        // token load this block came with
+                    const uint32_t xslot = xl % x_loads;
+                    {
+                        W4_PROBE_BEGIN();
+                        ok = mbar_wait(bar_x_full + xslot * 8, (xl / x_loads) & 1, s_abort, p.status, kDevTimeoutMma);
+                        W4_PROBE_END(warp == 1 ? 4 : 5);
+                    }
+                    {
+                        W4_PROBE_BEGIN();
+                        ok = ok && mbar_wait(bar_c_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma);
+                        W4_PROBE_END(warp == 1 ? 6 : 7);
+                    }
                     if (!ok) {
                         break;
                     }
+                    W4_PROBE_BEGIN();
                     tcgen05_fence_after();
                     const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA A operand
-                    const uint32_t sx_tile = ring + S::kTokenRing + (slot / kW4Load) * (kW4Load * S::kTokenBytes) +
-                                             (slot % kW4Load) * p.mt * 128;                   // UMMA B operand
+                    const uint32_t sx_tile =
+                        ring + S::kTokenRing + xslot * x_load_bytes + (i % kW4Load) * p.mt * 128;  // UMMA B operand
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint64_t da = make_smem_desc_sw128(sw_tile + q * kUmmaK, 16, 1024);
                         const uint64_t db = make_smem_desc_sw128(sx_tile + q * kUmmaK, 16, 1024);
                         umma_i8<1>(tmem_d, da, db, idesc, (b | q) != 0 ? 1u : 0u);
                     }
-                    umma_commit<1>(bar_tiles_free + slot * 8);  // both tiles may be overwritten
+                    umma_commit<1>(bar_tiles_free + slot * 8);  // the unpacked tile may be overwritten
+                    umma_commit<1>(bar_x_free + xslot * 8);     // ... and this block's half of the token load
+                    W4_PROBE_END(warp == 1 ? 8 : 9);
                 }
                 if (!ok) {
                     break;
@@ -374,13 +416,27 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             const uint32_t pph = ((i / kW4Load) / kW4PackedLoads) & 1;
             const uint32_t ps = i % kW4PackedSlots;                      // tile slot inside the ring
             const uint32_t cs = i % kW4Tiles;
-            bool ok = mbar_wait(bar_p_full + pl * 8, pph, s_abort, p.status, kDevTimeoutConvert) &&
-                      mbar_wait(bar_tiles_free + cs * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
-                                kDevTimeoutConvert);
+            bool ok;
+            {
+                W4_PROBE_BEGIN();
+                ok = mbar_wait(bar_p_full + pl * 8, pph, s_abort, p.status, kDevTimeoutConvert);
+                if (lane == 0 && u == 0) {
+                    W4_PROBE_END(10);
+                }
+            }
+            {
+                W4_PROBE_BEGIN();
+                ok = ok && mbar_wait(bar_tiles_free + cs * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
+                                     kDevTimeoutConvert);
+                if (lane == 0 && u == 0) {
+                    W4_PROBE_END(11);
+                }
+            }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
             }
+            W4_PROBE_BEGIN();
             const uint8_t* packed = smem + S::kPackedRing + ps * S::kPackedBytes;
             uint8_t* cooked = smem + S::kCookedRing + cs * S::kCookedBytes;
             // (four rounds of four chunks, deliberately not unrolled across rounds: the loop body has to stay
@@ -422,6 +478,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             if (lane == 0) {
                 mbar_arrive(bar_c_full + cs * 8);
             }
+            if (lane == 0 && u == 0) {
+                W4_PROBE_END(12);
+            }
         }
     } else {
         // ------------------------------------------------------- epilogue warps 6..13
@@ -451,8 +510,12 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             return s;
         };
         auto acquire = [&](uint32_t pair) -> bool {
+            W4_PROBE_BEGIN();
             bool got = mbar_wait(bar_acc_full + (pair % kW4AccPairs) * 8, (pair / kW4AccPairs) & 1, s_abort, p.status,
                                  kDevTimeoutEpilogue);
+            if (lane == 0 && ew == 0) {
+                W4_PROBE_END(13);
+            }
             got = __all_sync(0xffffffffu, got);
             if (got) {
                 tcgen05_fence_after();
@@ -486,6 +549,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             if (ok && my_groups != 0) {
                 issue(0, 0, ra);
             }
+#ifdef CB200_DEVELOPER_KNOBS
+            const long long epi_t0 = clock64();
+#endif
             for (uint32_t j = 0; ok && j < my_groups; ++j) {
                 const float s = scale_of(j);
                 tmem_ld_wait_x16(ra);
@@ -518,6 +584,11 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     accumulate16<kOneBlockGroups, 8>(y2, rb, s);
                 }
             }
+#ifdef CB200_DEVELOPER_KNOBS
+            if (lane == 0 && ew == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+                atomicAdd(&g_w4a8_probe[14], static_cast<unsigned long long>(clock64() - epi_t0));  // whole epilogue loop
+            }
+#endif
         }
     }
 

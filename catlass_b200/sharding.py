@@ -12,27 +12,20 @@ Two placements are offered:
            on multiples of the kernel's 256-row tile, and an expert's weights are replicated only on the ranks
            its rows span (a hot expert with a quarter of all rows spans three of eight ranks).
 What is balanced is the kernel's cost, not the row count: the grouped kernel works in 256-row tiles per expert,
-so an expert costs its full tiles plus one (cheaper, when the kernel narrows it) partial tile.
+so an expert costs its full tiles plus one for a partial tile.
 """
 from dataclasses import dataclass
 from typing import List
 
-ROW_TILE = 256          # the pair kernel's row tile (kPairTileM): shard cuts fall on its multiples
-TAIL_GRANULE = 32       # a group's last, partial tile is issued in steps of this many rows ...
-TAIL_FIXED_COST = 0.15  # ... and costs this fraction of a full tile on top (pipeline fill and drain)
-NARROW_TAILS = False    # whether the kernel narrows partial tiles (else a partial tile costs a full one)
+# Mirror of the grouped kernel's row tile (kPairTileM in catlass_b200/csrc/w8a8_gemm_pair.cuh; a test compares them):
+# shard cuts fall on its multiples.
+ROW_TILE = 256
 
 
 def tile_cost(rows):
-    """Cost of `rows` rows of one expert on one rank, in full 256-row tiles."""
-    rows = int(rows)
-    full, rem = divmod(rows, ROW_TILE)
-    if rem == 0:
-        return float(full)
-    if not NARROW_TAILS:
-        return float(full + 1)
-    issued = (rem + TAIL_GRANULE - 1) // TAIL_GRANULE * TAIL_GRANULE
-    return full + min(1.0, TAIL_FIXED_COST + (1.0 - TAIL_FIXED_COST) * issued / ROW_TILE)
+    """Cost of `rows` rows of one expert on one rank, in 256-row tiles: a partial tile costs a full one (a
+    narrower tensor-core shape for it was measured and did not pay: the MMA issue rate, not the math, bounds it)."""
+    return float((int(rows) + ROW_TILE - 1) // ROW_TILE)
 
 
 @dataclass(frozen=True)

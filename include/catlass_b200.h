@@ -236,8 +236,14 @@ CB200_API int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_
  * running sum each at most), plus the final rounding of D; the GPU tests check the output against the exact
  * (float64) sum with that bound, and bit for bit against the fused definition.
  *
- * Requirements: group_size a multiple of 128 that divides round_up(k, 128), or group_size = k (one group);
- * k % 32 == 0 (the packed rows must be 16-byte multiples for the bulk copies); group_size <= 16384.
+ * Requirements: group_size a multiple of 128 (the last group may be shorter), or group_size >= k (one group over
+ * any k, also odd: the reference's runner case m=860 n=5712 k=4535); at most 16384 elements per group.
+ * Fast path: weights packed along K, k a multiple of 128 (and of group_size), a and w_packed 16-byte aligned: the
+ * operands are streamed in place and the workspace is not used.  Everything else (k not a whole number of blocks,
+ * weights packed along N as in tests/optest/tests/test_32_w4a8_matmul.py:11-28, unaligned operands) first goes
+ * through an ingestion pre-pass that writes zero-padded, K-packed copies of both operands into the workspace
+ * (cb200_w4a8_matmul_workspace_size bytes): one extra pass over A and W; keep weights in the fast-path form
+ * where speed matters.
  * Summation order: by default the groups are summed in ascending order, exactly as written above (D is
  * bit-exact against that definition).  With CB200_W4A8_SPLIT_K in `flags`, shapes with few 128-channel tiles
  * split the groups over the 2 or 4 CTAs of a cluster and add the fp32 partial sums at the end: faster, but an
@@ -246,6 +252,8 @@ CB200_API int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_
  * Thread safety: any number of host threads may call concurrently, on any streams.
  */
 #define CB200_W4A8_SPLIT_K 1u
+#define CB200_W4_PACKED_ALONG_K 0 /* w_packed: n columns of ceil(k/2) bytes (the reference's column-major B) */
+#define CB200_W4_PACKED_ALONG_N 1 /* w_packed: k rows of ceil(n/2) bytes (the reference's row-major B) */
 typedef struct cb200_w4a8_matmul_args {
     uint32_t m, n, k;
     uint32_t group_size;
@@ -259,7 +267,7 @@ typedef struct cb200_w4a8_matmul_args {
     uint32_t block_num;
     uint32_t flags;               /* 0, CB200_W4A8_SPLIT_K and/or CB200_FLAG_STATIC_WEIGHTS */
     uint32_t d_type;              /* CB200_DTYPE_BF16 (0 accepted) or CB200_DTYPE_F16 */
-    uint32_t reserved;
+    uint32_t pack_axis;           /* CB200_W4_PACKED_ALONG_K (0, default) or CB200_W4_PACKED_ALONG_N */
 } cb200_w4a8_matmul_args;
 
 CB200_API int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args *args);
@@ -267,34 +275,48 @@ CB200_API uint64_t cb200_w4a8_matmul_workspace_size(const cb200_w4a8_matmul_args
 CB200_API int cb200_w4a8_matmul(const cb200_w4a8_matmul_args *args, void *stream);
 
 /*
- * MX block-scaled matmul (OCP microscaling): elements E4M3 (one byte) or E2M1 (two per byte, even k in bits
+ * MX block-scaled matmul (OCP microscaling): elements E4M3 (one byte) or E2M1 (two per byte, even index in bits
  * 0-3), one E8M0 scale byte per 32 contiguous K elements of every row of A and every column of B:
- *     D[i,j] = bf16_rne( sum_k (A[i,k] * 2^(scale_a[i,k/32]-127)) * (B[k,j] * 2^(scale_b[j,k/32]-127)) )
+ *     D[i,j] = round( sum_k (A[i,k] * 2^(scale_a[i,k/32]-127)) * (B[k,j] * 2^(scale_b[j,k/32]-127)) )
  * accumulated in fp32 inside the tensor core.  Replaces Gemm::Kernel::MxMatmulTla::Arguments
  * (include/catlass/gemm/kernel/mx_matmul_tla.hpp:95-108; operand order A, B, scaleA, scaleB of
  * tests/optest/kernels/53_ascend950_fp8_mx_matmul/fp8_mx_matmul_impl.cpp:80-84).
- * A is m x k row-major, B is k x n column-major (each column k contiguous elements); scale_a is
- * [m][k/32] bytes and scale_b is [n][k/32] bytes: the reference's [rows, k/64, 2] scale arrays
- * (examples/53_ascend950_fp8_mx_matmul/gen_data.py:390-401).  k must be a multiple of 128 (E4M3) or 256 (E2M1).
- * The workspace (cb200_mx_matmul_workspace_size bytes) receives the scales re-tiled for the tensor core.
+ *
+ * Layouts (the four transpose pairs of tests/optest/tests/test_53_ascend950_fp8_mx_matmul_aswt.py:21-30):
+ *   layout_a = CB200_ROW_MAJOR: A is [m][k];  CB200_COLUMN_MAJOR: A is stored [k][m] (the reference's transA)
+ *   layout_b = CB200_COLUMN_MAJOR: B is stored [n][k] (the reference's transB, its default);  CB200_ROW_MAJOR: [k][n]
+ *   E2M1 arrays pack two elements per byte along their contiguous axis (an odd count leaves the last high nibble
+ *   unused).
+ * Scales follow the operand, as the reference's do (tests/optest/tests/mx_golden.py:253-266), with
+ * KS = ceil(k/32) rounded up to even:
+ *   operand stored with rows along K ([m][k] / [n][k]):  scale array [rows][KS] bytes (the reference's [rows, KS/2, 2])
+ *   operand stored the other way ([k][m] / [k][n]):      scale array [KS/2][rows][2] bytes
+ * k is arbitrary (the reference's tests run k = 2, 33, 63, 129).
+ * Fast path: A [m][k] and B [n][k], k a multiple of 128 (E4M3) / 256 (E2M1), 16-byte aligned: the operands are
+ * streamed in place.  Anything else is first rewritten by an ingestion pre-pass (one extra pass over that operand)
+ * into zero-padded rows along K in the workspace.
+ * The workspace (cb200_mx_matmul_workspace_size bytes, 256-byte aligned) receives the scales re-tiled for the tensor
+ * core and the ingested operands.
+ * Output: bf16 by default; fp32 (what the reference's kernels write) with CB200_MX_OUT_F32 in `flags`.
  */
 #define CB200_MX_E4M3 0
 #define CB200_MX_E2M1 1
+#define CB200_MX_OUT_F32 1u
 
 typedef struct cb200_mx_matmul_args {
     uint32_t m, n, k;
     uint32_t format;              /* CB200_MX_E4M3 / CB200_MX_E2M1 */
-    uint32_t layout_a;            /* CB200_ROW_MAJOR */
-    uint32_t layout_b;            /* CB200_COLUMN_MAJOR */
+    uint32_t layout_a;            /* CB200_ROW_MAJOR ([m][k]) or CB200_COLUMN_MAJOR ([k][m]) */
+    uint32_t layout_b;            /* CB200_COLUMN_MAJOR ([n][k]) or CB200_ROW_MAJOR ([k][n]) */
     const void *a;
     const void *b;
     const void *scale_a;          /* E8M0 bytes */
     const void *scale_b;
-    void *d;                      /* bf16 m x n row-major */
+    void *d;                      /* m x n row-major: bf16, or fp32 with CB200_MX_OUT_F32 */
     void *workspace;
     uint64_t workspace_bytes;
     uint32_t block_num;
-    uint32_t reserved;
+    uint32_t flags;               /* 0 or CB200_MX_OUT_F32 */
 } cb200_mx_matmul_args;
 
 CB200_API int cb200_mx_matmul_can_implement(const cb200_mx_matmul_args *args);
@@ -314,8 +336,9 @@ CB200_API int cb200_mx_matmul(const cb200_mx_matmul_args *args, void *stream);
  * the process exits.  args->workspace and args->workspace_bytes are ignored; inputs and output are passed
  * as usual.  The call allocates nothing and calls no allocating routine.
  *
- *  - Limit: (ceil(m/128) + 2*ceil(n/256)) * (k/128) * 512 bytes must fit the array; m = n = k = 8192 needs
- *    4 MiB.  Larger problems return CB200_SCRATCH_TOO_SMALL and launch nothing.
+ *  - Limit: cb200_mx_matmul_workspace_size(args) bytes must fit the array: (ceil(m/128) + 2*ceil(n/256)) *
+ *    (k/128) * 512 bytes on the fast path (m = n = k = 8192 needs 4 MiB), plus the ingested operands off it.
+ *    Larger problems return CB200_SCRATCH_TOO_SMALL and launch nothing.
  *  - The first call on a device looks up the array's device address (with that device current) and keeps it;
  *    make that first call outside any stream capture.
  *  - All calls on a device share the one array.  Each call rewrites every byte of it that it later reads, so

@@ -92,9 +92,11 @@ def test_mx_invalid_arguments(cuda):
     z = torch.zeros(1 << 16, dtype=torch.uint8, device=cuda)
     d = torch.empty((128, 128), dtype=torch.bfloat16, device=cuda)
     with pytest.raises(capi.CallError) as e:
-        capi.mx_matmul(z, z, z, z, d, 128, 128, 192, capi.MX_E4M3, z)   # k not a multiple of 128
+        capi.mx_matmul(z, z, z, z, d, 128, 128, 256, 7, z)   # unknown element format
     assert e.value.status == capi.INVALID
     with pytest.raises(capi.CallError):
-        capi.mx_matmul(z, z, z, z, d, 128, 128, 128, capi.MX_E2M1, z)   # fp4 needs k % 256
+        capi.mx_matmul(z, z, z, z, d, 128, 128, 256, capi.MX_E2M1, z, layout_a=5)
     with pytest.raises(capi.CallError):
         capi.mx_matmul(z, z, z, z, d, 128, 128, 256, capi.MX_E4M3, None)  # no workspace
+    with pytest.raises(capi.CallError):
+        capi.mx_matmul(z, z, z, z, d, 128, 128, 192, capi.MX_E4M3, z[:4096])  # ragged k: workspace too small

@@ -67,6 +67,14 @@ def test_local_groups_merge_pieces_of_one_expert():
         assert sum(r for _, r in sh.local_groups()) == sh.rows
 
 
+def test_tile_constants_mirror_the_kernel():
+    import re
+    text = open(os.path.join(ROOT, "catlass_b200", "csrc", "w8a8_gemm_pair.cuh")).read()
+    val = lambda name: int(re.search(r"constexpr int " + name + r" = (\d+);", text).group(1))  # noqa: E731
+    assert val("kPairTileM") == sharding.ROW_TILE
+    assert sharding.tile_cost(512) == 2.0 and sharding.tile_cost(513) == 3.0 and sharding.tile_cost(0) == 0.0
+
+
 def test_edge_cases():
     assert [s.rows for s in sharding.plan([0, 0], 2)] == [0, 0]
     with pytest.raises(ValueError):

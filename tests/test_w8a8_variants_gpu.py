@@ -197,3 +197,58 @@ def test_static_weights_flag_gives_the_same_result(cuda):
             capi.quant_matmul(*args, static_weights=True)
         assert capi.device_status()[0] == 0
         assert np.array_equal(d.view(torch.int16).cpu().numpy().view(np.uint16), want)
+
+
+@pytest.mark.parametrize("layout", ["row", "col", "zn"])
+def test_grouped_partial_row_tiles_of_every_width(cuda, layout):
+    """Groups whose last row tile holds 1 ... 255 rows, beside full tiles and alone, with column tiles cut by n:
+    rows past a group's end belong to the next group and must keep its results."""
+    from catlass_b200 import capi
+    torch = _torch()
+    rems = [1, 15, 16, 17, 31, 32, 33, 63, 64, 65, 96, 127, 128, 129, 160, 191, 192, 193, 224, 255]
+    sizes = []
+    for i, r in enumerate(rems):
+        sizes.append(r + 256 * (i % 3))   # alone, after one full tile, after two
+    sizes.insert(5, 0)
+    n, k = (392 if layout != "row" else 400), 272
+    a, b, scale, pt, gl = P.w8a8_grouped(sizes, n, k, seed=7, m_capacity=sum(sizes) + 70)
+    m, g = a.shape[0], len(sizes)
+    if layout == "row":
+        b_flat, lb, olb = b, capi.ROW_MAJOR, O.ROW_MAJOR
+    elif layout == "col":
+        b_flat, lb, olb = np.ascontiguousarray(b.transpose(0, 2, 1)), capi.COLUMN_MAJOR, O.COL_MAJOR
+    else:
+        b_flat, lb, olb = np.stack([P.zn_storage(b[e]) for e in range(g)]), capi.ZN, O.ROW_MAJOR
+    canary = 5.0
+    d = torch.full((m, n), canary, dtype=torch.bfloat16, device=cuda)
+    acc = torch.full((m, n), -7, dtype=torch.int32, device=cuda)
+    capi.grouped_quant_matmul(_dev(a), _dev(b_flat), _dev(gl), _dev(scale), _dev(pt), d, m, n, k, g, layout_b=lb,
+                              acc=acc)
+    st, code = capi.device_status()
+    assert st == 0, f"device status {st} code {code:#x}"
+    init = np.full((m, n), canary, np.float32)
+    want, want_acc = O.grouped_quant_matmul(a, b if layout == "zn" else b_flat, gl, scale, pt, m, n, k, olb,
+                                            want_acc=True, out_init=init)
+    rows = int(gl[-1])
+    got_acc = acc.cpu().numpy()
+    assert np.array_equal(got_acc[:rows], want_acc[:rows])
+    assert (got_acc[rows:] == -7).all()
+    got = d.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, O.out_bits(want)), f"{(got != O.out_bits(want)).sum()} outputs differ"
+
+
+@pytest.mark.parametrize("m", [44, 129, 192, 300, 448, 512 + 33])
+def test_dense_partial_last_row_tile(cuda, m):
+    """Dense problems are one group: a partial last row tile, alone and after full tiles."""
+    from catlass_b200 import capi
+    torch = _torch()
+    n, k = 520, 1040
+    a, b, scale, pt = P.w8a8_dense(m, n, k, seed=m)
+    b_flat = P.b_storage(b, True)
+    d = torch.zeros((m, n), dtype=torch.bfloat16, device=cuda)
+    acc = torch.zeros((m, n), dtype=torch.int32, device=cuda)
+    capi.quant_matmul(_dev(a), _dev(b_flat), _dev(scale), _dev(pt), d, m, n, k, acc=acc)
+    assert capi.device_status()[0] == 0
+    want, want_acc = O.quant_matmul(a, b_flat, scale, pt, m, n, k, want_acc=True)
+    assert np.array_equal(acc.cpu().numpy(), want_acc)
+    assert np.array_equal(d.view(torch.int16).cpu().numpy().view(np.uint16), O.out_bits(want))
