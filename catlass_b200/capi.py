@@ -72,6 +72,25 @@ class MxMatmulArgs(ctypes.Structure):
     ]
 
 
+class MxGroupedMatmulArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("format", _u32), ("layout_b", _u32),
+        ("group_list_type", _u32), ("group_list_kind", _u32),
+        ("a", _vp), ("b", _vp), ("group_list", _vp), ("scale_a", _vp), ("scale_b", _vp), ("d", _vp),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("flags", _u32),
+    ]
+
+
+GROUP_LIST_SIZES, GROUP_LIST_PREFIX_SUMS = 0, 1
+
+
+class MxQuantizeArgs(ctypes.Structure):
+    _fields_ = [
+        ("rows", _u32), ("k", _u32), ("format", _u32), ("x_type", _u32), ("x_pitch", _u64),
+        ("x", _vp), ("q", _vp), ("scale", _vp),
+    ]
+
+
 MX_E4M3, MX_E2M1 = 0, 1
 MX_OUT_F32 = 1
 W4_PACKED_ALONG_K, W4_PACKED_ALONG_N = 0, 1
@@ -98,7 +117,8 @@ def load():
                          ("cb200_grouped_quant_matmul_slice_m", GroupedQuantMatmulArgs),
                          ("cb200_grouped_matmul_slice_m_fixpipe_dequant", GroupedFixpipeDequantArgs),
                          ("cb200_w4a8_matmul", W4A8MatmulArgs),
-                         ("cb200_mx_matmul", MxMatmulArgs)):
+                         ("cb200_mx_matmul", MxMatmulArgs),
+                         ("cb200_mx_grouped_matmul_slice_m", MxGroupedMatmulArgs)):
         getattr(lib, name + "_can_implement").argtypes = [ctypes.POINTER(args_t)]
         getattr(lib, name + "_can_implement").restype = ctypes.c_int
         getattr(lib, name + "_workspace_size").argtypes = [ctypes.POINTER(args_t)]
@@ -109,6 +129,10 @@ def load():
     lib.cb200_grouped_quant_matmul_slice_m_host.restype = ctypes.c_int
     lib.cb200_grouped_quant_matmul_slice_m_host_workspace_size.argtypes = [ctypes.POINTER(GroupedQuantMatmulHostArgs)]
     lib.cb200_grouped_quant_matmul_slice_m_host_workspace_size.restype = _u64
+    lib.cb200_mx_quantize.argtypes = [ctypes.POINTER(MxQuantizeArgs), _vp]
+    lib.cb200_mx_quantize.restype = ctypes.c_int
+    lib.cb200_mx_quantize_can_implement.argtypes = [ctypes.POINTER(MxQuantizeArgs)]
+    lib.cb200_mx_quantize_can_implement.restype = ctypes.c_int
     lib.cb200_mx_matmul_static.argtypes = [ctypes.POINTER(MxMatmulArgs), _vp]
     lib.cb200_mx_matmul_static.restype = ctypes.c_int
     lib.cb200_mx_matmul_static_scratch_bytes.restype = _u64
@@ -246,6 +270,39 @@ def mx_matmul_static(a, b, scale_a, scale_b, d, m, n, k, fmt, stream=None, layou
     """cb200_mx_matmul_static: as mx_matmul, scratch inside the library image, no workspace argument."""
     args = _mx_args(a, b, scale_a, scale_b, d, m, n, k, fmt, None, layout_a, layout_b, out_f32)
     _check("cb200_mx_matmul_static", load().cb200_mx_matmul_static(ctypes.byref(args), _stream(stream)))
+
+
+def _mx_grouped_args(a, b, group_list, scale_a, scale_b, d, m, n, k, group_count, fmt, workspace, layout_b,
+                     group_list_type, group_list_kind, out_f32):
+    return MxGroupedMatmulArgs(m=m, n=n, k=k, group_count=group_count, format=fmt, layout_b=layout_b,
+                               group_list_type=group_list_type, group_list_kind=group_list_kind, a=_p(a), b=_p(b),
+                               group_list=_p(group_list), scale_a=_p(scale_a), scale_b=_p(scale_b), d=_p(d),
+                               workspace=_p(workspace),
+                               workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(),
+                               block_num=0, flags=MX_OUT_F32 if out_f32 else 0)
+
+
+def mx_grouped_matmul_workspace_size(m, n, k, group_count, fmt, layout_b=COLUMN_MAJOR):
+    args = MxGroupedMatmulArgs(m=m, n=n, k=k, group_count=group_count, format=fmt, layout_b=layout_b, a=256, b=256,
+                               group_list=256, scale_a=256, scale_b=256, d=256)
+    return int(load().cb200_mx_grouped_matmul_slice_m_workspace_size(ctypes.byref(args)))
+
+
+def mx_grouped_matmul(a, b, group_list, scale_a, scale_b, d, m, n, k, group_count, fmt, workspace, stream=None,
+                      layout_b=COLUMN_MAJOR, group_list_type=GROUP_LIST_INT64, group_list_kind=GROUP_LIST_SIZES,
+                      out_f32=False):
+    """Grouped slice-M MX matmul: a [m][k], b [G][n][k] (or [G][k][n] with layout_b = ROW_MAJOR), group_list the
+    groups' row counts (or prefix sums), scales as for mx_matmul with a leading group axis on scale_b."""
+    args = _mx_grouped_args(a, b, group_list, scale_a, scale_b, d, m, n, k, group_count, fmt, workspace, layout_b,
+                            group_list_type, group_list_kind, out_f32)
+    _check("cb200_mx_grouped_matmul_slice_m",
+           load().cb200_mx_grouped_matmul_slice_m(ctypes.byref(args), _stream(stream)))
+
+
+def mx_quantize(x, q, scale, rows, k, fmt, x_type=DTYPE_F32, x_pitch=0, stream=None):
+    """x: fp32 / bf16 [rows][k] -> q codes ([rows][k] bytes, E2M1 [rows][ceil(k/2)]) and scale [rows][KS] bytes."""
+    args = MxQuantizeArgs(rows=rows, k=k, format=fmt, x_type=x_type, x_pitch=x_pitch, x=_p(x), q=_p(q), scale=_p(scale))
+    _check("cb200_mx_quantize", load().cb200_mx_quantize(ctypes.byref(args), _stream(stream)))
 
 
 def _host_args(a_host, group_list_host, per_token_host, d_host, b, scale, m, n, k, group_count, layout_b, chunks,

@@ -14,6 +14,7 @@
 #include "w4a8_gemm.cuh"
 #include "mx_gemm.cuh"
 #include "ingest.cuh"
+#include "mx_quantize.cuh"
 
 using namespace cb200;
 using namespace cb200::host;
@@ -395,9 +396,15 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
         return rc_dev;
     }
     {
-        const double sm_all = static_cast<double>(dev.sm_count);
-        const double fixed = 3.5e-6 * 6.5e12 / sm_all;   // per-CTA start-up + epilogue, as bytes at full rate
-        const double reduce = 2.0e-6 * 6.5e12 / sm_all;  // cluster barrier + DSMEM reduction
+        // Time of a candidate split: every wave pays a fixed start-up / epilogue (a split adds the cluster reduction),
+        // and the weight stream is bounded both by what one CTA's pipeline moves (~70 GB/s: measured, 128 rows x
+        // 14336 bytes in 7.7 us) and by what HBM delivers to all of them.  The tile is always 128 weight rows:
+        // shorter tiles make more CTAs but each K block takes a CTA as long as before (the MMA reads 128 rows
+        // anyway), and measured they never won (16 x 14336 x 4096: 112 CTAs of 128 rows beat 138 of 104 by 2 %;
+        // 16 x 4096 x 14336, 2-way split: 64 CTAs of 128 rows 15.2 us, 114 of 72 rows 15.7 us).
+        const double fixed = 3.5e-6, reduce = 2.0e-6, per_cta_rate = 70.0e9, hbm_rate = 6.0e12;
+        const double total_bytes = static_cast<double>(q.n) * q.k;
+        const uint32_t tiles = (q.n + kSmallMTileN - 1) / kSmallMTileN;
         double best = 1e300;
         int si = 0;
         for (uint32_t s = 1; s <= static_cast<uint32_t>(kSmallMMaxSplits); s *= 2, ++si) {
@@ -405,21 +412,15 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
                 break;
             }
             const double sm = static_cast<double>(resident_ctas[devid][si]);
-            for (uint32_t r = kSmallMTileN; r >= 64; r -= 8) {
-                if (kWMn && r != static_cast<uint32_t>(kSmallMTileN)) {
-                    break;  // row-major weights: a tile is 128 contiguous bytes of n
-                }
-                const uint32_t tiles = (q.n + r - 1) / r;
-                const double ctas = static_cast<double>(tiles) * s;
-                const double waves = ceil(ctas / sm);
-                const double kb_per = ceil(static_cast<double>(p.num_k_blocks) / s);
-                const double cta_bytes = static_cast<double>(r + p.mt) * kb_per * kBlockKBytes;
-                const double cost = waves * (fixed + (s > 1 ? reduce : 0.0) + cta_bytes);
-                if (cost < best) {
-                    best = cost;
-                    splits = s;
-                    tile_rows = r;
-                }
+            const double waves = ceil(static_cast<double>(tiles) * s / sm);
+            const double kb_per = ceil(static_cast<double>(p.num_k_blocks) / s);
+            const double cta_bytes = static_cast<double>(kSmallMTileN + p.mt) * kb_per * kBlockKBytes;
+            const double stream = waves * cta_bytes / per_cta_rate;
+            const double cost = waves * (fixed + (s > 1 ? reduce : 0.0)) +
+                                (stream > total_bytes / hbm_rate ? stream : total_bytes / hbm_rate);
+            if (cost < best) {
+                best = cost;
+                splits = s;
             }
         }
     }
@@ -615,105 +616,152 @@ int plan_w4a8(const cb200_w4a8_matmul_args* a, W4Plan* plan)
     return CB200_SUCCESS;
 }
 
-// How an MX call is served.  The kernel wants both operands with rows along K, padded to whole K stages
-// (128 E4M3 / 256 E2M1 elements) and 16-byte aligned; an operand that is not is rewritten by the ingestion
-// pre-pass into the workspace, behind the re-tiled scales.
-struct MxPlan {
-    uint32_t k_padded;
-    uint32_t row_bytes;     // bytes of one padded operand row
-    bool ingest_a, ingest_b;
-    uint64_t sf_bytes, a_bytes, b_bytes;
-    uint64_t total() const { return sf_bytes + (ingest_a ? a_bytes : 0) + (ingest_b ? b_bytes : 0); }
+// An MX problem as the launcher sees it: the dense call is one group whose rows are all of A.
+struct MxProblem {
+    uint32_t m, n, k;
+    uint32_t group_count;      // 0 = dense
+    uint32_t format;
+    uint32_t layout_a, layout_b;
+    uint32_t group_list_type, group_list_is_prefix_sum;
+    const void* a;
+    const void* b;
+    const void* group_list;
+    const void* scale_a;
+    const void* scale_b;
+    void* d;
+    void* workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t flags;
 };
 
-int plan_mx(const cb200_mx_matmul_args* a, MxPlan* plan)
-{
-    if (a == nullptr) {
-        return CB200_INVALID;
+// How an MX call is served.  The kernel wants both operands with rows along K, padded to whole K stages
+// (128 E4M3 / 256 E2M1 elements) and 16-byte aligned; an operand that is not is rewritten by the ingestion
+// pre-pass into the workspace, behind the re-tiled scales (and, for a grouped problem, the row-tile table).
+struct MxPlan {
+    uint32_t k_padded;
+    uint32_t row_bytes;       // bytes of one padded operand row
+    uint32_t max_row_tiles;   // 128-row tiles of A at most: ceil(m/128), plus one partial tile per group
+    uint32_t b_matrices;      // weight matrices: 1, or the group count
+    bool ingest_a, ingest_b;
+    uint64_t table_bytes, sfa_bytes, sfb_bytes, a_bytes, b_bytes;
+    uint64_t total() const
+    {
+        return table_bytes + sfa_bytes + sfb_bytes + (ingest_a ? a_bytes : 0) + (ingest_b ? b_bytes : 0);
     }
+};
+
+int plan_mx(const MxProblem& q, MxPlan* plan)
+{
     *plan = MxPlan{};
-    if (a->m == 0 || a->n == 0) {
+    if (q.m == 0 || q.n == 0) {
         return CB200_SUCCESS;
     }
-    if (a->a == nullptr || a->b == nullptr || a->scale_a == nullptr || a->scale_b == nullptr || a->d == nullptr) {
+    if (q.a == nullptr || q.b == nullptr || q.scale_a == nullptr || q.scale_b == nullptr || q.d == nullptr) {
         return CB200_INVALID;
     }
-    if (a->format != CB200_MX_E4M3 && a->format != CB200_MX_E2M1) {
+    if (q.format != CB200_MX_E4M3 && q.format != CB200_MX_E2M1) {
         return CB200_INVALID;
     }
-    if ((a->layout_a != CB200_ROW_MAJOR && a->layout_a != CB200_COLUMN_MAJOR) ||
-        (a->layout_b != CB200_ROW_MAJOR && a->layout_b != CB200_COLUMN_MAJOR)) {
+    if ((q.layout_a != CB200_ROW_MAJOR && q.layout_a != CB200_COLUMN_MAJOR) ||
+        (q.layout_b != CB200_ROW_MAJOR && q.layout_b != CB200_COLUMN_MAJOR)) {
         return CB200_INVALID;
     }
-    if ((a->flags & ~CB200_MX_OUT_F32) != 0) {
+    if (q.group_count != 0) {
+        if (q.group_count > static_cast<uint32_t>(kMaxGroups) || q.group_list == nullptr ||
+            q.layout_a != CB200_ROW_MAJOR ||  // slice-M groups cut A by rows
+            (q.group_list_type != CB200_GROUP_LIST_INT64 && q.group_list_type != CB200_GROUP_LIST_INT32)) {
+            return CB200_INVALID;
+        }
+    }
+    if ((q.flags & ~CB200_MX_OUT_F32) != 0) {
         return CB200_INVALID;
     }
-    if (a->k == 0 || a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u) {
+    if (q.k == 0 || q.m > 0x7fffff00u || q.n > 0x7fffff00u || q.k > 0x7fffff00u) {
         return CB200_INVALID;
     }
-    const bool f32 = (a->flags & CB200_MX_OUT_F32) != 0;
-    if ((reinterpret_cast<uintptr_t>(a->d) & (f32 ? 3u : 1u)) != 0) {
+    const bool f32 = (q.flags & CB200_MX_OUT_F32) != 0;
+    if ((reinterpret_cast<uintptr_t>(q.d) & (f32 ? 3u : 1u)) != 0) {
         return CB200_INVALID;
     }
-    if (((a->n & (f32 ? 3u : 7u)) == 0) && !aligned16(a->d)) {
+    if (((q.n & (f32 ? 3u : 7u)) == 0) && !aligned16(q.d)) {
         return CB200_INVALID;  // 16-byte vector stores
     }
-    const bool fp4 = a->format == CB200_MX_E2M1;
+    const bool fp4 = q.format == CB200_MX_E2M1;
     const uint32_t kmul = fp4 ? 256u : 128u;
-    plan->k_padded = (a->k + kmul - 1u) / kmul * kmul;
+    plan->k_padded = (q.k + kmul - 1u) / kmul * kmul;
     plan->row_bytes = fp4 ? plan->k_padded / 2u : plan->k_padded;
-    plan->ingest_a = a->layout_a != CB200_ROW_MAJOR || plan->k_padded != a->k || !aligned16(a->a);
-    plan->ingest_b = a->layout_b != CB200_COLUMN_MAJOR || plan->k_padded != a->k || !aligned16(a->b);
+    plan->ingest_a = q.layout_a != CB200_ROW_MAJOR || plan->k_padded != q.k || !aligned16(q.a);
+    plan->ingest_b = q.layout_b != CB200_COLUMN_MAJOR || plan->k_padded != q.k || !aligned16(q.b);
+    plan->b_matrices = q.group_count == 0 ? 1u : q.group_count;
+    plan->max_row_tiles = (q.m + 127u) / 128u + q.group_count;
     const uint64_t kq = plan->k_padded / 128u;
+    plan->table_bytes = q.group_count == 0 ? 0 : align256(static_cast<uint64_t>(plan->max_row_tiles) * 16u + 16u);
     // scale blocks of 128 rows; B's are padded to whole 256-column tiles
-    plan->sf_bytes = (static_cast<uint64_t>((a->m + 127u) / 128u) + 2u * ((a->n + 255u) / 256u)) * kq * 512u;
-    plan->a_bytes = align256(static_cast<uint64_t>(a->m) * plan->row_bytes);
-    plan->b_bytes = align256(static_cast<uint64_t>(a->n) * plan->row_bytes);
+    plan->sfa_bytes = static_cast<uint64_t>(plan->max_row_tiles) * kq * 512u;
+    plan->sfb_bytes = static_cast<uint64_t>(plan->b_matrices) * 2u * ((q.n + 255u) / 256u) * kq * 512u;
+    plan->a_bytes = align256(static_cast<uint64_t>(q.m) * plan->row_bytes);
+    plan->b_bytes = align256(static_cast<uint64_t>(plan->b_matrices) * q.n * plan->row_bytes);
     return CB200_SUCCESS;
 }
 
-// One operand into its canonical form: `rows` rows of row_bytes bytes along K.
-// stored_k_major: the caller's array is [k][rows] (elements, packed two per byte along `rows` for E2M1).
+// `batch` operands into their canonical form: `rows` rows of row_bytes bytes along K each.
+// stored_k_major: the caller's arrays are [k][rows] (elements, packed two per byte along `rows` for E2M1).
 void ingest_mx_operand(const void* src, uint8_t* dst, uint32_t rows, uint32_t k, bool fp4, bool stored_k_major,
-                       uint32_t row_bytes, int sm_count, cudaStream_t stream)
+                       uint32_t row_bytes, uint32_t batch, int sm_count, cudaStream_t stream)
 {
     const uint8_t* s = static_cast<const uint8_t*>(src);
-    const uint32_t blocks = static_cast<uint32_t>(sm_count) * 8u;
+    const uint32_t per_batch = static_cast<uint32_t>(sm_count) * 8u / (batch > 8u ? 8u : batch);
+    const dim3 grid(per_batch == 0 ? 1u : per_batch, batch, 1);
+    const uint64_t dst_batch = static_cast<uint64_t>(rows) * row_bytes;
     if (!stored_k_major) {
         const uint32_t valid = fp4 ? (k + 1u) / 2u : k;
-        pad_rows_kernel<<<blocks, 256, 0, stream>>>(s, dst, rows, valid, row_bytes, valid, fp4 ? (k & 1u) : 0u);
+        pad_rows_kernel<<<grid, 256, 0, stream>>>(s, dst, rows, valid, row_bytes, valid, fp4 ? (k & 1u) : 0u,
+                                                  static_cast<uint64_t>(rows) * valid, dst_batch);
     } else if (fp4) {
-        transpose_nibbles_kernel<<<blocks, 256, 0, stream>>>(s, dst, rows, k, (rows + 1u) / 2u, row_bytes);
+        const uint64_t pitch = (rows + 1u) / 2u;
+        transpose_nibbles_kernel<<<grid, 256, 0, stream>>>(s, dst, rows, k, pitch, row_bytes, pitch * k, dst_batch);
     } else {
-        transpose_bytes_kernel<<<blocks, dim3(32, 8), 0, stream>>>(s, dst, rows, k, rows, row_bytes);
+        transpose_bytes_kernel<<<grid, dim3(32, 8), 0, stream>>>(s, dst, rows, k, rows, row_bytes,
+                                                                 static_cast<uint64_t>(rows) * k, dst_batch);
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
-template <bool kFp4>
-int launch_mx(const cb200_mx_matmul_args* args, const MxPlan& plan, const DeviceState& dev, cudaStream_t stream)
+template <bool kFp4, bool kGrouped>
+int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cudaStream_t stream)
 {
-    uint8_t* ws = static_cast<uint8_t*>(args->workspace);
-    const void* a_ptr = args->a;
-    const void* b_ptr = args->b;
+    uint8_t* ws = static_cast<uint8_t*>(q.workspace);
+    int4* table = reinterpret_cast<int4*>(ws);
+    uint32_t* num_row_tiles = reinterpret_cast<uint32_t*>(ws + static_cast<uint64_t>(plan.max_row_tiles) * 16u);
+    uint8_t* sfa = ws + plan.table_bytes;
+    uint8_t* sfb = sfa + plan.sfa_bytes;
+    const void* a_ptr = q.a;
+    const void* b_ptr = q.b;
     {
-        uint8_t* next = ws + plan.sf_bytes;
+        uint8_t* next = sfb + plan.sfb_bytes;
         if (plan.ingest_a) {
-            ingest_mx_operand(args->a, next, args->m, args->k, kFp4, args->layout_a == CB200_COLUMN_MAJOR,
-                              plan.row_bytes, dev.sm_count, stream);
+            ingest_mx_operand(q.a, next, q.m, q.k, kFp4, q.layout_a == CB200_COLUMN_MAJOR, plan.row_bytes, 1,
+                              dev.sm_count, stream);
             a_ptr = next;
             next += plan.a_bytes;
         }
         if (plan.ingest_b) {
-            ingest_mx_operand(args->b, next, args->n, args->k, kFp4, args->layout_b == CB200_ROW_MAJOR, plan.row_bytes,
+            ingest_mx_operand(q.b, next, q.n, q.k, kFp4, q.layout_b == CB200_ROW_MAJOR, plan.row_bytes, plan.b_matrices,
                               dev.sm_count, stream);
             b_ptr = next;
         }
     }
+    if constexpr (kGrouped) {
+        mx_group_plan_kernel<<<1, 1024, 0, stream>>>(q.group_list, q.group_list_type == CB200_GROUP_LIST_INT32 ? 1u : 0u,
+                                                     q.group_list_is_prefix_sum, q.group_count, q.m, table, num_row_tiles);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
     const uint32_t row_bytes = plan.row_bytes;
+    const uint32_t sfb_blocks = 2u * ((q.n + 255u) / 256u);
     MxParams p;
-    p.m = args->m;
-    p.n = args->n;
+    p.m = q.m;
+    p.n = q.n;
     p.k = plan.k_padded;
     p.fp4 = kFp4 ? 1u : 0u;
     p.num_k_blocks = row_bytes / 128u;
@@ -729,29 +777,35 @@ int launch_mx(const cb200_mx_matmul_args* args, const MxPlan& plan, const Device
             p.band_rows = v;
         }
     }
-    const uint64_t sfa_bytes = static_cast<uint64_t>((args->m + 127u) / 128u) * p.kq_total * 512u;
-    p.sfa = ws;
-    p.sfb = ws + sfa_bytes;
-    p.d = args->d;
+    p.sfa = sfa;
+    p.sfb = sfb;
+    p.d = q.d;
     p.status = dev.status;
-    p.out_f32 = (args->flags & CB200_MX_OUT_F32) ? 1u : 0u;
+    p.out_f32 = (q.flags & CB200_MX_OUT_F32) ? 1u : 0u;
+    p.tile_table = kGrouped ? table : nullptr;
+    p.num_row_tiles = kGrouped ? num_row_tiles : nullptr;
+    p.sfb_blocks_per_group = sfb_blocks;
 
     // the caller's scale arrays: ceil(k/32) blocks per row, held in an even number of columns; stored along the
     // operand's rows, or K-major when the operand itself is stored K-major
-    const uint32_t kblocks = (args->k + 31u) / 32u;
+    const uint32_t kblocks = (q.k + 31u) / 32u;
     const uint32_t ks_pitch = (kblocks + 1u) & ~1u;
-    mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(
-        static_cast<const uint8_t*>(args->scale_a), ws, args->m, kblocks, ks_pitch, p.kq_total, (args->m + 127u) / 128u,
-        args->layout_a == CB200_COLUMN_MAJOR ? 1u : 0u);
-    mx_pack_scales_kernel<<<dev.sm_count * 2, 256, 0, stream>>>(
-        static_cast<const uint8_t*>(args->scale_b), ws + sfa_bytes, args->n, kblocks, ks_pitch, p.kq_total,
-        2u * ((args->n + 255u) / 256u), args->layout_b == CB200_ROW_MAJOR ? 1u : 0u);
+    mx_pack_scales_kernel<<<dim3(dev.sm_count * 2, 1, 1), 256, 0, stream>>>(
+        static_cast<const uint8_t*>(q.scale_a), sfa, q.m, kblocks, ks_pitch, p.kq_total, plan.max_row_tiles,
+        q.layout_a == CB200_COLUMN_MAJOR ? 1u : 0u, 0, 0, p.tile_table, p.num_row_tiles);
+    {
+        const uint32_t gx = plan.b_matrices > 8u ? static_cast<uint32_t>(dev.sm_count) / 4u : dev.sm_count * 2u;
+        mx_pack_scales_kernel<<<dim3(gx, plan.b_matrices, 1), 256, 0, stream>>>(
+            static_cast<const uint8_t*>(q.scale_b), sfb, q.n, kblocks, ks_pitch, p.kq_total, sfb_blocks,
+            q.layout_b == CB200_ROW_MAJOR ? 1u : 0u, static_cast<uint64_t>(q.n) * ks_pitch,
+            static_cast<uint64_t>(sfb_blocks) * p.kq_total * 512u, nullptr, nullptr);
+    }
     CB200_CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(2, std::memory_order_relaxed);
 
     CUtensorMap tmap_a, tmap_b;
     {
-        const uint64_t dims[2] = {row_bytes, args->m};
+        const uint64_t dims[2] = {row_bytes, q.m};
         const uint64_t strides[1] = {row_bytes};
         const uint32_t box[2] = {kBlockKBytes, kBlockM};
         int rc = encode_tmap_u8(&tmap_a, a_ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -760,15 +814,15 @@ int launch_mx(const cb200_mx_matmul_args* args, const MxPlan& plan, const Device
         }
     }
     {
-        const uint64_t dims[2] = {row_bytes, args->n};
-        const uint64_t strides[1] = {row_bytes};
-        const uint32_t box[2] = {kBlockKBytes, kMxBlockN};
-        int rc = encode_tmap_u8(&tmap_b, b_ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        const uint64_t dims[3] = {row_bytes, q.n, plan.b_matrices};
+        const uint64_t strides[2] = {row_bytes, static_cast<uint64_t>(q.n) * row_bytes};
+        const uint32_t box[3] = {kBlockKBytes, kMxBlockN, 1};
+        int rc = encode_tmap_u8(&tmap_b, b_ptr, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != CB200_SUCCESS) {
             return rc;
         }
     }
-    auto kernel = mx_gemm_kernel<kFp4>;
+    auto kernel = mx_gemm_kernel<kFp4, kGrouped>;
     static PerDeviceOnce once;
     int devid = 0;
     int rc_dev = current_device(&devid);
@@ -782,10 +836,10 @@ int launch_mx(const cb200_mx_matmul_args* args, const MxPlan& plan, const Device
     if (rc_dev != CB200_SUCCESS) {
         return rc_dev;
     }
-    const uint64_t tiles = static_cast<uint64_t>((args->m + kBlockM - 1) / kBlockM) * ((args->n + kMxBlockN - 1) / kMxBlockN);
+    const uint64_t tiles = static_cast<uint64_t>(plan.max_row_tiles) * ((q.n + kMxBlockN - 1) / kMxBlockN);
     uint32_t grid = static_cast<uint32_t>(dev.sm_count);
-    if (args->block_num != 0 && args->block_num < grid) {
-        grid = args->block_num;
+    if (q.block_num != 0 && q.block_num < grid) {
+        grid = q.block_num;
     }
     if (tiles < grid) {
         grid = static_cast<uint32_t>(tiles);
@@ -796,34 +850,62 @@ int launch_mx(const cb200_mx_matmul_args* args, const MxPlan& plan, const Device
     return CB200_SUCCESS;
 }
 
-}  // namespace
-
-extern "C" {
-
-int cb200_mx_matmul_can_implement(const cb200_mx_matmul_args* args)
+MxProblem mx_dense_problem(const cb200_mx_matmul_args* a)
 {
-    MxPlan plan;
-    return plan_mx(args, &plan);
+    MxProblem q{};
+    q.m = a->m;
+    q.n = a->n;
+    q.k = a->k;
+    q.group_count = 0;
+    q.format = a->format;
+    q.layout_a = a->layout_a;
+    q.layout_b = a->layout_b;
+    q.a = a->a;
+    q.b = a->b;
+    q.scale_a = a->scale_a;
+    q.scale_b = a->scale_b;
+    q.d = a->d;
+    q.workspace = a->workspace;
+    q.workspace_bytes = a->workspace_bytes;
+    q.block_num = a->block_num;
+    q.flags = a->flags;
+    return q;
 }
 
-uint64_t cb200_mx_matmul_workspace_size(const cb200_mx_matmul_args* args)
+MxProblem mx_grouped_problem(const cb200_mx_grouped_matmul_args* a)
 {
-    MxPlan plan;
-    if (plan_mx(args, &plan) != CB200_SUCCESS) {
-        return 0;
-    }
-    return plan.total();
+    MxProblem q{};
+    q.m = a->m;
+    q.n = a->n;
+    q.k = a->k;
+    q.group_count = a->group_count;
+    q.format = a->format;
+    q.layout_a = CB200_ROW_MAJOR;
+    q.layout_b = a->layout_b;
+    q.group_list_type = a->group_list_type;
+    q.group_list_is_prefix_sum = a->group_list_kind == CB200_GROUP_LIST_PREFIX_SUMS ? 1u : 0u;
+    q.a = a->a;
+    q.b = a->b;
+    q.group_list = a->group_list;
+    q.scale_a = a->scale_a;
+    q.scale_b = a->scale_b;
+    q.d = a->d;
+    q.workspace = a->workspace;
+    q.workspace_bytes = a->workspace_bytes;
+    q.block_num = a->block_num;
+    q.flags = a->flags;
+    return q;
 }
 
-int cb200_mx_matmul(const cb200_mx_matmul_args* args, void* stream_v)
+int run_mx(const MxProblem& q, void* stream_v)
 {
     MxPlan plan;
-    int rc = plan_mx(args, &plan);
-    if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
+    int rc = plan_mx(q, &plan);
+    if (rc != CB200_SUCCESS || q.m == 0 || q.n == 0) {
         return rc;
     }
-    if (args->workspace == nullptr || args->workspace_bytes < plan.total() ||
-        (reinterpret_cast<uintptr_t>(args->workspace) & 255u) != 0) {
+    if (q.workspace == nullptr || q.workspace_bytes < plan.total() ||
+        (reinterpret_cast<uintptr_t>(q.workspace) & 255u) != 0) {
         return CB200_INVALID;
     }
     DeviceState* dev = nullptr;
@@ -832,8 +914,60 @@ int cb200_mx_matmul(const cb200_mx_matmul_args* args, void* stream_v)
         return rc;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    return args->format == CB200_MX_E2M1 ? launch_mx<true>(args, plan, *dev, stream)
-                                         : launch_mx<false>(args, plan, *dev, stream);
+    const bool fp4 = q.format == CB200_MX_E2M1;
+    if (q.group_count != 0) {
+        return fp4 ? launch_mx<true, true>(q, plan, *dev, stream) : launch_mx<false, true>(q, plan, *dev, stream);
+    }
+    return fp4 ? launch_mx<true, false>(q, plan, *dev, stream) : launch_mx<false, false>(q, plan, *dev, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb200_mx_matmul_can_implement(const cb200_mx_matmul_args* args)
+{
+    MxPlan plan;
+    return args == nullptr ? CB200_INVALID : plan_mx(mx_dense_problem(args), &plan);
+}
+
+uint64_t cb200_mx_matmul_workspace_size(const cb200_mx_matmul_args* args)
+{
+    MxPlan plan;
+    if (args == nullptr || plan_mx(mx_dense_problem(args), &plan) != CB200_SUCCESS) {
+        return 0;
+    }
+    return plan.total();
+}
+
+int cb200_mx_matmul(const cb200_mx_matmul_args* args, void* stream)
+{
+    return args == nullptr ? CB200_INVALID : run_mx(mx_dense_problem(args), stream);
+}
+
+int cb200_mx_grouped_matmul_slice_m_can_implement(const cb200_mx_grouped_matmul_args* args)
+{
+    MxPlan plan;
+    if (args == nullptr || args->group_count == 0 || args->group_list_kind > CB200_GROUP_LIST_PREFIX_SUMS) {
+        return CB200_INVALID;
+    }
+    return plan_mx(mx_grouped_problem(args), &plan);
+}
+
+uint64_t cb200_mx_grouped_matmul_slice_m_workspace_size(const cb200_mx_grouped_matmul_args* args)
+{
+    MxPlan plan;
+    if (cb200_mx_grouped_matmul_slice_m_can_implement(args) != CB200_SUCCESS ||
+        plan_mx(mx_grouped_problem(args), &plan) != CB200_SUCCESS) {
+        return 0;
+    }
+    return plan.total();
+}
+
+int cb200_mx_grouped_matmul_slice_m(const cb200_mx_grouped_matmul_args* args, void* stream)
+{
+    const int rc = cb200_mx_grouped_matmul_slice_m_can_implement(args);
+    return rc != CB200_SUCCESS ? rc : run_mx(mx_grouped_problem(args), stream);
 }
 
 int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args* args)
@@ -936,6 +1070,10 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args_in, void* stream_v)
     p.status = dev->status;
     p.out_f16 = args->d_type == CB200_DTYPE_F16 ? 1u : 0u;
     p.static_weights = (args->flags & CB200_FLAG_STATIC_WEIGHTS) ? 1u : 0u;
+    {
+        const long v = dev_knob("CB200_W4A8_TOKEN_LOADS", kW4MaxTokenLoads);
+        p.token_loads_max = (v >= 1 && v <= kW4MaxTokenLoads) ? static_cast<uint32_t>(v) : kW4MaxTokenLoads;
+    }
     CUtensorMap tmap_w, tmap_x;
     {
         // packed weights as (64 bytes of a K block, channel, K block): a box is kW4Load consecutive blocks
@@ -1415,30 +1553,97 @@ uint64_t cb200_mx_matmul_static_scratch_bytes(void)
 // Allocates nothing.  The first call on a device performs the address look-up above.
 int cb200_mx_matmul_static(const cb200_mx_matmul_args* args, void* stream_v)
 {
+    if (args == nullptr) {
+        return CB200_INVALID;
+    }
+    MxProblem q = mx_dense_problem(args);
     MxPlan plan;
-    int rc = plan_mx(args, &plan);
+    int rc = plan_mx(q, &plan);
     if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
         return rc;
     }
     if (plan.total() > kMxStaticScratchBytes) {
         return CB200_SCRATCH_TOO_SMALL;
     }
-    DeviceState* dev = nullptr;
-    rc = device_state(&dev);
-    if (rc != CB200_SUCCESS) {
-        return rc;
-    }
     uint8_t* scratch = nullptr;
     rc = mx_static_scratch(&scratch);
     if (rc != CB200_SUCCESS) {
         return rc;
     }
-    cb200_mx_matmul_args with_scratch = *args;
-    with_scratch.workspace = scratch;
-    with_scratch.workspace_bytes = kMxStaticScratchBytes;
+    q.workspace = scratch;
+    q.workspace_bytes = kMxStaticScratchBytes;
+    return run_mx(q, stream_v);
+}
+
+}  // extern "C"
+
+extern "C" {
+
+int cb200_mx_quantize_can_implement(const cb200_mx_quantize_args* args)
+{
+    if (args == nullptr) {
+        return CB200_INVALID;
+    }
+    if (args->rows == 0 || args->k == 0) {
+        return CB200_SUCCESS;
+    }
+    if (args->x == nullptr || args->q == nullptr || args->scale == nullptr) {
+        return CB200_INVALID;
+    }
+    if ((args->format != CB200_MX_E4M3 && args->format != CB200_MX_E2M1) ||
+        (args->x_type != CB200_DTYPE_F32 && args->x_type != CB200_DTYPE_BF16)) {
+        return CB200_INVALID;
+    }
+    if (args->x_pitch != 0 && args->x_pitch < args->k) {
+        return CB200_INVALID;
+    }
+    const uintptr_t x_mask = args->x_type == CB200_DTYPE_F32 ? 3u : 1u;
+    if ((reinterpret_cast<uintptr_t>(args->x) & x_mask) != 0) {
+        return CB200_INVALID;
+    }
+    return CB200_SUCCESS;
+}
+
+int cb200_mx_quantize(const cb200_mx_quantize_args* args, void* stream_v)
+{
+    int rc = cb200_mx_quantize_can_implement(args);
+    if (rc != CB200_SUCCESS || args->rows == 0 || args->k == 0) {
+        return rc;
+    }
+    DeviceState* dev = nullptr;
+    rc = device_state(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    return args->format == CB200_MX_E2M1 ? launch_mx<true>(&with_scratch, plan, *dev, stream)
-                                         : launch_mx<false>(&with_scratch, plan, *dev, stream);
+    const bool fp4 = args->format == CB200_MX_E2M1;
+    const bool bf16 = args->x_type == CB200_DTYPE_BF16;
+    const uint64_t x_pitch = args->x_pitch != 0 ? args->x_pitch : args->k;
+    const uint32_t q_pitch = fp4 ? (args->k + 1u) / 2u : args->k;
+    const uint32_t sf_pitch = (((args->k + 31u) / 32u) + 1u) & ~1u;
+    // vector accesses need aligned bases; the kernel falls back to element accesses on odd pitches by itself
+    const bool x_vec = (reinterpret_cast<uintptr_t>(args->x) & 15u) == 0;
+    const bool q_vec = (reinterpret_cast<uintptr_t>(args->q) & 3u) == 0;
+    if (!x_vec || !q_vec) {
+        return CB200_INVALID;  // torch / cudaMalloc buffers are 256-byte aligned; unaligned views are not taken
+    }
+    const uint32_t blocks = static_cast<uint32_t>(dev->sm_count) * 8u;
+    uint8_t* q = static_cast<uint8_t*>(args->q);
+    uint8_t* sf = static_cast<uint8_t*>(args->scale);
+    if (fp4) {
+        if (bf16) {
+            mx_quantize_kernel<true, true><<<blocks, 256, 0, stream>>>(args->x, q, sf, args->rows, args->k, x_pitch, q_pitch, sf_pitch);
+        } else {
+            mx_quantize_kernel<true, false><<<blocks, 256, 0, stream>>>(args->x, q, sf, args->rows, args->k, x_pitch, q_pitch, sf_pitch);
+        }
+    } else if (bf16) {
+        mx_quantize_kernel<false, true><<<blocks, 256, 0, stream>>>(args->x, q, sf, args->rows, args->k, x_pitch, q_pitch, sf_pitch);
+    } else {
+        mx_quantize_kernel<false, false><<<blocks, 256, 0, stream>>>(args->x, q, sf, args->rows, args->k, x_pitch, q_pitch, sf_pitch);
+    }
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return CB200_SUCCESS;
 }
 
 }  // extern "C"

@@ -20,9 +20,13 @@ namespace cb200 {
 
 // dst[r][0 .. dst_pitch) = src[r][0 .. valid) followed by zeros; when `clear_last_high_nibble` the upper four bits
 // of byte valid-1 are cleared too (packed 4-bit rows with an odd element count).
+// (All three kernels: blockIdx.y walks a batch of matrices, src_batch / dst_batch bytes apart.)
 __global__ void pad_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint32_t rows,
-                                uint64_t src_pitch, uint32_t dst_pitch, uint32_t valid, uint32_t clear_last_high_nibble)
+                                uint64_t src_pitch, uint32_t dst_pitch, uint32_t valid, uint32_t clear_last_high_nibble,
+                                uint64_t src_batch = 0, uint64_t dst_batch = 0)
 {
+    src += blockIdx.y * src_batch;
+    dst += blockIdx.y * dst_batch;
     const uint64_t words_per_row = dst_pitch / 16;  // dst_pitch is a multiple of 16
     const uint64_t total = static_cast<uint64_t>(rows) * words_per_row;
     for (uint64_t w = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; w < total;
@@ -47,8 +51,11 @@ __global__ void pad_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __rest
 // Transposes a byte matrix: src is [k][rows] (pitch src_pitch), dst is [rows][dst_pitch] with columns >= k zero.
 // 32 x 32 tiles through shared memory: reads and writes are both coalesced.
 __global__ void transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint32_t rows,
-                                       uint32_t k, uint64_t src_pitch, uint32_t dst_pitch)
+                                       uint32_t k, uint64_t src_pitch, uint32_t dst_pitch, uint64_t src_batch = 0,
+                                       uint64_t dst_batch = 0)
 {
+    src += blockIdx.y * src_batch;
+    dst += blockIdx.y * dst_batch;
     __shared__ uint8_t tile[32][33];
     const uint32_t tiles_r = (rows + 31) / 32, tiles_k = dst_pitch / 32;  // dst_pitch is a multiple of 32
     const uint64_t total = static_cast<uint64_t>(tiles_r) * tiles_k;
@@ -73,8 +80,11 @@ __global__ void transpose_bytes_kernel(const uint8_t* __restrict__ src, uint8_t*
 // 0-3, pitch src_pitch bytes); dst holds [rows][k] values, two per byte along k (pitch dst_pitch bytes, columns
 // >= k zero).  One thread builds one 32-bit word of dst (eight k values of one row).
 __global__ void transpose_nibbles_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint32_t rows,
-                                         uint32_t k, uint64_t src_pitch, uint32_t dst_pitch)
+                                         uint32_t k, uint64_t src_pitch, uint32_t dst_pitch, uint64_t src_batch = 0,
+                                         uint64_t dst_batch = 0)
 {
+    src += blockIdx.y * src_batch;
+    dst += blockIdx.y * dst_batch;
     const uint32_t words_per_row = dst_pitch / 4;
     const uint64_t total = static_cast<uint64_t>(rows) * words_per_row;
     // consecutive threads take consecutive rows of one word column: they read neighbouring source bytes

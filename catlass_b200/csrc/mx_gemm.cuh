@@ -47,7 +47,47 @@ struct MxParams {
     void* d;                   // [m][n] bf16, or fp32 when out_f32
     unsigned* status;
     uint32_t out_f32;
+    // grouped (slice-M) problems: the row tiles come from a table a planning kernel wrote (see mx_group_plan_kernel)
+    const int4* tile_table;           // [row tile] = (first row, one past the group's last row, group, 0)
+    const uint32_t* num_row_tiles;    // number of table entries
+    uint32_t sfb_blocks_per_group;    // 128-row scale blocks of B per group: 2 * ceil(n / 256)
 };
+
+// One block: turns the group list of a grouped slice-M problem into the row-tile table the matmul and the scale
+// re-tiling walk.  Group g owns rows [start_g, start_g + size_g) of A and D, clamped to m; its row tiles are 128
+// rows each (the last one partial); empty groups add nothing.  The list holds sizes (the reference's example 55:
+// examples/55_ascend950_mx_grouped_matmul_slice_m/mx_grouped_matmul_slice_m.cpp:265, non-cumsum) or prefix sums.
+__global__ void mx_group_plan_kernel(const void* group_list, uint32_t is_i32, uint32_t is_prefix_sum, uint32_t groups,
+                                     uint32_t m, int4* table, uint32_t* num_row_tiles)
+{
+    __shared__ uint32_t s_begin[kMaxGroups + 1];
+    __shared__ uint32_t s_tile[kMaxGroups + 1];
+    if (threadIdx.x == 0) {
+        long long prev = 0;
+        uint32_t tiles = 0;
+        for (uint32_t g = 0; g < groups; ++g) {
+            long long v = is_i32 ? static_cast<long long>(static_cast<const int32_t*>(group_list)[g])
+                                 : static_cast<const long long*>(group_list)[g];
+            long long end = is_prefix_sum ? v : prev + (v < 0 ? 0 : v);
+            end = end < prev ? prev : (end > static_cast<long long>(m) ? static_cast<long long>(m) : end);
+            s_begin[g] = static_cast<uint32_t>(prev);
+            s_tile[g] = tiles;
+            tiles += static_cast<uint32_t>((end - prev + kBlockM - 1) / kBlockM);
+            prev = end;
+        }
+        s_begin[groups] = static_cast<uint32_t>(prev);
+        s_tile[groups] = tiles;
+        *num_row_tiles = tiles;
+    }
+    __syncthreads();
+    for (uint32_t g = threadIdx.x; g < groups; g += blockDim.x) {
+        const uint32_t begin = s_begin[g], end = s_begin[g + 1];
+        for (uint32_t t = s_tile[g]; t < s_tile[g + 1]; ++t) {
+            table[t] = make_int4(static_cast<int>(begin + (t - s_tile[g]) * kBlockM), static_cast<int>(end),
+                                 static_cast<int>(g), 0);
+        }
+    }
+}
 
 struct MxSmem {
     static constexpr int kABytes = kBlockM * kBlockKBytes;      // 16 KB
@@ -67,17 +107,27 @@ struct MxSmem {
 // the reference's two scale layouts (tests/optest/tests/mx_golden.py:253-266), with ks_pitch = the even number of
 // scale blocks per row the caller's array holds.  Blocks at or beyond `kblocks_valid` = ceil(K / 32), and rows
 // past the end, get the neutral scale 2^0 (their elements are zero).
+// blockIdx.y walks a batch (the weight matrices of a grouped problem): input and output advance by in_batch /
+// out_batch bytes.  With a row-tile table (grouped A) output block t holds the 128 rows that start at the table's
+// row for tile t, which need not be a multiple of 128.
 __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t rows,
                                       uint32_t kblocks_valid, uint32_t ks_pitch, uint32_t kq_total,
-                                      uint32_t row_blocks, uint32_t k_major)
+                                      uint32_t row_blocks, uint32_t k_major, uint64_t in_batch, uint64_t out_batch,
+                                      const int4* tile_table, const uint32_t* num_row_tiles)
 {
+    in += blockIdx.y * in_batch;
+    out += blockIdx.y * out_batch;
+    if (tile_table != nullptr) {
+        row_blocks = *num_row_tiles < row_blocks ? *num_row_tiles : row_blocks;
+    }
     const size_t words = static_cast<size_t>(row_blocks) * kq_total * 128;
     const bool word_loads = !k_major && (ks_pitch & 3u) == 0 && (reinterpret_cast<uintptr_t>(in) & 3u) == 0;
     for (size_t w = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; w < words;
          w += static_cast<size_t>(gridDim.x) * blockDim.x) {
         // consecutive threads walk consecutive scale words of one row: coalesced reads
         const uint32_t kq = static_cast<uint32_t>(w % kq_total);
-        const uint32_t row = static_cast<uint32_t>(w / kq_total);  // padded row index
+        const uint32_t prow = static_cast<uint32_t>(w / kq_total);  // row index inside the padded output
+        const uint32_t row = tile_table == nullptr ? prow : static_cast<uint32_t>(tile_table[prow / 128].x) + prow % 128;
         uint32_t v = 0x7F7F7F7Fu;
         if (row < rows) {
             if (word_loads && kq * 4 + 4 <= kblocks_valid) {
@@ -96,7 +146,7 @@ __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* _
                 }
             }
         }
-        const uint32_t rb = row / 128, r = row % 128;
+        const uint32_t rb = prow / 128, r = prow % 128;
         uint8_t* dst = out + (static_cast<size_t>(rb) * kq_total + kq) * 512 + (r % 32) * 16 + (r / 32) * 4;
         *reinterpret_cast<uint32_t*>(dst) = v;
     }
@@ -117,7 +167,9 @@ __device__ __forceinline__ void mx_tile_coords(uint32_t idx, uint32_t m_tiles, u
     mt = band * band_rows + (r - nt * rows);
 }
 
-template <bool kFp4>
+// kGrouped: slice-M groups (the reference's GroupedMxMatmulSliceMTla, example 55): row tiles come from the tile
+// table, every group has its own weight matrix (third coordinate of B's tensor map) and B scales.
+template <bool kFp4, bool kGrouped>
 __global__ void __launch_bounds__(kMxThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const MxParams p)
@@ -146,9 +198,22 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t m_tiles = (p.m + kBlockM - 1) / kBlockM;
+    const uint32_t m_tiles = kGrouped ? *p.num_row_tiles : (p.m + kBlockM - 1) / kBlockM;
     const uint32_t n_tiles = (p.n + kMxBlockN - 1) / kMxBlockN;
     const uint32_t total_tiles = m_tiles * n_tiles;
+    // first row, end of the rows that may be stored, group of row tile mt
+    auto row_tile = [&](uint32_t mt, int32_t& row0, int32_t& row_end, int32_t& group) {
+        if constexpr (kGrouped) {
+            const int4 e = __ldg(p.tile_table + mt);
+            row0 = e.x;
+            row_end = e.y;
+            group = e.z;
+        } else {
+            row0 = static_cast<int32_t>(mt) * kBlockM;
+            row_end = static_cast<int32_t>(p.m);
+            group = 0;
+        }
+    };
     const uint32_t num_kb = p.num_k_blocks;
 
     if (threadIdx.x == 0) {
@@ -183,6 +248,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
                 uint32_t mt, nt;
                 mx_tile_coords(idx, m_tiles, n_tiles, p.band_rows, mt, nt);
+                int32_t row0, row_end, group;
+                row_tile(mt, row0, row_end, group);
+                const size_t sfb_block = static_cast<size_t>(group) * p.sfb_blocks_per_group + 2 * nt;
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer);
                     if (!ok) {
@@ -195,13 +263,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const int32_t k0 = static_cast<int32_t>(kb) * kBlockKBytes;
                     const size_t kq = static_cast<size_t>(kb) * kWords;
                     mbar_expect_tx(full, kStageTx);
-                    tma_load_2d(sa, &tmap_a, full, k0, static_cast<int32_t>(mt) * kBlockM);
-                    tma_load_2d(sb, &tmap_b, full, k0, static_cast<int32_t>(nt) * kMxBlockN);
+                    tma_load_2d(sa, &tmap_a, full, k0, row0);
+                    tma_load_3d(sb, &tmap_b, full, k0, static_cast<int32_t>(nt) * kMxBlockN, group);
                     bulk_load(ssf, p.sfa + (static_cast<size_t>(mt) * p.kq_total + kq) * 512, kWords * 512, full);
                     // the tile's 256 columns are two 128-row scale blocks of B (the workspace pads to a pair)
-                    bulk_load(ssf + 1024, p.sfb + (static_cast<size_t>(2 * nt) * p.kq_total + kq) * 512, kWords * 512,
-                              full);
-                    bulk_load(ssf + 1024 + kWords * 512, p.sfb + (static_cast<size_t>(2 * nt + 1) * p.kq_total + kq) * 512,
+                    bulk_load(ssf + 1024, p.sfb + (sfb_block * p.kq_total + kq) * 512, kWords * 512, full);
+                    bulk_load(ssf + 1024 + kWords * 512, p.sfb + ((sfb_block + 1) * p.kq_total + kq) * 512,
                               kWords * 512, full);
                     if (++stage == kMxStages) {
                         stage = 0;
@@ -330,8 +397,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 break;
             }
             tcgen05_fence_after();
-            const uint32_t row = mt * kBlockM + quad * 32 + lane;
-            const bool row_ok = row < p.m;
+            int32_t row0, row_end, group;
+            row_tile(mt, row0, row_end, group);
+            const uint32_t row = static_cast<uint32_t>(row0) + quad * 32 + lane;
+            const bool row_ok = static_cast<int32_t>(row) < row_end;
             const uint32_t taddr = tmem_base + acc * kMxBlockN + half * 128 + ((quad * 32u) << 16);
             if (p.out_f32) {
                 // fp32 output (what the reference's MX kernels write): the accumulator goes out as it is, 32 columns

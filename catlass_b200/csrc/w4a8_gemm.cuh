@@ -60,7 +60,10 @@ constexpr int kW4AccPairs = 2;      // accumulators are handed over two at a tim
 constexpr int kW4Tiles = 4;         // token tiles / unpacked weight tiles in flight (= unpack warps, see there)
 constexpr int kW4PackedSlots = 12;  // packed-weight tiles in flight (8 KB each): covers HBM latency
 constexpr int kW4MaxSplits = 4;     // CTAs of a cluster sharing one channel tile along K
-constexpr int kW4Load = 2;          // K blocks per TMA load (3-D boxes): half the loads and barrier round trips
+#ifndef CB200_W4_LOAD
+#define CB200_W4_LOAD 2
+#endif
+constexpr int kW4Load = CB200_W4_LOAD;  // K blocks per TMA load (3-D boxes): half the loads and barrier round trips
 constexpr int kW4PackedLoads = kW4PackedSlots / kW4Load;  // load slots of the packed-weight ring
 constexpr int kW4MaxTokenLoads = 8;                       // load slots of the token ring at most (see x_loads)
 
@@ -92,6 +95,7 @@ struct W4A8Params {
     unsigned* status;
     uint32_t out_f16;
     uint32_t static_weights;    // weights and their scales may be read before the stream dependency resolves
+    uint32_t token_loads_max;   // cap on the token ring's load slots (<= kW4MaxTokenLoads)
 };
 
 struct W4A8Smem {
@@ -232,7 +236,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     // so the bytes in flight decide the rate; the ring is independent of the four unpacked-tile slots.
     const uint32_t x_load_bytes = kW4Load * p.mt * 128;
     const uint32_t x_loads_fit = (kW4Tiles * S::kTokenBytes) / x_load_bytes;
-    const uint32_t x_loads = x_loads_fit < static_cast<uint32_t>(kW4MaxTokenLoads) ? x_loads_fit : kW4MaxTokenLoads;
+    const uint32_t x_loads = x_loads_fit < p.token_loads_max ? x_loads_fit : p.token_loads_max;
 
     if (threadIdx.x == 0) {
         *s_abort = 0;

@@ -8,7 +8,7 @@ the quantized-matmul path can be run against CUDA tensors by importing this modu
 Covered: quant_matmul (example 12), quant_optimized_matmul_tla (42), grouped_matmul_slice_m_per_token_dequant (07),
 grouped_matmul_slice_m_per_token_dequant_multistage (10), ascend950_grouped_matmul_slice_m_per_token_dequant (47),
 ascend950_grouped_matmul_slice_m_per_tensor_per_channel_dequant (48), w4a8_matmul (32),
-ascend950_fp8_mx_matmul[_aswt] (53), ascend950_fp4_mx_matmul[_aswt] (54).
+ascend950_fp8_mx_matmul[_aswt] (53), ascend950_fp4_mx_matmul[_aswt] (54), ascend950_mx_grouped_matmul_slice_m (55).
 
 Tensors are CUDA tensors; outputs are allocated with torch (this module is the binding, not the library: the
 library itself never allocates).  Every call enqueues on the current stream and returns without synchronising.
@@ -193,6 +193,31 @@ def _mx(mat1, mat2, mx_scale_a, mx_scale_b, transA, transB, fmt):
     ws = torch.empty(max(capi.mx_matmul_workspace_size(m, n, k, fmt, la, lb), 1), dtype=torch.uint8, device=mat1.device)
     capi.mx_matmul(a_bytes, b_bytes, mx_scale_a.contiguous().view(torch.uint8), mx_scale_b.contiguous().view(torch.uint8),
                    d, m, n, k, fmt, ws, layout_a=la, layout_b=lb, out_f32=True)
+    return d
+
+
+def ascend950_mx_grouped_matmul_slice_m(mat1, mat2, groupList, mx_scale_a, mx_scale_b, transA=False, transB=False,
+                                        enable_aswt=False, enable_preload=False):
+    """Example 55: mat1 (M, K), mat2 (G, K, N) or with transB (G, N, K), groupList the groups' row counts (int64,
+    not prefix sums), block scales per group for mat2; fp32 output.  The two scheduler switches of the reference
+    select variants of its kernel and change no result: they are accepted and ignored."""
+    _require_cuda(mat1, mat2, groupList, mx_scale_a, mx_scale_b)
+    if transA:
+        raise ValueError("slice-M groups cut A by rows: A is (M, K)")
+    mat1, mat2, groupList = mat1.contiguous(), mat2.contiguous(), groupList.contiguous()
+    fmt = capi.MX_E2M1 if mat1.dtype == getattr(torch, "float4_e2m1fn_x2", None) else capi.MX_E4M3
+    m, k = tuple(mat1.shape)
+    g = groupList.numel()
+    n = mat2.shape[1] if transB else mat2.shape[2]
+    lb = capi.COLUMN_MAJOR if transB else capi.ROW_MAJOR
+    d = torch.zeros((m, n), dtype=torch.float32, device=mat1.device)
+    ws = torch.empty(max(capi.mx_grouped_matmul_workspace_size(m, n, k, g, fmt, lb), 1), dtype=torch.uint8,
+                     device=mat1.device)
+    capi.mx_grouped_matmul(mat1.view(torch.uint8), mat2.view(torch.uint8), groupList,
+                           mx_scale_a.contiguous().view(torch.uint8), mx_scale_b.contiguous().view(torch.uint8), d, m, n,
+                           k, g, fmt, ws, layout_b=lb,
+                           group_list_type=capi.GROUP_LIST_INT32 if groupList.dtype == torch.int32
+                           else capi.GROUP_LIST_INT64, group_list_kind=capi.GROUP_LIST_SIZES, out_f32=True)
     return d
 
 

@@ -324,6 +324,45 @@ CB200_API uint64_t cb200_mx_matmul_workspace_size(const cb200_mx_matmul_args *ar
 CB200_API int cb200_mx_matmul(const cb200_mx_matmul_args *args, void *stream);
 
 /*
+ * Grouped (slice-M) MX block-scaled matmul: group g owns a run of rows of A and D, its own weight matrix B[g] and
+ * that matrix's scales.  Replaces Gemm::Kernel::GroupedMxMatmulSliceMTla::Arguments (example 55:
+ * examples/55_ascend950_mx_grouped_matmul_slice_m/mx_grouped_matmul_slice_m.cpp:168-176, 325-357: problemShape,
+ * problemCount, ptrGroupList, ptrA, ptrB, ptrMxScaleA, ptrMxScaleB, ptrC), golden
+ * tests/optest/tests/mx_golden.py:325-378.
+ *   a        [m][k] elements, rows along K (E2M1 two per byte)          scale_a [m][KS]
+ *   b        CB200_COLUMN_MAJOR: [G][n][k];  CB200_ROW_MAJOR: [G][k][n]   scale_b [G][n][KS] / [G][KS/2][n][2]
+ *   group_list  `group_count` entries on the device, int64 or int32: the groups' row counts (the reference's
+ *            example passes sizes, not prefix sums) or ascending prefix sums, as group_list_kind says; rows past
+ *            the last group are not written, entries are clamped to m
+ * Arbitrary k, ingestion and output type as for cb200_mx_matmul; the workspace also holds the row-tile table a
+ * small planning kernel derives from the group list.
+ */
+#define CB200_GROUP_LIST_SIZES 0
+#define CB200_GROUP_LIST_PREFIX_SUMS 1
+typedef struct cb200_mx_grouped_matmul_args {
+    uint32_t m, n, k;
+    uint32_t group_count;         /* 1 .. 1024 */
+    uint32_t format;              /* CB200_MX_E4M3 / CB200_MX_E2M1 */
+    uint32_t layout_b;            /* CB200_COLUMN_MAJOR ([G][n][k]) or CB200_ROW_MAJOR ([G][k][n]) */
+    uint32_t group_list_type;     /* CB200_GROUP_LIST_INT64 / _INT32 */
+    uint32_t group_list_kind;     /* CB200_GROUP_LIST_SIZES / CB200_GROUP_LIST_PREFIX_SUMS */
+    const void *a;
+    const void *b;
+    const void *group_list;
+    const void *scale_a;
+    const void *scale_b;
+    void *d;                      /* m x n row-major: bf16, or fp32 with CB200_MX_OUT_F32 */
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t flags;               /* 0 or CB200_MX_OUT_F32 */
+} cb200_mx_grouped_matmul_args;
+
+CB200_API int cb200_mx_grouped_matmul_slice_m_can_implement(const cb200_mx_grouped_matmul_args *args);
+CB200_API uint64_t cb200_mx_grouped_matmul_slice_m_workspace_size(const cb200_mx_grouped_matmul_args *args);
+CB200_API int cb200_mx_grouped_matmul_slice_m(const cb200_mx_grouped_matmul_args *args, void *stream);
+
+/*
  * cb200_mx_matmul_static: the MX matmul above for callers that cannot give it a workspace.
  * (No counterpart in the reference: every reference kernel takes its workspace from the caller or allocates
  * it per call, examples/shared_lib/src/common/common.hpp:36-46.)
@@ -347,6 +386,31 @@ CB200_API int cb200_mx_matmul(const cb200_mx_matmul_args *args, void *stream);
  */
 CB200_API int cb200_mx_matmul_static(const cb200_mx_matmul_args *args, void *stream);
 CB200_API uint64_t cb200_mx_matmul_static_scratch_bytes(void);
+
+/*
+ * MX quantisation of activations on the device: x (fp32 or bf16, rows x k, row pitch x_pitch elements) ->
+ * element codes q and E8M0 scales in exactly the form cb200_mx_matmul takes for an operand whose rows run along K:
+ *     q      [rows][k] bytes (E4M3), or [rows][ceil(k/2)] bytes (E2M1, even index in bits 0-3)
+ *     scale  [rows][KS] bytes, KS = ceil(k/32) rounded up to even (padding = 2^0)
+ * Rule (the reference's host-side generators, examples/53_ascend950_fp8_mx_matmul/gen_data.py:186-265 and
+ * examples/54_ascend950_fp4_mx_matmul/gen_data.py:46-95): per block of 32, exponent = floor(log2(max|x|)) - emax
+ * (emax 8 / 2; 0 for an all-zero block), element = x / 2^exponent clamped and snapped to the nearest code, ties to
+ * the smaller magnitude.  On the device the reference does this only inside its experimental fused MoE epilogue
+ * (experimental/gmm/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant); this entry is the stand-alone step
+ * in front of the MX matmul.  No workspace.
+ */
+typedef struct cb200_mx_quantize_args {
+    uint32_t rows, k;
+    uint32_t format;      /* CB200_MX_E4M3 / CB200_MX_E2M1 */
+    uint32_t x_type;      /* CB200_DTYPE_F32 or CB200_DTYPE_BF16 */
+    uint64_t x_pitch;     /* elements between rows of x; 0 = k */
+    const void *x;
+    void *q;
+    void *scale;
+} cb200_mx_quantize_args;
+
+CB200_API int cb200_mx_quantize_can_implement(const cb200_mx_quantize_args *args);
+CB200_API int cb200_mx_quantize(const cb200_mx_quantize_args *args, void *stream);
 
 /* ---- library / device state ---- */
 

@@ -200,3 +200,53 @@ def test_w4a8_weights_written_on_the_stream_right_before_the_call(cuda):
         assert capi.device_status()[0] == 0
         got = d.view(torch.int16).cpu().numpy().view(np.uint16)[:, cols]
         assert np.array_equal(got, want)
+
+
+# ------------------------------------------------------------------------------------------------ grouped MX
+
+@pytest.mark.parametrize("fmt", [O.MX_E4M3, O.MX_E2M1])
+@pytest.mark.parametrize("sizes,n,k,trans_b,prefix", [
+    ((128, 128), 128, 256, False, False),           # the reference's optest shape
+    ((130, 0, 64, 257, 1, 300), 264, 512, True, False),
+    ((5, 200, 0, 129), 520, 330, False, True),      # ragged K, prefix-sum list
+    ((1000, 24), 1025, 96, True, True),
+])
+def test_mx_grouped_slice_m(cuda, fmt, sizes, n, k, trans_b, prefix):
+    """Example 55: per-group weights and weight scales, the group list given as row counts (the reference's
+    convention) or prefix sums; every group checked against the oracle's dequantised matmul of its own rows; rows
+    past the last group keep the caller's bytes."""
+    import torch
+    from catlass_b200 import capi
+    rng = np.random.default_rng(sum(sizes) + n + k)
+    g = len(sizes)
+    rows = sum(sizes)
+    m = rows + 37
+    a = (rng.standard_normal((m, k)) * 10.0 - 5.0).astype(np.float32)
+    aq, sfa = O.mx_quantize(a, fmt)
+    bq, sfb, want = [], [], np.zeros((m, n), np.float32)
+    start = 0
+    for e in range(g):
+        bt = (rng.standard_normal((n, k)) * 10.0 - 5.0).astype(np.float32)
+        q_e, s_e = O.mx_quantize(bt, fmt)
+        bq.append(q_e)
+        sfb.append(s_e)
+        if sizes[e]:
+            want[start:start + sizes[e]] = O.mx_matmul(aq[start:start + sizes[e]], sfa[start:start + sizes[e]], q_e, s_e,
+                                                       sizes[e], n, k, fmt)
+        start += sizes[e]
+    lb = capi.COLUMN_MAJOR if trans_b else capi.ROW_MAJOR
+    b_dev = _dev(np.stack([_stored_operand(q_e, fmt, not trans_b) for q_e in bq]))
+    sb_dev = _dev(np.stack([_stored_scales(s_e, not trans_b) for s_e in sfb]))
+    gl = np.cumsum(sizes) if prefix else np.array(sizes)
+    canary = -7.0
+    d = torch.full((m, n), canary, dtype=torch.float32, device=cuda)
+    ws = torch.empty(max(capi.mx_grouped_matmul_workspace_size(m, n, k, g, fmt, lb), 256), dtype=torch.uint8, device=cuda)
+    capi.mx_grouped_matmul(_dev(_stored_operand(aq, fmt, False)), b_dev, _dev(gl.astype(np.int64)),
+                           _dev(_stored_scales(sfa, False)), sb_dev, d, m, n, k, g, fmt, ws, layout_b=lb,
+                           group_list_kind=capi.GROUP_LIST_PREFIX_SUMS if prefix else capi.GROUP_LIST_SIZES, out_f32=True)
+    st, code = capi.device_status()
+    assert st == 0, f"device status {st} code {code:#x}"
+    got = d.cpu().numpy()
+    assert (got[rows:] == canary).all(), "rows past the last group were written"
+    err = np.abs(got[:rows] - want[:rows]) / np.maximum(1.0, np.abs(want[:rows]))
+    assert np.isfinite(got[:rows]).all() and err.max() <= 1e-3, f"max rel err {err.max():.5f}"

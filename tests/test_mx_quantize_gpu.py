@@ -1,0 +1,86 @@
+"""cb200_mx_quantize on the GPU against the CPU oracle's quantiser (itself pinned to the reference's generators):
+element codes and scale bytes must be identical, for E4M3 and E2M1, fp32 and bf16 inputs, ragged K, zero blocks,
+saturating and tiny values; and its output must feed cb200_mx_matmul unchanged."""
+import numpy as np
+import pytest
+
+import oracle_lib as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(rows, k, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((rows, k)).astype(np.float32)
+    x *= np.float32(2.0) ** rng.integers(-12, 13, (rows, 1)).astype(np.float32)   # a spread of row magnitudes
+    if rows > 4 and k >= 64:
+        x[1, :32] = 0.0                       # an all-zero block
+        x[2, 5] = 3.0e4                       # saturates its block's grid
+        x[3, 32:64] *= np.float32(1.0e-20)    # tiny values (exponent clamp)
+        x[4, :] = np.float32(448.0)           # exactly the largest E4M3 value
+    # exact grid ties: halves between neighbouring codes
+    x[0, :min(k, 8)] = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0], np.float32)[:min(k, 8)]
+    return x
+
+
+def _run(cuda, x, fmt, bf16):
+    import torch
+    from catlass_b200 import capi
+    rows, k = x.shape
+    xt = torch.from_numpy(x).cuda()
+    if bf16:
+        xt = xt.to(torch.bfloat16)
+    ks = ((k + 31) // 32 + 1) // 2 * 2
+    q_cols = (k + 1) // 2 if fmt == O.MX_E2M1 else k
+    q = torch.full((rows, q_cols), 0xAA, dtype=torch.uint8, device=cuda)
+    sf = torch.full((rows, ks), 0xAA, dtype=torch.uint8, device=cuda)
+    capi.mx_quantize(xt, q, sf, rows, k, fmt, x_type=capi.DTYPE_BF16 if bf16 else capi.DTYPE_F32)
+    assert capi.device_status()[0] == 0
+    ref_in = xt.float().cpu().numpy() if bf16 else x
+    return q.cpu().numpy(), sf.cpu().numpy(), ref_in
+
+
+@pytest.mark.parametrize("fmt", [O.MX_E4M3, O.MX_E2M1])
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("rows,k", [(64, 1024), (7, 129), (33, 63), (5, 2), (300, 4096), (16, 96)])
+def test_mx_quantize_matches_the_oracle_bit_for_bit(cuda, fmt, bf16, rows, k):
+    x = _inputs(rows, k, seed=rows + k)
+    q, sf, ref_in = _run(cuda, x, fmt, bf16)
+    want_q, want_sf = O.mx_quantize(ref_in, fmt)
+    blocks = want_sf.shape[1]
+    assert np.array_equal(sf[:, :blocks], want_sf)
+    assert (sf[:, blocks:] == 127).all()
+    if fmt == O.MX_E2M1:
+        kk = want_q.shape[1]
+        padded = np.concatenate([want_q, np.zeros((rows, kk & 1), np.uint8)], axis=1)
+        want_q = (padded[:, 0::2] | (padded[:, 1::2] << 4)).astype(np.uint8)
+    assert np.array_equal(q, want_q), f"{(q != want_q).sum()} of {q.size} codes differ"
+
+
+@pytest.mark.parametrize("fmt", [O.MX_E4M3, O.MX_E2M1])
+def test_quantize_then_matmul(cuda, fmt):
+    """Activations quantised on the device go straight into the MX matmul (same layouts, no host step)."""
+    import torch
+    from catlass_b200 import capi
+    m, n, k = 200, 264, 1024
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    bt = rng.standard_normal((n, k)).astype(np.float32)
+    ks = k // 32
+    q_cols = k // 2 if fmt == O.MX_E2M1 else k
+    dev = lambda z: torch.from_numpy(np.ascontiguousarray(z)).cuda()  # noqa: E731
+    qa = torch.empty((m, q_cols), dtype=torch.uint8, device=cuda)
+    qb = torch.empty((n, q_cols), dtype=torch.uint8, device=cuda)
+    sa = torch.empty((m, ks), dtype=torch.uint8, device=cuda)
+    sb = torch.empty((n, ks), dtype=torch.uint8, device=cuda)
+    capi.mx_quantize(dev(a), qa, sa, m, k, fmt)
+    capi.mx_quantize(dev(bt), qb, sb, n, k, fmt)
+    d = torch.empty((m, n), dtype=torch.float32, device=cuda)
+    ws = torch.empty(capi.mx_matmul_workspace_size(m, n, k, fmt), dtype=torch.uint8, device=cuda)
+    capi.mx_matmul(qa, qb, sa, sb, d, m, n, k, fmt, ws, out_f32=True)
+    assert capi.device_status()[0] == 0
+    aq, sfa = O.mx_quantize(a, fmt)
+    bq, sfb = O.mx_quantize(bt, fmt)
+    want = O.mx_matmul(aq, sfa, bq, sfb, m, n, k, fmt)
+    err = np.abs(d.cpu().numpy() - want) / np.maximum(1.0, np.abs(want))
+    assert err.max() <= 1e-3, err.max()

@@ -169,3 +169,33 @@ def test_ascend950_fp8_mx_matmul_aswt(torch_catlass, trans_a, trans_b):
     assert result.shape == (m, n) and result.dtype == torch.float32 and result.device.type == "cuda"
     assert torch.allclose(result.cpu(), expected, rtol=1e-2, atol=1e-2), \
         f"max diff = {(result.cpu() - expected).abs().max().item()}"
+
+
+@pytest.mark.parametrize("trans_b", [False, True], ids=["b_kn", "b_nk"])
+def test_ascend950_mx_grouped_matmul_slice_m(torch_catlass, trans_b):
+    """tests/optest/tests/test_55_*.py with the inputs of mx_golden.py:prepare_fp8_mx_grouped_slice_m_inputs: group
+    sizes (not prefix sums), per-group B and B scales, fp32 output, allclose(1e-2)."""
+    group_sizes, n, k = (128, 128), 128, 256
+    m = sum(group_sizes)
+    a32 = torch.randn(m, k) * 10.0 - 5.0
+    a8, a_scale, a_deq = _quantize_axis_last(a32)
+    a_scale = a_scale.reshape(m, a_scale.shape[1] // 2, 2).contiguous()
+    b_list, s_list, expected, offset = [], [], [], 0
+    for size in group_sizes:
+        b32 = torch.randn(k, n) * 10.0 - 5.0
+        bt8, bt_scale, bt_deq = _quantize_axis_last(b32.t().contiguous())        # [n][k], scales [n][KS]
+        scale = bt_scale.reshape(n, bt_scale.shape[1] // 2, 2)                   # [n, KS/2, 2]
+        if trans_b:
+            b_list.append(bt8.contiguous())
+            s_list.append(scale.contiguous())
+        else:
+            b_list.append(bt8.t().contiguous())                                  # [k][n]
+            s_list.append(scale.permute(1, 0, 2).contiguous())                   # [KS/2, n, 2]
+        expected.append(a_deq[offset:offset + size] @ bt_deq.t())
+        offset += size
+    result = torch_catlass.ascend950_mx_grouped_matmul_slice_m(
+        a8.cuda(), torch.stack(b_list).cuda(), torch.tensor(group_sizes, dtype=torch.int64).cuda(), a_scale.cuda(),
+        torch.stack(s_list).cuda(), transA=False, transB=trans_b)
+    expected = torch.cat(expected, dim=0)
+    assert result.shape == (m, n) and result.dtype == torch.float32
+    assert torch.allclose(result.cpu(), expected, rtol=1e-2, atol=1e-2)
