@@ -37,6 +37,14 @@ class GroupedQuantMatmulArgs(ctypes.Structure):
     ]
 
 
+class GroupedSliceKArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("group_list_type", _u32), ("scale_type", _u32),
+        ("a", _vp), ("b", _vp), ("group_list", _vp), ("scale", _vp), ("per_token_scale", _vp), ("d", _vp),
+        ("acc", _vp), ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("d_type", _u32),
+    ]
+
+
 class GroupedFixpipeDequantArgs(ctypes.Structure):
     _fields_ = [
         ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("layout_b", _u32),
@@ -116,6 +124,7 @@ def load():
     for name, args_t in (("cb200_quant_matmul", QuantMatmulArgs),
                          ("cb200_grouped_quant_matmul_slice_m", GroupedQuantMatmulArgs),
                          ("cb200_grouped_matmul_slice_m_fixpipe_dequant", GroupedFixpipeDequantArgs),
+                         ("cb200_grouped_quant_matmul_slice_k", GroupedSliceKArgs),
                          ("cb200_w4a8_matmul", W4A8MatmulArgs),
                          ("cb200_mx_matmul", MxMatmulArgs),
                          ("cb200_mx_grouped_matmul_slice_m", MxGroupedMatmulArgs)):
@@ -214,6 +223,26 @@ def grouped_fixpipe_dequant(a, b, group_list, d, m, n, k, group_count, quant_mod
                                      d_type=d_type, flags=0)
     _check("cb200_grouped_matmul_slice_m_fixpipe_dequant",
            load().cb200_grouped_matmul_slice_m_fixpipe_dequant(ctypes.byref(args), _stream(stream)))
+
+
+def grouped_quant_matmul_slice_k_workspace_size(m, n, k, group_count):
+    args = GroupedSliceKArgs(m=m, n=n, k=k, group_count=group_count, a=256, b=256, group_list=256, scale=256,
+                             per_token_scale=256, d=256)
+    return int(load().cb200_grouped_quant_matmul_slice_k_workspace_size(ctypes.byref(args)))
+
+
+def grouped_quant_matmul_slice_k(a, b, group_list, scale, per_token, d, m, n, k, group_count, workspace, acc=None,
+                                 stream=None, group_list_type=GROUP_LIST_INT64, scale_type=DTYPE_F32,
+                                 d_type=DTYPE_BF16, block_num=0):
+    """Grouped slice-K W8A8: a [k][m] (A column-major), b [k][n], group_list prefix sums over K, scale [G][n],
+    per_token [G][m], d [G][m][n]."""
+    args = GroupedSliceKArgs(m=m, n=n, k=k, group_count=group_count, group_list_type=group_list_type,
+                             scale_type=scale_type, a=_p(a), b=_p(b), group_list=_p(group_list), scale=_p(scale),
+                             per_token_scale=_p(per_token), d=_p(d), acc=_p(acc), workspace=_p(workspace),
+                             workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(),
+                             block_num=block_num, d_type=d_type)
+    _check("cb200_grouped_quant_matmul_slice_k",
+           load().cb200_grouped_quant_matmul_slice_k(ctypes.byref(args), _stream(stream)))
 
 
 W4A8_SPLIT_K = 1  # flags: split the K range over a CTA cluster (faster, fp32 sums reassociated)

@@ -1276,6 +1276,183 @@ int cb200_grouped_quant_matmul_slice_m(const cb200_grouped_quant_matmul_args* ar
     return run_w8a8(grouped_problem(args), stream);
 }
 
+}  // extern "C"
+
+namespace {
+
+struct SliceKPlan {
+    uint32_t rows_max;  // padded K rows at most
+    uint64_t table_bytes, blocks_bytes, a_bytes, b_bytes;
+    uint64_t total() const { return table_bytes + blocks_bytes + a_bytes + b_bytes; }
+};
+
+int plan_slice_k(const cb200_grouped_quant_matmul_slice_k_args* a, SliceKPlan* plan)
+{
+    if (a == nullptr || a->group_count == 0 || a->group_count > static_cast<uint32_t>(kMaxGroups)) {
+        return CB200_INVALID;
+    }
+    *plan = SliceKPlan{};
+    if (a->m == 0 || a->n == 0) {
+        return CB200_SUCCESS;
+    }
+    if (a->a == nullptr || a->b == nullptr || a->group_list == nullptr || a->scale == nullptr ||
+        a->per_token_scale == nullptr || a->d == nullptr) {
+        return CB200_INVALID;
+    }
+    if ((a->group_list_type != CB200_GROUP_LIST_INT64 && a->group_list_type != CB200_GROUP_LIST_INT32) ||
+        a->scale_type > CB200_DTYPE_F16 || (a->d_type != 0 && a->d_type != CB200_DTYPE_BF16 && a->d_type != CB200_DTYPE_F16)) {
+        return CB200_INVALID;
+    }
+    if ((a->m & 15u) != 0 || (a->n & 15u) != 0 || !aligned16(a->a) || !aligned16(a->b) || !aligned16(a->d)) {
+        return CB200_INVALID;
+    }
+    const uintptr_t scale_mask = scale_elem_bytes(a->scale_type) - 1u;
+    if ((reinterpret_cast<uintptr_t>(a->scale) & scale_mask) != 0 ||
+        (reinterpret_cast<uintptr_t>(a->per_token_scale) & scale_mask) != 0) {
+        return CB200_INVALID;
+    }
+    const uint64_t out_rows = static_cast<uint64_t>(a->group_count) * a->m;
+    if (a->m > 0x7fffff00u || a->n > 0x7fffff00u || a->k > 0x7fffff00u || out_rows > 0x7fffff00u) {
+        return CB200_INVALID;
+    }
+    plan->rows_max = ((a->k + 127u) / 128u + a->group_count) * 128u;
+    plan->table_bytes = align256(static_cast<uint64_t>(a->group_count) * 16u + 16u);
+    plan->blocks_bytes = align256(static_cast<uint64_t>(a->group_count) * 8u);
+    plan->a_bytes = align256(static_cast<uint64_t>(plan->rows_max) * a->m);
+    plan->b_bytes = align256(static_cast<uint64_t>(plan->rows_max) * a->n);
+    return CB200_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cb200_grouped_quant_matmul_slice_k_can_implement(const cb200_grouped_quant_matmul_slice_k_args* args)
+{
+    SliceKPlan plan;
+    return plan_slice_k(args, &plan);
+}
+
+uint64_t cb200_grouped_quant_matmul_slice_k_workspace_size(const cb200_grouped_quant_matmul_slice_k_args* args)
+{
+    SliceKPlan plan;
+    if (plan_slice_k(args, &plan) != CB200_SUCCESS) {
+        return 0;
+    }
+    return plan.total();
+}
+
+int cb200_grouped_quant_matmul_slice_k(const cb200_grouped_quant_matmul_slice_k_args* args, void* stream_v)
+{
+    SliceKPlan plan;
+    int rc = plan_slice_k(args, &plan);
+    if (rc != CB200_SUCCESS || args->m == 0 || args->n == 0) {
+        return rc;
+    }
+    if (args->workspace == nullptr || args->workspace_bytes < plan.total() ||
+        (reinterpret_cast<uintptr_t>(args->workspace) & 255u) != 0) {
+        return CB200_INVALID;
+    }
+    DeviceState* dev = nullptr;
+    rc = device_state(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    uint8_t* ws = static_cast<uint8_t*>(args->workspace);
+    int4* table = reinterpret_cast<int4*>(ws);
+    uint32_t* total_blocks = reinterpret_cast<uint32_t*>(ws + static_cast<uint64_t>(args->group_count) * 16u);
+    int2* blocks = reinterpret_cast<int2*>(ws + plan.table_bytes);
+    uint8_t* a_pad = ws + plan.table_bytes + plan.blocks_bytes;
+    uint8_t* b_pad = a_pad + plan.a_bytes;
+    // 1) where every group's padded K range lies; 2) A and B copied there, padding rows zeroed
+    slice_k_plan_kernel<<<1, 32, 0, stream>>>(args->group_list, args->group_list_type == CB200_GROUP_LIST_INT32 ? 1u : 0u,
+                                              args->group_count, args->k, table, blocks, total_blocks);
+    const uint32_t copy_blocks = static_cast<uint32_t>(dev->sm_count) * 4u;
+    slice_k_scatter_kernel<<<copy_blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(args->a), a_pad, args->m, table,
+                                                            args->group_count, total_blocks);
+    slice_k_scatter_kernel<<<copy_blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(args->b), b_pad, args->n, table,
+                                                            args->group_count, total_blocks);
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(3, std::memory_order_relaxed);
+
+    // 3) the pair kernel over (group, row tile, column tile), each tile running its group's K blocks
+    using S = W8A8PairSmem;
+    CUtensorMap tmap_a, tmap_b, tmap_d;
+    {
+        const uint64_t dims[2] = {args->m, plan.rows_max};
+        const uint64_t strides[1] = {args->m};
+        const uint32_t box[2] = {128, 128};
+        rc = encode_tmap_u8(&tmap_a, a_pad, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    {
+        const uint64_t dims[3] = {args->n, plan.rows_max, 1};
+        const uint64_t strides[2] = {args->n, static_cast<uint64_t>(args->n) * plan.rows_max};
+        const uint32_t box[3] = {128, 128, 1};
+        rc = encode_tmap_u8(&tmap_b, b_pad, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+    }
+    W8A8Problem q{};
+    q.m = args->m;
+    q.n = args->n;
+    q.k = args->k;
+    q.group_count = args->group_count;
+    q.group_list_type = CB200_GROUP_LIST_INT64;
+    q.group_list = blocks;
+    q.scale = args->scale;
+    q.per_token = args->per_token_scale;
+    q.d = args->d;
+    q.acc = args->acc;
+    q.scale_type = args->scale_type;
+    q.d_type = args->d_type;
+    q.scale_stride = args->n;
+    W8A8Params p;
+    fill_params(p, q, *dev);
+    memset(&tmap_d, 0, sizeof(tmap_d));
+    if ((args->n & 7u) == 0) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(args->n) * 2u, static_cast<uint64_t>(args->group_count) * args->m};
+        const uint64_t strides[1] = {static_cast<uint64_t>(args->n) * 2u};
+        const uint32_t box[2] = {64, 32};
+        rc = encode_tmap_u8(&tmap_d, args->d, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        p.tma_store = 1;
+    }
+    auto kernel = w8a8_pair_kernel<BLayout::kRowMajor, true, true>;
+    static PerDeviceOnce once;
+    int devid = 0;
+    rc = current_device(&devid);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    rc = once.run(devid, [&]() -> int {
+        CB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotalBytes));
+        return CB200_SUCCESS;
+    });
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    const uint64_t tiles = static_cast<uint64_t>(args->group_count) * ((args->m + kPairTileM - 1) / kPairTileM) *
+                           ((args->n + kPairBN - 1) / kPairBN);
+    uint32_t pairs = static_cast<uint32_t>(dev->sm_count) / 2u;
+    if (args->block_num != 0 && args->block_num / 2u < pairs) {
+        pairs = args->block_num / 2u == 0 ? 1u : args->block_num / 2u;
+    }
+    if (tiles < pairs) {
+        pairs = static_cast<uint32_t>(tiles);
+    }
+    kernel<<<2 * pairs, kGemmThreads, S::kTotalBytes, stream>>>(tmap_a, tmap_b, tmap_d, p);
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return CB200_SUCCESS;
+}
+
 int cb200_grouped_matmul_slice_m_fixpipe_dequant_can_implement(const cb200_grouped_fixpipe_dequant_args* args)
 {
     if (!fixpipe_args_ok(args)) {

@@ -106,4 +106,62 @@ __global__ void transpose_nibbles_kernel(const uint8_t* __restrict__ src, uint8_
     }
 }
 
+// ---- grouped slice-K: pad every group's K range to whole 128-row blocks ----
+// One block.  group_list holds ascending prefix sums over K (clamped to k).  Per group: src[g] = (first source row,
+// rows, first destination block, destination blocks); blocks[g] = (first destination block, destination blocks),
+// the table the matmul kernel reads.  *total_blocks = destination blocks in all.
+__global__ void slice_k_plan_kernel(const void* group_list, uint32_t is_i32, uint32_t groups, uint32_t k, int4* src,
+                                    int2* blocks, uint32_t* total_blocks)
+{
+    if (threadIdx.x == 0) {
+        long long prev = 0;
+        uint32_t blk = 0;
+        for (uint32_t g = 0; g < groups; ++g) {
+            long long e = is_i32 ? static_cast<long long>(static_cast<const int32_t*>(group_list)[g])
+                                 : static_cast<const long long*>(group_list)[g];
+            e = e > static_cast<long long>(k) ? static_cast<long long>(k) : e;
+            const uint32_t len = e > prev ? static_cast<uint32_t>(e - prev) : 0u;
+            const uint32_t nb = (len + 127u) / 128u;
+            src[g] = make_int4(static_cast<int>(prev), static_cast<int>(len), static_cast<int>(blk), static_cast<int>(nb));
+            blocks[g] = make_int2(static_cast<int>(blk), static_cast<int>(nb));
+            blk += nb;
+            prev = e > prev ? e : prev;  // the golden restarts at the previous entry (also when the list is not ascending)
+        }
+        *total_blocks = blk;
+    }
+}
+
+// dst row r (of the padded layout) = the source row of its group, or zeros in a group's padding.  One warp per row,
+// 16-byte chunks; `width` (bytes per row, a multiple of 16) is m for A ([k][m]) and n for B ([k][n]).
+__global__ void slice_k_scatter_kernel(const uint8_t* __restrict__ src_rows, uint8_t* __restrict__ dst_rows,
+                                       uint32_t width, const int4* __restrict__ table, uint32_t groups,
+                                       const uint32_t* __restrict__ total_blocks)
+{
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warps = (gridDim.x * blockDim.x) >> 5;
+    const uint32_t rows = *total_blocks * 128u;
+    for (uint32_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const uint32_t blk = r >> 7;
+        // first group whose block range ends beyond blk (skips empty groups)
+        uint32_t lo = 0, hi = groups - 1;
+        while (lo < hi) {
+            const uint32_t mid = (lo + hi) >> 1;
+            const int4 e = table[mid];
+            if (static_cast<uint32_t>(e.z + e.w) > blk) {
+                hi = mid;
+            } else {
+                lo = mid + 1;
+            }
+        }
+        const int4 e = table[lo];
+        const uint32_t local = r - static_cast<uint32_t>(e.z) * 128u;
+        const bool real = local < static_cast<uint32_t>(e.y);
+        const uint4* s = reinterpret_cast<const uint4*>(src_rows + (static_cast<uint64_t>(e.x) + local) * width);
+        uint4* d = reinterpret_cast<uint4*>(dst_rows + static_cast<uint64_t>(r) * width);
+        for (uint32_t c = lane; c < width / 16u; c += 32) {
+            d[c] = real ? s[c] : make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
 }  // namespace cb200

@@ -51,7 +51,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank)
 
 // kAMn: A is column-major ([k][m], m contiguous; dense problems only): its tiles are loaded as MN-major
 // operand panels, 128 rows of K x 128 bytes of M, exactly as a row-major B is.
-template <BLayout kB, bool kAMn>
+// kSliceK: grouped slice-K (the reference's GroupedMatmulSliceKPerTokenDequant,
+// include/catlass/gemm/kernel/grouped_matmul_slice_k_per_token_dequant.hpp:125-134, example 11): the groups cut K, not
+// M; group g multiplies A[:, K_g] with B[K_g, :] into its own m x n output block (row g*m + i of D) with its own scale
+// and per-token vectors.  A is column-major and B row-major there, so both operands are MN-major tiles whose rows run
+// along K: a group's K range starts at any row.  An ingestion pre-pass has padded every group to whole 128-row K blocks
+// (zeros); p.group_list then points to its table of (first K block, number of K blocks) per group.
+template <BLayout kB, bool kAMn, bool kSliceK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const W8A8Params p)
@@ -90,7 +96,14 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t groups = p.group_count == 0 ? 1u : p.group_count;
 
     // ------------------------------------------------------------------ set-up (as in w8a8_gemm_kernel)
-    if (p.group_count == 0) {
+    if constexpr (kSliceK) {
+        // per group: first K block and number of K blocks of its padded K range
+        for (uint32_t g = threadIdx.x; g < groups; g += blockDim.x) {
+            const int2 e = static_cast<const int2*>(p.group_list)[g];
+            s_row_begin[g] = e.x;
+            s_row_end[g] = e.y;
+        }
+    } else if (p.group_count == 0) {
         if (threadIdx.x == 0) {
             s_row_end[0] = static_cast<int32_t>(p.m);
         }
@@ -117,19 +130,25 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         prefetch_tmap(&tmap_b);
     }
     __syncthreads();
+    // slice-K: every group has the same m x n grid of tiles
+    const uint32_t tiles_per_group = ((p.m + kPairTileM - 1) / kPairTileM) * n_tiles;
     if (threadIdx.x == 0) {
-        int32_t prev = 0;
-        uint32_t tiles = 0;
-        for (uint32_t g = 0; g < groups; ++g) {
-            const int32_t e = s_row_end[g];
-            s_row_begin[g] = prev;
-            s_tile_begin[g] = tiles;
-            if (e > prev) {
-                tiles += static_cast<uint32_t>((e - prev + kPairTileM - 1) / kPairTileM) * n_tiles;
+        if constexpr (kSliceK) {
+            s_tile_begin[groups] = groups * tiles_per_group;
+        } else {
+            int32_t prev = 0;
+            uint32_t tiles = 0;
+            for (uint32_t g = 0; g < groups; ++g) {
+                const int32_t e = s_row_end[g];
+                s_row_begin[g] = prev;
+                s_tile_begin[g] = tiles;
+                if (e > prev) {
+                    tiles += static_cast<uint32_t>((e - prev + kPairTileM - 1) / kPairTileM) * n_tiles;
+                }
+                prev = e;
             }
-            prev = e;
+            s_tile_begin[groups] = tiles;
         }
-        s_tile_begin[groups] = tiles;
     }
     if (warp == 1) {
         tmem_alloc<2>(smem_u32(s_tmem_ptr), kTmemCols);
@@ -143,6 +162,23 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t tmem_base = *s_tmem_ptr;
     const uint32_t total_tiles = s_tile_begin[groups];
     const uint32_t num_kb = p.num_k_blocks;
+    // tile idx -> rows, columns, group; K blocks [kb0, kb0 + nkb) of the tile
+    auto get_tile = [&](TileScheduler& sched, uint32_t idx, TileScheduler::Tile& t, uint32_t& kb0, uint32_t& nkb) {
+        if constexpr (kSliceK) {
+            t.group = idx / tiles_per_group;
+            const uint32_t local = idx - t.group * tiles_per_group;
+            const uint32_t mt = local / n_tiles;
+            t.row0 = static_cast<int32_t>(mt) * kPairTileM;
+            t.row_end = static_cast<int32_t>(p.m);
+            t.n0 = static_cast<int32_t>(local - mt * n_tiles) * BN;
+            kb0 = static_cast<uint32_t>(s_row_begin[t.group]);
+            nkb = static_cast<uint32_t>(s_row_end[t.group]);
+        } else {
+            sched.get<BN, kPairTileM>(idx, t);
+            kb0 = 0;
+            nkb = num_kb;
+        }
+    };
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (both CTAs)
@@ -152,11 +188,12 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             bool ok = true;
             for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
                 TileScheduler::Tile t;
-                sched.get<BN, kPairTileM>(idx, t);
-                const int32_t bz = (p.group_count == 0) ? 0 : static_cast<int32_t>(t.group);
+                uint32_t kb0, nkb;
+                get_tile(sched, idx, t, kb0, nkb);
+                const int32_t bz = (kSliceK || p.group_count == 0) ? 0 : static_cast<int32_t>(t.group);
                 const int32_t row0 = t.row0 + static_cast<int32_t>(cta_rank) * kBlockM;
                 const int32_t ncol0 = t.n0 + static_cast<int32_t>(cta_rank) * (BN / 2);
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t kb = kb0; kb < kb0 + nkb; ++kb) {
                     ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer);
                     if (!ok) {
                         break;
@@ -197,13 +234,17 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
+                uint32_t nkb = num_kb;
+                if constexpr (kSliceK) {
+                    nkb = static_cast<uint32_t>(s_row_end[idx / tiles_per_group]);  // none for an empty group
+                }
                 ok = mbar_wait(bar_tmem_empty + acc * 8, acc_phase ^ 1, s_abort, p.status, kDevTimeoutMmaTmem);
                 if (!ok) {
                     break;
                 }
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t kb = 0; kb < nkb; ++kb) {
                     ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
                     if (!ok) {
                         break;
@@ -260,7 +301,11 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         bool ok = true;
         for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
             TileScheduler::Tile t;
-            sched.get<BN, kPairTileM>(idx, t);
+            uint32_t kb0_unused, nkb;
+            get_tile(sched, idx, t, kb0_unused, nkb);
+            // slice-K: group g writes rows [g*m, g*m + m) of D and reads that range of the per-token scales
+            const int32_t out_row_offset = kSliceK ? static_cast<int32_t>(t.group * p.m) : 0;
+            const bool no_k = kSliceK && nkb == 0;  // an empty group: the accumulator was not written, the sums are 0
             float* sc = s_scale + (warp - 2) * BN;
             __syncwarp();
             stage_tile_scales(sc, p, t.group, static_cast<uint32_t>(t.n0), BN, lane);
@@ -275,10 +320,11 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
             const int32_t row = t.row0 + static_cast<int32_t>(cta_rank * kBlockM + quad * 32 + lane);
             const bool row_ok = row < t.row_end;
-            const float pt = !row_ok ? 0.0f : (p.per_token ? load_scale(p.per_token, row, p.scale_type) : 1.0f);
+            const int32_t out_row = row + out_row_offset;
+            const float pt = !row_ok ? 0.0f : (p.per_token ? load_scale(p.per_token, out_row, p.scale_type) : 1.0f);
             const uint32_t taddr = tmem_base + acc * BN + ((quad * 32u) << 16);
-            uint16_t* drow = p.d + static_cast<size_t>(row_ok ? row : 0) * p.n;
-            int32_t* arow = p.acc ? p.acc + static_cast<size_t>(row_ok ? row : 0) * p.n : nullptr;
+            uint16_t* drow = p.d + static_cast<size_t>(row_ok ? out_row : 0) * p.n;
+            int32_t* arow = p.acc ? p.acc + static_cast<size_t>(row_ok ? out_row : 0) * p.n : nullptr;
             // a whole warp without valid rows (ragged tail of a group) skips the drain
             const int32_t warp_row0 = t.row0 + static_cast<int32_t>(cta_rank * kBlockM + quad * 32);
             const bool warp_rows = warp_row0 < t.row_end;
@@ -292,6 +338,14 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(taddr + c * 32, r);
                 tmem_ld_wait();
+                if constexpr (kSliceK) {
+                    if (no_k) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            r[j] = 0;
+                        }
+                    }
+                }
                 const uint32_t col0 = t.n0 + c * 32;
                 if (slab_store && col0 < p.n) {
                     const float* scc = sc + c * 32;
@@ -318,7 +372,7 @@ w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&tmap_d, smem_u32(slab), static_cast<int32_t>(col0 * 2), warp_row0);
+                        tma_store_2d(&tmap_d, smem_u32(slab), static_cast<int32_t>(col0 * 2), warp_row0 + out_row_offset);
                         tma_store_commit();
                     }
                     if (arow != nullptr) {

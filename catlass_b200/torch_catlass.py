@@ -6,7 +6,8 @@ the quantized-matmul path can be run against CUDA tensors by importing this modu
     d = torch_catlass.quant_matmul(a, b, scale, per_token_scale)           # tests/optest/tests/test_12_quant_matmul.py
 
 Covered: quant_matmul (example 12), quant_optimized_matmul_tla (42), grouped_matmul_slice_m_per_token_dequant (07),
-grouped_matmul_slice_m_per_token_dequant_multistage (10), ascend950_grouped_matmul_slice_m_per_token_dequant (47),
+grouped_matmul_slice_m_per_token_dequant_multistage (10), grouped_matmul_slice_k_per_token_dequant (11),
+ascend950_grouped_matmul_slice_m_per_token_dequant (47),
 ascend950_grouped_matmul_slice_m_per_tensor_per_channel_dequant (48), w4a8_matmul (32),
 ascend950_fp8_mx_matmul[_aswt] (53), ascend950_fp4_mx_matmul[_aswt] (54), ascend950_mx_grouped_matmul_slice_m (55).
 
@@ -111,6 +112,30 @@ def grouped_matmul_slice_m_per_token_dequant_multistage(mat1, mat2, groupList, s
                                                         useNzA=False, useNzB=False):
     """Example 10: int64 groupList, bf16 scales, bf16 output."""
     return _grouped(mat1, mat2, groupList, scale, perTokenScale, outDType, transA, transB, useNzA, useNzB)
+
+
+def grouped_matmul_slice_k_per_token_dequant(mat1, mat2, groupList, scale, perTokenScale, outDType=torch.bfloat16,
+                                             transA=False, transB=False, useNzA=False, useNzB=False):
+    """Example 11: the groups cut K.  mat1 is A column-major, passed as (K, M) with transA=True; mat2 (K, N);
+    groupList int64 prefix sums over K; scale (G, N), perTokenScale (G, M); output (G, M, N)."""
+    _require_cuda(mat1, mat2, groupList, scale, perTokenScale)
+    if not transA or transB or useNzA or useNzB:
+        raise ValueError("slice-K takes A as (K, M) with transA=True and B as (K, N)")
+    mat1, mat2, groupList = mat1.contiguous(), mat2.contiguous(), groupList.contiguous()
+    k, m = mat1.shape
+    n = mat2.shape[1]
+    g = groupList.numel()
+    s, p, st = _scales(scale, perTokenScale)
+    out_dtype = _dtype(outDType)
+    if out_dtype not in _OUT_TYPES:
+        raise ValueError("outDType must be float16 or bfloat16")
+    d = torch.empty((g, m, n), dtype=out_dtype, device=mat1.device)
+    ws = torch.empty(max(capi.grouped_quant_matmul_slice_k_workspace_size(m, n, k, g), 1), dtype=torch.uint8,
+                     device=mat1.device)
+    capi.grouped_quant_matmul_slice_k(mat1, mat2, groupList, s, p, d, m, n, k, g, ws,
+                                      group_list_type=capi.GROUP_LIST_INT32 if groupList.dtype == torch.int32
+                                      else capi.GROUP_LIST_INT64, scale_type=st, d_type=_OUT_TYPES[out_dtype])
+    return d
 
 
 def ascend950_grouped_matmul_slice_m_per_token_dequant(mat1, mat2, groupList, scale, perTokenScale,

@@ -182,6 +182,42 @@ CB200_API int cb200_grouped_matmul_slice_m_fixpipe_dequant(const cb200_grouped_f
                                                            void *stream);
 
 /*
+ * Grouped slice-K W8A8 matmul with per-token dequant: the groups cut K.  group_list holds `group_count` ascending
+ * prefix sums over K; group g multiplies A[:, K_g] with B[K_g, :] into its own m x n block of D:
+ *     D[g][i][j] = round( (float(sum_{kk in K_g} A[i,kk] * B[kk,j]) * scale[g][j]) * per_token_scale[g][i] )
+ * (an empty group gives zeros).  Replaces Gemm::Kernel::GroupedMatmulSliceKPerTokenDequant::Arguments
+ * (include/catlass/gemm/kernel/grouped_matmul_slice_k_per_token_dequant.hpp:125-134: problemShape, problemCount,
+ * ptrGroupList, ptrA, ptrB, ptrScale, ptrPerTokenScale, ptrD; example 11), golden
+ * golden::ComputeGroupedMatmulSliceKPerTokenDequant (examples/common/golden/matmul.hpp:326-359).
+ * Layouts are the reference's for this operator: A column-major (stored [k][m]), B row-major ([k][n]).
+ * Requirements: m % 16 == 0, n % 16 == 0, a and b 16-byte aligned.  The groups' K ranges start at arbitrary rows;
+ * an ingestion pre-pass copies A and B into the workspace with every group padded to whole 128-row K blocks
+ * (cb200_grouped_quant_matmul_slice_k_workspace_size bytes: about (k + 128 * group_count) * (m + n)).
+ */
+typedef struct cb200_grouped_quant_matmul_slice_k_args {
+    uint32_t m, n, k;
+    uint32_t group_count;         /* 1 .. 1024 */
+    uint32_t group_list_type;     /* CB200_GROUP_LIST_INT64 / _INT32 */
+    uint32_t scale_type;          /* CB200_DTYPE_F32 (0, default), _BF16 or _F16 */
+    const void *a;                /* int8 [k][m] */
+    const void *b;                /* int8 [k][n] */
+    const void *group_list;       /* device pointer */
+    const void *scale;            /* [group_count][n] */
+    const void *per_token_scale;  /* [group_count][m] */
+    void *d;                      /* [group_count][m][n], d_type elements */
+    int32_t *acc;                 /* optional raw accumulators [group_count][m][n] */
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t d_type;              /* CB200_DTYPE_BF16 (default; 0 accepted) or CB200_DTYPE_F16 */
+} cb200_grouped_quant_matmul_slice_k_args;
+
+CB200_API int cb200_grouped_quant_matmul_slice_k_can_implement(const cb200_grouped_quant_matmul_slice_k_args *args);
+CB200_API uint64_t cb200_grouped_quant_matmul_slice_k_workspace_size(
+    const cb200_grouped_quant_matmul_slice_k_args *args);
+CB200_API int cb200_grouped_quant_matmul_slice_k(const cb200_grouped_quant_matmul_slice_k_args *args, void *stream);
+
+/*
  * The grouped matmul for HOST-resident activations and output: what the reference's example mains do around
  * the kernel (aclrtMemcpy host->device, launch, aclrtMemcpy device->host:
  * examples/07_grouped_matmul_slice_m_per_token_dequant_moe/grouped_matmul_slice_m_per_token_dequant_moe.cpp:

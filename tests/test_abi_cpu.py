@@ -56,27 +56,34 @@ def test_can_implement_validates_without_a_device(lib):
 
 
 def test_struct_layout_matches_the_header(lib):
-    """Field offsets of the ctypes mirrors equal those a C compiler gives the header's structs."""
+    """Size and every field offset of the ctypes mirrors equal what a C compiler gives the header's structs."""
     import subprocess
     import tempfile
     from catlass_b200 import capi
-    src = r'''
-#include <stdio.h>
-#include <stddef.h>
-#include "catlass_b200.h"
-int main(void) {
-  printf("%zu %zu %zu %zu\n", sizeof(cb200_quant_matmul_args), offsetof(cb200_quant_matmul_args, a),
-         offsetof(cb200_quant_matmul_args, acc), offsetof(cb200_quant_matmul_args, block_num));
-  printf("%zu %zu %zu %zu\n", sizeof(cb200_grouped_quant_matmul_args),
-         offsetof(cb200_grouped_quant_matmul_args, a), offsetof(cb200_grouped_quant_matmul_args, group_list),
-         offsetof(cb200_grouped_quant_matmul_args, block_num));
-  return 0; }'''
+    pairs = [
+        ("cb200_quant_matmul_args", capi.QuantMatmulArgs),
+        ("cb200_grouped_quant_matmul_args", capi.GroupedQuantMatmulArgs),
+        ("cb200_grouped_fixpipe_dequant_args", capi.GroupedFixpipeDequantArgs),
+        ("cb200_grouped_quant_matmul_slice_k_args", capi.GroupedSliceKArgs),
+        ("cb200_grouped_quant_matmul_host_args", capi.GroupedQuantMatmulHostArgs),
+        ("cb200_w4a8_matmul_args", capi.W4A8MatmulArgs),
+        ("cb200_mx_matmul_args", capi.MxMatmulArgs),
+        ("cb200_mx_grouped_matmul_args", capi.MxGroupedMatmulArgs),
+        ("cb200_mx_quantize_args", capi.MxQuantizeArgs),
+    ]
+    lines = []
+    for cname, ctype in pairs:
+        offs = ", ".join(f"offsetof({cname}, {f[0]})" for f in ctype._fields_)
+        fmt = " ".join(["%zu"] * (len(ctype._fields_) + 1))
+        lines.append(f'  printf("{fmt}\\n", sizeof({cname}), {offs});')
+    src = "#include <stdio.h>\n#include <stddef.h>\n#include \"catlass_b200.h\"\nint main(void) {\n" + \
+        "\n".join(lines) + "\n  return 0; }\n"
     with tempfile.TemporaryDirectory() as td:
         c = os.path.join(td, "t.c")
         open(c, "w").write(src)
         exe = os.path.join(td, "t")
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
-        out = subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()
-    q, g = capi.QuantMatmulArgs, capi.GroupedQuantMatmulArgs
-    assert [int(x) for x in out[:4]] == [ctypes.sizeof(q), q.a.offset, q.acc.offset, q.block_num.offset]
-    assert [int(x) for x in out[4:]] == [ctypes.sizeof(g), g.a.offset, g.group_list.offset, g.block_num.offset]
+        out = subprocess.run([exe], capture_output=True, text=True, check=True).stdout.strip().splitlines()
+    for (cname, ctype), line in zip(pairs, out):
+        want = [ctypes.sizeof(ctype)] + [getattr(ctype, f[0]).offset for f in ctype._fields_]
+        assert [int(x) for x in line.split()] == want, cname

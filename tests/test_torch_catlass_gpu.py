@@ -199,3 +199,22 @@ def test_ascend950_mx_grouped_matmul_slice_m(torch_catlass, trans_b):
     expected = torch.cat(expected, dim=0)
     assert result.shape == (m, n) and result.dtype == torch.float32
     assert torch.allclose(result.cpu(), expected, rtol=1e-2, atol=1e-2)
+
+
+def test_grouped_matmul_slice_k_per_token_dequant(torch_catlass):
+    """tests/optest/tests/test_11_grouped_matmul_slice_k_per_token_dequant.py:11-40"""
+    g, m, n, k_total = 4, 128, 128, 256
+    group_list = torch.tensor([64, 128, 192, 256], dtype=torch.int64, device="cuda")
+    a = torch.randint(-8, 8, (k_total, m), dtype=torch.int8, device="cuda")
+    b = torch.randint(-8, 8, (k_total, n), dtype=torch.int8, device="cuda")
+    scale = (torch.randn(g, n, device="cuda").abs() * 0.1).to(torch.bfloat16)
+    pts = (torch.randn(g, m, device="cuda").abs() * 0.1).to(torch.bfloat16)
+    result = torch_catlass.grouped_matmul_slice_k_per_token_dequant(a, b, group_list, scale, pts, transA=True)
+    expected, offset = [], 0
+    for i in range(g):
+        part = torch.matmul(a[offset:offset + 64].T.float(), b[offset:offset + 64].float())
+        expected.append(part * scale[i].float() * pts[i].float().unsqueeze(1))
+        offset += 64
+    expected = torch.stack(expected, dim=0)
+    assert result.shape == (g, m, n) and result.dtype == torch.bfloat16
+    assert torch.allclose(result.float(), expected, rtol=1e-1, atol=1e-1)

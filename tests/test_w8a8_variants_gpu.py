@@ -252,3 +252,33 @@ def test_dense_partial_last_row_tile(cuda, m):
     want, want_acc = O.quant_matmul(a, b_flat, scale, pt, m, n, k, want_acc=True)
     assert np.array_equal(acc.cpu().numpy(), want_acc)
     assert np.array_equal(d.view(torch.int16).cpu().numpy().view(np.uint16), O.out_bits(want))
+
+
+@pytest.mark.parametrize("cuts,m,n,k", [
+    ((64, 128, 192, 256), 128, 128, 256),               # the reference's optest shape (example 11)
+    ((5, 5, 133, 300, 300, 1000), 272, 392 + 8, 1000),  # ragged cuts, empty groups, rows and columns cut by tiles
+    ((0, 0), 64, 64, 128),                              # nothing but empty groups
+    ((700, 2048), 512, 1024, 2048),
+])
+@pytest.mark.parametrize("f16_out", [False, True])
+def test_grouped_slice_k(cuda, cuts, m, n, k, f16_out):
+    """Groups along K (example 11): A column-major, B row-major, one m x n output block per group."""
+    from catlass_b200 import capi
+    torch = _torch()
+    rng = np.random.default_rng(k + m)
+    g = len(cuts)
+    a = rng.integers(-127, 128, (k, m), dtype=np.int8)     # [k][m]: A column-major
+    b = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    scale = rng.uniform(1e-3, 1e-2, (g, n)).astype(np.float32)
+    pt = rng.uniform(1e-3, 1e-2, (g, m)).astype(np.float32)
+    gl = np.array(cuts, np.int64)
+    d = torch.full((g, m, n), -1.0, dtype=torch.float16 if f16_out else torch.bfloat16, device=cuda)
+    acc = torch.full((g, m, n), -7, dtype=torch.int32, device=cuda)
+    ws = torch.empty(capi.grouped_quant_matmul_slice_k_workspace_size(m, n, k, g), dtype=torch.uint8, device=cuda)
+    capi.grouped_quant_matmul_slice_k(_dev(a), _dev(b), _dev(gl), _dev(scale), _dev(pt), d, m, n, k, g, ws, acc=acc,
+                                      d_type=capi.DTYPE_F16 if f16_out else capi.DTYPE_BF16)
+    st, code = capi.device_status()
+    assert st == 0, f"device status {st} code {code:#x}"
+    want, want_acc = O.grouped_quant_matmul_slice_k(a, b, gl, scale, pt, m, n, k, want_acc=True)
+    assert np.array_equal(acc.cpu().numpy(), want_acc)
+    check_out(d.view(torch.int16).cpu().numpy().view(np.uint16), want, f16_out, "slice-K")
