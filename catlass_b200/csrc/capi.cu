@@ -426,7 +426,7 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
     }
     p.tile_rows = tile_rows;
     // a ring stage holds 4 neighbouring K blocks: 512 contiguous bytes per weight row are requested together
-    uint32_t kbs = static_cast<uint32_t>(dev_knob("CB200_SMALLM_KBS", 4));
+    uint32_t kbs = static_cast<uint32_t>(dev_knob("CB200_SMALLM_KBS", 0));
     kbs = (kbs >= 1 && kbs <= 8) ? kbs : 4;
     uint32_t ring_budget = static_cast<uint32_t>(dev_knob("CB200_SMALLM_RING_KB", 216));
     ring_budget = (ring_budget >= 36 && ring_budget <= 216 ? ring_budget : 216u) * 1024u;
@@ -451,6 +451,24 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
         }
     }
     p.splits = splits;
+    p.own_partials = (smallm_own_partials(p.mt, splits) && dev_knob("CB200_SMALLM_OWN_PARTIALS", 1) != 0) ? 1u : 0u;
+    if (p.own_partials) {
+        // the partial sums take their memory out of the ring's budget; K blocks per stage are re-chosen so that
+        // whole stages fill what is left (4 blocks = 72 KB stages would leave 48 of 192 KB unused)
+        const uint32_t budget = ring_budget - (splits - 1) * kSmallMTileN * p.mt * 4u;
+        uint32_t best_kbs = p.kbs, best_fill = (budget / smallm_stage_bytes(p.mt, p.kbs)) * smallm_stage_bytes(p.mt, p.kbs);
+        for (uint32_t cand = p.kbs / 2; cand >= 1; cand /= 2) {
+            const uint32_t sb = smallm_stage_bytes(p.mt, cand);
+            if ((budget / sb) * sb > best_fill) {
+                best_fill = (budget / sb) * sb;
+                best_kbs = cand;
+            }
+        }
+        if (dev_knob("CB200_SMALLM_KBS", 0) == 0) {
+            p.kbs = best_kbs;
+        }
+        stages = budget / smallm_stage_bytes(p.mt, p.kbs);
+    }
     stages = stages > static_cast<uint32_t>(kSmallMMaxStages) ? kSmallMMaxStages : (stages < 2 ? 2 : stages);
     p.stages = stages;
     p.scale = q.scale;
@@ -484,7 +502,7 @@ int launch_smallm(const W8A8Problem& q, const DeviceState& dev, cudaStream_t str
             return rc;
         }
     }
-    const uint32_t smem = smallm_smem_bytes(p.mt, p.stages, p.splits, p.kbs);
+    const uint32_t smem = smallm_smem_bytes(p.mt, p.stages, p.splits, p.kbs, p.own_partials != 0);
     const uint32_t n_tiles = (q.n + p.tile_rows - 1) / p.tile_rows;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles * p.splits, 1, 1);

@@ -99,6 +99,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+// try_wait that also acquires writes made by other CTAs of the cluster before they arrived on the barrier.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Non-blocking probe of a barrier phase.  (try_wait may suspend the thread for a hardware-chosen time when the
 // phase is not complete; a thread that polls several barriers in turn must not be held up by any one of them.)
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
@@ -132,6 +148,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     uint32_t spins = 0;
     for (;;) {
         if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        if ((++spins & 0x3f) == 0) {
+            if (*abort != 0) {
+                return false;
+            }
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > limit_ns) {
+                *abort = 1;
+                atomicMax(status, code);
+                return false;
+            }
+        }
+    }
+}
+
+// Bounded wait on a barrier other CTAs of the cluster arrive on (see mbar_wait for the contract).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
+                                                  unsigned* status, unsigned code,
+                                                  unsigned long long limit_ns = kWaitLimitNs)
+{
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    for (;;) {
+        if (mbar_try_wait_cluster(bar, parity)) {
             return true;
         }
         if ((++spins & 0x3f) == 0) {

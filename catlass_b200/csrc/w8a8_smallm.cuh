@@ -43,10 +43,20 @@ struct SmallMParams {
     float scalar_scale;
     uint32_t out_f16;
     uint32_t static_weights;  // weights and channel scales may be read before the stream dependency resolves
+    uint32_t own_partials;    // the partial-sum buffer has shared memory of its own (see smallm_smem_bytes)
 };
 
-// dynamic smem: [1024 align pad][stages x (16 KB W + mt*128 B X)][(splits-1) x 128 x mt x 4 B partials,
-// aliased onto the ring][barriers]
+// dynamic smem: [1024 align pad][stages x (16 KB W + mt*128 B X)][(splits-1) x 128 x mt x 4 B partials][barriers]
+// The partial sums of the other CTAs of a cluster land in the first CTA.  When they are small (few tokens: 24 KB for
+// 16 tokens and a 4-way split) they get memory of their own behind the ring, and a CTA pushes its sums the moment
+// its own K slice is done, then arrives on a barrier in the first CTA: no cluster-wide barrier on the critical path.
+// Large ones (up to 192 KB) are aliased onto the first CTA's ring and need a cluster barrier before (the ring must be
+// idle) and after the pushes.
+constexpr uint32_t kSmallMOwnPartialsMax = 32u * 1024u;
+__host__ __device__ inline bool smallm_own_partials(uint32_t mt, uint32_t splits)
+{
+    return splits > 1 && (splits - 1) * kSmallMTileN * mt * 4 <= kSmallMOwnPartialsMax;
+}
 __host__ __device__ inline uint32_t smallm_block_bytes(uint32_t mt)
 {
     return kSmallMTileN * kBlockKBytes + mt * kBlockKBytes;
@@ -55,12 +65,20 @@ __host__ __device__ inline uint32_t smallm_stage_bytes(uint32_t mt, uint32_t kbs
 {
     return kbs * smallm_block_bytes(mt);
 }
-__host__ __device__ inline uint32_t smallm_smem_bytes(uint32_t mt, uint32_t stages, uint32_t splits, uint32_t kbs)
+__host__ __device__ inline uint32_t smallm_body_bytes(uint32_t mt, uint32_t stages, uint32_t splits, uint32_t kbs,
+                                                      bool own_partials)
 {
     uint32_t ring = stages * smallm_stage_bytes(mt, kbs);
     uint32_t partials = (splits - 1) * kSmallMTileN * mt * 4;
-    uint32_t body = ring > partials ? ring : partials;
-    return 1024 + body + (2 * kSmallMMaxStages + 1) * 8 + 16;
+    if (own_partials) {
+        return ring + partials;
+    }
+    return ring > partials ? ring : partials;
+}
+__host__ __device__ inline uint32_t smallm_smem_bytes(uint32_t mt, uint32_t stages, uint32_t splits, uint32_t kbs,
+                                                      bool own_partials)
+{
+    return 1024 + smallm_body_bytes(mt, stages, splits, kbs, own_partials) + (2 * kSmallMMaxStages + 2) * 8 + 16;
 }
 
 template <bool kWMnMajor>
@@ -77,15 +95,17 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const uint32_t block_bytes = smallm_block_bytes(p.mt);
     const uint32_t stage_bytes = smallm_stage_bytes(p.mt, p.kbs);
     const uint32_t ring_bytes = p.stages * stage_bytes;
-    const uint32_t partial_bytes = (p.splits - 1) * kSmallMTileN * p.mt * 4;
-    const uint32_t body = ring_bytes > partial_bytes ? ring_bytes : partial_bytes;
+    const bool own_partials = p.own_partials != 0;
+    const uint32_t body = smallm_body_bytes(p.mt, p.stages, p.splits, p.kbs, own_partials);
     uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + body);
     const uint32_t bar_full = smem_u32(s_bars);
     const uint32_t bar_empty = bar_full + kSmallMMaxStages * 8;
     const uint32_t bar_tmem_full = bar_empty + kSmallMMaxStages * 8;
-    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 2 * kSmallMMaxStages + 1);
+    const uint32_t bar_partials = bar_tmem_full + 8;  // first CTA: the other CTAs' sums have landed
+    uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + 2 * kSmallMMaxStages + 2);
     volatile uint32_t* s_abort = s_tmem_ptr + 1;
-    int32_t* s_partials = reinterpret_cast<int32_t*>(smem);  // [(splits-1)][128][mt], leader CTA only
+    // [(splits-1)][128][mt], first CTA only: behind the ring, or aliased onto it
+    int32_t* s_partials = reinterpret_cast<int32_t*>(smem + (own_partials ? ring_bytes : 0));
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -111,6 +131,7 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             mbar_init(bar_empty + s * 8, 1);
         }
         mbar_init(bar_tmem_full, 1);
+        mbar_init(bar_partials, (p.splits - 1) * kEpilogueThreads);  // one arrival per pushing thread
         fence_mbar_init();
         prefetch_tmap(&tmap_w);
         prefetch_tmap(&tmap_x);
@@ -123,6 +144,9 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_ptr;
+    if (own_partials) {
+        cluster_sync();  // the first CTA's barrier exists before any other CTA can arrive on it (off the critical path)
+    }
     grid_launch_dependents();  // a dependent launch may start its own set-up and weight prefetch from here on
 
     if (warp == 0) {
@@ -264,7 +288,9 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const uint32_t chunks = p.mt / 16;
 
     if (p.splits > 1) {
-        cluster_sync();  // the leader's ring is idle from here on: it becomes the partial-sum buffer
+        if (!own_partials) {
+            cluster_sync();  // the first CTA's ring is idle from here on: it becomes the partial-sum buffer
+        }
         if (split != 0 && epi) {
             // remote address of slot (split-1), this thread's row
             const uint32_t local = smem_u32(s_partials) + ((split - 1) * kSmallMTileN + row) * p.mt * 4;
@@ -288,8 +314,18 @@ w8a8_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                                  : "memory");
                 }
             }
+            if (own_partials) {
+                mbar_arrive_cluster(bar_partials, 0);  // release: this thread's stores are visible to the waiter
+            }
         }
-        cluster_sync();  // partial sums have landed in the leader's smem
+        if (!own_partials) {
+            cluster_sync();  // partial sums have landed in the first CTA's smem
+        } else if (split == 0 && epi) {
+            // (a CTA that timed out still arrives, with zeros: every thread of the cluster passes this point)
+            bool ok = mbar_wait_cluster(bar_partials, 0, s_abort, p.status, kDevTimeoutPeerCta);
+            ok = __all_sync(0xffffffffu, ok);
+            (void)ok;
+        }
     }
 
     if (split == 0 && epi) {
