@@ -825,7 +825,7 @@ def main():
         else:
             if world != 1:
                 raise SystemExit("this workload is single-GPU")
-            res = standalone_line(run_secondary(args.workload, sampler, max(args.secondary_seconds, 0.2), args), args)
+            res = standalone_line(run_secondary(args.workload, sampler, max(args.secondary_seconds, 0.01), args), args)
     finally:
         if sampler:
             sampler.stop()
