@@ -40,4 +40,4 @@ def test_recorded_dram_traffic_matches_the_kernel_sources():
     """The profiler figures the bench quotes name the tile constants they were captured with."""
     from catlass_b200 import kernel_facts
     assert kernel_facts.check() == []
-    assert kernel_facts.traffic("w8a8_pair_kernel/moe_small", 8.0) == 8 * 540.2e6
+    assert kernel_facts.traffic("w8a8_pair_kernel/moe_small", 8.0) == 8 * kernel_facts.DRAM_TRAFFIC["w8a8_pair_kernel/moe_small"]["bytes"]
