@@ -92,6 +92,15 @@ class MxGroupedMatmulArgs(ctypes.Structure):
 GROUP_LIST_SIZES, GROUP_LIST_PREFIX_SUMS = 0, 1
 
 
+class MxGroupedSwigluQuantArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("layout_b", _u32),
+        ("group_list_type", _u32), ("group_list_kind", _u32), ("flags", _u32),
+        ("a", _vp), ("b", _vp), ("group_list", _vp), ("scale_a", _vp), ("scale_b", _vp), ("q", _vp), ("q_scale", _vp),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("reserved", _u32),
+    ]
+
+
 class MxQuantizeArgs(ctypes.Structure):
     _fields_ = [
         ("rows", _u32), ("k", _u32), ("format", _u32), ("x_type", _u32), ("x_pitch", _u64),
@@ -127,7 +136,8 @@ def load():
                          ("cb200_grouped_quant_matmul_slice_k", GroupedSliceKArgs),
                          ("cb200_w4a8_matmul", W4A8MatmulArgs),
                          ("cb200_mx_matmul", MxMatmulArgs),
-                         ("cb200_mx_grouped_matmul_slice_m", MxGroupedMatmulArgs)):
+                         ("cb200_mx_grouped_matmul_slice_m", MxGroupedMatmulArgs),
+                         ("cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant", MxGroupedSwigluQuantArgs)):
         getattr(lib, name + "_can_implement").argtypes = [ctypes.POINTER(args_t)]
         getattr(lib, name + "_can_implement").restype = ctypes.c_int
         getattr(lib, name + "_workspace_size").argtypes = [ctypes.POINTER(args_t)]
@@ -326,6 +336,25 @@ def mx_grouped_matmul(a, b, group_list, scale_a, scale_b, d, m, n, k, group_coun
                             group_list_type, group_list_kind, out_f32)
     _check("cb200_mx_grouped_matmul_slice_m",
            load().cb200_mx_grouped_matmul_slice_m(ctypes.byref(args), _stream(stream)))
+
+
+def mx_grouped_swiglu_quant_workspace_size(m, n, k, group_count, layout_b=COLUMN_MAJOR):
+    args = MxGroupedSwigluQuantArgs(m=m, n=n, k=k, group_count=group_count, layout_b=layout_b, a=256, b=256,
+                                    group_list=256, scale_a=256, scale_b=256, q=256, q_scale=256)
+    return int(load().cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_workspace_size(ctypes.byref(args)))
+
+
+def mx_grouped_swiglu_quant(a, b, group_list, scale_a, scale_b, q, q_scale, m, n, k, group_count, workspace,
+                            stream=None, layout_b=COLUMN_MAJOR, group_list_type=GROUP_LIST_INT64,
+                            group_list_kind=GROUP_LIST_SIZES):
+    """Grouped slice-M MXFP8 matmul + SwiGLU + MX quantisation: q [m][n/2] E4M3 bytes, q_scale [m][n/64] E8M0."""
+    args = MxGroupedSwigluQuantArgs(
+        m=m, n=n, k=k, group_count=group_count, layout_b=layout_b, group_list_type=group_list_type,
+        group_list_kind=group_list_kind, flags=0, a=_p(a), b=_p(b), group_list=_p(group_list), scale_a=_p(scale_a),
+        scale_b=_p(scale_b), q=_p(q), q_scale=_p(q_scale), workspace=_p(workspace),
+        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(), block_num=0)
+    _check("cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant",
+           load().cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(ctypes.byref(args), _stream(stream)))
 
 
 def mx_quantize(x, q, scale, rows, k, fmt, x_type=DTYPE_F32, x_pitch=0, stream=None):

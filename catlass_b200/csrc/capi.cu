@@ -651,6 +651,9 @@ struct MxProblem {
     uint64_t workspace_bytes;
     uint32_t block_num;
     uint32_t flags;
+    // SwiGLU + MX quantisation instead of the plain output: d = Q (E4M3 [m][n/2]), q_scale = E8M0 [m][n/64]
+    bool swiglu_quant;
+    void* q_scale;
 };
 
 // How an MX call is served.  The kernel wants both operands with rows along K, padded to whole K stages
@@ -699,11 +702,19 @@ int plan_mx(const MxProblem& q, MxPlan* plan)
         return CB200_INVALID;
     }
     const bool f32 = (q.flags & CB200_MX_OUT_F32) != 0;
-    if ((reinterpret_cast<uintptr_t>(q.d) & (f32 ? 3u : 1u)) != 0) {
-        return CB200_INVALID;
-    }
-    if (((q.n & (f32 ? 3u : 7u)) == 0) && !aligned16(q.d)) {
-        return CB200_INVALID;  // 16-byte vector stores
+    if (q.swiglu_quant) {
+        // tiles pair 128 columns of either half of C, and the halves' scale blocks start on 128-row boundaries
+        if (q.group_count == 0 || q.format != CB200_MX_E4M3 || q.flags != 0 || (q.n % 256u) != 0 ||
+            q.q_scale == nullptr || !aligned16(q.d)) {
+            return CB200_INVALID;
+        }
+    } else {
+        if ((reinterpret_cast<uintptr_t>(q.d) & (f32 ? 3u : 1u)) != 0) {
+            return CB200_INVALID;
+        }
+        if (((q.n & (f32 ? 3u : 7u)) == 0) && !aligned16(q.d)) {
+            return CB200_INVALID;  // 16-byte vector stores
+        }
     }
     const bool fp4 = q.format == CB200_MX_E2M1;
     const uint32_t kmul = fp4 ? 256u : 128u;
@@ -746,7 +757,7 @@ void ingest_mx_operand(const void* src, uint8_t* dst, uint32_t rows, uint32_t k,
     g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
-template <bool kFp4, bool kGrouped>
+template <bool kFp4, bool kGrouped, bool kSwiglu = false>
 int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cudaStream_t stream)
 {
     uint8_t* ws = static_cast<uint8_t*>(q.workspace);
@@ -803,6 +814,7 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
     p.tile_table = kGrouped ? table : nullptr;
     p.num_row_tiles = kGrouped ? num_row_tiles : nullptr;
     p.sfb_blocks_per_group = sfb_blocks;
+    p.q_scale = static_cast<uint8_t*>(q.q_scale);
 
     // the caller's scale arrays: ceil(k/32) blocks per row, held in an even number of columns; stored along the
     // operand's rows, or K-major when the operand itself is stored K-major
@@ -834,13 +846,14 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
     {
         const uint64_t dims[3] = {row_bytes, q.n, plan.b_matrices};
         const uint64_t strides[2] = {row_bytes, static_cast<uint64_t>(q.n) * row_bytes};
-        const uint32_t box[3] = {kBlockKBytes, kMxBlockN, 1};
+        // (the SwiGLU epilogue's tiles take 128 rows from either half of B: two loads per stage)
+        const uint32_t box[3] = {kBlockKBytes, kSwiglu ? 128u : static_cast<uint32_t>(kMxBlockN), 1};
         int rc = encode_tmap_u8(&tmap_b, b_ptr, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != CB200_SUCCESS) {
             return rc;
         }
     }
-    auto kernel = mx_gemm_kernel<kFp4, kGrouped>;
+    auto kernel = mx_gemm_kernel<kFp4, kGrouped, kSwiglu>;
     static PerDeviceOnce once;
     int devid = 0;
     int rc_dev = current_device(&devid);
@@ -854,7 +867,8 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
     if (rc_dev != CB200_SUCCESS) {
         return rc_dev;
     }
-    const uint64_t tiles = static_cast<uint64_t>(plan.max_row_tiles) * ((q.n + kMxBlockN - 1) / kMxBlockN);
+    const uint64_t tiles =
+        static_cast<uint64_t>(plan.max_row_tiles) * (kSwiglu ? q.n / 256u : (q.n + kMxBlockN - 1) / kMxBlockN);
     uint32_t grid = static_cast<uint32_t>(dev.sm_count);
     if (q.block_num != 0 && q.block_num < grid) {
         grid = q.block_num;
@@ -915,6 +929,33 @@ MxProblem mx_grouped_problem(const cb200_mx_grouped_matmul_args* a)
     return q;
 }
 
+MxProblem mx_swiglu_problem(const cb200_mx_grouped_swiglu_quant_args* a)
+{
+    MxProblem q{};
+    q.m = a->m;
+    q.n = a->n;
+    q.k = a->k;
+    q.group_count = a->group_count;
+    q.format = CB200_MX_E4M3;
+    q.layout_a = CB200_ROW_MAJOR;
+    q.layout_b = a->layout_b;
+    q.group_list_type = a->group_list_type;
+    q.group_list_is_prefix_sum = a->group_list_kind == CB200_GROUP_LIST_PREFIX_SUMS ? 1u : 0u;
+    q.a = a->a;
+    q.b = a->b;
+    q.group_list = a->group_list;
+    q.scale_a = a->scale_a;
+    q.scale_b = a->scale_b;
+    q.d = a->q;
+    q.q_scale = a->q_scale;
+    q.swiglu_quant = true;
+    q.workspace = a->workspace;
+    q.workspace_bytes = a->workspace_bytes;
+    q.block_num = a->block_num;
+    q.flags = a->flags;
+    return q;
+}
+
 int run_mx(const MxProblem& q, void* stream_v)
 {
     MxPlan plan;
@@ -933,6 +974,9 @@ int run_mx(const MxProblem& q, void* stream_v)
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const bool fp4 = q.format == CB200_MX_E2M1;
+    if (q.swiglu_quant) {
+        return launch_mx<false, true, true>(q, plan, *dev, stream);
+    }
     if (q.group_count != 0) {
         return fp4 ? launch_mx<true, true>(q, plan, *dev, stream) : launch_mx<false, true>(q, plan, *dev, stream);
     }
@@ -986,6 +1030,31 @@ int cb200_mx_grouped_matmul_slice_m(const cb200_mx_grouped_matmul_args* args, vo
 {
     const int rc = cb200_mx_grouped_matmul_slice_m_can_implement(args);
     return rc != CB200_SUCCESS ? rc : run_mx(mx_grouped_problem(args), stream);
+}
+
+int cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_can_implement(const cb200_mx_grouped_swiglu_quant_args* args)
+{
+    MxPlan plan;
+    if (args == nullptr || args->group_count == 0 || args->group_list_kind > CB200_GROUP_LIST_PREFIX_SUMS) {
+        return CB200_INVALID;
+    }
+    return plan_mx(mx_swiglu_problem(args), &plan);
+}
+
+uint64_t cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_workspace_size(const cb200_mx_grouped_swiglu_quant_args* args)
+{
+    MxPlan plan;
+    if (cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_can_implement(args) != CB200_SUCCESS ||
+        plan_mx(mx_swiglu_problem(args), &plan) != CB200_SUCCESS) {
+        return 0;
+    }
+    return plan.total();
+}
+
+int cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(const cb200_mx_grouped_swiglu_quant_args* args, void* stream)
+{
+    const int rc = cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_can_implement(args);
+    return rc != CB200_SUCCESS ? rc : run_mx(mx_swiglu_problem(args), stream);
 }
 
 int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args* args)

@@ -21,9 +21,19 @@
 //                          capped 128-wide tiles at half the tensor rate; 256 columns plus the scale columns do
 //                          not leave room for a second accumulator, so the epilogue pulls its columns out of TMEM
 //                          first, hands the accumulator back, and stores afterwards.
+//
+// kSwiglu (grouped E4M3 problems): the reference's GroupedMxMatmulSliceMSwigluMxQuantTla with its
+// BlockEpilogueSwigluMxQuant (include/catlass/gemm/kernel/grouped_mx_matmul_slice_m_swiglu_mx_quant_tla.hpp:29-408,
+// include/catlass/epilogue/tile/tile_swiglu_mx_quant.hpp:27-286).  The matmul result C [m][n] is never written:
+// a tile pairs 128 columns of its left half ("act") with the same 128 columns of its right half ("gate") as one
+// 128 x 256 accumulator, and the epilogue computes S = act / (1 + exp(-act)) * gate in fp32, rounds S to bf16
+// and MX-quantises it along N, 32 columns per E8M0 scale, into E4M3 bytes Q [m][n/2] and scales [m][n/64].  A
+// thread owns one row of the accumulator, so a block of 32 columns is 32 registers of one thread: the block's
+// largest exponent needs no exchange between threads.
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "ptx.cuh"
 #include "w8a8_gemm.cuh"
@@ -51,6 +61,8 @@ struct MxParams {
     const int4* tile_table;           // [row tile] = (first row, one past the group's last row, group, 0)
     const uint32_t* num_row_tiles;    // number of table entries
     uint32_t sfb_blocks_per_group;    // 128-row scale blocks of B per group: 2 * ceil(n / 256)
+    // SwiGLU + MX quantisation epilogue (kSwiglu): d holds E4M3 bytes [m][n/2], q_scale E8M0 bytes [m][n/64]
+    uint8_t* q_scale;
 };
 
 // One block: turns the group list of a grouped slice-M problem into the row-tile table the matmul and the scale
@@ -152,6 +164,49 @@ __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* _
     }
 }
 
+// MX quantisation of 32 bf16 values (their bit patterns in `bits`) to E4M3 with one E8M0 scale, the arithmetic of
+// the reference's epilogue on bf16 exponent fields (include/catlass/epilogue/tile/tile_swiglu_mx_quant.hpp:167-215;
+// restated for the CPU in experimental/gmm/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant/compare.py:41-121):
+//   max_exp = largest exponent field of the block, raised to 8 + 127 at least (E4M3's largest exponent is 8)
+//   scale   = max_exp - 8 as an E8M0 byte (0 for an all-zero block, 0xFF if the block holds Inf or NaN)
+//   q       = e4m3_rne_saturating(bf16(x * 2^-(max_exp - 8 - 127)))
+// Returns the scale byte; out[8] receives the 32 E4M3 bytes, column order.
+__device__ __forceinline__ uint32_t mx_quant_block_bf16_e4m3(const uint32_t (&bits)[32], uint32_t (&out)[8])
+{
+    uint32_t max_exp = 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const uint32_t e = bits[i] & 0x7f80u;
+        max_exp = e > max_exp ? e : max_exp;
+    }
+    const bool finite = max_exp != 0x7f80u;
+    const bool nonzero = max_exp != 0u;
+    const uint32_t clamped = max_exp <= 0x0400u ? 0x0400u : max_exp;
+    const uint32_t shared = clamped - 0x0400u;
+    uint32_t scale = shared >> 7;
+    scale = finite ? scale : 0xffu;
+    scale = nonzero ? scale : 0u;
+    uint32_t inv = 0x7f00u - shared;  // bf16 bits of 2^-(shared exponent)
+    inv = finite ? inv : 0x7f81u;     // NaN: the whole block becomes NaN
+    inv = nonzero ? inv : 0u;
+    inv = shared == 0x7f00u ? 0x0040u : inv;  // 2^-127 is a bf16 denormal
+    const float inv_f = __uint_as_float(inv << 16);
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const float x = __uint_as_float(bits[4 * w + b] << 16);
+            // the product of two bf16 values is exact in fp32; the reference multiplies in bf16 (one rounding)
+            const float scaled = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x, inv_f)));
+            const uint32_t code = __nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
+            word |= (code & 0xffu) << (8 * b);
+        }
+        out[w] = word;
+    }
+    return scale;
+}
+
 // Tile order: bands of `band_rows` tile rows, walked column by column inside a band.  The 148 tiles in flight at
 // any time then share the band's row panels of A (the host sizes a band to ~32 MB of A) and a few column panels
 // of B, which stay in L2; with a plain row-major order every wave streamed all of B from HBM again (measured at
@@ -169,7 +224,7 @@ __device__ __forceinline__ void mx_tile_coords(uint32_t idx, uint32_t m_tiles, u
 
 // kGrouped: slice-M groups (the reference's GroupedMxMatmulSliceMTla, example 55): row tiles come from the tile
 // table, every group has its own weight matrix (third coordinate of B's tensor map) and B scales.
-template <bool kFp4, bool kGrouped>
+template <bool kFp4, bool kGrouped, bool kSwiglu = false>
 __global__ void __launch_bounds__(kMxThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const MxParams p)
@@ -199,7 +254,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t m_tiles = kGrouped ? *p.num_row_tiles : (p.m + kBlockM - 1) / kBlockM;
-    const uint32_t n_tiles = (p.n + kMxBlockN - 1) / kMxBlockN;
+    static_assert(!kSwiglu || (kGrouped && !kFp4), "the SwiGLU + quantisation epilogue serves grouped E4M3 problems");
+    // kSwiglu: a tile is 128 columns of the left half of C next to the same 128 columns of the right half
+    const uint32_t n_tiles = kSwiglu ? (p.n / 2 + 127) / 128 : (p.n + kMxBlockN - 1) / kMxBlockN;
     const uint32_t total_tiles = m_tiles * n_tiles;
     // first row, end of the rows that may be stored, group of row tile mt
     auto row_tile = [&](uint32_t mt, int32_t& row0, int32_t& row_end, int32_t& group) {
@@ -250,7 +307,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 mx_tile_coords(idx, m_tiles, n_tiles, p.band_rows, mt, nt);
                 int32_t row0, row_end, group;
                 row_tile(mt, row0, row_end, group);
-                const size_t sfb_block = static_cast<size_t>(group) * p.sfb_blocks_per_group + 2 * nt;
+                // the tile's two 128-row scale blocks of B (the workspace pads every matrix to a pair)
+                const size_t sfb_first = static_cast<size_t>(group) * p.sfb_blocks_per_group;
+                const size_t sfb_block0 = sfb_first + (kSwiglu ? nt : 2 * nt);
+                const size_t sfb_block1 = sfb_first + (kSwiglu ? p.n / 256 + nt : 2 * nt + 1);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer);
                     if (!ok) {
@@ -264,12 +324,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const size_t kq = static_cast<size_t>(kb) * kWords;
                     mbar_expect_tx(full, kStageTx);
                     tma_load_2d(sa, &tmap_a, full, k0, row0);
-                    tma_load_3d(sb, &tmap_b, full, k0, static_cast<int32_t>(nt) * kMxBlockN, group);
+                    if constexpr (kSwiglu) {  // (B's tensor map then has boxes of 128 rows)
+                        tma_load_3d(sb, &tmap_b, full, k0, static_cast<int32_t>(nt) * 128, group);
+                        tma_load_3d(sb + S::kBBytes / 2, &tmap_b, full, k0, static_cast<int32_t>(p.n / 2 + nt * 128),
+                                    group);
+                    } else {
+                        tma_load_3d(sb, &tmap_b, full, k0, static_cast<int32_t>(nt) * kMxBlockN, group);
+                    }
                     bulk_load(ssf, p.sfa + (static_cast<size_t>(mt) * p.kq_total + kq) * 512, kWords * 512, full);
-                    // the tile's 256 columns are two 128-row scale blocks of B (the workspace pads to a pair)
-                    bulk_load(ssf + 1024, p.sfb + (sfb_block * p.kq_total + kq) * 512, kWords * 512, full);
-                    bulk_load(ssf + 1024 + kWords * 512, p.sfb + ((sfb_block + 1) * p.kq_total + kq) * 512,
-                              kWords * 512, full);
+                    bulk_load(ssf + 1024, p.sfb + (sfb_block0 * p.kq_total + kq) * 512, kWords * 512, full);
+                    bulk_load(ssf + 1024 + kWords * 512, p.sfb + (sfb_block1 * p.kq_total + kq) * 512, kWords * 512,
+                              full);
                     if (++stage == kMxStages) {
                         stage = 0;
                         phase ^= 1;
@@ -402,6 +467,55 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const uint32_t row = static_cast<uint32_t>(row0) + quad * 32 + lane;
             const bool row_ok = static_cast<int32_t>(row) < row_end;
             const uint32_t taddr = tmem_base + acc * kMxBlockN + half * 128 + ((quad * 32u) << 16);
+            if constexpr (kSwiglu) {
+                // This warp: output columns [half * 64, half * 64 + 64) of the tile's 128, as two blocks of 32; "act"
+                // sits in accumulator columns 0..127, "gate" in 128..255.
+                const uint32_t tcols = tmem_base + acc * kMxBlockN + ((quad * 32u) << 16);
+                const uint32_t half_n = p.n / 2;
+                uint8_t* qrow = static_cast<uint8_t*>(p.d) + static_cast<size_t>(row_ok ? row : 0) * half_n;
+                uint8_t* srow = p.q_scale + static_cast<size_t>(row_ok ? row : 0) * (half_n / 32);
+                // all four pieces (2 x 32 columns of act and of gate) come out of TMEM first and the accumulator goes
+                // back to the MMA issuer before any arithmetic: the next tile's MMAs wait for reads only
+                uint32_t ra[2][32], rg[2][32];
+#pragma unroll
+                for (uint32_t blk = 0; blk < 2; ++blk) {
+                    tmem_ld_32x32b_x32(tcols + half * 64 + blk * 32, ra[blk]);
+                    tmem_ld_32x32b_x32(tcols + 128 + half * 64 + blk * 32, rg[blk]);
+                }
+                tmem_ld_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(bar_tmem_empty + acc * 8);
+                }
+#pragma unroll
+                for (uint32_t blk = 0; blk < 2; ++blk) {
+                    const uint32_t c0 = half * 64 + blk * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        // S = act / (1 + exp(-act)) * gate, step by step in fp32 as the reference's epilogue does
+                        // (tile_swiglu_mx_quant.hpp:96-103), rounded to bf16 (RNE)
+                        const float a = __uint_as_float(ra[blk][i]);
+                        const float g = __uint_as_float(rg[blk][i]);
+                        const float t = __fadd_rn(expf(-a), 1.0f);
+                        const float sw = __fmul_rn(__fdiv_rn(a, t), g);
+                        ra[blk][i] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sw)));
+                    }
+                    uint32_t q[8];
+                    const uint32_t scale = mx_quant_block_bf16_e4m3(ra[blk], q);
+                    const uint32_t col0 = nt * 128 + c0;
+                    if (row_ok && col0 < half_n) {  // (n is a multiple of 256: whole blocks)
+                        *reinterpret_cast<uint4*>(qrow + col0) = make_uint4(q[0], q[1], q[2], q[3]);
+                        *reinterpret_cast<uint4*>(qrow + col0 + 16) = make_uint4(q[4], q[5], q[6], q[7]);
+                        srow[col0 / 32] = static_cast<uint8_t>(scale);
+                    }
+                }
+                if (++acc == kMxAccs) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+                continue;
+            }
             if (p.out_f32) {
                 // fp32 output (what the reference's MX kernels write): the accumulator goes out as it is, 32 columns
                 // at a time, before the accumulator is handed back (nothing to round, nothing to keep in registers)

@@ -246,6 +246,31 @@ def ascend950_mx_grouped_matmul_slice_m(mat1, mat2, groupList, mx_scale_a, mx_sc
     return d
 
 
+def ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant(mat1, mat2, mx_scale_a, mx_scale_b, group_list,
+                                                            transB=True):
+    """Example 65 (tests/optest/torch_catlass/ops/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant.py): grouped
+    MXFP8 matmul, SwiGLU over the two halves of its columns, MX quantisation of the result.  mat1 (M, K)
+    float8_e4m3fn, mat2 (G, N, K) with transB else (G, K, N), group_list the groups' row counts (int64).
+    Returns [Q (M, N/2) float8_e4m3fn, Q_scale (M, N/64) float8_e8m0fnu]; rows past the last group are zero."""
+    _require_cuda(mat1, mat2, mx_scale_a, mx_scale_b, group_list)
+    mat1, mat2, group_list = mat1.contiguous(), mat2.contiguous(), group_list.contiguous()
+    m, k = tuple(mat1.shape)
+    g = group_list.numel()
+    n = mat2.shape[1] if transB else mat2.shape[2]
+    lb = capi.COLUMN_MAJOR if transB else capi.ROW_MAJOR
+    q = torch.zeros((m, n // 2), dtype=torch.uint8, device=mat1.device)
+    q_scale = torch.zeros((m, n // 64), dtype=torch.uint8, device=mat1.device)
+    ws = torch.empty(max(capi.mx_grouped_swiglu_quant_workspace_size(m, n, k, g, lb), 1), dtype=torch.uint8,
+                     device=mat1.device)
+    capi.mx_grouped_swiglu_quant(mat1.view(torch.uint8), mat2.view(torch.uint8), group_list,
+                                 mx_scale_a.contiguous().view(torch.uint8), mx_scale_b.contiguous().view(torch.uint8),
+                                 q, q_scale, m, n, k, g, ws, layout_b=lb,
+                                 group_list_type=capi.GROUP_LIST_INT32 if group_list.dtype == torch.int32
+                                 else capi.GROUP_LIST_INT64, group_list_kind=capi.GROUP_LIST_SIZES)
+    e8m0 = getattr(torch, "float8_e8m0fnu", None)
+    return [q.view(torch.float8_e4m3fn), q_scale.view(e8m0) if e8m0 is not None else q_scale]
+
+
 def ascend950_fp8_mx_matmul_aswt(mat1, mat2, mx_scale_a, mx_scale_b, transA=False, transB=True):
     """Example 53: float8_e4m3fn operands, float8_e8m0fnu block scales, fp32 output."""
     return _mx(mat1, mat2, mx_scale_a, mx_scale_b, transA, transB, capi.MX_E4M3)

@@ -399,6 +399,51 @@ CB200_API uint64_t cb200_mx_grouped_matmul_slice_m_workspace_size(const cb200_mx
 CB200_API int cb200_mx_grouped_matmul_slice_m(const cb200_mx_grouped_matmul_args *args, void *stream);
 
 /*
+ * Grouped (slice-M) MXFP8 matmul with the SwiGLU + MX quantisation epilogue fused in: the first half of an MoE
+ * expert MLP that feeds the second half's MX matmul directly.  Replaces
+ * Gemm::Kernel::GroupedMxMatmulSliceMSwigluMxQuantTla::Arguments with Epilogue::BlockEpilogueSwigluMxQuant
+ * (include/catlass/gemm/kernel/grouped_mx_matmul_slice_m_swiglu_mx_quant_tla.hpp:72-162,
+ * experimental/gmm/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant/fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant.cpp:196-227;
+ * reserved optest entry tests/optest/include/catlass_kernel_jit.h:477), golden compare.py:31-121 of that example:
+ *     C          = (scale_a * A) @ (scale_b * B[g])          fp32, never written
+ *     act, gate  = C[:, :n/2], C[:, n/2:]
+ *     S          = bf16_rne( act / (1 + exp(-act)) * gate )   each step in fp32
+ *     Q, q_scale = MX quantisation of S along n: per 32 columns scale = 2^(largest bf16 exponent of the block - 8)
+ *                  (at least 2^-127 ... the block's exponent floor is 8), Q = e4m3_rne_sat(bf16(S / scale));
+ *                  scale byte 0 for an all-zero block, 0xFF (and NaN codes) for a block holding Inf or NaN
+ *   a, b, scales, group_list: as for cb200_mx_grouped_matmul_slice_m with format E4M3
+ *   q        [m][n/2] E4M3 bytes, 16-byte aligned            q_scale  [m][n/64] E8M0 bytes
+ * n must be a multiple of 256 here (the reference asks for 128): a tile pairs 128 columns of either half of C.
+ * Rows past the last group are not written.
+ */
+typedef struct cb200_mx_grouped_swiglu_quant_args {
+    uint32_t m, n, k;
+    uint32_t group_count;         /* 1 .. 1024 */
+    uint32_t layout_b;            /* CB200_COLUMN_MAJOR ([G][n][k]) or CB200_ROW_MAJOR ([G][k][n]) */
+    uint32_t group_list_type;     /* CB200_GROUP_LIST_INT64 / _INT32 */
+    uint32_t group_list_kind;     /* CB200_GROUP_LIST_SIZES / CB200_GROUP_LIST_PREFIX_SUMS */
+    uint32_t flags;               /* 0 */
+    const void *a;
+    const void *b;
+    const void *group_list;
+    const void *scale_a;
+    const void *scale_b;
+    void *q;
+    void *q_scale;
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t reserved;
+} cb200_mx_grouped_swiglu_quant_args;
+
+CB200_API int cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_can_implement(
+    const cb200_mx_grouped_swiglu_quant_args *args);
+CB200_API uint64_t cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_workspace_size(
+    const cb200_mx_grouped_swiglu_quant_args *args);
+CB200_API int cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(const cb200_mx_grouped_swiglu_quant_args *args,
+                                                              void *stream);
+
+/*
  * cb200_mx_matmul_static: the MX matmul above for callers that cannot give it a workspace.
  * (No counterpart in the reference: every reference kernel takes its workspace from the caller or allocates
  * it per call, examples/shared_lib/src/common/common.hpp:36-46.)

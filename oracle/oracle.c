@@ -450,3 +450,105 @@ void orc_mx_matmul(uint32_t m, uint32_t n, uint32_t k, int fmt, const uint8_t *a
     free(a_deq);
     free(b_deq);
 }
+
+/* ------------------------------------------------------------------ SwiGLU + MX quantisation epilogue */
+
+/* Nearest E4M3 (fn: no infinities, max 448) code, ties to even, saturating; NaN -> 0x7F.
+ * What torch's float32 -> float8_e4m3fn conversion does after the golden's clamp to +-448
+ * (experimental/gmm/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant/compare.py:106-108). */
+uint8_t orc_e4m3_rne_sat(float x)
+{
+    uint32_t bits;
+    memcpy(&bits, &x, 4);
+    const uint8_t sign = (uint8_t)((bits >> 24) & 0x80u);
+    if (x != x) {
+        return 0x7F;
+    }
+    float mag = fabsf(x);
+    if (mag >= 448.0f) {
+        return (uint8_t)(sign | 0x7E);
+    }
+    /* grid spacing: 2^-9 below 2^-6 (subnormals), else 2^(e-3) for 2^e <= mag < 2^(e+1) */
+    int e;
+    (void)frexpf(mag, &e);   /* mag = f * 2^e, f in [0.5, 1) -> exponent of the leading bit is e - 1 */
+    int lead = e - 1;
+    if (mag == 0.0f || lead < -6) {
+        lead = -6;
+    }
+    const float step = ldexpf(1.0f, lead - 3);
+    const float scaled = mag / step;            /* exact: a power-of-two division */
+    float r = nearbyintf(scaled);               /* default rounding mode: ties to even */
+    /* r is in [0, 16]; 16 means the next binade's first value */
+    int ri = (int)r;
+    int exp_field = lead + 7;                   /* bias 7 */
+    if (lead == -6 && ri < 8) {
+        return (uint8_t)(sign | (uint8_t)ri);   /* subnormal (exp field 0) */
+    }
+    if (ri == 16) {
+        ri = 8;
+        exp_field += 1;
+    }
+    return (uint8_t)(sign | (uint8_t)(exp_field << 3) | (uint8_t)(ri - 8));
+}
+
+/* S = bf16_rne(act / (1 + exp(-act)) * gate) with act = c[:, :n/2], gate = c[:, n/2:], every step in fp32:
+ * compare.py:31-39 (swiglu) and :174-175 (the rounding to bfloat16) of the example named above. */
+void orc_swiglu_bf16(const float *c, uint64_t m, uint64_t n, uint16_t *s_bits)
+{
+    const uint64_t h = n / 2;
+    for (uint64_t i = 0; i < m; ++i) {
+        for (uint64_t j = 0; j < h; ++j) {
+            const float act = c[i * n + j];
+            const float gate = c[i * n + h + j];
+            const float t1 = -act;
+            const float t2 = expf(t1);
+            const float t3 = t2 + 1.0f;
+            const float t4 = act / t3;
+            const float t5 = t4 * gate;
+            s_bits[i * h + j] = orc_bf16_rne(t5);
+        }
+    }
+}
+
+/* MX quantisation of bf16 values along the contiguous axis, 32 per block, to E4M3 + E8M0:
+ * compare.py:41-121 (mx_quant_dtype 36) of the example named above, itself a restatement of the device
+ * epilogue's integer arithmetic on bf16 exponent fields (include/catlass/epilogue/tile/tile_swiglu_mx_quant.hpp:167-215).
+ * s_bits [rows][cols] (cols a multiple of 32), q [rows][cols], scale [rows][cols/32]. */
+void orc_mx_quant_bf16_e4m3(const uint16_t *s_bits, uint64_t rows, uint64_t cols, uint8_t *q, uint8_t *scale)
+{
+    const uint64_t blocks = cols / 32;
+    for (uint64_t i = 0; i < rows; ++i) {
+        for (uint64_t b = 0; b < blocks; ++b) {
+            const uint16_t *x = s_bits + i * cols + b * 32;
+            uint32_t max_exp = 0;
+            for (int e = 0; e < 32; ++e) {
+                const uint32_t ex = x[e] & 0x7f80u;
+                max_exp = ex > max_exp ? ex : max_exp;
+            }
+            const int finite = max_exp != 0x7f80u;
+            const int nonzero = max_exp != 0;
+            const uint32_t clamped = max_exp <= 0x0400u ? 0x0400u : max_exp;
+            const uint32_t shared = clamped - 0x0400u;
+            uint32_t sv = shared >> 7;
+            sv = finite ? sv : 0xffu;
+            sv = nonzero ? sv : 0u;
+            uint32_t hs = 0x7f00u - shared;
+            hs = finite ? hs : 0x7f81u;
+            hs = nonzero ? hs : 0u;
+            hs = shared == 0x7f00u ? 0x0040u : hs;
+            const float inv = orc_bf16_to_float((uint16_t)hs);
+            scale[i * blocks + b] = (uint8_t)sv;
+            for (int e = 0; e < 32; ++e) {
+                /* bf16 * bf16 -> bf16: the exact product, rounded once */
+                const float prod = orc_bf16_to_float(x[e]) * inv;
+                float f = orc_bf16_to_float(orc_bf16_rne(prod));
+                if (f > 448.0f) {
+                    f = 448.0f;
+                } else if (f < -448.0f) {
+                    f = -448.0f;
+                }
+                q[i * cols + b * 32 + e] = orc_e4m3_rne_sat(f);
+            }
+        }
+    }
+}

@@ -152,4 +152,15 @@ void orc_f16_rne_array(const float *x, uint16_t *y, size_t count);
 #ifdef __cplusplus
 }
 #endif
+/*
+ * SwiGLU + MX quantisation epilogue of the grouped MXFP8 matmul      [pinned: reference python]
+ * (experimental/gmm/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant/compare.py:31-121).
+ *   orc_swiglu_bf16         c [m][n] fp32 -> s_bits [m][n/2] bf16 bit patterns
+ *   orc_mx_quant_bf16_e4m3  s_bits [rows][cols], cols % 32 == 0 -> q [rows][cols] E4M3, scale [rows][cols/32] E8M0
+ *   orc_e4m3_rne_sat        nearest E4M3 code, ties to even, saturating at 448
+ */
+uint8_t orc_e4m3_rne_sat(float x);
+void orc_swiglu_bf16(const float *c, uint64_t m, uint64_t n, uint16_t *s_bits);
+void orc_mx_quant_bf16_e4m3(const uint16_t *s_bits, uint64_t rows, uint64_t cols, uint8_t *q, uint8_t *scale);
+
 #endif

@@ -5,7 +5,8 @@ Run where the reference tree is present (it is not needed to run the tests):
     python tests/golden/make_golden.py /path/to/reference
 
 It uses (a) the reference's C++ CPU golden, compiled from the reference tree into oracle/_ref/libref.so by
-oracle/Makefile, and (b) the reference's Python data generators for MX and W4A8, imported as modules.
+oracle/Makefile, and (b) the reference's Python data generators and goldens for MX, W4A8 and the SwiGLU +
+MX quantisation epilogue, imported as modules.
 Only small arrays (inputs and the reference's outputs for them) are stored; no reference code is copied.
 """
 import importlib.util
@@ -127,6 +128,45 @@ def w4a8(reference):
                         b_int8=b_int8, b_packed=b_int4.view(np.uint8), expected=expected.astype(np.float32))
 
 
+def swiglu_quant(reference):
+    """SwiGLU + MX quantisation epilogue: the golden functions of the reference's example, on a small fp32 matrix
+    that covers ordinary values, saturation of the swish, all-zero blocks, blocks below E4M3's exponent floor,
+    values that round up across a binade, and a block holding Inf."""
+    import types
+
+    import torch
+    # the script imports two dtype packages for its file I/O only; its swiglu() and quant() are pure torch
+    for name, attrs in (("en_dtypes", ["float8_e8m0"]), ("ml_dtypes", ["float8_e4m3fn", "float8_e5m2"])):
+        if name not in sys.modules:
+            stub = types.ModuleType(name)
+            for attr in attrs:
+                setattr(stub, attr, np.uint8)
+            sys.modules[name] = stub
+    cmp_mod = _load(os.path.join(
+        reference, "experimental/gmm/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant/compare.py"), "swq")
+    rng = np.random.default_rng(65)
+    m, n = 24, 256
+    c = (rng.standard_normal((m, n)) * 3.0).astype(np.float32)
+    h = n // 2
+    c[1, :] *= 40.0                      # swish saturates, products reach the E4M3 clamp after scaling
+    c[2, :32] = 0.0                      # an all-zero block (act = 0)
+    c[3, :] *= 1e-4                      # blocks whose largest exponent is below the floor
+    c[4, :] *= 1e-30
+    c[5, 0:32] = 1.9999                  # rounds up across a binade in bf16
+    c[5, h:h + 32] = 1.0
+    c[6, 3] = np.inf                     # Inf in act: swish(inf) = inf
+    c[6, h + 3] = 2.0
+    c[7, :h] = np.linspace(-30, 30, h, dtype=np.float32)
+    c[7, h:] = 448.0
+    c[8, :h] = rng.uniform(-1, 1, h).astype(np.float32) * np.float32(2.0) ** rng.integers(-20, 20, h)
+    t = torch.from_numpy(c)
+    s = cmp_mod.swiglu(t).to(torch.bfloat16)
+    s_bits = s.view(torch.int16).numpy().view(np.uint16)
+    q, sc = cmp_mod.quant(s.to(torch.float32), 36)
+    np.savez_compressed(os.path.join(HERE, "swiglu_quant_ref_golden.npz"), c=c, s_bits=s_bits,
+                        q=q.view(np.uint8), scale=sc.astype(np.uint8))
+
+
 if __name__ == "__main__":
     reference = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CATLASS_REFERENCE", "")
     if not os.path.isdir(reference):
@@ -138,4 +178,5 @@ if __name__ == "__main__":
     w8a8(ref_lib)
     mx(reference)
     w4a8(reference)
+    swiglu_quant(reference)
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))

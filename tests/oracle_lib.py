@@ -50,6 +50,8 @@ def lib():
         for name in ("orc_e4m3_to_float", "orc_e2m1_to_float", "orc_e8m0_to_float"):
             getattr(_lib, name).restype = ctypes.c_float
             getattr(_lib, name).argtypes = [ctypes.c_uint8]
+        _lib.orc_e4m3_rne_sat.restype = ctypes.c_uint8
+        _lib.orc_e4m3_rne_sat.argtypes = [ctypes.c_float]
     return _lib
 
 
@@ -167,6 +169,25 @@ def mx_matmul(aq, sfa, bq, sfb, m, n, k, fmt):
     lib().orc_mx_matmul(_c_u32(m), _c_u32(n), _c_u32(k), fmt, _ptr(aq), _ptr(sfa), _ptr(bq), _ptr(sfb),
                         _ptr(out))
     return out
+
+
+def swiglu_bf16(c):
+    """c: fp32 [m, n] (act | gate) -> bf16 bit patterns [m, n/2] of act / (1 + exp(-act)) * gate."""
+    c = _c(c, np.float32)
+    m, n = c.shape
+    out = np.empty((m, n // 2), np.uint16)
+    lib().orc_swiglu_bf16(_ptr(c), ctypes.c_uint64(m), ctypes.c_uint64(n), _ptr(out))
+    return out
+
+
+def mx_quant_bf16_e4m3(s_bits):
+    """s_bits: bf16 bit patterns [rows, cols], cols % 32 == 0 -> (E4M3 codes [rows, cols], E8M0 [rows, cols/32])."""
+    s_bits = _c(s_bits, np.uint16)
+    rows, cols = s_bits.shape
+    q = np.empty((rows, cols), np.uint8)
+    scale = np.empty((rows, cols // 32), np.uint8)
+    lib().orc_mx_quant_bf16_e4m3(_ptr(s_bits), ctypes.c_uint64(rows), ctypes.c_uint64(cols), _ptr(q), _ptr(scale))
+    return q, scale
 
 
 def bf16_bits(x):

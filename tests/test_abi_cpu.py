@@ -69,6 +69,7 @@ def test_struct_layout_matches_the_header(lib):
         ("cb200_w4a8_matmul_args", capi.W4A8MatmulArgs),
         ("cb200_mx_matmul_args", capi.MxMatmulArgs),
         ("cb200_mx_grouped_matmul_args", capi.MxGroupedMatmulArgs),
+        ("cb200_mx_grouped_swiglu_quant_args", capi.MxGroupedSwigluQuantArgs),
         ("cb200_mx_quantize_args", capi.MxQuantizeArgs),
     ]
     lines = []

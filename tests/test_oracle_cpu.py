@@ -1,6 +1,7 @@
 """The CPU oracle against the reference: committed golden vectors (produced by the reference's own C++
 golden and Python generators, see tests/golden/make_golden.py) and, where oracle/_ref was built, the
 reference golden itself on fresh random inputs."""
+import ctypes
 import os
 
 import numpy as np
@@ -200,6 +201,41 @@ def test_mx_element_decoders():
 
 
 # ------------------------------------------------------------------ W4A8
+
+def test_swiglu_mx_quant_matches_reference_golden():
+    """Pins the epilogue restatement to the reference's own swiglu() and quant()
+    (experimental/gmm/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant/compare.py:31-121)."""
+    g = np.load(os.path.join(GOLDEN, "swiglu_quant_ref_golden.npz"))
+    # the quantiser is integer arithmetic on bf16 fields plus exact products: bit for bit, fed the reference's S
+    q, scale = O.mx_quant_bf16_e4m3(g["s_bits"])
+    nan_blocks = np.repeat(g["scale"] == 0xFF, 32, axis=1)
+    assert np.array_equal(scale, g["scale"])
+    assert np.array_equal(q[~nan_blocks], g["q"][~nan_blocks])
+    assert np.all((q[nan_blocks] & 0x7F) == 0x7F) and nan_blocks.any()  # a block holding Inf: all NaN codes
+    # the swish goes through exp(): another libm may differ in the last place, which the rounding to bf16 hides
+    # almost always; demand equality up to one bf16 step on a handful of values at most
+    s = O.swiglu_bf16(g["c"])
+    diff = np.abs(s.astype(np.int32) - g["s_bits"].astype(np.int32))
+    finite = (g["s_bits"] & 0x7F80) != 0x7F80
+    assert diff[finite].max() <= 1 and (diff[finite] != 0).mean() < 2e-3
+    assert np.array_equal(s[~finite] & 0x7F80, g["s_bits"][~finite] & 0x7F80)
+
+
+def test_e4m3_rne_encoder_against_decoder():
+    """Every E4M3 code decodes and re-encodes to itself; midpoints go to the even code; 448 saturates."""
+    for code in range(256):
+        if (code & 0x7F) == 0x7F:
+            continue
+        v = O.lib().orc_e4m3_to_float(code)
+        assert O.lib().orc_e4m3_rne_sat(ctypes.c_float(v)) == (code if v != 0 or code == 0 else code), code
+    lib = O.lib()
+    for code in range(0, 0x7E):
+        lo, hi = lib.orc_e4m3_to_float(code), lib.orc_e4m3_to_float(code + 1)
+        mid = np.float32((np.float64(lo) + np.float64(hi)) / 2)
+        want = code if code % 2 == 0 else code + 1
+        assert lib.orc_e4m3_rne_sat(ctypes.c_float(mid)) == want, (code, mid)
+    assert lib.orc_e4m3_rne_sat(ctypes.c_float(1e9)) == 0x7E and lib.orc_e4m3_rne_sat(ctypes.c_float(-500.0)) == 0xFE
+
 
 def test_w4a8_per_tensor_matches_reference_generator():
     g = np.load(os.path.join(GOLDEN, "w4a8_ref_golden.npz"))

@@ -201,6 +201,36 @@ def test_ascend950_mx_grouped_matmul_slice_m(torch_catlass, trans_b):
     assert torch.allclose(result.cpu(), expected, rtol=1e-2, atol=1e-2)
 
 
+def test_ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant(torch_catlass):
+    """The reference op's signature (tests/optest/torch_catlass/ops/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant.py)
+    on the example's own run (4 groups, m = 256, n = 512, k = 1024): the dequantised output within the example's
+    tolerance (2^-4 relative, doubled) of SwiGLU applied to the dequantised matmul."""
+    group_sizes, n, k = (64, 64, 64, 64), 512, 1024
+    m = sum(group_sizes)
+    a32 = torch.randn(m, k)
+    a8, a_scale, a_deq = _quantize_axis_last(a32)
+    a_scale = a_scale.reshape(m, a_scale.shape[1] // 2, 2).contiguous()
+    b_list, s_list, expected, offset = [], [], [], 0
+    for size in group_sizes:
+        b32 = torch.randn(k, n)
+        bt8, bt_scale, bt_deq = _quantize_axis_last(b32.t().contiguous())
+        b_list.append(bt8.contiguous())
+        s_list.append(bt_scale.reshape(n, bt_scale.shape[1] // 2, 2).contiguous())
+        c = a_deq[offset:offset + size] @ bt_deq.t()
+        act, gate = c.chunk(2, dim=-1)
+        expected.append(act / (torch.exp(-act) + 1) * gate)
+        offset += size
+    expected = torch.cat(expected, dim=0)
+    q, q_scale = torch_catlass.ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant(
+        a8.cuda(), torch.stack(b_list).cuda(), a_scale.cuda(), torch.stack(s_list).cuda(),
+        torch.tensor(group_sizes, dtype=torch.int64).cuda(), transB=True)
+    assert q.shape == (m, n // 2) and q.dtype == torch.float8_e4m3fn and q_scale.shape == (m, n // 64)
+    scales = torch.pow(2.0, q_scale.view(torch.uint8).cpu().float() - 127.0).repeat_interleave(32, dim=1)
+    deq = q.cpu().float() * scales
+    err = (deq - expected).abs() / expected.abs().clamp(min=1.0)
+    assert err.max().item() <= 2 * 2.0 ** -4, err.max().item()
+
+
 def test_grouped_matmul_slice_k_per_token_dequant(torch_catlass):
     """tests/optest/tests/test_11_grouped_matmul_slice_k_per_token_dequant.py:11-40"""
     g, m, n, k_total = 4, 128, 128, 256
