@@ -42,7 +42,7 @@ DENSE = {
     "decode_a": (16, 14336, 4096),
     "decode_b": (16, 4096, 14336),
 }
-SECONDARY = ["decode_a", "decode_b", "prefill", "w4a8", "mxfp8", "mxfp4", "mx_swiglu"]
+SECONDARY = ["decode_a", "decode_b", "prefill", "w4a8", "mxfp8", "mxfp4", "mx_swiglu", "mx_routing"]
 INT8_PER_BF16 = 2.0  # kind::i8 issues at twice the bf16 rate on the same tensor cores
 L2_BYTES = 126e6
 
@@ -772,9 +772,60 @@ def run_mx_swiglu(sampler, seconds):
     }
 
 
+def run_mx_routing(sampler, seconds):
+    """Grouped MXFP8 matmul with the finalize-routing epilogue fused in: the second GEMM of an MoE expert MLP
+    (2048 tokens x top-8 = 16384 routed rows over 8 experts, K=2048, N=7168), every row weighted and added into its
+    token's fp32 output row.  Random codes and exponents: timing only."""
+    import torch
+    from catlass_b200 import capi
+    g, rows, n, k, batch = 8, 2048, 7168, 2048, 2048
+    m = g * rows
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(71)
+    a = torch.randint(0, 256, (m, k), dtype=torch.uint8, device=dev, generator=gen) & 0xBF
+    b = torch.randint(0, 256, (g, n, k), dtype=torch.uint8, device=dev, generator=gen) & 0xBF
+    sfa = torch.randint(120, 130, (m, k // 32), dtype=torch.uint8, device=dev, generator=gen)
+    sfb = torch.randint(120, 130, (g, n, k // 32), dtype=torch.uint8, device=dev, generator=gen)
+    gl = torch.full((g,), rows, dtype=torch.int64, device=dev)
+    logit = torch.rand(m, device=dev, generator=gen)
+    row_index = torch.randperm(m, device=dev, generator=gen) % batch     # every token meets top-8 rows
+    bias = torch.randn((g, n), device=dev, generator=gen).to(torch.bfloat16)
+    out = torch.empty((batch, n), dtype=torch.float32, device=dev)
+    ws = torch.empty(capi.mx_grouped_finalize_routing_workspace_size(m, n, k, g, batch), dtype=torch.uint8, device=dev)
+
+    def launch(i):
+        capi.mx_grouped_finalize_routing(a, b, gl, sfa, sfb, logit, row_index, out, m, n, k, g, batch, ws, bias=bias)
+
+    r = graph_region(launch, 1, seconds, sampler)
+    check_device_status()
+    flops = 2.0 * m * n * k
+    peaks = measured_peaks()
+    value = flops / (r["ms"] * 1e-3) / 1e12
+    burst = flops / (r["burst_ms"] * 1e-3) / 1e12
+    peak = peaks["bf16_tflops_sustained"] * 2.0
+    return {
+        "name": "mx_routing", "metric": "mxfp8_grouped_finalize_routing_tflops", "value": value, "unit": "TFLOP/s",
+        "ms_per_step": r["ms"], "burst_value": burst, "burst_ms_per_step": r["burst_ms"],
+        "regime": f"sustained: {r['launches_timed']} steps back to back, {r['region_s']:.2f} s",
+        "config": {"workload": f"mx_routing: grouped slice-M MXFP8, {g} experts x {rows} rows, K={k}, N={n}, rows "
+                               f"weighted and added into {batch} fp32 token rows (vector atomics in the epilogue), "
+                               "bf16 bias; step = output init + group planning + scale re-tiling + matmul",
+                   "l2": "B 117 MB streams; the 59 MB output stays in L2"},
+        "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
+                     "traffic": None,
+                     "peak_source": f"2 x {peaks['source']} cuBLAS bf16 sustained ({peaks['bf16_tflops_sustained']} TF/s)",
+                     "burst_frac": burst / (peaks["bf16_tflops"] * 2.0), "frac_of_nominal": value / 4500.0},
+        "gpu_launches": r["launches_timed"], "kernels_per_step": r["kernels_per_step"], "cuda_graph": r["cuda_graph"],
+        "clocks": r["clocks"],
+    }
+
+
 def run_secondary(name, sampler, seconds, args):
     if name == "mx_swiglu":
         return run_mx_swiglu(sampler, seconds)
+    if name == "mx_routing":
+        return run_mx_routing(sampler, seconds)
     if name in DENSE:
         return run_dense(name, sampler, seconds)
     if name == "w4a8":

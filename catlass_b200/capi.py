@@ -108,6 +108,17 @@ class MxQuantizeArgs(ctypes.Structure):
     ]
 
 
+class MxGroupedFinalizeRoutingArgs(ctypes.Structure):
+    _fields_ = [
+        ("m", _u32), ("n", _u32), ("k", _u32), ("group_count", _u32), ("layout_b", _u32),
+        ("group_list_type", _u32), ("group_list_kind", _u32), ("row_index_type", _u32), ("batch", _u32),
+        ("shared_rows", _u32), ("shared_offset", _u32), ("shared_weight", ctypes.c_float),
+        ("a", _vp), ("b", _vp), ("group_list", _vp), ("scale_a", _vp), ("scale_b", _vp), ("logit", _vp),
+        ("row_index", _vp), ("bias", _vp), ("shared_input", _vp), ("out", _vp),
+        ("workspace", _vp), ("workspace_bytes", _u64), ("block_num", _u32), ("flags", _u32),
+    ]
+
+
 MX_E4M3, MX_E2M1 = 0, 1
 MX_OUT_F32 = 1
 W4_PACKED_ALONG_K, W4_PACKED_ALONG_N = 0, 1
@@ -137,7 +148,8 @@ def load():
                          ("cb200_w4a8_matmul", W4A8MatmulArgs),
                          ("cb200_mx_matmul", MxMatmulArgs),
                          ("cb200_mx_grouped_matmul_slice_m", MxGroupedMatmulArgs),
-                         ("cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant", MxGroupedSwigluQuantArgs)):
+                         ("cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant", MxGroupedSwigluQuantArgs),
+                         ("cb200_mx_grouped_matmul_finalize_routing", MxGroupedFinalizeRoutingArgs)):
         getattr(lib, name + "_can_implement").argtypes = [ctypes.POINTER(args_t)]
         getattr(lib, name + "_can_implement").restype = ctypes.c_int
         getattr(lib, name + "_workspace_size").argtypes = [ctypes.POINTER(args_t)]
@@ -355,6 +367,31 @@ def mx_grouped_swiglu_quant(a, b, group_list, scale_a, scale_b, q, q_scale, m, n
         workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(), block_num=0)
     _check("cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant",
            load().cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(ctypes.byref(args), _stream(stream)))
+
+
+def mx_grouped_finalize_routing_workspace_size(m, n, k, group_count, batch, layout_b=COLUMN_MAJOR):
+    args = MxGroupedFinalizeRoutingArgs(m=m, n=n, k=k, group_count=group_count, layout_b=layout_b, batch=batch, a=256,
+                                        b=256, group_list=256, scale_a=256, scale_b=256, logit=256, row_index=256,
+                                        out=256)
+    return int(load().cb200_mx_grouped_matmul_finalize_routing_workspace_size(ctypes.byref(args)))
+
+
+def mx_grouped_finalize_routing(a, b, group_list, scale_a, scale_b, logit, row_index, out, m, n, k, group_count, batch,
+                                workspace, bias=None, shared_input=None, shared_rows=0, shared_offset=0,
+                                shared_weight=0.0, stream=None, layout_b=COLUMN_MAJOR,
+                                group_list_type=GROUP_LIST_INT64, group_list_kind=GROUP_LIST_SIZES,
+                                row_index_type=GROUP_LIST_INT64):
+    """Grouped slice-M MXFP8 matmul + finalize routing: out [batch][n] fp32 = shared contribution +
+    sum over rows p of logit[p] * (C[p] + bias[group]) at row row_index[p]."""
+    args = MxGroupedFinalizeRoutingArgs(
+        m=m, n=n, k=k, group_count=group_count, layout_b=layout_b, group_list_type=group_list_type,
+        group_list_kind=group_list_kind, row_index_type=row_index_type, batch=batch, shared_rows=shared_rows,
+        shared_offset=shared_offset, shared_weight=shared_weight, a=_p(a), b=_p(b), group_list=_p(group_list),
+        scale_a=_p(scale_a), scale_b=_p(scale_b), logit=_p(logit), row_index=_p(row_index), bias=_p(bias),
+        shared_input=_p(shared_input), out=_p(out), workspace=_p(workspace),
+        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(), block_num=0, flags=0)
+    _check("cb200_mx_grouped_matmul_finalize_routing",
+           load().cb200_mx_grouped_matmul_finalize_routing(ctypes.byref(args), _stream(stream)))
 
 
 def mx_quantize(x, q, scale, rows, k, fmt, x_type=DTYPE_F32, x_pitch=0, stream=None):

@@ -654,6 +654,14 @@ struct MxProblem {
     // SwiGLU + MX quantisation instead of the plain output: d = Q (E4M3 [m][n/2]), q_scale = E8M0 [m][n/64]
     bool swiglu_quant;
     void* q_scale;
+    // finalize routing instead of the plain output: d = out (fp32 [batch][n]), rows added with weights
+    bool routing;
+    const void* logit;
+    const void* row_index;
+    const void* bias;
+    const void* shared_input;
+    uint32_t row_index_i32, batch, shared_rows, shared_offset;
+    float shared_weight;
 };
 
 // How an MX call is served.  The kernel wants both operands with rows along K, padded to whole K stages
@@ -708,6 +716,18 @@ int plan_mx(const MxProblem& q, MxPlan* plan)
             q.q_scale == nullptr || !aligned16(q.d)) {
             return CB200_INVALID;
         }
+    } else if (q.routing) {
+        if (q.group_count == 0 || q.format != CB200_MX_E4M3 || q.flags != 0 || q.logit == nullptr ||
+            q.row_index == nullptr || q.batch == 0 || (reinterpret_cast<uintptr_t>(q.d) & 3u) != 0 ||
+            ((q.n & 3u) == 0 && !aligned16(q.d)) || (reinterpret_cast<uintptr_t>(q.logit) & 3u) != 0 ||
+            (reinterpret_cast<uintptr_t>(q.row_index) & (q.row_index_i32 ? 3u : 7u)) != 0 ||
+            (reinterpret_cast<uintptr_t>(q.bias) & 1u) != 0 || (reinterpret_cast<uintptr_t>(q.shared_input) & 1u) != 0) {
+            return CB200_INVALID;
+        }
+        if (q.shared_input != nullptr &&
+            (q.shared_offset > q.batch || q.shared_rows > q.batch - q.shared_offset)) {
+            return CB200_INVALID;
+        }
     } else {
         if ((reinterpret_cast<uintptr_t>(q.d) & (f32 ? 3u : 1u)) != 0) {
             return CB200_INVALID;
@@ -757,9 +777,10 @@ void ingest_mx_operand(const void* src, uint8_t* dst, uint32_t rows, uint32_t k,
     g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
-template <bool kFp4, bool kGrouped, bool kSwiglu = false>
+template <bool kFp4, bool kGrouped, int kEpi = kMxEpiPlain>
 int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cudaStream_t stream)
 {
+    constexpr bool kSwiglu = kEpi == kMxEpiSwiglu;
     uint8_t* ws = static_cast<uint8_t*>(q.workspace);
     int4* table = reinterpret_cast<int4*>(ws);
     uint32_t* num_row_tiles = reinterpret_cast<uint32_t*>(ws + static_cast<uint64_t>(plan.max_row_tiles) * 16u);
@@ -815,6 +836,17 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
     p.num_row_tiles = kGrouped ? num_row_tiles : nullptr;
     p.sfb_blocks_per_group = sfb_blocks;
     p.q_scale = static_cast<uint8_t*>(q.q_scale);
+    p.logit = static_cast<const float*>(q.logit);
+    p.row_index = q.row_index;
+    p.bias = static_cast<const __nv_bfloat16*>(q.bias);
+    p.row_index_i32 = q.row_index_i32;
+    p.batch = q.batch;
+    if constexpr (kEpi == kMxEpiRouting) {
+        finalize_routing_init_kernel<<<dev.sm_count * 4, 256, 0, stream>>>(
+            static_cast<float*>(q.d), q.batch, q.n, static_cast<const __nv_bfloat16*>(q.shared_input), q.shared_weight,
+            q.shared_offset, q.shared_input != nullptr ? q.shared_rows : 0u);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
 
     // the caller's scale arrays: ceil(k/32) blocks per row, held in an even number of columns; stored along the
     // operand's rows, or K-major when the operand itself is stored K-major
@@ -853,7 +885,7 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
             return rc;
         }
     }
-    auto kernel = mx_gemm_kernel<kFp4, kGrouped, kSwiglu>;
+    auto kernel = mx_gemm_kernel<kFp4, kGrouped, kEpi>;
     static PerDeviceOnce once;
     int devid = 0;
     int rc_dev = current_device(&devid);
@@ -956,6 +988,41 @@ MxProblem mx_swiglu_problem(const cb200_mx_grouped_swiglu_quant_args* a)
     return q;
 }
 
+MxProblem mx_routing_problem(const cb200_mx_grouped_finalize_routing_args* a)
+{
+    MxProblem q{};
+    q.m = a->m;
+    q.n = a->n;
+    q.k = a->k;
+    q.group_count = a->group_count;
+    q.format = CB200_MX_E4M3;
+    q.layout_a = CB200_ROW_MAJOR;
+    q.layout_b = a->layout_b;
+    q.group_list_type = a->group_list_type;
+    q.group_list_is_prefix_sum = a->group_list_kind == CB200_GROUP_LIST_PREFIX_SUMS ? 1u : 0u;
+    q.a = a->a;
+    q.b = a->b;
+    q.group_list = a->group_list;
+    q.scale_a = a->scale_a;
+    q.scale_b = a->scale_b;
+    q.d = a->out;
+    q.routing = true;
+    q.logit = a->logit;
+    q.row_index = a->row_index;
+    q.bias = a->bias;
+    q.shared_input = a->shared_input;
+    q.row_index_i32 = a->row_index_type == CB200_GROUP_LIST_INT32 ? 1u : 0u;
+    q.batch = a->batch;
+    q.shared_rows = a->shared_rows;
+    q.shared_offset = a->shared_offset;
+    q.shared_weight = a->shared_weight;
+    q.workspace = a->workspace;
+    q.workspace_bytes = a->workspace_bytes;
+    q.block_num = a->block_num;
+    q.flags = a->flags;
+    return q;
+}
+
 int run_mx(const MxProblem& q, void* stream_v)
 {
     MxPlan plan;
@@ -975,7 +1042,10 @@ int run_mx(const MxProblem& q, void* stream_v)
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const bool fp4 = q.format == CB200_MX_E2M1;
     if (q.swiglu_quant) {
-        return launch_mx<false, true, true>(q, plan, *dev, stream);
+        return launch_mx<false, true, kMxEpiSwiglu>(q, plan, *dev, stream);
+    }
+    if (q.routing) {
+        return launch_mx<false, true, kMxEpiRouting>(q, plan, *dev, stream);
     }
     if (q.group_count != 0) {
         return fp4 ? launch_mx<true, true>(q, plan, *dev, stream) : launch_mx<false, true>(q, plan, *dev, stream);
@@ -1055,6 +1125,32 @@ int cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(const cb200_mx_grouped_swigl
 {
     const int rc = cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_can_implement(args);
     return rc != CB200_SUCCESS ? rc : run_mx(mx_swiglu_problem(args), stream);
+}
+
+int cb200_mx_grouped_matmul_finalize_routing_can_implement(const cb200_mx_grouped_finalize_routing_args* args)
+{
+    MxPlan plan;
+    if (args == nullptr || args->group_count == 0 || args->group_list_kind > CB200_GROUP_LIST_PREFIX_SUMS ||
+        (args->row_index_type != CB200_GROUP_LIST_INT64 && args->row_index_type != CB200_GROUP_LIST_INT32)) {
+        return CB200_INVALID;
+    }
+    return plan_mx(mx_routing_problem(args), &plan);
+}
+
+uint64_t cb200_mx_grouped_matmul_finalize_routing_workspace_size(const cb200_mx_grouped_finalize_routing_args* args)
+{
+    MxPlan plan;
+    if (cb200_mx_grouped_matmul_finalize_routing_can_implement(args) != CB200_SUCCESS ||
+        plan_mx(mx_routing_problem(args), &plan) != CB200_SUCCESS) {
+        return 0;
+    }
+    return plan.total();
+}
+
+int cb200_mx_grouped_matmul_finalize_routing(const cb200_mx_grouped_finalize_routing_args* args, void* stream)
+{
+    const int rc = cb200_mx_grouped_matmul_finalize_routing_can_implement(args);
+    return rc != CB200_SUCCESS ? rc : run_mx(mx_routing_problem(args), stream);
 }
 
 int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args* args)

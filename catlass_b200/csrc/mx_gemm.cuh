@@ -30,6 +30,14 @@
 // and MX-quantises it along N, 32 columns per E8M0 scale, into E4M3 bytes Q [m][n/2] and scales [m][n/64].  A
 // thread owns one row of the accumulator, so a block of 32 columns is 32 registers of one thread: the block's
 // largest exponent needs no exchange between threads.
+//
+// kMxEpiRouting (grouped E4M3 problems): the reference's GroupedMxMatmulFinalizeRoutingNoDeterTla with
+// BlockEpilogueFinalizeRoutingNoDeter (include/catlass/gemm/kernel/grouped_mx_matmul_finalize_routing_no_deter_tla.hpp,
+// include/catlass/epilogue/block/block_epilogue_finalize_routing_no_deter.hpp): the second half of an MoE expert MLP.
+// Row p of C, plus its group's bias, is weighted with logit[p] and added into row row_index[p] of the fp32 output
+// with vector reductions (red.global.add.v4.f32) straight from the accumulator's registers; C is never written.
+// Rows of different tiles that meet in one output row are added in the order the tiles finish: like the reference's
+// kernel of that name the result is not bit-reproducible from run to run.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -61,9 +69,19 @@ struct MxParams {
     const int4* tile_table;           // [row tile] = (first row, one past the group's last row, group, 0)
     const uint32_t* num_row_tiles;    // number of table entries
     uint32_t sfb_blocks_per_group;    // 128-row scale blocks of B per group: 2 * ceil(n / 256)
-    // SwiGLU + MX quantisation epilogue (kSwiglu): d holds E4M3 bytes [m][n/2], q_scale E8M0 bytes [m][n/64]
+    // SwiGLU + MX quantisation epilogue (kMxEpiSwiglu): d holds E4M3 bytes [m][n/2], q_scale E8M0 bytes [m][n/64]
     uint8_t* q_scale;
+    // finalize-routing epilogue (kMxEpiRouting): d is the fp32 output [batch][n] that rows are added into
+    const float* logit;          // [m] weight of row p
+    const void* row_index;       // [m] output row of row p (int64, or int32 when row_index_i32)
+    const __nv_bfloat16* bias;   // [groups][n] or nullptr
+    uint32_t row_index_i32;
+    uint32_t batch;
 };
+
+constexpr int kMxEpiPlain = 0;    // D = C as bf16 or fp32
+constexpr int kMxEpiSwiglu = 1;   // Q, scales = MX quantisation of SwiGLU(C)
+constexpr int kMxEpiRouting = 2;  // out[row_index[p]] += logit[p] * (C[p] + bias[group])
 
 // One block: turns the group list of a grouped slice-M problem into the row-tile table the matmul and the scale
 // re-tiling walk.  Group g owns rows [start_g, start_g + size_g) of A and D, clamped to m; its row tiles are 128
@@ -207,6 +225,26 @@ __device__ __forceinline__ uint32_t mx_quant_block_bf16_e4m3(const uint32_t (&bi
     return scale;
 }
 
+// Prepares the output of the finalize-routing epilogue: zeros, plus weight * shared_input in rows
+// [offset, offset + shared_rows) (the shared expert's contribution, bf16 -> fp32 before the multiplication:
+// experimental/gmm/ascend950_fp8_mx_grouped_matmul_finalize_routing/gen_data_compare.py:744-751).
+__global__ void finalize_routing_init_kernel(float* __restrict__ out, uint32_t batch, uint32_t n,
+                                             const __nv_bfloat16* __restrict__ shared, float weight, uint32_t offset,
+                                             uint32_t shared_rows)
+{
+    const uint64_t total = static_cast<uint64_t>(batch) * n;
+    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t r = static_cast<uint32_t>(i / n);
+        const uint32_t c = static_cast<uint32_t>(i - static_cast<uint64_t>(r) * n);
+        float v = 0.0f;
+        if (shared != nullptr && r >= offset && r - offset < shared_rows) {
+            v = __fmul_rn(weight, __bfloat162float(shared[static_cast<size_t>(r - offset) * n + c]));
+        }
+        out[i] = v;
+    }
+}
+
 // Tile order: bands of `band_rows` tile rows, walked column by column inside a band.  The 148 tiles in flight at
 // any time then share the band's row panels of A (the host sizes a band to ~32 MB of A) and a few column panels
 // of B, which stay in L2; with a plain row-major order every wave streamed all of B from HBM again (measured at
@@ -224,7 +262,7 @@ __device__ __forceinline__ void mx_tile_coords(uint32_t idx, uint32_t m_tiles, u
 
 // kGrouped: slice-M groups (the reference's GroupedMxMatmulSliceMTla, example 55): row tiles come from the tile
 // table, every group has its own weight matrix (third coordinate of B's tensor map) and B scales.
-template <bool kFp4, bool kGrouped, bool kSwiglu = false>
+template <bool kFp4, bool kGrouped, int kEpi = kMxEpiPlain>
 __global__ void __launch_bounds__(kMxThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const MxParams p)
@@ -254,7 +292,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t m_tiles = kGrouped ? *p.num_row_tiles : (p.m + kBlockM - 1) / kBlockM;
-    static_assert(!kSwiglu || (kGrouped && !kFp4), "the SwiGLU + quantisation epilogue serves grouped E4M3 problems");
+    constexpr bool kSwiglu = kEpi == kMxEpiSwiglu;
+    static_assert(kEpi == kMxEpiPlain || (kGrouped && !kFp4), "the fused epilogues serve grouped E4M3 problems");
     // kSwiglu: a tile is 128 columns of the left half of C next to the same 128 columns of the right half
     const uint32_t n_tiles = kSwiglu ? (p.n / 2 + 127) / 128 : (p.n + kMxBlockN - 1) / kMxBlockN;
     const uint32_t total_tiles = m_tiles * n_tiles;
@@ -508,6 +547,66 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         *reinterpret_cast<uint4*>(qrow + col0) = make_uint4(q[0], q[1], q[2], q[3]);
                         *reinterpret_cast<uint4*>(qrow + col0 + 16) = make_uint4(q[4], q[5], q[6], q[7]);
                         srow[col0 / 32] = static_cast<uint8_t>(scale);
+                    }
+                }
+                if (++acc == kMxAccs) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+                continue;
+            }
+            if constexpr (kEpi == kMxEpiRouting) {
+                long long target = -1;
+                float weight = 0.0f;
+                if (row_ok) {
+                    target = p.row_index_i32 ? static_cast<long long>(static_cast<const int32_t*>(p.row_index)[row])
+                                             : static_cast<const long long*>(p.row_index)[row];
+                    weight = __ldg(p.logit + row);
+                }
+                const bool tgt_ok = target >= 0 && target < static_cast<long long>(p.batch);
+                float* orow = static_cast<float*>(p.d) + static_cast<size_t>(tgt_ok ? target : 0) * p.n;
+                const __nv_bfloat16* brow = p.bias != nullptr ? p.bias + static_cast<size_t>(group) * p.n : nullptr;
+                const uint32_t col_base = nt * kMxBlockN + half * 128;
+                const bool vec4 = (p.n & 3u) == 0;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(taddr + c * 32, r);
+                    tmem_ld_wait();
+                    if (c == 3) {  // the last read of the accumulator has completed
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive(bar_tmem_empty + acc * 8);
+                        }
+                    }
+                    const uint32_t col0 = col_base + c * 32;
+                    if (tgt_ok && col0 < p.n) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            float x[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const uint32_t col = col0 + v * 4 + e;
+                                float y = __uint_as_float(r[4 * v + e]);
+                                if (brow != nullptr && col < p.n) {
+                                    y = __fadd_rn(y, __bfloat162float(brow[col]));
+                                }
+                                x[e] = __fmul_rn(y, weight);
+                            }
+                            const uint32_t col = col0 + v * 4;
+                            if (vec4 && col + 4 <= p.n) {
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(orow + col), "f"(x[0]),
+                                             "f"(x[1]), "f"(x[2]), "f"(x[3])
+                                             : "memory");
+                            } else {
+                                for (int e = 0; e < 4; ++e) {
+                                    if (col + e < p.n) {
+                                        atomicAdd(orow + col + e, x[e]);
+                                    }
+                                }
+                            }
+                        }
                     }
                 }
                 if (++acc == kMxAccs) {

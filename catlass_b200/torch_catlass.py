@@ -271,6 +271,44 @@ def ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant(mat1, mat2, mx_scale
     return [q.view(torch.float8_e4m3fn), q_scale.view(e8m0) if e8m0 is not None else q_scale]
 
 
+def ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(mat1, mat2, mx_scale_a, mx_scale_b, group_list, logit,
+                                                              row_index, bias, shared_input, batch,
+                                                              data_parallel_size=1, shared_input_weight=0.0,
+                                                              shared_input_offset=0, group_list_type=0, trans_a=False,
+                                                              trans_b=False):
+    """Example 71, non-deterministic variant (tests/optest/torch_catlass/ops/
+    ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter.py): grouped MXFP8 matmul whose rows are weighted
+    with `logit` and added into rows `row_index` of an fp32 (batch, N) output, with an optional bf16 bias per group
+    and an optional shared-expert input added at `shared_input_offset`.  group_list_type 0 = prefix sums, 1 = sizes.
+    Empty tensors stand for "no bias" / "no shared input", as in the reference."""
+    _require_cuda(mat1, mat2, mx_scale_a, mx_scale_b, group_list, logit, row_index)
+    if trans_a:
+        raise ValueError("slice-M groups cut A by rows: A is (M, K)")
+    mat1, mat2, group_list = mat1.contiguous(), mat2.contiguous(), group_list.contiguous()
+    m, k = tuple(mat1.shape)
+    g = group_list.numel()
+    n = mat2.shape[1] if trans_b else mat2.shape[2]
+    lb = capi.COLUMN_MAJOR if trans_b else capi.ROW_MAJOR
+    has_bias = bias is not None and bias.numel() != 0
+    has_shared = shared_input is not None and shared_input.numel() != 0
+    bsdp = batch // max(int(data_parallel_size), 1)
+    out = torch.empty((batch, n), dtype=torch.float32, device=mat1.device)
+    ws = torch.empty(max(capi.mx_grouped_finalize_routing_workspace_size(m, n, k, g, batch, lb), 1), dtype=torch.uint8,
+                     device=mat1.device)
+    row_index = row_index.contiguous()
+    capi.mx_grouped_finalize_routing(
+        mat1.view(torch.uint8), mat2.view(torch.uint8), group_list, mx_scale_a.contiguous().view(torch.uint8),
+        mx_scale_b.contiguous().view(torch.uint8), logit.contiguous().float(), row_index, out, m, n, k, g, batch, ws,
+        bias=bias.contiguous().to(torch.bfloat16) if has_bias else None,
+        shared_input=shared_input.contiguous().to(torch.bfloat16) if has_shared else None,
+        shared_rows=bsdp if has_shared else 0, shared_offset=int(shared_input_offset),
+        shared_weight=float(shared_input_weight), layout_b=lb,
+        group_list_type=capi.GROUP_LIST_INT32 if group_list.dtype == torch.int32 else capi.GROUP_LIST_INT64,
+        group_list_kind=capi.GROUP_LIST_PREFIX_SUMS if group_list_type == 0 else capi.GROUP_LIST_SIZES,
+        row_index_type=capi.GROUP_LIST_INT32 if row_index.dtype == torch.int32 else capi.GROUP_LIST_INT64)
+    return out
+
+
 def ascend950_fp8_mx_matmul_aswt(mat1, mat2, mx_scale_a, mx_scale_b, transA=False, transB=True):
     """Example 53: float8_e4m3fn operands, float8_e8m0fnu block scales, fp32 output."""
     return _mx(mat1, mat2, mx_scale_a, mx_scale_b, transA, transB, capi.MX_E4M3)

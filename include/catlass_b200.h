@@ -444,6 +444,59 @@ CB200_API int cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(const cb200_mx_gro
                                                               void *stream);
 
 /*
+ * Grouped (slice-M) MXFP8 matmul with the MoE finalize-routing epilogue fused in: the second half of an expert
+ * MLP, which adds every routed row, weighted, into its token's output row.  Replaces
+ * Gemm::Kernel::GroupedMxMatmulFinalizeRoutingNoDeterTla::Arguments with
+ * Epilogue::BlockEpilogueFinalizeRoutingNoDeter
+ * (include/catlass/gemm/kernel/grouped_mx_matmul_finalize_routing_no_deter_tla.hpp,
+ * experimental/gmm/ascend950_fp8_mx_grouped_matmul_finalize_routing/fp8_mx_grouped_matmul_finalize_routing_no_deter.cpp;
+ * optest parameters tests/optest/include/catlass_kernel_jit.h:489-495), golden gen_data_compare.py:718-757 of
+ * that example:
+ *     out                          = 0                                        [batch][n] fp32
+ *     out[offset : offset+rows]   += shared_weight * float(shared_input)      (when shared_input != NULL)
+ *     out[row_index[p]]           += logit[p] * (C[p] + float(bias[group of p]))     for every row p of a group
+ * with C = (scale_a * A) @ (scale_b * B[g]) in fp32, never written.  Rows whose row_index is outside [0, batch)
+ * are dropped.  The additions into an output row happen in the order tiles finish (vector atomics): as in the
+ * reference's kernel of this name, results are not bit-reproducible from run to run; the reference's second,
+ * deterministic scheduler variant is not provided.  The call overwrites all of out.
+ *   logit [m] fp32; row_index [m] int64 or int32 (row_index_type: CB200_GROUP_LIST_INT64 / _INT32);
+ *   bias [group_count][n] bf16 or NULL; shared_input [shared_rows][n] bf16 or NULL.
+ */
+typedef struct cb200_mx_grouped_finalize_routing_args {
+    uint32_t m, n, k;
+    uint32_t group_count;         /* 1 .. 1024 */
+    uint32_t layout_b;            /* CB200_COLUMN_MAJOR ([G][n][k]) or CB200_ROW_MAJOR ([G][k][n]) */
+    uint32_t group_list_type;     /* CB200_GROUP_LIST_INT64 / _INT32 */
+    uint32_t group_list_kind;     /* CB200_GROUP_LIST_SIZES / CB200_GROUP_LIST_PREFIX_SUMS */
+    uint32_t row_index_type;      /* CB200_GROUP_LIST_INT64 / _INT32 */
+    uint32_t batch;               /* rows of out */
+    uint32_t shared_rows;         /* rows of shared_input (the reference's bsdp) */
+    uint32_t shared_offset;       /* first row of out the shared input is added to */
+    float shared_weight;
+    const void *a;
+    const void *b;
+    const void *group_list;
+    const void *scale_a;
+    const void *scale_b;
+    const void *logit;
+    const void *row_index;
+    const void *bias;
+    const void *shared_input;
+    void *out;
+    void *workspace;
+    uint64_t workspace_bytes;
+    uint32_t block_num;
+    uint32_t flags;               /* 0 */
+} cb200_mx_grouped_finalize_routing_args;
+
+CB200_API int cb200_mx_grouped_matmul_finalize_routing_can_implement(
+    const cb200_mx_grouped_finalize_routing_args *args);
+CB200_API uint64_t cb200_mx_grouped_matmul_finalize_routing_workspace_size(
+    const cb200_mx_grouped_finalize_routing_args *args);
+CB200_API int cb200_mx_grouped_matmul_finalize_routing(const cb200_mx_grouped_finalize_routing_args *args,
+                                                       void *stream);
+
+/*
  * cb200_mx_matmul_static: the MX matmul above for callers that cannot give it a workspace.
  * (No counterpart in the reference: every reference kernel takes its workspace from the caller or allocates
  * it per call, examples/shared_lib/src/common/common.hpp:36-46.)

@@ -70,6 +70,7 @@ def test_struct_layout_matches_the_header(lib):
         ("cb200_mx_matmul_args", capi.MxMatmulArgs),
         ("cb200_mx_grouped_matmul_args", capi.MxGroupedMatmulArgs),
         ("cb200_mx_grouped_swiglu_quant_args", capi.MxGroupedSwigluQuantArgs),
+        ("cb200_mx_grouped_finalize_routing_args", capi.MxGroupedFinalizeRoutingArgs),
         ("cb200_mx_quantize_args", capi.MxQuantizeArgs),
     ]
     lines = []

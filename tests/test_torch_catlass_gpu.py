@@ -231,6 +231,38 @@ def test_ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant(torch_catlass):
     assert err.max().item() <= 2 * 2.0 ** -4, err.max().item()
 
 
+def test_ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(torch_catlass):
+    """The reference op's signature (tests/optest/torch_catlass/ops/
+    ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter.py) on the example's own run
+    (4 groups, m = n = k = 128, prefix-sum list, batch 16, dp 2) with bias and shared input switched on."""
+    g, m, n, k, batch, dp = 4, 128, 128, 128, 16, 2
+    sizes = [12, 25, 38, 53]
+    a8, a_scale, a_deq = _quantize_axis_last(torch.randn(m, k))
+    a_scale = a_scale.reshape(m, a_scale.shape[1] // 2, 2).contiguous()
+    b_list, s_list, c_parts, offset = [], [], [], 0
+    bias = torch.randn(g, n).to(torch.bfloat16)
+    for i, size in enumerate(sizes):
+        bt8, bt_scale, bt_deq = _quantize_axis_last(torch.randn(k, n).t().contiguous())
+        b_list.append(bt8.t().contiguous())                                                  # [k][n]
+        s_list.append(bt_scale.reshape(n, bt_scale.shape[1] // 2, 2).permute(1, 0, 2).contiguous())
+        c_parts.append(a_deq[offset:offset + size] @ bt_deq.t() + bias[i].float().unsqueeze(0))
+        offset += size
+    c = torch.cat(c_parts, dim=0)
+    logit = torch.randn(m)
+    row_index = torch.arange(m, dtype=torch.int64) % batch
+    shared = torch.randn(batch // dp, n).to(torch.bfloat16)
+    expected = torch.zeros(batch, n)
+    expected[3:3 + batch // dp] += 0.5 * shared.float()
+    expected.index_add_(0, row_index, logit.unsqueeze(1) * c)
+    group_list = torch.tensor(sizes, dtype=torch.int64).cumsum(0)
+    result = torch_catlass.ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(
+        a8.cuda(), torch.stack(b_list).cuda(), a_scale.cuda(), torch.stack(s_list).cuda(), group_list.cuda(),
+        logit.cuda(), row_index.cuda(), bias.cuda(), shared.cuda(), batch, data_parallel_size=dp,
+        shared_input_weight=0.5, shared_input_offset=3, group_list_type=0, trans_a=False, trans_b=False)
+    assert result.shape == (batch, n) and result.dtype == torch.float32
+    assert torch.allclose(result.cpu(), expected, rtol=1e-2, atol=1e-2), (result.cpu() - expected).abs().max().item()
+
+
 def test_grouped_matmul_slice_k_per_token_dequant(torch_catlass):
     """tests/optest/tests/test_11_grouped_matmul_slice_k_per_token_dequant.py:11-40"""
     g, m, n, k_total = 4, 128, 128, 256
