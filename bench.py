@@ -716,7 +716,7 @@ def run_mx(name, sampler, seconds):
                                "step = scale re-tiling + matmul",
                    "l2": "operands exceed L2" if not fp4 else "operands 64 MB + 134 MB output per pass"},
         "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TFLOP/s", "frac": value / peak,
-                     "traffic": kernel_facts.traffic("mx_gemm_kernel/" + name),
+                     "traffic": kernel_facts.traffic("mx_pair_kernel/" + name),
                      "peak_source": f"{factor:.0f} x {peaks['source']} cuBLAS bf16 sustained "
                                     f"({peaks['bf16_tflops_sustained']} TF/s)",
                      "burst_frac": burst / (peaks["bf16_tflops"] * factor),

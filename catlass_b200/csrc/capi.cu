@@ -13,6 +13,7 @@
 #include "w8a8_smallm.cuh"
 #include "w4a8_gemm.cuh"
 #include "mx_gemm.cuh"
+#include "mx_gemm_pair.cuh"
 #include "ingest.cuh"
 #include "mx_quantize.cuh"
 
@@ -883,6 +884,76 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
         int rc = encode_tmap_u8(&tmap_b, b_ptr, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != CB200_SUCCESS) {
             return rc;
+        }
+    }
+    if constexpr (!kGrouped && kEpi == kMxEpiPlain) {
+        // Dense problems with at least two waves of 256 x 256 tiles run on CTA pairs (half the B traffic per SM).
+        const uint64_t pair_tiles = static_cast<uint64_t>((q.m + 255u) / 256u) * ((q.n + 255u) / 256u);
+        const uint32_t pairs = static_cast<uint32_t>(dev.sm_count) / 2u;
+        bool use_pair = q.m >= 512u && pair_tiles >= 2ull * pairs && (q.block_num == 0 || q.block_num >= 2u * pairs);
+        {
+            const long v = dev_knob("CB200_MX_PAIR", -1);
+            if (v == 0) {
+                use_pair = false;
+            } else if (v == 1) {
+                use_pair = pairs != 0;
+            }
+        }
+        if (use_pair) {
+            CUtensorMap tmap_bh, tmap_sfa, tmap_sfb;
+            {
+                const uint64_t dims[2] = {row_bytes, q.n};
+                const uint64_t strides[1] = {row_bytes};
+                const uint32_t box[2] = {kBlockKBytes, kMxBlockN / 2};  // a CTA loads half of the tile's columns
+                int rc = encode_tmap_u8(&tmap_bh, b_ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+                if (rc != CB200_SUCCESS) {
+                    return rc;
+                }
+            }
+            const uint32_t words = kFp4 ? 2u : 1u;
+            {
+                // packed A scales [row block][kq_total][512 bytes] as rows of 256 bytes
+                const uint64_t dims[2] = {256, 2ull * p.kq_total * plan.max_row_tiles};
+                const uint64_t strides[1] = {256};
+                const uint32_t box[2] = {256, 2u * words};
+                int rc = encode_tmap_u8(&tmap_sfa, sfa, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+                if (rc != CB200_SUCCESS) {
+                    return rc;
+                }
+            }
+            {
+                // packed B scales [column block][kq_total][512 bytes]: a box takes the same K words of two blocks
+                const uint64_t dims[3] = {256, 2ull * p.kq_total, sfb_blocks};
+                const uint64_t strides[2] = {256, 512ull * p.kq_total};
+                const uint32_t box[3] = {256, 2u * words, 2};
+                int rc = encode_tmap_u8(&tmap_sfb, sfb, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+                if (rc != CB200_SUCCESS) {
+                    return rc;
+                }
+            }
+            auto pair_kernel = mx_pair_kernel<kFp4>;
+            static PerDeviceOnce once_pair;
+            int devid_pair = 0;
+            int rc_pair = current_device(&devid_pair);
+            if (rc_pair != CB200_SUCCESS) {
+                return rc_pair;
+            }
+            rc_pair = once_pair.run(devid_pair, [&]() -> int {
+                CB200_CUDA_TRY(cudaFuncSetAttribute(pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    MxPairSmem::kTotalBytes));
+                return CB200_SUCCESS;
+            });
+            if (rc_pair != CB200_SUCCESS) {
+                return rc_pair;
+            }
+            const uint32_t launch_pairs = pair_tiles < pairs ? static_cast<uint32_t>(pair_tiles) : pairs;
+            MxParams pp = p;
+            pp.band_rows = p.band_rows / 2u < 2u ? 2u : p.band_rows / 2u;  // tile rows are 256 rows here: same bytes of A per band
+            pair_kernel<<<2 * launch_pairs, kMxPairThreads, MxPairSmem::kTotalBytes, stream>>>(tmap_a, tmap_bh, tmap_sfa,
+                                                                                           tmap_sfb, pp);
+            CB200_CUDA_TRY(cudaGetLastError());
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return CB200_SUCCESS;
         }
     }
     auto kernel = mx_gemm_kernel<kFp4, kGrouped, kEpi>;

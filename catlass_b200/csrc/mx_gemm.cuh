@@ -395,14 +395,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * kMxBlockN;
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
-                    ok = mbar_wait(bar_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
-                    if (!ok) {
-                        break;
-                    }
-                    tcgen05_fence_after();
                     const uint32_t sa = ring + stage * S::kStageBytes;
                     const uint32_t sb = sa + S::kABytes;
-                    // the stage's scale blocks are copied into TMEM slot `stage` by the copier warp
+                    // The stage's scale blocks are copied into TMEM slot `stage` by the copier threads, which wait
+                    // for the stage's "full" barrier first and whose commit arrives (release) when the copies are
+                    // done: acquiring "sf_full" therefore orders this thread after the operand tiles' arrival too,
+                    // and one probe per stage less on the thread whose instruction issue sets the kernel's pace.
                     ok = mbar_wait(bar_sf_full + stage * 8, phase, s_abort, p.status, kDevTimeoutMma);
                     if (!ok) {
                         break;

@@ -97,6 +97,17 @@ def test_mx_bf16_output_off_the_fast_path(cuda, fmt):
     _mx_case(cuda, 300, 264, 520, fmt, True, False, out_f32=False, seed=9)
 
 
+@pytest.mark.parametrize("fmt,out_f32,m,n,k", [
+    (O.MX_E4M3, False, 1100, 7700, 384), (O.MX_E2M1, True, 1100, 7700, 512), (O.MX_E4M3, True, 530, 19200, 160),
+])
+def test_mx_on_cta_pairs(cuda, fmt, out_f32, m, n, k):
+    """Dense shapes with at least two waves of 256 x 256 tiles run on CTA pairs: ragged last tile row (the second
+    CTA of a pair past the end of A), ragged last tile column, both output types, a ragged K through the ingestion
+    pre-pass."""
+    assert ((m + 255) // 256) * ((n + 255) // 256) >= 148
+    _mx_case(cuda, m, n, k, fmt, False, True, out_f32=out_f32, seed=m + n)
+
+
 def test_mx_static_scratch_entry_takes_the_same_layouts(cuda):
     _mx_case(cuda, 200, 136, 330, O.MX_E4M3, True, False, out_f32=True, seed=11, static=True)
     _mx_case(cuda, 130, 520, 190, O.MX_E2M1, False, False, out_f32=False, seed=12, static=True)
