@@ -29,10 +29,19 @@ DRAM_TRAFFIC = {
         "bytes": 36.8e6,
         "facts": {"w4a8_gemm.cuh": {"kW4Channels": 128, "kW4Tokens": 128}},
     },
-    # MX 8192^3 (E4M3, E2M1)
+    # MX 8192^3 (E4M3, E2M1) on the single-CTA kernel (CB200_MX_PAIR=0 in developer builds)
     "mx_gemm_kernel/mxfp8": {
         "bytes": 342.4e6,
         "facts": {"mx_gemm.cuh": {"kMxBlockN": 256, "kMxStages": 4}},
+    },
+    # MX 8192^3 on CTA pairs (the default for large dense problems)
+    "mx_pair_kernel/mxfp8": {
+        "bytes": 444.3e6,
+        "facts": {"mx_gemm_pair.cuh": {"kMxPairStages": 6}, "mx_gemm.cuh": {"kMxBlockN": 256}},
+    },
+    "mx_pair_kernel/mxfp4": {
+        "bytes": 211.4e6,
+        "facts": {"mx_gemm_pair.cuh": {"kMxPairStages": 6}, "mx_gemm.cuh": {"kMxBlockN": 256}},
     },
     "mx_gemm_kernel/mxfp4": {
         "bytes": 184.4e6,
