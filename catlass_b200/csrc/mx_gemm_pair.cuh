@@ -16,11 +16,15 @@
 // forwarded) with one thread requesting, forwarding and copying: that thread's ~10 instructions per stage set
 // the pace at 0.9-1.5 PFLOP/s.  Now every single-thread role issues at most five instructions per stage:
 //   warp 0   operand producer (both CTAs): wait empty, expect (leader), A, B half
-//   warp 11  scale producer (both CTAs): wait empty, A scales, B scales (one 3-D box for both column blocks)
-//   warps 6, 12  scale copiers (leader): wait full, smem -> TMEM copies for the pair (tcgen05.cp.cta_group::2: each
+//   warp 2   scale producer (both CTAs): wait empty, A scales, B scales (one 3-D box for both column blocks)
+//   warps 3, 4  scale copiers (leader): wait full, smem -> TMEM copies for the pair (tcgen05.cp.cta_group::2: each
 //            CTA copies from its own shared memory into its own TMEM), commit to "sf_full" (two arrivals)
 //   warp 1   MMA issuer (leader): wait sf_full, four MMAs, one multicast commit that frees the stage in both CTAs
-//   warps 2-5, 7-10  epilogue (both CTAs), as in the single-CTA kernel
+//   warps 5-20  epilogue (both CTAs): sixteen warps, four per TMEM lane quarter with 64 columns each.  There is one
+//            accumulator (256 columns + the scale slots fill TMEM), so between two tiles the tensor core waits for
+//            the epilogue to pull the accumulator out: ~2.5 us with eight warps reading four 32-column pieces one
+//            after the other, against 8.8 us (fp4) or 17.7 us (fp8) of MMAs per tile.  A warp here issues its two
+//            reads together, waits once and hands its share back before it rounds or stores anything.
 #pragma once
 
 #include "mx_gemm.cuh"
@@ -29,7 +33,8 @@
 namespace cb200 {
 
 constexpr int kMxPairStages = 6;
-constexpr int kMxPairThreads = 416;  // 13 warps, see above
+constexpr int kMxPairThreads = 672;  // 21 warps, see above
+constexpr int kMxPairEpiWarps = 16;  // per CTA: four per TMEM lane quarter, 64 columns each
 
 struct MxPairSmem {
     static constexpr int kABytes = kBlockM * kBlockKBytes;          // 16 KB: this CTA's 128 rows of A
@@ -124,7 +129,7 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(bar_sf_full + s * 8, 2);  // one arrival per copier thread
         }
         mbar_init(bar_tmem_full, 1);
-        mbar_init(bar_tmem_empty, 2 * 8);  // eight epilogue warps in each CTA
+        mbar_init(bar_tmem_empty, 2 * kMxPairEpiWarps);  // the epilogue warps of both CTAs
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
@@ -173,7 +178,7 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp == 11) {
+    } else if (warp == 2) {
         // ---------------------------------------------------------------- scale producer (both CTAs)
         // (waits on the same "empty" barrier as the operand producer; the bytes are expected by the leader's
         // operand producer, in whatever order the loads and the expectation reach the barrier)
@@ -252,13 +257,13 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp == 6 || warp == 12) {
+    } else if (warp == 3 || warp == 4) {
         // ---------------------------------------------------------------- scale copiers (leader CTA only)
         // TMEM slot `stage` is free when the stage's "full" barrier fires: the MMAs that read its previous contents
         // completed before the producers were allowed to refill the stage.
-        // fp8 (three copies per stage): warp 6 copies A's block and B's first, warp 12 B's second;
-        // fp4 (six): warp 6 takes scale word 0 of all three blocks, warp 12 word 1.
-        const uint32_t me = warp == 6 ? 0u : 1u;
+        // fp8 (three copies per stage): warp 3 copies A's block and B's first, warp 4 B's second;
+        // fp4 (six): warp 3 takes scale word 0 of all three blocks, warp 4 word 1.
+        const uint32_t me = warp == 3 ? 0u : 1u;
         if (lane == 0 && cta_rank == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
@@ -301,9 +306,9 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         __syncwarp();
     } else {
-        // ---------------------------------------------------------------- epilogue: eight warps per CTA
-        const uint32_t quad = warp & 3;
-        const uint32_t half = warp >= 7 ? 1u : 0u;
+        // ---------------------------------------------------------------- epilogue: sixteen warps per CTA
+        const uint32_t quad = warp & 3;           // TMEM lane quarter this warp may read
+        const uint32_t part = (warp - 5) >> 2;    // which 64 columns of the tile's 256
         const bool vec_ok = (p.n & 7u) == 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -318,83 +323,72 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tcgen05_fence_after();
             const uint32_t row = (2 * mt + cta_rank) * kBlockM + quad * 32 + lane;
             const bool row_ok = row < p.m;
-            const uint32_t taddr = tmem_base + half * 128 + ((quad * 32u) << 16);
-            if (p.out_f32) {
-                // fp32 output: the accumulator goes out as it is, 32 columns at a time, then the hand-back
-                float* frow = static_cast<float*>(p.d) + static_cast<size_t>(row_ok ? row : 0) * p.n;
-                const uint32_t col_base = nt * kMxBlockN + half * 128;
-                const bool vec4 = (p.n & 3u) == 0;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, r);
-                    tmem_ld_wait();
-                    const uint32_t col0 = col_base + c * 32;
-                    if (row_ok && col0 < p.n) {
-                        if (vec4 && col0 + 32 <= p.n) {
-#pragma unroll
-                            for (int v = 0; v < 8; ++v) {
-                                *reinterpret_cast<uint4*>(frow + col0 + v * 4) =
-                                    make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j) {
-                                if (col0 + j < p.n) {
-                                    frow[col0 + j] = __uint_as_float(r[j]);
-                                }
-                            }
-                        }
-                    }
-                }
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive_cluster(bar_tmem_empty, 0);
-                }
-                acc_phase ^= 1;
-                continue;
-            }
-            __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + static_cast<size_t>(row_ok ? row : 0) * p.n;
-            // All four 32-column pieces are pulled out of TMEM and rounded to bf16 first (64 registers), the accumulator
-            // goes back to the MMA issuer (remote arrive from the peer CTA), the stores follow.  (Streaming piece by
-            // piece, stores between the reads, delayed the hand-back: MXFP4, whose tiles take half as long, lost 9 %.)
-            uint32_t packed[64];  // bf16 pairs: columns 2i, 2i+1 of this warp's 128
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const __nv_bfloat162 h =
-                        __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
-                    packed[c * 16 + e] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-            }
+            const uint32_t taddr = tmem_base + part * 64 + ((quad * 32u) << 16);
+            uint32_t r[2][32];
+            tmem_ld_32x32b_x32(taddr, r[0]);
+            tmem_ld_32x32b_x32(taddr + 32, r[1]);
+            tmem_ld_wait();
+            // this warp's share of the accumulator is in registers: hand it back (remote arrive from the peer CTA)
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive_cluster(bar_tmem_empty, 0);
             }
             acc_phase ^= 1;
-            const uint32_t col_base = nt * kMxBlockN + half * 128;
-            if (row_ok && col_base < p.n) {
-                if (vec_ok && col_base + 128 <= p.n) {
+            const uint32_t col_base = nt * kMxBlockN + part * 64;
+            if (!row_ok || col_base >= p.n) {
+                continue;
+            }
+            if (p.out_f32) {
+                float* frow = static_cast<float*>(p.d) + static_cast<size_t>(row) * p.n;
+                if ((p.n & 3u) == 0 && col_base + 64 <= p.n) {
 #pragma unroll
-                    for (int v = 0; v < 16; ++v) {
-                        *reinterpret_cast<uint4*>(drow + col_base + v * 8) =
-                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            *reinterpret_cast<uint4*>(frow + col_base + c * 32 + v * 4) =
+                                make_uint4(r[c][4 * v], r[c][4 * v + 1], r[c][4 * v + 2], r[c][4 * v + 3]);
+                        }
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&packed[i]);
-                        if (col_base + 2 * i < p.n) {
-                            drow[col_base + 2 * i] = h.x;
+                    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col_base + c * 32 + j < p.n) {
+                                frow[col_base + c * 32 + j] = __uint_as_float(r[c][j]);
+                            }
                         }
-                        if (col_base + 2 * i + 1 < p.n) {
-                            drow[col_base + 2 * i + 1] = h.y;
-                        }
+                    }
+                }
+                continue;
+            }
+            __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + static_cast<size_t>(row) * p.n;
+            uint32_t packed[32];  // bf16 pairs: columns 2i, 2i+1 of this warp's 64
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const __nv_bfloat162 h =
+                        __floats2bfloat162_rn(__uint_as_float(r[c][2 * e]), __uint_as_float(r[c][2 * e + 1]));
+                    packed[c * 16 + e] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+            }
+            if (vec_ok && col_base + 64 <= p.n) {
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    *reinterpret_cast<uint4*>(drow + col_base + v * 8) =
+                        make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&packed[i]);
+                    if (col_base + 2 * i < p.n) {
+                        drow[col_base + 2 * i] = h.x;
+                    }
+                    if (col_base + 2 * i + 1 < p.n) {
+                        drow[col_base + 2 * i + 1] = h.y;
                     }
                 }
             }
