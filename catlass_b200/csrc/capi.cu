@@ -979,7 +979,7 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
     if (tiles < grid) {
         grid = static_cast<uint32_t>(tiles);
     }
-    kernel<<<grid, kMxThreads, MxSmem::kTotalBytes, stream>>>(tmap_a, tmap_b, p);
+    kernel<<<grid, mx_threads(kEpi), MxSmem::kTotalBytes, stream>>>(tmap_a, tmap_b, p);
     CB200_CUDA_TRY(cudaGetLastError());
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return CB200_SUCCESS;

@@ -51,7 +51,10 @@ namespace cb200 {
 constexpr int kMxBlockN = 256;  // one tcgen05.mma of 128 x 256 runs about as long as issuing it costs its thread
 constexpr int kMxAccs = 1;      // one accumulator: 256 columns + the scale columns leave no room for a second
 constexpr int kMxStages = 4;
-constexpr int kMxThreads = 384;  // warps: 0 TMA producer, 1 MMA issuer, 2..5 and 7..10 epilogue, 6 and 11 scale copiers
+// warps: 0 TMA producer, 1 MMA issuer, 2 and 3 scale copiers, then the epilogue warps: sixteen (four per TMEM lane
+// quarter, 64 columns each), or eight with 128 columns each for the SwiGLU epilogue, whose threads need the registers
+__host__ __device__ constexpr int mx_epilogue_warps(int epi) { return epi == 1 ? 8 : 16; }
+__host__ __device__ constexpr int mx_threads(int epi) { return (4 + mx_epilogue_warps(epi)) * 32; }
 
 struct MxParams {
     uint32_t m, n, k;
@@ -263,7 +266,7 @@ __device__ __forceinline__ void mx_tile_coords(uint32_t idx, uint32_t m_tiles, u
 // kGrouped: slice-M groups (the reference's GroupedMxMatmulSliceMTla, example 55): row tiles come from the tile
 // table, every group has its own weight matrix (third coordinate of B's tensor map) and B scales.
 template <bool kFp4, bool kGrouped, int kEpi = kMxEpiPlain>
-__global__ void __launch_bounds__(kMxThreads, 1)
+__global__ void __launch_bounds__(mx_threads(kEpi), 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const MxParams p)
 {
@@ -321,7 +324,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         for (int a = 0; a < kMxAccs; ++a) {
             mbar_init(bar_tmem_full + a * 8, 1);
-            mbar_init(bar_tmem_empty + a * 8, 8);  // one arrival per epilogue warp
+            mbar_init(bar_tmem_empty + a * 8, mx_epilogue_warps(kEpi));  // one arrival per epilogue warp
         }
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
@@ -437,14 +440,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         }
         __syncwarp();
-    } else if (warp == 6 || warp == 11) {
+    } else if (warp == 2 || warp == 3) {
         // ---- scale copier: smem -> TMEM, one thread.  Issuing a tcgen05 instruction costs its thread ~70 ns
         // whatever it does; three copies on top of four MMAs and a commit per stage made the MMA thread the
         // limit of the kernel, so the copies have a thread of their own.  TMEM slot `stage` is free when the
         // stage's "full" barrier fires: the MMAs that read its previous contents completed before the producer
         // was allowed to refill the stage.
-        // (fp4 has two scale words per stage, six copies: warp 6 takes word 0, warp 11 word 1)
-        const uint32_t my_word = warp == 6 ? 0u : 1u;
+        // (fp4 has two scale words per stage, six copies: warp 2 takes word 0, warp 3 word 1)
+        const uint32_t my_word = warp == 2 ? 0u : 1u;
         if (lane == 0 && my_word < kWords) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
@@ -481,12 +484,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         __syncwarp();
     } else {
-        // ---- epilogue: eight warps, two per TMEM lane quarter, 128 columns each.  There is room for one
-        // accumulator only, so a warp first pulls its 128 columns out of TMEM and rounds them to bf16 into
-        // registers (64 per thread), hands the accumulator back, and stores afterwards: the next tile's MMAs wait
-        // for four TMEM reads, not for the stores.
+        // ---- epilogue.  There is room for one accumulator only (256 columns + the scale slots fill TMEM), so between
+        // two tiles the tensor core waits for the epilogue to pull the accumulator out: with eight warps reading
+        // four 32-column pieces one after the other that took ~2.5 us, against 8.8 us of MMAs per fp8 tile at K = 8192.
+        // Sixteen warps (four per lane quarter, 64 columns each) issue their two reads together, wait once and hand
+        // their share back before they round or store anything.  (The SwiGLU epilogue keeps eight warps: its
+        // threads hold four pieces, 128 registers, and hand back before their arithmetic as well.)
         const uint32_t quad = warp & 3;
-        const uint32_t half = warp >= 7 ? 1u : 0u;
+        const uint32_t part = (warp - 4) >> 2;   // 0..3: which 64 columns; SwiGLU: 0..1 = `half`
+        const uint32_t half = part;
         const bool vec_ok = (p.n & 7u) == 0;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
@@ -503,7 +509,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             row_tile(mt, row0, row_end, group);
             const uint32_t row = static_cast<uint32_t>(row0) + quad * 32 + lane;
             const bool row_ok = static_cast<int32_t>(row) < row_end;
-            const uint32_t taddr = tmem_base + acc * kMxBlockN + half * 128 + ((quad * 32u) << 16);
             if constexpr (kSwiglu) {
                 // This warp: output columns [half * 64, half * 64 + 64) of the tile's 128, as two blocks of 32; "act"
                 // sits in accumulator columns 0..127, "gate" in 128..255.
@@ -553,119 +558,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 continue;
             }
-            if constexpr (kEpi == kMxEpiRouting) {
-                long long target = -1;
-                float weight = 0.0f;
-                if (row_ok) {
-                    target = p.row_index_i32 ? static_cast<long long>(static_cast<const int32_t*>(p.row_index)[row])
-                                             : static_cast<const long long*>(p.row_index)[row];
-                    weight = __ldg(p.logit + row);
-                }
-                const bool tgt_ok = target >= 0 && target < static_cast<long long>(p.batch);
-                float* orow = static_cast<float*>(p.d) + static_cast<size_t>(tgt_ok ? target : 0) * p.n;
-                const __nv_bfloat16* brow = p.bias != nullptr ? p.bias + static_cast<size_t>(group) * p.n : nullptr;
-                const uint32_t col_base = nt * kMxBlockN + half * 128;
-                const bool vec4 = (p.n & 3u) == 0;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, r);
-                    tmem_ld_wait();
-                    if (c == 3) {  // the last read of the accumulator has completed
-                        tcgen05_fence_before();
-                        __syncwarp();
-                        if (lane == 0) {
-                            mbar_arrive(bar_tmem_empty + acc * 8);
-                        }
-                    }
-                    const uint32_t col0 = col_base + c * 32;
-                    if (tgt_ok && col0 < p.n) {
-#pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            float x[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const uint32_t col = col0 + v * 4 + e;
-                                float y = __uint_as_float(r[4 * v + e]);
-                                if (brow != nullptr && col < p.n) {
-                                    y = __fadd_rn(y, __bfloat162float(brow[col]));
-                                }
-                                x[e] = __fmul_rn(y, weight);
-                            }
-                            const uint32_t col = col0 + v * 4;
-                            if (vec4 && col + 4 <= p.n) {
-                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(orow + col), "f"(x[0]),
-                                             "f"(x[1]), "f"(x[2]), "f"(x[3])
-                                             : "memory");
-                            } else {
-                                for (int e = 0; e < 4; ++e) {
-                                    if (col + e < p.n) {
-                                        atomicAdd(orow + col + e, x[e]);
-                                    }
-                                }
-                            }
-                        }
-                    }
-                }
-                if (++acc == kMxAccs) {
-                    acc = 0;
-                    acc_phase ^= 1;
-                }
-                continue;
-            }
-            if (p.out_f32) {
-                // fp32 output (what the reference's MX kernels write): the accumulator goes out as it is, 32 columns
-                // at a time, before the accumulator is handed back (nothing to round, nothing to keep in registers)
-                float* frow = static_cast<float*>(p.d) + static_cast<size_t>(row_ok ? row : 0) * p.n;
-                const uint32_t col_base = nt * kMxBlockN + half * 128;
-                const bool vec4 = (p.n & 3u) == 0;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, r);
-                    tmem_ld_wait();
-                    const uint32_t col0 = col_base + c * 32;
-                    if (row_ok && col0 < p.n) {
-                        if (vec4 && col0 + 32 <= p.n) {
-#pragma unroll
-                            for (int v = 0; v < 8; ++v) {
-                                *reinterpret_cast<uint4*>(frow + col0 + v * 4) =
-                                    make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j) {
-                                if (col0 + j < p.n) {
-                                    frow[col0 + j] = __uint_as_float(r[j]);
-                                }
-                            }
-                        }
-                    }
-                }
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bar_tmem_empty + acc * 8);
-                }
-                if (++acc == kMxAccs) {
-                    acc = 0;
-                    acc_phase ^= 1;
-                }
-                continue;
-            }
-            __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + static_cast<size_t>(row_ok ? row : 0) * p.n;
-            uint32_t packed[64];  // bf16 pairs: columns 2i, 2i+1 of this warp's 128
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(taddr + c * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const __nv_bfloat162 h =
-                        __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
-                    packed[c * 16 + e] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-            }
+            // ---- the other epilogues: this warp's 64 columns come out of TMEM at once, then the hand-back
+            const uint32_t taddr = tmem_base + acc * kMxBlockN + part * 64 + ((quad * 32u) << 16);
+            uint32_t r[2][32];
+            tmem_ld_32x32b_x32(taddr, r[0]);
+            tmem_ld_32x32b_x32(taddr + 32, r[1]);
+            tmem_ld_wait();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -675,24 +573,107 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 acc = 0;
                 acc_phase ^= 1;
             }
-            const uint32_t col_base = nt * kMxBlockN + half * 128;
-            if (row_ok && col_base < p.n) {
-                if (vec_ok && col_base + 128 <= p.n) {
+            const uint32_t col_base = nt * kMxBlockN + part * 64;
+            if (col_base >= p.n) {
+                continue;
+            }
+            if constexpr (kEpi == kMxEpiRouting) {
+                long long target = -1;
+                float weight = 0.0f;
+                if (row_ok) {
+                    target = p.row_index_i32 ? static_cast<long long>(static_cast<const int32_t*>(p.row_index)[row])
+                                             : static_cast<const long long*>(p.row_index)[row];
+                    weight = __ldg(p.logit + row);
+                }
+                if (target < 0 || target >= static_cast<long long>(p.batch)) {
+                    continue;
+                }
+                float* orow = static_cast<float*>(p.d) + static_cast<size_t>(target) * p.n;
+                const __nv_bfloat16* brow = p.bias != nullptr ? p.bias + static_cast<size_t>(group) * p.n : nullptr;
+                const bool vec4 = (p.n & 3u) == 0;
 #pragma unroll
-                    for (int v = 0; v < 16; ++v) {
-                        *reinterpret_cast<uint4*>(drow + col_base + v * 8) =
-                            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        float x[4];
+                        const uint32_t col = col_base + c * 32 + v * 4;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float y = __uint_as_float(r[c][4 * v + e]);
+                            if (brow != nullptr && col + e < p.n) {
+                                y = __fadd_rn(y, __bfloat162float(brow[col + e]));
+                            }
+                            x[e] = __fmul_rn(y, weight);
+                        }
+                        if (vec4 && col + 4 <= p.n) {
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(orow + col), "f"(x[0]),
+                                         "f"(x[1]), "f"(x[2]), "f"(x[3])
+                                         : "memory");
+                        } else {
+                            for (int e = 0; e < 4; ++e) {
+                                if (col + e < p.n) {
+                                    atomicAdd(orow + col + e, x[e]);
+                                }
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
+            if (!row_ok) {
+                continue;
+            }
+            if (p.out_f32) {
+                // fp32 output (what the reference's MX kernels write): the accumulator goes out as it is
+                float* frow = static_cast<float*>(p.d) + static_cast<size_t>(row) * p.n;
+                if ((p.n & 3u) == 0 && col_base + 64 <= p.n) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            *reinterpret_cast<uint4*>(frow + col_base + c * 32 + v * 4) =
+                                make_uint4(r[c][4 * v], r[c][4 * v + 1], r[c][4 * v + 2], r[c][4 * v + 3]);
+                        }
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&packed[i]);
-                        if (col_base + 2 * i < p.n) {
-                            drow[col_base + 2 * i] = h.x;
+                    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col_base + c * 32 + j < p.n) {
+                                frow[col_base + c * 32 + j] = __uint_as_float(r[c][j]);
+                            }
                         }
-                        if (col_base + 2 * i + 1 < p.n) {
-                            drow[col_base + 2 * i + 1] = h.y;
-                        }
+                    }
+                }
+                continue;
+            }
+            __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.d) + static_cast<size_t>(row) * p.n;
+            uint32_t packed[32];  // bf16 pairs: columns 2i, 2i+1 of this warp's 64
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const __nv_bfloat162 h =
+                        __floats2bfloat162_rn(__uint_as_float(r[c][2 * e]), __uint_as_float(r[c][2 * e + 1]));
+                    packed[c * 16 + e] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+            }
+            if (vec_ok && col_base + 64 <= p.n) {
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    *reinterpret_cast<uint4*>(drow + col_base + v * 8) =
+                        make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&packed[i]);
+                    if (col_base + 2 * i < p.n) {
+                        drow[col_base + 2 * i] = h.x;
+                    }
+                    if (col_base + 2 * i + 1 < p.n) {
+                        drow[col_base + 2 * i + 1] = h.y;
                     }
                 }
             }
