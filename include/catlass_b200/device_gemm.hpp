@@ -250,6 +250,196 @@ struct MxMatmul {
     static int Run(CArgs const* c, void* stream) { return cb200_mx_matmul(c, stream); }
 };
 
+/// Grouped slice-K W8A8 with per-token dequant: GroupedMatmulSliceKPerTokenDequant::Arguments of the reference
+/// (include/catlass/gemm/kernel/grouped_matmul_slice_k_per_token_dequant.hpp:125-134: problemShape, problemCount,
+/// ptrGroupList, ptrA [k][m], ptrB [k][n], ptrScale [G][n], ptrPerTokenScale [G][m], ptrD [G][m][n]).
+template <class ElementGroupList = int64_t>
+struct GroupedMatmulSliceKPerTokenDequant {
+    struct Arguments {
+        GemmCoord problemShape;
+        uint32_t problemCount = 0;
+        uint8_t* ptrGroupList = nullptr;
+        uint8_t* ptrA = nullptr;
+        uint8_t* ptrB = nullptr;
+        uint8_t* ptrScale = nullptr;
+        uint8_t* ptrPerTokenScale = nullptr;
+        uint8_t* ptrD = nullptr;
+        uint32_t scaleType = CB200_DTYPE_F32;
+        uint32_t dType = CB200_DTYPE_BF16;
+    };
+    using CArgs = cb200_grouped_quant_matmul_slice_k_args;
+    static CArgs ToUnderlyingArguments(Arguments const& a, void* workspace, size_t workspaceBytes)
+    {
+        CArgs c{};
+        c.m = a.problemShape.m();
+        c.n = a.problemShape.n();
+        c.k = a.problemShape.k();
+        c.group_count = a.problemCount;
+        c.group_list_type = sizeof(ElementGroupList) == 8 ? CB200_GROUP_LIST_INT64 : CB200_GROUP_LIST_INT32;
+        c.scale_type = a.scaleType;
+        c.a = a.ptrA;
+        c.b = a.ptrB;
+        c.group_list = a.ptrGroupList;
+        c.scale = a.ptrScale;
+        c.per_token_scale = a.ptrPerTokenScale;
+        c.d = a.ptrD;
+        c.workspace = workspace;
+        c.workspace_bytes = workspaceBytes;
+        c.d_type = a.dType;
+        return c;
+    }
+    static int CanImplement(CArgs const* c) { return cb200_grouped_quant_matmul_slice_k_can_implement(c); }
+    static uint64_t WorkspaceSize(CArgs const* c) { return cb200_grouped_quant_matmul_slice_k_workspace_size(c); }
+    static int Run(CArgs const* c, void* stream) { return cb200_grouped_quant_matmul_slice_k(c, stream); }
+};
+
+/// Grouped slice-M MX matmul: GroupedMxMatmulSliceMTla::Arguments of the reference (example 55:
+/// examples/55_ascend950_mx_grouped_matmul_slice_m/mx_grouped_matmul_slice_m.cpp:325-357).  The group list holds
+/// the groups' row counts, as there.  LayoutB: ColumnMajor = [G][n][k] (the example's "trans" case), RowMajor = [G][k][n].
+template <bool kFp4, class LayoutB = layout::ColumnMajor, class ElementGroupList = int64_t>
+struct GroupedMxMatmulSliceM {
+    struct Arguments {
+        GemmCoord problemShape;
+        uint32_t problemCount = 0;
+        uint8_t* ptrGroupList = nullptr;
+        uint8_t* ptrA = nullptr;
+        uint8_t* ptrB = nullptr;
+        uint8_t* ptrMxScaleA = nullptr;
+        uint8_t* ptrMxScaleB = nullptr;
+        uint8_t* ptrC = nullptr;       // fp32 [m][n], what the reference's kernel writes
+    };
+    using CArgs = cb200_mx_grouped_matmul_args;
+    static CArgs ToUnderlyingArguments(Arguments const& a, void* workspace, size_t workspaceBytes)
+    {
+        CArgs c{};
+        c.m = a.problemShape.m();
+        c.n = a.problemShape.n();
+        c.k = a.problemShape.k();
+        c.group_count = a.problemCount;
+        c.format = kFp4 ? CB200_MX_E2M1 : CB200_MX_E4M3;
+        c.layout_b = detail::LayoutTag<LayoutB>::value;
+        c.group_list_type = sizeof(ElementGroupList) == 8 ? CB200_GROUP_LIST_INT64 : CB200_GROUP_LIST_INT32;
+        c.group_list_kind = CB200_GROUP_LIST_SIZES;
+        c.a = a.ptrA;
+        c.b = a.ptrB;
+        c.group_list = a.ptrGroupList;
+        c.scale_a = a.ptrMxScaleA;
+        c.scale_b = a.ptrMxScaleB;
+        c.d = a.ptrC;
+        c.workspace = workspace;
+        c.workspace_bytes = workspaceBytes;
+        c.flags = CB200_MX_OUT_F32;
+        return c;
+    }
+    static int CanImplement(CArgs const* c) { return cb200_mx_grouped_matmul_slice_m_can_implement(c); }
+    static uint64_t WorkspaceSize(CArgs const* c) { return cb200_mx_grouped_matmul_slice_m_workspace_size(c); }
+    static int Run(CArgs const* c, void* stream) { return cb200_mx_grouped_matmul_slice_m(c, stream); }
+};
+
+/// Grouped MXFP8 matmul + SwiGLU + MX quantisation: GroupedMxMatmulSliceMSwigluMxQuantTla::Arguments of the reference
+/// (include/catlass/gemm/kernel/grouped_mx_matmul_slice_m_swiglu_mx_quant_tla.hpp:72-118: problemShape, problemCount,
+/// ptrGroupList, ptrA, ptrB, ptrMxScaleA, ptrMxScaleB, ptrQ, ptrQScale).
+template <class LayoutB = layout::ColumnMajor, class ElementGroupList = int64_t>
+struct GroupedMxMatmulSliceMSwigluMxQuant {
+    struct Arguments {
+        GemmCoord problemShape;
+        uint32_t problemCount = 0;
+        uint8_t* ptrGroupList = nullptr;
+        uint8_t* ptrA = nullptr;
+        uint8_t* ptrB = nullptr;
+        uint8_t* ptrMxScaleA = nullptr;
+        uint8_t* ptrMxScaleB = nullptr;
+        uint8_t* ptrQ = nullptr;       // E4M3 [m][n/2]
+        uint8_t* ptrQScale = nullptr;  // E8M0 [m][n/64]
+    };
+    using CArgs = cb200_mx_grouped_swiglu_quant_args;
+    static CArgs ToUnderlyingArguments(Arguments const& a, void* workspace, size_t workspaceBytes)
+    {
+        CArgs c{};
+        c.m = a.problemShape.m();
+        c.n = a.problemShape.n();
+        c.k = a.problemShape.k();
+        c.group_count = a.problemCount;
+        c.layout_b = detail::LayoutTag<LayoutB>::value;
+        c.group_list_type = sizeof(ElementGroupList) == 8 ? CB200_GROUP_LIST_INT64 : CB200_GROUP_LIST_INT32;
+        c.group_list_kind = CB200_GROUP_LIST_SIZES;
+        c.a = a.ptrA;
+        c.b = a.ptrB;
+        c.group_list = a.ptrGroupList;
+        c.scale_a = a.ptrMxScaleA;
+        c.scale_b = a.ptrMxScaleB;
+        c.q = a.ptrQ;
+        c.q_scale = a.ptrQScale;
+        c.workspace = workspace;
+        c.workspace_bytes = workspaceBytes;
+        return c;
+    }
+    static int CanImplement(CArgs const* c) { return cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_can_implement(c); }
+    static uint64_t WorkspaceSize(CArgs const* c)
+    {
+        return cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant_workspace_size(c);
+    }
+    static int Run(CArgs const* c, void* stream) { return cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(c, stream); }
+};
+
+/// Grouped MXFP8 matmul + finalize routing (the reference's GroupedMxMatmulFinalizeRoutingNoDeterTla; parameters as
+/// GroupedMxFinalizeRoutingParams, tests/optest/include/catlass_kernel_jit.h:489-495): out [batch][n] fp32.
+template <class LayoutB = layout::ColumnMajor, class ElementGroupList = int64_t>
+struct GroupedMxMatmulFinalizeRouting {
+    struct Arguments {
+        GemmCoord problemShape;
+        uint32_t problemCount = 0;
+        uint32_t groupListType = 0;    // 0: prefix sums, 1: row counts (the reference's convention)
+        uint8_t* ptrGroupList = nullptr;
+        uint8_t* ptrA = nullptr;
+        uint8_t* ptrB = nullptr;
+        uint8_t* ptrMxScaleA = nullptr;
+        uint8_t* ptrMxScaleB = nullptr;
+        uint8_t* ptrLogit = nullptr;        // fp32 [m]
+        uint8_t* ptrRowIndex = nullptr;     // int64 [m]
+        uint8_t* ptrBias = nullptr;         // bf16 [problemCount][n] or null
+        uint8_t* ptrSharedInput = nullptr;  // bf16 [bsdp][n] or null
+        uint8_t* ptrOut = nullptr;          // fp32 [batch][n]
+        uint32_t batch = 0;
+        uint32_t bsdp = 0;
+        float sharedInputWeight = 0.0f;
+        uint32_t sharedInputOffset = 0;
+    };
+    using CArgs = cb200_mx_grouped_finalize_routing_args;
+    static CArgs ToUnderlyingArguments(Arguments const& a, void* workspace, size_t workspaceBytes)
+    {
+        CArgs c{};
+        c.m = a.problemShape.m();
+        c.n = a.problemShape.n();
+        c.k = a.problemShape.k();
+        c.group_count = a.problemCount;
+        c.layout_b = detail::LayoutTag<LayoutB>::value;
+        c.group_list_type = sizeof(ElementGroupList) == 8 ? CB200_GROUP_LIST_INT64 : CB200_GROUP_LIST_INT32;
+        c.group_list_kind = a.groupListType == 0 ? CB200_GROUP_LIST_PREFIX_SUMS : CB200_GROUP_LIST_SIZES;
+        c.row_index_type = CB200_GROUP_LIST_INT64;
+        c.batch = a.batch;
+        c.shared_rows = a.bsdp;
+        c.shared_offset = a.sharedInputOffset;
+        c.shared_weight = a.sharedInputWeight;
+        c.a = a.ptrA;
+        c.b = a.ptrB;
+        c.group_list = a.ptrGroupList;
+        c.scale_a = a.ptrMxScaleA;
+        c.scale_b = a.ptrMxScaleB;
+        c.logit = a.ptrLogit;
+        c.row_index = a.ptrRowIndex;
+        c.bias = a.ptrBias;
+        c.shared_input = a.ptrSharedInput;
+        c.out = a.ptrOut;
+        c.workspace = workspace;
+        c.workspace_bytes = workspaceBytes;
+        return c;
+    }
+    static int CanImplement(CArgs const* c) { return cb200_mx_grouped_matmul_finalize_routing_can_implement(c); }
+    static uint64_t WorkspaceSize(CArgs const* c) { return cb200_mx_grouped_matmul_finalize_routing_workspace_size(c); }
+    static int Run(CArgs const* c, void* stream) { return cb200_mx_grouped_matmul_finalize_routing(c, stream); }
+};
+
 }  // namespace Kernel
 
 namespace Device {

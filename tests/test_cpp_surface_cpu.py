@@ -71,3 +71,43 @@ def test_example_programs_compile_against_the_surface():
     # without arguments they print the reference's usage line and exit non-zero, touching no GPU
     r = subprocess.run([exes[0]], capture_output=True, text=True)
     assert r.returncode == 64 and "usage: 12_quant_matmul m n k" in r.stderr
+
+
+DESCRIPTORS = r"""
+#include <cstdio>
+#include "catlass_b200/catlass_kernel.hpp"
+using namespace Catlass;
+template <class K> int probe(typename K::Arguments const& a) {
+    // null operands: every descriptor must map onto its C-ABI struct and be refused by the argument check
+    return Gemm::Device::DeviceGemm<K>::CanImplement(a) == Status::kSuccess ? 1 : 0;
+}
+int main() {
+    int accepted = 0;
+    { using K = Gemm::Kernel::GroupedMatmulSliceKPerTokenDequant<>; K::Arguments a{}; a.problemShape = GemmCoord{128, 128, 256}; a.problemCount = 2; accepted += probe<K>(a); }
+    { using K = Gemm::Kernel::GroupedMxMatmulSliceM<false>; K::Arguments a{}; a.problemShape = GemmCoord{128, 128, 256}; a.problemCount = 2; accepted += probe<K>(a); }
+    { using K = Gemm::Kernel::GroupedMxMatmulSliceM<true, layout::RowMajor, int32_t>; K::Arguments a{}; a.problemShape = GemmCoord{128, 128, 256}; a.problemCount = 2; accepted += probe<K>(a); }
+    { using K = Gemm::Kernel::GroupedMxMatmulSliceMSwigluMxQuant<>; K::Arguments a{}; a.problemShape = GemmCoord{128, 512, 256}; a.problemCount = 2; accepted += probe<K>(a); }
+    { using K = Gemm::Kernel::GroupedMxMatmulFinalizeRouting<>; K::Arguments a{}; a.problemShape = GemmCoord{128, 512, 256}; a.problemCount = 2; a.batch = 16; accepted += probe<K>(a); }
+    std::printf("%d\n", accepted);
+    return accepted;
+}
+"""
+
+
+def test_grouped_and_fused_descriptors_map_onto_the_c_abi():
+    """The C++ descriptors of the grouped siblings and the fused MoE epilogues compile, link against the library and
+    reach its argument checks (which refuse the null operands without touching a device)."""
+    import sys
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    from catlass_b200 import build as libbuild
+    lib = libbuild.build()
+    libdir = os.path.dirname(lib)
+    with tempfile.TemporaryDirectory() as td:
+        src = os.path.join(td, "d.cpp")
+        open(src, "w").write(DESCRIPTORS)
+        exe = os.path.join(td, "d")
+        subprocess.run(["nvcc", "-std=c++17", "-x", "cu", "-I", os.path.join(ROOT, "include"), src, "-o", exe, "-L", libdir,
+                        "-lcatlass_b200", "-Xlinker", f"-rpath={libdir}"], check=True)
+        r = subprocess.run([exe], capture_output=True, text=True)
+        assert r.returncode == 0 and r.stdout.strip() == "0", (r.returncode, r.stdout, r.stderr)
