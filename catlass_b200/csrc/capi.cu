@@ -744,7 +744,9 @@ int plan_mx(const MxProblem& q, MxPlan* plan)
     plan->ingest_a = q.layout_a != CB200_ROW_MAJOR || plan->k_padded != q.k || !aligned16(q.a);
     plan->ingest_b = q.layout_b != CB200_COLUMN_MAJOR || plan->k_padded != q.k || !aligned16(q.b);
     plan->b_matrices = q.group_count == 0 ? 1u : q.group_count;
-    plan->max_row_tiles = (q.m + 127u) / 128u + q.group_count;
+    // 128-row blocks at most: ceil(m/128), plus one partial 128-row tile per group, or (CTA pairs: 256-row tiles of two
+    // blocks each) up to two blocks per group
+    plan->max_row_tiles = (q.m + 127u) / 128u + 2u * q.group_count;
     const uint64_t kq = plan->k_padded / 128u;
     plan->table_bytes = q.group_count == 0 ? 0 : align256(static_cast<uint64_t>(plan->max_row_tiles) * 16u + 16u);
     // scale blocks of 128 rows; B's are padded to whole 256-column tiles
@@ -782,6 +784,24 @@ template <bool kFp4, bool kGrouped, int kEpi = kMxEpiPlain>
 int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cudaStream_t stream)
 {
     constexpr bool kSwiglu = kEpi == kMxEpiSwiglu;
+    // Large problems run on CTA pairs (256 x 256 tiles, half the B traffic per SM): dense ones with at least two waves
+    // of pair tiles, grouped ones (plain and SwiGLU epilogues) whose groups average at least 512 rows.
+    constexpr bool kPairCapable = kEpi == kMxEpiPlain || kSwiglu;
+    const uint32_t pairs = static_cast<uint32_t>(dev.sm_count) / 2u;
+    const uint32_t pair_n_tiles = kSwiglu ? q.n / 256u : (q.n + 255u) / 256u;
+    bool use_pair = false;
+    if constexpr (kPairCapable) {
+        const uint64_t pair_tiles = static_cast<uint64_t>((q.m + 255u) / 256u) * pair_n_tiles;
+        use_pair = q.m >= 512u && pair_tiles >= 2ull * pairs && (q.block_num == 0 || q.block_num >= 2u * pairs) &&
+                   (!kGrouped || q.m / q.group_count >= 512u);
+        const long v = dev_knob("CB200_MX_PAIR", -1);
+        if (v == 0) {
+            use_pair = false;
+        } else if (v == 1) {
+            use_pair = pairs != 0;
+        }
+    }
+    const uint32_t tile_rows = use_pair ? 256u : 128u;
     uint8_t* ws = static_cast<uint8_t*>(q.workspace);
     int4* table = reinterpret_cast<int4*>(ws);
     uint32_t* num_row_tiles = reinterpret_cast<uint32_t*>(ws + static_cast<uint64_t>(plan.max_row_tiles) * 16u);
@@ -805,7 +825,8 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
     }
     if constexpr (kGrouped) {
         mx_group_plan_kernel<<<1, 1024, 0, stream>>>(q.group_list, q.group_list_type == CB200_GROUP_LIST_INT32 ? 1u : 0u,
-                                                     q.group_list_is_prefix_sum, q.group_count, q.m, table, num_row_tiles);
+                                                     q.group_list_is_prefix_sum, q.group_count, q.m, table, num_row_tiles,
+                                                     tile_rows);
         g_launches.fetch_add(1, std::memory_order_relaxed);
     }
     const uint32_t row_bytes = plan.row_bytes;
@@ -855,7 +876,7 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
     const uint32_t ks_pitch = (kblocks + 1u) & ~1u;
     mx_pack_scales_kernel<<<dim3(dev.sm_count * 2, 1, 1), 256, 0, stream>>>(
         static_cast<const uint8_t*>(q.scale_a), sfa, q.m, kblocks, ks_pitch, p.kq_total, plan.max_row_tiles,
-        q.layout_a == CB200_COLUMN_MAJOR ? 1u : 0u, 0, 0, p.tile_table, p.num_row_tiles);
+        q.layout_a == CB200_COLUMN_MAJOR ? 1u : 0u, 0, 0, p.tile_table, p.num_row_tiles, tile_rows);
     {
         const uint32_t gx = plan.b_matrices > 8u ? static_cast<uint32_t>(dev.sm_count) / 4u : dev.sm_count * 2u;
         mx_pack_scales_kernel<<<dim3(gx, plan.b_matrices, 1), 256, 0, stream>>>(
@@ -886,26 +907,14 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
             return rc;
         }
     }
-    if constexpr (!kGrouped && kEpi == kMxEpiPlain) {
-        // Dense problems with at least two waves of 256 x 256 tiles run on CTA pairs (half the B traffic per SM).
-        const uint64_t pair_tiles = static_cast<uint64_t>((q.m + 255u) / 256u) * ((q.n + 255u) / 256u);
-        const uint32_t pairs = static_cast<uint32_t>(dev.sm_count) / 2u;
-        bool use_pair = q.m >= 512u && pair_tiles >= 2ull * pairs && (q.block_num == 0 || q.block_num >= 2u * pairs);
-        {
-            const long v = dev_knob("CB200_MX_PAIR", -1);
-            if (v == 0) {
-                use_pair = false;
-            } else if (v == 1) {
-                use_pair = pairs != 0;
-            }
-        }
+    if constexpr (kPairCapable) {
         if (use_pair) {
             CUtensorMap tmap_bh, tmap_sfa, tmap_sfb;
             {
-                const uint64_t dims[2] = {row_bytes, q.n};
-                const uint64_t strides[1] = {row_bytes};
-                const uint32_t box[2] = {kBlockKBytes, kMxBlockN / 2};  // a CTA loads half of the tile's columns
-                int rc = encode_tmap_u8(&tmap_bh, b_ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+                const uint64_t dims[3] = {row_bytes, q.n, plan.b_matrices};
+                const uint64_t strides[2] = {row_bytes, static_cast<uint64_t>(q.n) * row_bytes};
+                const uint32_t box[3] = {kBlockKBytes, kMxBlockN / 2, 1};  // a CTA loads half of the tile's columns
+                int rc = encode_tmap_u8(&tmap_bh, b_ptr, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
                 if (rc != CB200_SUCCESS) {
                     return rc;
                 }
@@ -922,16 +931,16 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
                 }
             }
             {
-                // packed B scales [column block][kq_total][512 bytes]: a box takes the same K words of two blocks
-                const uint64_t dims[3] = {256, 2ull * p.kq_total, sfb_blocks};
+                // packed B scales [column block][kq_total][512 bytes], all weight matrices one after the other
+                const uint64_t dims[3] = {256, 2ull * p.kq_total, static_cast<uint64_t>(sfb_blocks) * plan.b_matrices};
                 const uint64_t strides[2] = {256, 512ull * p.kq_total};
-                const uint32_t box[3] = {256, 2u * words, 2};
+                const uint32_t box[3] = {256, 2u * words, 1};
                 int rc = encode_tmap_u8(&tmap_sfb, sfb, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
                 if (rc != CB200_SUCCESS) {
                     return rc;
                 }
             }
-            auto pair_kernel = mx_pair_kernel<kFp4>;
+            auto pair_kernel = mx_pair_kernel<kFp4, kGrouped, kEpi>;
             static PerDeviceOnce once_pair;
             int devid_pair = 0;
             int rc_pair = current_device(&devid_pair);
@@ -946,7 +955,9 @@ int launch_mx(const MxProblem& q, const MxPlan& plan, const DeviceState& dev, cu
             if (rc_pair != CB200_SUCCESS) {
                 return rc_pair;
             }
-            const uint32_t launch_pairs = pair_tiles < pairs ? static_cast<uint32_t>(pair_tiles) : pairs;
+            const uint64_t pair_tiles_max =
+                static_cast<uint64_t>((q.m + 255u) / 256u + (kGrouped ? q.group_count : 0u)) * pair_n_tiles;
+            const uint32_t launch_pairs = pair_tiles_max < pairs ? static_cast<uint32_t>(pair_tiles_max) : pairs;
             MxParams pp = p;
             pp.band_rows = p.band_rows / 2u < 2u ? 2u : p.band_rows / 2u;  // tile rows are 256 rows here: same bytes of A per band
             pair_kernel<<<2 * launch_pairs, kMxPairThreads, MxPairSmem::kTotalBytes, stream>>>(tmap_a, tmap_bh, tmap_sfa,

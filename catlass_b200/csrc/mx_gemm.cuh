@@ -90,8 +90,9 @@ constexpr int kMxEpiRouting = 2;  // out[row_index[p]] += logit[p] * (C[p] + bia
 // re-tiling walk.  Group g owns rows [start_g, start_g + size_g) of A and D, clamped to m; its row tiles are 128
 // rows each (the last one partial); empty groups add nothing.  The list holds sizes (the reference's example 55:
 // examples/55_ascend950_mx_grouped_matmul_slice_m/mx_grouped_matmul_slice_m.cpp:265, non-cumsum) or prefix sums.
+// tile_rows: 128, or 256 for the CTA-pair kernel (a pair's tile is 256 rows of one group).
 __global__ void mx_group_plan_kernel(const void* group_list, uint32_t is_i32, uint32_t is_prefix_sum, uint32_t groups,
-                                     uint32_t m, int4* table, uint32_t* num_row_tiles)
+                                     uint32_t m, int4* table, uint32_t* num_row_tiles, uint32_t tile_rows)
 {
     __shared__ uint32_t s_begin[kMaxGroups + 1];
     __shared__ uint32_t s_tile[kMaxGroups + 1];
@@ -105,7 +106,7 @@ __global__ void mx_group_plan_kernel(const void* group_list, uint32_t is_i32, ui
             end = end < prev ? prev : (end > static_cast<long long>(m) ? static_cast<long long>(m) : end);
             s_begin[g] = static_cast<uint32_t>(prev);
             s_tile[g] = tiles;
-            tiles += static_cast<uint32_t>((end - prev + kBlockM - 1) / kBlockM);
+            tiles += static_cast<uint32_t>((end - prev + tile_rows - 1) / tile_rows);
             prev = end;
         }
         s_begin[groups] = static_cast<uint32_t>(prev);
@@ -116,7 +117,7 @@ __global__ void mx_group_plan_kernel(const void* group_list, uint32_t is_i32, ui
     for (uint32_t g = threadIdx.x; g < groups; g += blockDim.x) {
         const uint32_t begin = s_begin[g], end = s_begin[g + 1];
         for (uint32_t t = s_tile[g]; t < s_tile[g + 1]; ++t) {
-            table[t] = make_int4(static_cast<int>(begin + (t - s_tile[g]) * kBlockM), static_cast<int>(end),
+            table[t] = make_int4(static_cast<int>(begin + (t - s_tile[g]) * tile_rows), static_cast<int>(end),
                                  static_cast<int>(g), 0);
         }
     }
@@ -146,12 +147,14 @@ struct MxSmem {
 __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, uint32_t rows,
                                       uint32_t kblocks_valid, uint32_t ks_pitch, uint32_t kq_total,
                                       uint32_t row_blocks, uint32_t k_major, uint64_t in_batch, uint64_t out_batch,
-                                      const int4* tile_table, const uint32_t* num_row_tiles)
+                                      const int4* tile_table, const uint32_t* num_row_tiles,
+                                      uint32_t table_tile_rows = 128)
 {
     in += blockIdx.y * in_batch;
     out += blockIdx.y * out_batch;
-    if (tile_table != nullptr) {
-        row_blocks = *num_row_tiles < row_blocks ? *num_row_tiles : row_blocks;
+    if (tile_table != nullptr) {  // (a 256-row table tile fills two consecutive 128-row output blocks)
+        const uint32_t blocks = *num_row_tiles * (table_tile_rows / 128u);
+        row_blocks = blocks < row_blocks ? blocks : row_blocks;
     }
     const size_t words = static_cast<size_t>(row_blocks) * kq_total * 128;
     const bool word_loads = !k_major && (ks_pitch & 3u) == 0 && (reinterpret_cast<uintptr_t>(in) & 3u) == 0;
@@ -160,7 +163,9 @@ __global__ void mx_pack_scales_kernel(const uint8_t* __restrict__ in, uint8_t* _
         // consecutive threads walk consecutive scale words of one row: coalesced reads
         const uint32_t kq = static_cast<uint32_t>(w % kq_total);
         const uint32_t prow = static_cast<uint32_t>(w / kq_total);  // row index inside the padded output
-        const uint32_t row = tile_table == nullptr ? prow : static_cast<uint32_t>(tile_table[prow / 128].x) + prow % 128;
+        const uint32_t row = tile_table == nullptr
+                                 ? prow
+                                 : static_cast<uint32_t>(tile_table[prow / table_tile_rows].x) + prow % table_tile_rows;
         uint32_t v = 0x7F7F7F7Fu;
         if (row < rows) {
             if (word_loads && kq * 4 + 4 <= kblocks_valid) {

@@ -1,4 +1,5 @@
-// MXFP8 / MXFP4 block-scaled GEMM on CTA pairs (tcgen05.mma.cta_group::2): pair tile 256 x 256, dense problems.
+// MXFP8 / MXFP4 block-scaled GEMM on CTA pairs (tcgen05.mma.cta_group::2): pair tile 256 x 256; dense problems,
+// grouped slice-M problems (a pair's tile is 256 rows of one group) and the SwiGLU + MX quantisation epilogue.
 //
 // Same arithmetic, operand formats, scale re-tiling and TMEM scale layout as mx_gemm_kernel (mx_gemm.cuh), with the
 // pairing of w8a8_pair_kernel: CTA r of a cluster of two owns rows [128 r, 128 r + 128) of the tile (its A tile,
@@ -16,7 +17,7 @@
 // forwarded) with one thread requesting, forwarding and copying: that thread's ~10 instructions per stage set
 // the pace at 0.9-1.5 PFLOP/s.  Now every single-thread role issues at most five instructions per stage:
 //   warp 0   operand producer (both CTAs): wait empty, expect (leader), A, B half
-//   warp 2   scale producer (both CTAs): wait empty, A scales, B scales (one 3-D box for both column blocks)
+//   warp 2   scale producer (both CTAs): wait empty, A scales, the two B scale blocks
 //   warps 3, 4  scale copiers (leader): wait full, smem -> TMEM copies for the pair (tcgen05.cp.cta_group::2: each
 //            CTA copies from its own shared memory into its own TMEM), commit to "sf_full" (two arrivals)
 //   warp 1   MMA issuer (leader): wait sf_full, four MMAs, one multicast commit that frees the stage in both CTAs
@@ -80,9 +81,13 @@ __device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
 }
 
-// tmap_sfa: the packed A scales as a byte tensor {256, 2 * kq_total * row blocks}; tmap_sfb: the packed B scales as
-// {256, 2 * kq_total, column blocks} (see the host side).
-template <bool kFp4>
+// tmap_b: {row bytes, n, weight matrices} with boxes of 128 rows; tmap_sfa: the packed A scales as a byte tensor
+// {256, 2 * kq_total * row blocks}; tmap_sfb: the packed B scales as {256, 2 * kq_total, column blocks} with boxes of
+// one block (see the host side).
+// kGrouped: row tiles (256 rows of one group) come from the table of mx_group_plan_kernel; the packed A scales hold
+// two 128-row blocks per table tile.  kEpi: kMxEpiPlain or kMxEpiSwiglu (see mx_gemm.cuh; the pair's leader then loads
+// the tile's 128 "act" columns of B and its peer the 128 "gate" columns).
+template <bool kFp4, bool kGrouped = false, int kEpi = kMxEpiPlain>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxPairThreads, 1)
 mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -116,10 +121,25 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
     const uint32_t pair = blockIdx.x >> 1;
     const uint32_t num_pairs = gridDim.x >> 1;
-    const uint32_t m_tiles = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
-    const uint32_t n_tiles = (p.n + kMxBlockN - 1) / kMxBlockN;
+    constexpr bool kSwiglu = kEpi == kMxEpiSwiglu;
+    static_assert(kEpi == kMxEpiPlain || (kSwiglu && kGrouped && !kFp4), "epilogues of the pair kernel");
+    const uint32_t m_tiles = kGrouped ? *p.num_row_tiles : (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
+    const uint32_t n_tiles = kSwiglu ? (p.n / 2 + 127) / 128 : (p.n + kMxBlockN - 1) / kMxBlockN;
     const uint32_t total_tiles = m_tiles * n_tiles;
     const uint32_t num_kb = p.num_k_blocks;
+    // first row of the pair's tile, end of the rows that may be stored, group
+    auto row_tile = [&](uint32_t mt, int32_t& row0, int32_t& row_end, int32_t& group) {
+        if constexpr (kGrouped) {
+            const int4 e = __ldg(p.tile_table + mt);
+            row0 = e.x;
+            row_end = e.y;
+            group = e.z;
+        } else {
+            row0 = static_cast<int32_t>(mt) * 2 * kBlockM;
+            row_end = static_cast<int32_t>(p.m);
+            group = 0;
+        }
+    };
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
@@ -154,8 +174,11 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             for (uint32_t idx = pair; ok && idx < total_tiles; idx += num_pairs) {
                 uint32_t mt, nt;
                 mx_tile_coords(idx, m_tiles, n_tiles, p.band_rows, mt, nt);
-                const int32_t row0 = static_cast<int32_t>((2 * mt + cta_rank) * kBlockM);
-                const int32_t col0 = static_cast<int32_t>(nt * kMxBlockN + cta_rank * (kMxBlockN / 2));
+                int32_t tile_row0, row_end, group;
+                row_tile(mt, tile_row0, row_end, group);
+                const int32_t row0 = tile_row0 + static_cast<int32_t>(cta_rank * kBlockM);
+                const int32_t col0 = kSwiglu ? static_cast<int32_t>(cta_rank == 0 ? nt * 128 : p.n / 2 + nt * 128)
+                                             : static_cast<int32_t>(nt * kMxBlockN + cta_rank * (kMxBlockN / 2));
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer);
                     if (!ok) {
@@ -169,7 +192,7 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     }
                     const uint32_t full = map_to_cta(bar_full + stage * 8, 0);  // the leader's barrier
                     tma_load_2d_pair(sa, &tmap_a, full, k0, row0);
-                    tma_load_2d_pair(sb, &tmap_b, full, k0, col0);
+                    tma_load_3d_pair(sb, &tmap_b, full, k0, col0, group);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -191,6 +214,11 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // rows of the scale tensors: 256 bytes each, two per 512-byte block; this CTA's 128-row block of A
                 // (past the end of A the box reads zeros: those rows are never stored) and the tile's two blocks of B
                 const int32_t a_row0 = static_cast<int32_t>((2 * mt + cta_rank) * p.kq_total * 2);
+                int32_t tile_row0, row_end, group;
+                row_tile(mt, tile_row0, row_end, group);
+                const int32_t sfb_first = group * static_cast<int32_t>(p.sfb_blocks_per_group);
+                const int32_t sfb0 = sfb_first + static_cast<int32_t>(kSwiglu ? nt : 2 * nt);
+                const int32_t sfb1 = sfb_first + static_cast<int32_t>(kSwiglu ? p.n / 256 + nt : 2 * nt + 1);
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(bar_empty + stage * 8, phase ^ 1, s_abort, p.status, kDevTimeoutProducer);
                     if (!ok) {
@@ -200,7 +228,8 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t full = map_to_cta(bar_full + stage * 8, 0);
                     const int32_t kq2 = static_cast<int32_t>(kb * kWords * 2);
                     tma_load_2d_pair(ssf, &tmap_sfa, full, 0, a_row0 + kq2);
-                    tma_load_3d_pair(ssf + 1024, &tmap_sfb, full, 0, kq2, static_cast<int32_t>(2 * nt));
+                    tma_load_3d_pair(ssf + 1024, &tmap_sfb, full, 0, kq2, sfb0);
+                    tma_load_3d_pair(ssf + 1024 + kWords * 512, &tmap_sfb, full, 0, kq2, sfb1);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -321,8 +350,45 @@ mx_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 break;
             }
             tcgen05_fence_after();
-            const uint32_t row = (2 * mt + cta_rank) * kBlockM + quad * 32 + lane;
-            const bool row_ok = row < p.m;
+            int32_t tile_row0, row_end, group;
+            row_tile(mt, tile_row0, row_end, group);
+            const uint32_t row = static_cast<uint32_t>(tile_row0) + cta_rank * kBlockM + quad * 32 + lane;
+            const bool row_ok = static_cast<int32_t>(row) < row_end;
+            if constexpr (kSwiglu) {
+                // This warp: output columns [32 * part, 32 * part + 32) of the tile's 128; "act" sits in accumulator
+                // columns 0..127, "gate" in 128..255.  Both pieces leave TMEM, the share goes back, then the arithmetic.
+                const uint32_t tcols = tmem_base + part * 32 + ((quad * 32u) << 16);
+                uint32_t ra[32], rg[32];
+                tmem_ld_32x32b_x32(tcols, ra);
+                tmem_ld_32x32b_x32(tcols + 128, rg);
+                tmem_ld_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_cluster(bar_tmem_empty, 0);
+                }
+                acc_phase ^= 1;
+                const uint32_t half_n = p.n / 2;
+                const uint32_t col0 = nt * 128 + part * 32;
+                if (!row_ok || col0 >= half_n) {
+                    continue;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float a = __uint_as_float(ra[i]);
+                    const float g = __uint_as_float(rg[i]);
+                    const float t = __fadd_rn(expf(-a), 1.0f);
+                    const float sw = __fmul_rn(__fdiv_rn(a, t), g);
+                    ra[i] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(sw)));
+                }
+                uint32_t q[8];
+                const uint32_t scale = mx_quant_block_bf16_e4m3(ra, q);
+                uint8_t* qrow = static_cast<uint8_t*>(p.d) + static_cast<size_t>(row) * half_n;
+                *reinterpret_cast<uint4*>(qrow + col0) = make_uint4(q[0], q[1], q[2], q[3]);
+                *reinterpret_cast<uint4*>(qrow + col0 + 16) = make_uint4(q[4], q[5], q[6], q[7]);
+                p.q_scale[static_cast<size_t>(row) * (half_n / 32) + col0 / 32] = static_cast<uint8_t>(scale);
+                continue;
+            }
             const uint32_t taddr = tmem_base + part * 64 + ((quad * 32u) << 16);
             uint32_t r[2][32];
             tmem_ld_32x32b_x32(taddr, r[0]);

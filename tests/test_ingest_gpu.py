@@ -221,6 +221,7 @@ def test_w4a8_weights_written_on_the_stream_right_before_the_call(cuda):
     ((130, 0, 64, 257, 1, 300), 264, 512, True, False),
     ((5, 200, 0, 129), 520, 330, False, True),      # ragged K, prefix-sum list
     ((1000, 24), 1025, 96, True, True),
+    ((700, 37, 600), 19200, 128, True, False),      # large enough for the CTA-pair kernel: 256-row tiles of one group
 ])
 def test_mx_grouped_slice_m(cuda, fmt, sizes, n, k, trans_b, prefix):
     """Example 55: per-group weights and weight scales, the group list given as row counts (the reference's

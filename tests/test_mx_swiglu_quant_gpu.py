@@ -28,6 +28,7 @@ def _e4m3_values(codes):
     ((130, 0, 64, 257, 1), 256, 512, True, False, 1.0),
     ((5, 200, 129), 768, 330, False, True, 1.0),      # B stored [G][k][n], ragged K, prefix sums
     ((300, 77), 1024, 256, True, False, 0.02),        # small products: blocks below the exponent floor
+    ((700, 600), 19456, 128, True, False, 1.0),       # large enough for the CTA-pair kernel (leader: act, peer: gate)
 ])
 def test_mx_grouped_swiglu_mx_quant(cuda, sizes, n, k, trans_b, prefix, scale):
     import torch
