@@ -369,10 +369,13 @@ def mx_grouped_swiglu_quant(a, b, group_list, scale_a, scale_b, q, q_scale, m, n
            load().cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(ctypes.byref(args), _stream(stream)))
 
 
-def mx_grouped_finalize_routing_workspace_size(m, n, k, group_count, batch, layout_b=COLUMN_MAJOR):
+ROUTING_DETERMINISTIC = 1
+
+
+def mx_grouped_finalize_routing_workspace_size(m, n, k, group_count, batch, layout_b=COLUMN_MAJOR, deterministic=False):
     args = MxGroupedFinalizeRoutingArgs(m=m, n=n, k=k, group_count=group_count, layout_b=layout_b, batch=batch, a=256,
                                         b=256, group_list=256, scale_a=256, scale_b=256, logit=256, row_index=256,
-                                        out=256)
+                                        out=256, flags=ROUTING_DETERMINISTIC if deterministic else 0)
     return int(load().cb200_mx_grouped_matmul_finalize_routing_workspace_size(ctypes.byref(args)))
 
 
@@ -380,7 +383,7 @@ def mx_grouped_finalize_routing(a, b, group_list, scale_a, scale_b, logit, row_i
                                 workspace, bias=None, shared_input=None, shared_rows=0, shared_offset=0,
                                 shared_weight=0.0, stream=None, layout_b=COLUMN_MAJOR,
                                 group_list_type=GROUP_LIST_INT64, group_list_kind=GROUP_LIST_SIZES,
-                                row_index_type=GROUP_LIST_INT64):
+                                row_index_type=GROUP_LIST_INT64, deterministic=False):
     """Grouped slice-M MXFP8 matmul + finalize routing: out [batch][n] fp32 = shared contribution +
     sum over rows p of logit[p] * (C[p] + bias[group]) at row row_index[p]."""
     args = MxGroupedFinalizeRoutingArgs(
@@ -389,7 +392,8 @@ def mx_grouped_finalize_routing(a, b, group_list, scale_a, scale_b, logit, row_i
         shared_offset=shared_offset, shared_weight=shared_weight, a=_p(a), b=_p(b), group_list=_p(group_list),
         scale_a=_p(scale_a), scale_b=_p(scale_b), logit=_p(logit), row_index=_p(row_index), bias=_p(bias),
         shared_input=_p(shared_input), out=_p(out), workspace=_p(workspace),
-        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(), block_num=0, flags=0)
+        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(), block_num=0,
+        flags=ROUTING_DETERMINISTIC if deterministic else 0)
     _check("cb200_mx_grouped_matmul_finalize_routing",
            load().cb200_mx_grouped_matmul_finalize_routing(ctypes.byref(args), _stream(stream)))
 

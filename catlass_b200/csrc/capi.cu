@@ -14,6 +14,7 @@
 #include "w4a8_gemm.cuh"
 #include "mx_gemm.cuh"
 #include "mx_gemm_pair.cuh"
+#include "routing.cuh"
 #include "ingest.cuh"
 #include "mx_quantize.cuh"
 
@@ -1101,8 +1102,92 @@ MxProblem mx_routing_problem(const cb200_mx_grouped_finalize_routing_args* a)
     q.workspace = a->workspace;
     q.workspace_bytes = a->workspace_bytes;
     q.block_num = a->block_num;
-    q.flags = a->flags;
+    q.flags = a->flags & ~CB200_ROUTING_DETERMINISTIC;
     return q;
+}
+
+int run_mx(const MxProblem& q, void* stream_v);
+
+// Deterministic finalize routing: the grouped matmul writes C (fp32) into the workspace, then the rows of every
+// token are gathered in ascending row order (routing.cuh).  Workspace: C | lists | the matmul's own workspace.
+struct RoutingDetPlan {
+    uint64_t c_bytes, lists_bytes;
+    MxPlan mx;
+    uint64_t total() const { return c_bytes + lists_bytes + mx.total(); }
+};
+
+MxProblem routing_matmul_problem(const cb200_mx_grouped_finalize_routing_args* a, void* c, void* ws, uint64_t ws_bytes)
+{
+    MxProblem q = mx_routing_problem(a);
+    q.routing = false;
+    q.d = c;
+    q.flags = CB200_MX_OUT_F32;
+    q.workspace = ws;
+    q.workspace_bytes = ws_bytes;
+    return q;
+}
+
+int plan_routing_det(const cb200_mx_grouped_finalize_routing_args* a, RoutingDetPlan* plan)
+{
+    MxPlan check;
+    MxProblem as_fused = mx_routing_problem(a);
+    as_fused.flags = 0;
+    int rc = plan_mx(as_fused, &check);  // the operands, lists and output as for the fused variant
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    plan->c_bytes = align256(static_cast<uint64_t>(a->m) * a->n * 4u);
+    plan->lists_bytes = align256((static_cast<uint64_t>(a->group_count) + 1u + a->batch + a->batch + 1u + a->m) * 4u);
+    // (an aligned non-null value stands in for C while planning: it is not dereferenced)
+    return plan_mx(routing_matmul_problem(a, reinterpret_cast<void*>(uintptr_t{256}), nullptr, 0), &plan->mx);
+}
+
+int run_routing_det(const cb200_mx_grouped_finalize_routing_args* a, void* stream_v)
+{
+    RoutingDetPlan plan;
+    int rc = plan_routing_det(a, &plan);
+    if (rc != CB200_SUCCESS || a->m == 0 || a->n == 0) {
+        return rc;
+    }
+    if (a->workspace == nullptr || a->workspace_bytes < plan.total() ||
+        (reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0) {
+        return CB200_INVALID;
+    }
+    DeviceState* dev = nullptr;
+    rc = device_state(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    float* c = reinterpret_cast<float*>(ws);
+    int32_t* lists = reinterpret_cast<int32_t*>(ws + plan.c_bytes);
+    RoutingLists l;
+    l.group_end = lists;
+    l.total_rows = l.group_end + a->group_count;
+    l.count = l.total_rows + 1;
+    l.start = l.count + a->batch;
+    l.order = l.start + a->batch + 1;
+    rc = run_mx(routing_matmul_problem(a, c, ws + plan.c_bytes + plan.lists_bytes, plan.mx.total()), stream_v);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    const uint32_t idx_i32 = a->row_index_type == CB200_GROUP_LIST_INT32 ? 1u : 0u;
+    routing_prepare_kernel<<<1, 1024, 0, stream>>>(a->group_list, a->group_list_type == CB200_GROUP_LIST_INT32 ? 1u : 0u,
+                                                   a->group_list_kind == CB200_GROUP_LIST_PREFIX_SUMS ? 1u : 0u,
+                                                   a->group_count, a->m, a->batch, l);
+    const uint32_t row_blocks = (a->m + 255u) / 256u;
+    const uint32_t grid = row_blocks < static_cast<uint32_t>(dev->sm_count) * 4u ? row_blocks : dev->sm_count * 4u;
+    routing_count_kernel<<<grid, 256, 0, stream>>>(a->row_index, idx_i32, a->batch, l);
+    routing_scan_kernel<<<1, 1024, 0, stream>>>(a->batch, l);
+    routing_fill_kernel<<<grid, 256, 0, stream>>>(a->row_index, idx_i32, a->batch, l);
+    routing_gather_kernel<<<a->batch, 256, 0, stream>>>(
+        c, static_cast<float*>(a->out), a->n, a->group_count, static_cast<const float*>(a->logit),
+        static_cast<const __nv_bfloat16*>(a->bias), static_cast<const __nv_bfloat16*>(a->shared_input), a->shared_weight,
+        a->shared_offset, a->shared_input != nullptr ? a->shared_rows : 0u, l);
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(5, std::memory_order_relaxed);
+    return CB200_SUCCESS;
 }
 
 int run_mx(const MxProblem& q, void* stream_v)
@@ -1213,8 +1298,13 @@ int cb200_mx_grouped_matmul_finalize_routing_can_implement(const cb200_mx_groupe
 {
     MxPlan plan;
     if (args == nullptr || args->group_count == 0 || args->group_list_kind > CB200_GROUP_LIST_PREFIX_SUMS ||
-        (args->row_index_type != CB200_GROUP_LIST_INT64 && args->row_index_type != CB200_GROUP_LIST_INT32)) {
+        (args->row_index_type != CB200_GROUP_LIST_INT64 && args->row_index_type != CB200_GROUP_LIST_INT32) ||
+        (args->flags & ~CB200_ROUTING_DETERMINISTIC) != 0) {
         return CB200_INVALID;
+    }
+    if (args->flags & CB200_ROUTING_DETERMINISTIC) {
+        RoutingDetPlan det;
+        return plan_routing_det(args, &det);
     }
     return plan_mx(mx_routing_problem(args), &plan);
 }
@@ -1222,8 +1312,14 @@ int cb200_mx_grouped_matmul_finalize_routing_can_implement(const cb200_mx_groupe
 uint64_t cb200_mx_grouped_matmul_finalize_routing_workspace_size(const cb200_mx_grouped_finalize_routing_args* args)
 {
     MxPlan plan;
-    if (cb200_mx_grouped_matmul_finalize_routing_can_implement(args) != CB200_SUCCESS ||
-        plan_mx(mx_routing_problem(args), &plan) != CB200_SUCCESS) {
+    if (cb200_mx_grouped_matmul_finalize_routing_can_implement(args) != CB200_SUCCESS) {
+        return 0;
+    }
+    if (args->flags & CB200_ROUTING_DETERMINISTIC) {
+        RoutingDetPlan det;
+        return plan_routing_det(args, &det) == CB200_SUCCESS ? det.total() : 0;
+    }
+    if (plan_mx(mx_routing_problem(args), &plan) != CB200_SUCCESS) {
         return 0;
     }
     return plan.total();
@@ -1232,7 +1328,13 @@ uint64_t cb200_mx_grouped_matmul_finalize_routing_workspace_size(const cb200_mx_
 int cb200_mx_grouped_matmul_finalize_routing(const cb200_mx_grouped_finalize_routing_args* args, void* stream)
 {
     const int rc = cb200_mx_grouped_matmul_finalize_routing_can_implement(args);
-    return rc != CB200_SUCCESS ? rc : run_mx(mx_routing_problem(args), stream);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    if (args->flags & CB200_ROUTING_DETERMINISTIC) {
+        return run_routing_det(args, stream);
+    }
+    return run_mx(mx_routing_problem(args), stream);
 }
 
 int cb200_w4a8_matmul_can_implement(const cb200_w4a8_matmul_args* args)

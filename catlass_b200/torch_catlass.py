@@ -271,11 +271,23 @@ def ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant(mat1, mat2, mx_scale
     return [q.view(torch.float8_e4m3fn), q_scale.view(e8m0) if e8m0 is not None else q_scale]
 
 
+def ascend950_fp8_mx_grouped_matmul_finalize_routing(mat1, mat2, mx_scale_a, mx_scale_b, group_list, logit, row_index,
+                                                     bias, shared_input, batch, data_parallel_size=1,
+                                                     shared_input_weight=0.0, shared_input_offset=0, group_list_type=0,
+                                                     trans_a=False, trans_b=False):
+    """Example 71, deterministic variant (tests/optest/torch_catlass/ops/
+    ascend950_fp8_mx_grouped_matmul_finalize_routing.py): the same bits on every run."""
+    return ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(
+        mat1, mat2, mx_scale_a, mx_scale_b, group_list, logit, row_index, bias, shared_input, batch,
+        data_parallel_size, shared_input_weight, shared_input_offset, group_list_type, trans_a, trans_b,
+        _deterministic=True)
+
+
 def ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(mat1, mat2, mx_scale_a, mx_scale_b, group_list, logit,
                                                               row_index, bias, shared_input, batch,
                                                               data_parallel_size=1, shared_input_weight=0.0,
                                                               shared_input_offset=0, group_list_type=0, trans_a=False,
-                                                              trans_b=False):
+                                                              trans_b=False, _deterministic=False):
     """Example 71, non-deterministic variant (tests/optest/torch_catlass/ops/
     ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter.py): grouped MXFP8 matmul whose rows are weighted
     with `logit` and added into rows `row_index` of an fp32 (batch, N) output, with an optional bf16 bias per group
@@ -293,8 +305,8 @@ def ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(mat1, mat2, mx_sca
     has_shared = shared_input is not None and shared_input.numel() != 0
     bsdp = batch // max(int(data_parallel_size), 1)
     out = torch.empty((batch, n), dtype=torch.float32, device=mat1.device)
-    ws = torch.empty(max(capi.mx_grouped_finalize_routing_workspace_size(m, n, k, g, batch, lb), 1), dtype=torch.uint8,
-                     device=mat1.device)
+    ws = torch.empty(max(capi.mx_grouped_finalize_routing_workspace_size(m, n, k, g, batch, lb, _deterministic), 1),
+                     dtype=torch.uint8, device=mat1.device)
     row_index = row_index.contiguous()
     capi.mx_grouped_finalize_routing(
         mat1.view(torch.uint8), mat2.view(torch.uint8), group_list, mx_scale_a.contiguous().view(torch.uint8),
@@ -305,7 +317,8 @@ def ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(mat1, mat2, mx_sca
         shared_weight=float(shared_input_weight), layout_b=lb,
         group_list_type=capi.GROUP_LIST_INT32 if group_list.dtype == torch.int32 else capi.GROUP_LIST_INT64,
         group_list_kind=capi.GROUP_LIST_PREFIX_SUMS if group_list_type == 0 else capi.GROUP_LIST_SIZES,
-        row_index_type=capi.GROUP_LIST_INT32 if row_index.dtype == torch.int32 else capi.GROUP_LIST_INT64)
+        row_index_type=capi.GROUP_LIST_INT32 if row_index.dtype == torch.int32 else capi.GROUP_LIST_INT64,
+        deterministic=_deterministic)
     return out
 
 

@@ -456,12 +456,16 @@ CB200_API int cb200_mx_grouped_matmul_slice_m_swiglu_mx_quant(const cb200_mx_gro
  *     out[offset : offset+rows]   += shared_weight * float(shared_input)      (when shared_input != NULL)
  *     out[row_index[p]]           += logit[p] * (C[p] + float(bias[group of p]))     for every row p of a group
  * with C = (scale_a * A) @ (scale_b * B[g]) in fp32, never written.  Rows whose row_index is outside [0, batch)
- * are dropped.  The additions into an output row happen in the order tiles finish (vector atomics): as in the
- * reference's kernel of this name, results are not bit-reproducible from run to run; the reference's second,
- * deterministic scheduler variant is not provided.  The call overwrites all of out.
+ * are dropped.  By default the additions into an output row happen in the order tiles finish (vector atomics): as
+ * in the reference's kernel of this name, results are not bit-reproducible from run to run.  With
+ * CB200_ROUTING_DETERMINISTIC in flags (the reference's GroupedMxMatmulFinalizeRoutingTla,
+ * include/catlass/gemm/kernel/grouped_mx_matmul_finalize_routing_tla.hpp) C goes to the workspace in fp32 (m x n x 4
+ * more bytes) and every output row is summed in ascending row order, the order of the golden's index_add_: the same
+ * bits on every run.  The call overwrites all of out.
  *   logit [m] fp32; row_index [m] int64 or int32 (row_index_type: CB200_GROUP_LIST_INT64 / _INT32);
  *   bias [group_count][n] bf16 or NULL; shared_input [shared_rows][n] bf16 or NULL.
  */
+#define CB200_ROUTING_DETERMINISTIC 1u
 typedef struct cb200_mx_grouped_finalize_routing_args {
     uint32_t m, n, k;
     uint32_t group_count;         /* 1 .. 1024 */
@@ -486,7 +490,7 @@ typedef struct cb200_mx_grouped_finalize_routing_args {
     void *workspace;
     uint64_t workspace_bytes;
     uint32_t block_num;
-    uint32_t flags;               /* 0 */
+    uint32_t flags;               /* 0 or CB200_ROUTING_DETERMINISTIC */
 } cb200_mx_grouped_finalize_routing_args;
 
 CB200_API int cb200_mx_grouped_matmul_finalize_routing_can_implement(

@@ -91,6 +91,72 @@ def test_mx_grouped_finalize_routing(cuda, sizes, n, k, trans_b, prefix, batch, 
     assert (got[untouched] == 0).all()
 
 
+@pytest.mark.parametrize("sizes,n,k,batch,bias,shared,i32,top", [
+    ((130, 0, 64, 257, 1), 264, 512, 64, True, True, False, 8),
+    ((700, 37, 600), 1024, 128, 1, False, False, True, 600),     # more rows per token than the in-block sort holds
+    ((5, 200, 129), 520, 330, 400, True, False, True, 1),
+])
+def test_mx_grouped_finalize_routing_deterministic(cuda, sizes, n, k, batch, bias, shared, i32, top):
+    """CB200_ROUTING_DETERMINISTIC: the same bits on every run, and exactly the golden's arithmetic on the library's
+    own C: out = 0 + weight * shared, then += logit[p] * (C[p] + bias) for the rows of a token in ascending p
+    (gen_data_compare.py:744-757), with C taken from the grouped matmul's fp32 output."""
+    import torch
+    from catlass_b200 import capi
+    fmt = O.MX_E4M3
+    rng = np.random.default_rng(sum(sizes) + n + batch)
+    g, rows = len(sizes), sum(sizes)
+    m = rows + 7
+    aq, sfa = O.mx_quantize((rng.standard_normal((m, k)) * 2.0).astype(np.float32), fmt)
+    bq, sfb = zip(*[O.mx_quantize((rng.standard_normal((n, k)) * 2.0).astype(np.float32), fmt) for _ in range(g)])
+    a_dev = _dev(_stored_operand(aq, fmt, False))
+    b_dev = _dev(np.stack([_stored_operand(q_e, fmt, False) for q_e in bq]))
+    sa_dev = _dev(_stored_scales(sfa, False))
+    sb_dev = _dev(np.stack([_stored_scales(s_e, False) for s_e in sfb]))
+    gl_dev = _dev(np.array(sizes, np.int64))
+    logit = rng.standard_normal(m).astype(np.float32)
+    row_index = rng.integers(0, batch, m).astype(np.int64)
+    row_index[1] = -3
+    row_index[2] = batch
+    bias_bits = O.bf16_bits(rng.standard_normal((g, n)).astype(np.float32))
+    bsdp = max(batch // 2, 1)
+    offset = batch - bsdp
+    shared_bits = O.bf16_bits(rng.standard_normal((bsdp, n)).astype(np.float32))
+    weight = np.float32(-1.25)
+
+    c = torch.zeros((m, n), dtype=torch.float32, device=cuda)
+    ws = torch.empty(max(capi.mx_grouped_matmul_workspace_size(m, n, k, g, fmt), 256), dtype=torch.uint8, device=cuda)
+    capi.mx_grouped_matmul(a_dev, b_dev, gl_dev, sa_dev, sb_dev, c, m, n, k, g, fmt, ws, out_f32=True)
+    c_host = c.cpu().numpy()
+    want = np.zeros((batch, n), np.float32)
+    if shared:
+        want[offset:offset + bsdp] += weight * O.bf16_to_float(shared_bits)
+    group_of = np.repeat(np.arange(g), sizes)
+    bias_f = O.bf16_to_float(bias_bits)
+    for p in range(rows):
+        t = int(row_index[p])
+        if 0 <= t < batch:
+            y = c_host[p] + bias_f[group_of[p]] if bias else c_host[p]
+            want[t] = want[t] + logit[p] * y
+
+    outs = []
+    ws2 = torch.empty(max(capi.mx_grouped_finalize_routing_workspace_size(m, n, k, g, batch, deterministic=True), 256),
+                      dtype=torch.uint8, device=cuda)
+    ri = row_index.astype(np.int32) if i32 else row_index
+    for _ in range(2):
+        out = torch.full((batch, n), 5.0, dtype=torch.float32, device=cuda)
+        capi.mx_grouped_finalize_routing(
+            a_dev, b_dev, gl_dev, sa_dev, sb_dev, _dev(logit), _dev(ri), out, m, n, k, g, batch, ws2,
+            bias=_dev(bias_bits) if bias else None, shared_input=_dev(shared_bits) if shared else None,
+            shared_rows=bsdp if shared else 0, shared_offset=offset, shared_weight=float(weight),
+            row_index_type=capi.GROUP_LIST_INT32 if i32 else capi.GROUP_LIST_INT64, deterministic=True)
+        st, code = capi.device_status()
+        assert st == 0, f"device status {st} code {code:#x}"
+        outs.append(out.cpu().numpy())
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32)), "two runs differ"
+    assert np.array_equal(outs[0].view(np.uint32), want.view(np.uint32)), \
+        f"{(outs[0].view(np.uint32) != want.view(np.uint32)).sum()} values differ from the golden's order"
+
+
 def test_mx_grouped_finalize_routing_rejects(cuda):
     import ctypes
     import torch
@@ -105,7 +171,7 @@ def test_mx_grouped_finalize_routing_rejects(cuda):
                 workspace_bytes=1 << 20)
     ok = capi.MxGroupedFinalizeRoutingArgs(**base)
     assert lib.cb200_mx_grouped_matmul_finalize_routing_can_implement(ctypes.byref(ok)) == 0
-    for change in (dict(batch=0), dict(logit=None), dict(row_index=None), dict(shared_offset=20), dict(flags=1),
+    for change in (dict(batch=0), dict(logit=None), dict(row_index=None), dict(shared_offset=20), dict(flags=2),
                    dict(row_index_type=7), dict(out=buf.data_ptr() + 4), dict(row_index=buf.data_ptr() + 4)):
         bad = capi.MxGroupedFinalizeRoutingArgs(**{**base, **change})
         assert lib.cb200_mx_grouped_matmul_finalize_routing_can_implement(ctypes.byref(bad)) != 0, change

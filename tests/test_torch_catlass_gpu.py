@@ -231,7 +231,8 @@ def test_ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant(torch_catlass):
     assert err.max().item() <= 2 * 2.0 ** -4, err.max().item()
 
 
-def test_ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(torch_catlass):
+@pytest.mark.parametrize("deterministic", [False, True], ids=["no_deter", "deter"])
+def test_ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(torch_catlass, deterministic):
     """The reference op's signature (tests/optest/torch_catlass/ops/
     ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter.py) on the example's own run
     (4 groups, m = n = k = 128, prefix-sum list, batch 16, dp 2) with bias and shared input switched on."""
@@ -255,7 +256,9 @@ def test_ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(torch_catlass
     expected[3:3 + batch // dp] += 0.5 * shared.float()
     expected.index_add_(0, row_index, logit.unsqueeze(1) * c)
     group_list = torch.tensor(sizes, dtype=torch.int64).cumsum(0)
-    result = torch_catlass.ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter(
+    op = (torch_catlass.ascend950_fp8_mx_grouped_matmul_finalize_routing if deterministic
+          else torch_catlass.ascend950_fp8_mx_grouped_matmul_finalize_routing_no_deter)
+    result = op(
         a8.cuda(), torch.stack(b_list).cuda(), a_scale.cuda(), torch.stack(s_list).cuda(), group_list.cuda(),
         logit.cuda(), row_index.cuda(), bias.cuda(), shared.cuda(), batch, data_parallel_size=dp,
         shared_input_weight=0.5, shared_input_offset=3, group_list_type=0, trans_a=False, trans_b=False)
