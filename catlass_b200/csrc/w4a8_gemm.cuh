@@ -29,11 +29,12 @@
 //   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 12 in flight: they come from HBM) and token
 //               tiles (mt x 128 B, as many as fit 64 KB: 8 for 64 tokens; they come from L2), one thread and one
 //               ring each, two consecutive K blocks per load (3-D boxes)
-//   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x mt x 32); one-block scale groups alternate between them
-//               (issuing an MMA costs its thread ~70 ns), longer groups are all issued by warp 1.  A group
-//               accumulates into one of four int32 accumulators in TMEM.  Per K block one commit frees the
-//               unpacked tile and one its half of the token load; per group one more hands the accumulator to the
-//               epilogue.
+//   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x mt x 32; issuing an MMA costs its thread ~70 ns).
+//               One-block scale groups alternate between them, each group into one of four int32 accumulators in
+//               TMEM.  The K blocks of a longer group alternate between them as well: each issuer sums its
+//               blocks into an accumulator of its own and the epilogue adds the two, still as int32, so the
+//               group's sum stays exact.  Per K block one commit frees the unpacked tile and one its half of
+//               the token load; per group one more hands the accumulator to the epilogue.
 //   warps 2-5   unpack: nibble -> int8 holding 16*w (the nibble moved to the high half of the byte: no sign
 //               fix-up needed), written in the 128B-swizzled K-major operand layout, then handed to the MMA
 //               through a proxy fence + mbarrier.  The factor 16 is removed again, exactly, when the epilogue
@@ -337,68 +338,91 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         __syncwarp();
     } else if (warp == 1 || warp == 14) {
         // ------------------------------------------------------- MMA issuers
-        // One-block groups alternate between the two issuers: tile slots 0,2 and accumulators 0,2 are then only
-        // ever used by the first, 1,3 by the second, so each waits on its barriers one use after the other.
-        // Groups of several blocks accumulate in place and need their MMAs issued in order: one issuer does all.
-        constexpr uint32_t kIssuers = kOneBlockGroups ? 2 : 1;
+        // Even K blocks (tile slots 0,2) belong to the first issuer, odd ones (slots 1,3) to the second: each waits
+        // on its tile barriers one use after the other.  A one-block group is one block = one issuer = one
+        // accumulator (0,2 the first issuer's, 1,3 the second's), handed to the epilogue in pairs of groups.  A
+        // longer group owns an accumulator PAIR: each issuer sums its blocks of the group into its own
+        // accumulator of the pair (its MMAs into that accumulator are issued in order), both commit the pair's
+        // "full" barrier after their last block, and the epilogue adds the two int32 sums.
         static_assert(kW4Tiles % 2 == 0 && kW4Accs % 2 == 0, "slot ownership of the two issuers");
-        if (lane == 0 && (warp == 1 || kIssuers == 2)) {
+        if (lane == 0) {
             const uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, false, false, kW4Channels, p.mt);
+            const uint32_t w = warp == 1 ? 0u : 1u;
             bool ok = true;
-            for (uint32_t j = (warp == 1 ? 0 : 1); ok && j < my_groups; j += kIssuers) {
-                const uint32_t acc = j % kW4Accs;
-                const uint32_t pair = j >> 1, pslot = pair % kW4AccPairs;
+            // one K block: wait for its token tile and its unpacked tile, four MMAs, free both
+            auto issue_block = [&](uint32_t i, uint32_t tmem_d, bool first) -> bool {
+                const uint32_t slot = i % kW4Tiles;
+                const uint32_t ph = (i / kW4Tiles) & 1;
+                const uint32_t xl = i / kW4Load;        // token load this block came with
+                const uint32_t xslot = xl % x_loads;
+                bool got;
                 {
                     W4_PROBE_BEGIN();
-                    ok = mbar_wait(bar_acc_empty + pslot * 8, ((pair / kW4AccPairs) & 1) ^ 1, s_abort, p.status,
-                                   kDevTimeoutMmaTmem);
-                    W4_PROBE_END(warp == 1 ? 2 : 3);
+                    got = mbar_wait(bar_x_full + xslot * 8, (xl / x_loads) & 1, s_abort, p.status, kDevTimeoutMma);
+                    W4_PROBE_END(warp == 1 ? 4 : 5);
                 }
-                if (!ok) {
-                    break;
+                {
+                    W4_PROBE_BEGIN();
+                    got = got && mbar_wait(bar_c_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma);
+                    W4_PROBE_END(warp == 1 ? 6 : 7);
                 }
+                if (!got) {
+                    return false;
+                }
+                W4_PROBE_BEGIN();
                 tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * kW4Tokens;
-                for (uint32_t b = 0; b < bpg; ++b) {
-                    const uint32_t i = j * bpg + b;
-                    const uint32_t slot = i % kW4Tiles;
-                    const uint32_t ph = (i / kW4Tiles) & 1;
-                    const uint32_t xl = i / kW4Load;        // token load this block came with
-                    const uint32_t xslot = xl % x_loads;
+                const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA A operand
+                const uint32_t sx_tile =
+                    ring + S::kTokenRing + xslot * x_load_bytes + (i % kW4Load) * p.mt * 128;  // UMMA B operand
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint64_t da = make_smem_desc_sw128(sw_tile + q * kUmmaK, 16, 1024);
+                    const uint64_t db = make_smem_desc_sw128(sx_tile + q * kUmmaK, 16, 1024);
+                    umma_i8<1>(tmem_d, da, db, idesc, (!first || q != 0) ? 1u : 0u);
+                }
+                umma_commit<1>(bar_tiles_free + slot * 8);  // the unpacked tile may be overwritten
+                umma_commit<1>(bar_x_free + xslot * 8);     // ... and this block's half of the token load
+                W4_PROBE_END(warp == 1 ? 8 : 9);
+                return true;
+            };
+            if constexpr (kOneBlockGroups) {
+                for (uint32_t j = w; ok && j < my_groups; j += 2) {
+                    const uint32_t pair = j >> 1, pslot = pair % kW4AccPairs;
                     {
                         W4_PROBE_BEGIN();
-                        ok = mbar_wait(bar_x_full + xslot * 8, (xl / x_loads) & 1, s_abort, p.status, kDevTimeoutMma);
-                        W4_PROBE_END(warp == 1 ? 4 : 5);
+                        ok = mbar_wait(bar_acc_empty + pslot * 8, ((pair / kW4AccPairs) & 1) ^ 1, s_abort, p.status,
+                                       kDevTimeoutMmaTmem);
+                        W4_PROBE_END(warp == 1 ? 2 : 3);
                     }
+                    ok = ok && issue_block(j, tmem_base + (j % kW4Accs) * kW4Tokens, true);
+                    if (!ok) {
+                        break;
+                    }
+                    umma_commit<1>(bar_acc_full + pslot * 8);  // the group's accumulator is complete
+                    if (j + 1 == my_groups && (j & 1) == 0) {
+                        mbar_arrive(bar_acc_full + pslot * 8);  // an odd last group: the pair has no second member
+                    }
+                }
+            } else {
+                for (uint32_t j = 0; ok && j < my_groups; ++j) {
+                    const uint32_t pslot = j % kW4AccPairs;
                     {
                         W4_PROBE_BEGIN();
-                        ok = ok && mbar_wait(bar_c_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma);
-                        W4_PROBE_END(warp == 1 ? 6 : 7);
+                        ok = mbar_wait(bar_acc_empty + pslot * 8, ((j / kW4AccPairs) & 1) ^ 1, s_abort, p.status,
+                                       kDevTimeoutMmaTmem);
+                        W4_PROBE_END(warp == 1 ? 2 : 3);
+                    }
+                    const uint32_t tmem_d = tmem_base + (2 * pslot + w) * kW4Tokens;
+                    const uint32_t i0 = j * bpg;
+                    bool first = true;
+                    for (uint32_t i = i0 + ((i0 & 1) != w ? 1u : 0u); ok && i < i0 + bpg; i += 2) {
+                        ok = issue_block(i, tmem_d, first);
+                        first = false;
                     }
                     if (!ok) {
                         break;
                     }
-                    W4_PROBE_BEGIN();
-                    tcgen05_fence_after();
-                    const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA A operand
-                    const uint32_t sx_tile =
-                        ring + S::kTokenRing + xslot * x_load_bytes + (i % kW4Load) * p.mt * 128;  // UMMA B operand
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint64_t da = make_smem_desc_sw128(sw_tile + q * kUmmaK, 16, 1024);
-                        const uint64_t db = make_smem_desc_sw128(sx_tile + q * kUmmaK, 16, 1024);
-                        umma_i8<1>(tmem_d, da, db, idesc, (b | q) != 0 ? 1u : 0u);
-                    }
-                    umma_commit<1>(bar_tiles_free + slot * 8);  // the unpacked tile may be overwritten
-                    umma_commit<1>(bar_x_free + xslot * 8);     // ... and this block's half of the token load
-                    W4_PROBE_END(warp == 1 ? 8 : 9);
-                }
-                if (!ok) {
-                    break;
-                }
-                umma_commit<1>(bar_acc_full + pslot * 8);  // the group's accumulator is complete
-                if (j + 1 == my_groups && (j & 1) == 0) {
-                    mbar_arrive(bar_acc_full + pslot * 8);  // an odd last group: the pair has no second member
+                    umma_commit<1>(bar_acc_full + pslot * 8);  // this issuer's share of the group is complete
                 }
             }
         }
@@ -537,13 +561,53 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         auto issue = [&](uint32_t j, uint32_t piece, uint32_t(&r)[16]) {
             tmem_ld_32x32b_x16(tmem_mine + (j % kW4Accs) * kW4Tokens + piece * 16, r);
         };
+        // one-block groups are handed over two at a time; a longer group is a hand-over of its own
+        const uint32_t handovers = kOneBlockGroups ? (my_groups + 1) / 2 : my_groups;
         if (np == 0) {
             // no token columns here (few tokens): only keep the accumulator hand-shake going
-            for (uint32_t pair = 0; 2 * pair < my_groups; ++pair) {
+            for (uint32_t pair = 0; pair < handovers; ++pair) {
                 if (!acquire(pair)) {
                     break;
                 }
                 release(pair);
+            }
+        } else if constexpr (!kOneBlockGroups) {
+            // Longer groups: the two issuers' int32 sums of the group (accumulators 2*slot and 2*slot+1) are read
+            // together, 16 token columns at a time, and added before the int->float step.  These hand-overs are
+            // bpg K blocks apart, and the other accumulator pair is being filled meanwhile.
+            uint32_t ra[16], rb[16];
+            bool ok = true;
+            for (uint32_t j = 0; ok && j < my_groups; ++j) {
+                const float s = scale_of(j);
+                ok = acquire(j);
+                if (!ok) {
+                    break;
+                }
+                const uint32_t t0 = tmem_mine + 2 * (j % kW4AccPairs) * kW4Tokens;
+                auto piece = [&](uint32_t c) {
+                    tmem_ld_32x32b_x16(t0 + c * 16, ra);
+                    tmem_ld_32x32b_x16(t0 + kW4Tokens + c * 16, rb);
+                    tmem_ld_wait_x16(ra);
+                    tmem_ld_wait_x16(rb);
+#pragma unroll
+                    for (int v = 0; v < 16; ++v) {
+                        ra[v] += rb[v];
+                    }
+                };
+                piece(0);
+                accumulate16<false, 0>(y2, ra, s);
+                piece(1);
+                if (np == 2) {
+                    accumulate16<false, 8>(y2, ra, s);
+                    piece(2);
+                    accumulate16<false, 16>(y2, ra, s);
+                    piece(3);
+                    release(j);
+                    accumulate16<false, 24>(y2, ra, s);
+                } else {
+                    release(j);
+                    accumulate16<false, 8>(y2, ra, s);
+                }
             }
         } else {
             // Two register sets alternate over the 16-column pieces of a group; the read of the next piece (of
