@@ -9,13 +9,14 @@ One step = one pass over all routed rows.  Prints ONE JSON line on rank 0.
 
 The line's `value` is timed over exactly K steps.  Next to it the line carries
   sustained   the same launch repeated for >= 2 s (power-capped clocks), with the clock samples of that region
-  secondary   (1 GPU only) the other workloads of the metric - decode_a, decode_b, prefill, w4a8, mxfp8, mxfp4 -
+  secondary   (1 GPU only) the other workloads of the metric - decode_a, decode_b, prefill, w4a8, w4a8_per_tensor,
+              mxfp8, mxfp4, mx_swiglu, mx_routing -
               each replayed from a CUDA graph for >= 1.5 s so that its clock record holds >= 10 samples
   verify      the shard outputs of all ranks assembled with one all-gather and sampled rows of every expert,
               including the rows on both sides of every shard and tile boundary, compared with the CPU oracle
   e2e         the host-buffer entry point: inputs from pinned host memory, output back to it, every step
 
-Other workloads can be run alone (single GPU): prefill, decode_a, decode_b, w4a8, mxfp8, mxfp4, moe_small.
+Other workloads can be run alone (single GPU): the secondary ones and moe_small.
 
 `--impl reference` times the reference's own CPU golden (compiled from the reference tree into
 oracle/_ref, else the oracle's plain-C restatement) on the host cores, on a bounded row sample per step.
@@ -42,7 +43,7 @@ DENSE = {
     "decode_a": (16, 14336, 4096),
     "decode_b": (16, 4096, 14336),
 }
-SECONDARY = ["decode_a", "decode_b", "prefill", "w4a8", "mxfp8", "mxfp4", "mx_swiglu", "mx_routing"]
+SECONDARY = ["decode_a", "decode_b", "prefill", "w4a8", "w4a8_per_tensor", "mxfp8", "mxfp4", "mx_swiglu", "mx_routing"]
 INT8_PER_BF16 = 2.0  # kind::i8 issues at twice the bf16 rate on the same tensor cores
 L2_BYTES = 126e6
 
@@ -634,11 +635,14 @@ def run_dense(name, sampler, seconds):
     }
 
 
-def run_w4a8(sampler, seconds, split_k=False):
-    """M=128, N=8192, K=8192, group 128: int4 weights packed along K, HBM-bound."""
+def run_w4a8(sampler, seconds, split_k=False, per_tensor=False):
+    """M=128, N=8192, K=8192, int4 weights packed along K, HBM-bound.  Scale groups of 128 (BASELINE config 3), or
+    one group over the whole K range: the scaling of the reference's own W4A8 example (one rounding of the int32 sum)."""
     import torch
     from catlass_b200 import capi, kernel_facts
-    m, n, k, gs = 128, 8192, 8192, 128
+    m, n, k = 128, 8192, 8192
+    gs = k if per_tensor else 128
+    name = "w4a8_per_tensor" if per_tensor else "w4a8"
     dev = torch.device("cuda")
     gen = torch.Generator(device="cuda")
     gen.manual_seed(4321)
@@ -659,15 +663,16 @@ def run_w4a8(sampler, seconds, split_k=False):
     value = nbytes / (r["ms"] * 1e-3) / 1e9
     burst = nbytes / (r["burst_ms"] * 1e-3) / 1e9
     return {
-        "name": "w4a8", "metric": "w4a8_gemm_hbm_gbs", "value": value, "unit": "GB/s", "ms_per_step": r["ms"],
+        "name": name, "metric": "w4a8_gemm_hbm_gbs", "value": value, "unit": "GB/s", "ms_per_step": r["ms"],
         "burst_value": burst, "burst_ms_per_step": r["burst_ms"],
         "regime": f"sustained: {r['launches_timed']} launches back to back, {r['region_s']:.2f} s",
-        "config": {"workload": f"w4a8: M={m} N={n} K={k} group {gs}, int4 weights packed along K (static weights), bf16 out",
+        "config": {"workload": f"{name}: M={m} N={n} K={k} group {gs}, int4 weights packed along K (static weights), bf16 out",
                    "summation": "K split over a CTA cluster, fp32 partial sums reassociated (CB200_W4A8_SPLIT_K)"
                                 if split_k else "sequential over the scale groups (default: bit-exact)",
                    "l2": f"weights rotate over {copies} copies: every pass reads HBM"},
         "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": value / peaks["hbm_gbs"], "traffic": kernel_facts.traffic("w4a8_gemm_kernel/w4a8"),
+                     "frac": value / peaks["hbm_gbs"],
+                     "traffic": None if per_tensor else kernel_facts.traffic("w4a8_gemm_kernel/w4a8"),
                      "peak_source": f"{peaks['source']} HBM copy rate", "burst_frac": burst / peaks["hbm_gbs"],
                      "algorithmic_bytes": nbytes, "frac_of_8TBs": value / 8000.0},
         "gpu_launches": r["launches_timed"], "cuda_graph": r["cuda_graph"], "clocks": r["clocks"],
@@ -828,8 +833,8 @@ def run_secondary(name, sampler, seconds, args):
         return run_mx_routing(sampler, seconds)
     if name in DENSE:
         return run_dense(name, sampler, seconds)
-    if name == "w4a8":
-        return run_w4a8(sampler, seconds, split_k=bool(args.w4a8_split_k))
+    if name in ("w4a8", "w4a8_per_tensor"):
+        return run_w4a8(sampler, seconds, split_k=bool(args.w4a8_split_k), per_tensor=name == "w4a8_per_tensor")
     return run_mx(name, sampler, seconds)
 
 
@@ -838,7 +843,7 @@ def standalone_line(entry, args):
     line = {"metric": entry["metric"], "value": entry["value"], "unit": entry["unit"], "n_gpus": 1,
             "steps": entry["gpu_launches"], "warmup": args.warmup, "ms_per_step": entry["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"w4a8": "int4xint8->int32->f32", "mxfp8": "e4m3xe8m0", "mxfp4": "e2m1xe8m0"}.get(entry["name"], "int8"),
+            "dtype": {"w4a8": "int4xint8->int32->f32", "w4a8_per_tensor": "int4xint8->int32->f32", "mxfp8": "e4m3xe8m0", "mxfp4": "e2m1xe8m0"}.get(entry["name"], "int8"),
             "data": "synthetic"}
     line.update({k: v for k, v in entry.items() if k not in ("name", "metric", "value", "unit", "ms_per_step")})
     return line

@@ -1453,10 +1453,10 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args_in, void* stream_v)
         }
     }
     {
-        // tokens as (128 bytes of a K block, token, K block)
+        // tokens as (128 bytes of a K block, token, K block); groups longer than one block load block by block
         const uint64_t dims[3] = {128, args->m, args->k / 128u};
         const uint64_t strides[2] = {args->k, 128};
-        const uint32_t box[3] = {128, p.mt, kW4Load};
+        const uint32_t box[3] = {128, p.mt, args->group_size == 128 ? static_cast<uint32_t>(kW4Load) : 1u};
         rc = encode_tmap_u8(&tmap_x, args->a, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != CB200_SUCCESS) {
             return rc;

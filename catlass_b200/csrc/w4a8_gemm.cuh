@@ -28,7 +28,9 @@
 // Warp roles (16 warps):
 //   warps 0,15  TMA producers: packed weight tiles (128 x 64 B, 12 in flight: they come from HBM) and token
 //               tiles (mt x 128 B, as many as fit 64 KB: 8 for 64 tokens; they come from L2), one thread and one
-//               ring each, two consecutive K blocks per load (3-D boxes)
+//               ring each, two consecutive K blocks per load (3-D boxes).  Scale groups longer than one K block:
+//               the token tile of a K block shares the tile slot (and both barriers) of the block's unpacked
+//               weight tile instead, one block per load
 //   warps 1,14  MMA issuers (tcgen05.mma.kind::i8, 128 x mt x 32; issuing an MMA costs its thread ~70 ns).
 //               One-block scale groups alternate between them, each group into one of four int32 accumulators in
 //               TMEM.  The K blocks of a longer group alternate between them as well: each issuer sums its
@@ -250,7 +252,8 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             mbar_init(bar_x_free + i * 8, kW4Load);  // one commit per K block of the load
         }
         for (int i = 0; i < kW4Tiles; ++i) {
-            mbar_init(bar_c_full + i * 8, 1);
+            // longer groups: the slot's token tile lands on the same barrier (the producer's expect_tx arrival)
+            mbar_init(bar_c_full + i * 8, kOneBlockGroups ? 1 : 2);
             mbar_init(bar_tiles_free + i * 8, 1);
         }
         for (int i = 0; i < kW4AccPairs; ++i) {
@@ -318,7 +321,26 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         if (lane == 0) {
             grid_dependency_wait();
             bool ok = true;
-            const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
+            if constexpr (!kOneBlockGroups) {
+                // Longer groups: K block i's token tile shares tile slot i % kW4Tiles with its unpacked weight tile:
+                // it is loaded once the MMAs of the slot's previous block are done (the barrier the unpack warp
+                // waits on, too) and lands on the slot's "full" barrier, so an MMA issuer probes one barrier and
+                // commits one per K block.  (The tensor map's box is one K block deep in this mode.)
+                for (uint32_t i = 0; ok && i < my_kb; ++i) {
+                    const uint32_t slot = i % kW4Tiles;
+                    W4_PROBE_BEGIN();
+                    ok = mbar_wait(bar_tiles_free + slot * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
+                                   kDevTimeoutProducer);
+                    W4_PROBE_END(1);
+                    if (ok) {
+                        const uint32_t full = bar_c_full + slot * 8;
+                        mbar_expect_tx(full, p.mt * 128);
+                        tma_load_3d(ring + S::kTokenRing + slot * S::kTokenBytes, &tmap_x, full, 0, m0,
+                                    static_cast<int32_t>(kb_begin + i));
+                    }
+                }
+            }
+            const uint32_t loads = kOneBlockGroups ? (my_kb + kW4Load - 1) / kW4Load : 0u;
             for (uint32_t l = 0; ok && l < loads; ++l) {
                 const uint32_t slot = l % x_loads;
                 const uint32_t parity = ((l / x_loads) & 1) ^ 1;
@@ -353,6 +375,31 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             auto issue_block = [&](uint32_t i, uint32_t tmem_d, bool first) -> bool {
                 const uint32_t slot = i % kW4Tiles;
                 const uint32_t ph = (i / kW4Tiles) & 1;
+                if constexpr (!kOneBlockGroups) {
+                    // token tile and unpacked tile share the slot and its barriers (see the token producer)
+                    bool got;
+                    {
+                        W4_PROBE_BEGIN();
+                        got = mbar_wait(bar_c_full + slot * 8, ph, s_abort, p.status, kDevTimeoutMma);
+                        W4_PROBE_END(warp == 1 ? 6 : 7);
+                    }
+                    if (!got) {
+                        return false;
+                    }
+                    W4_PROBE_BEGIN();
+                    tcgen05_fence_after();
+                    const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA A operand
+                    const uint32_t sx_tile = ring + S::kTokenRing + slot * S::kTokenBytes;    // UMMA B operand
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint64_t da = make_smem_desc_sw128(sw_tile + q * kUmmaK, 16, 1024);
+                        const uint64_t db = make_smem_desc_sw128(sx_tile + q * kUmmaK, 16, 1024);
+                        umma_i8<1>(tmem_d, da, db, idesc, (!first || q != 0) ? 1u : 0u);
+                    }
+                    umma_commit<1>(bar_tiles_free + slot * 8);  // both tiles of the slot may be overwritten
+                    W4_PROBE_END(warp == 1 ? 8 : 9);
+                    return true;
+                }
                 const uint32_t xl = i / kW4Load;        // token load this block came with
                 const uint32_t xslot = xl % x_loads;
                 bool got;
