@@ -340,8 +340,8 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     }
                 }
             }
-            const uint32_t loads = kOneBlockGroups ? (my_kb + kW4Load - 1) / kW4Load : 0u;
-            for (uint32_t l = 0; ok && l < loads; ++l) {
+            const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
+            for (uint32_t l = 0; kOneBlockGroups && ok && l < loads; ++l) {
                 const uint32_t slot = l % x_loads;
                 const uint32_t parity = ((l / x_loads) & 1) ^ 1;
                 W4_PROBE_BEGIN();
