@@ -636,7 +636,7 @@ def run_dense(name, sampler, seconds):
 
 
 def run_w4a8(sampler, seconds, split_k=False, per_tensor=False):
-    """M=128, N=8192, K=8192, int4 weights packed along K, HBM-bound.  Scale groups of 128 (BASELINE config 3), or
+    """M=128, N=8192, K=8192, int4 weights packed along K, HBM-bound.  Scale groups of 128 (the headline W4A8 configuration), or
     one group over the whole K range: the scaling of the reference's own W4A8 example (one rounding of the int32 sum)."""
     import torch
     from catlass_b200 import capi, kernel_facts
