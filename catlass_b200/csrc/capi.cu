@@ -1470,9 +1470,11 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args_in, void* stream_v)
     }
     rc = once.run(devid, [&]() -> int {
         CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            W4A8Smem::kTotalBytes));
+                                            W4A8Smem<4>::kTotalBytes));
         CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            W4A8Smem::kTotalBytes));
+                                            W4A8Smem<4>::kTotalBytes));
+        CB200_CUDA_TRY(cudaFuncSetAttribute(w4a8_gemm_kernel<false, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            W4A8Smem<6>::kTotalBytes));
         return CB200_SUCCESS;
     });
     if (rc != CB200_SUCCESS) {
@@ -1482,7 +1484,9 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args_in, void* stream_v)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kW4Threads, 1, 1);
-    cfg.dynamicSmemBytes = W4A8Smem::kTotalBytes;
+    // scale groups of several K blocks and token tiles of at most 64 rows: six tile slots (see W4A8Smem)
+    const bool six_slots = args->group_size != 128 && p.mt <= 64 && dev_knob("CB200_W4A8_SIX_SLOTS", 1) != 0;
+    cfg.dynamicSmemBytes = six_slots ? W4A8Smem<6>::kTotalBytes : W4A8Smem<4>::kTotalBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1498,6 +1502,8 @@ int cb200_w4a8_matmul(const cb200_w4a8_matmul_args* args_in, void* stream_v)
     cfg.numAttrs = dev_knob("CB200_W4A8_PDL", 1) != 0 ? 2 : 1;
     if (args->group_size == 128) {
         CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a8_gemm_kernel<true>, tmap_w, tmap_x, p));
+    } else if (six_slots) {
+        CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a8_gemm_kernel<false, 6>, tmap_w, tmap_x, p));
     } else {
         CB200_CUDA_TRY(cudaLaunchKernelEx(&cfg, w4a8_gemm_kernel<false>, tmap_w, tmap_x, p));
     }

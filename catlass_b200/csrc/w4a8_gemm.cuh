@@ -60,14 +60,15 @@ constexpr int kW4Channels = 128;    // output channels per CTA (UMMA M)
 constexpr int kW4Tokens = 128;      // tokens per CTA at most (UMMA N)
 constexpr int kW4Accs = 4;          // int32 accumulators in TMEM (128 columns each)
 constexpr int kW4AccPairs = 2;      // accumulators are handed over two at a time (halves the hand-shakes per group)
-constexpr int kW4Tiles = 4;         // token tiles / unpacked weight tiles in flight (= unpack warps, see there)
-constexpr int kW4PackedSlots = 12;  // packed-weight tiles in flight (8 KB each): covers HBM latency
+constexpr int kW4Tiles = 4;         // unpacked weight tiles in flight (= unpack warps, see there); 6 in one mode
+constexpr int kW4MaxTiles = 6;
+constexpr int kW4MaxPackedSlots = 12;  // packed-weight tiles in flight at most (8 KB each): covers HBM latency
 constexpr int kW4MaxSplits = 4;     // CTAs of a cluster sharing one channel tile along K
 #ifndef CB200_W4_LOAD
 #define CB200_W4_LOAD 2
 #endif
 constexpr int kW4Load = CB200_W4_LOAD;  // K blocks per TMA load (3-D boxes): half the loads and barrier round trips
-constexpr int kW4PackedLoads = kW4PackedSlots / kW4Load;  // load slots of the packed-weight ring
+constexpr int kW4MaxPackedLoads = kW4MaxPackedSlots / kW4Load;  // load slots of the packed-weight ring at most
 constexpr int kW4MaxTokenLoads = 8;                       // load slots of the token ring at most (see x_loads)
 
 #ifdef CB200_DEVELOPER_KNOBS
@@ -101,28 +102,39 @@ struct W4A8Params {
     uint32_t token_loads_max;   // cap on the token ring's load slots (<= kW4MaxTokenLoads)
 };
 
+// How the 224 KB of ring space are split.  kTiles = 4: four 16 KB token slots (token tiles of up to 128 rows), four
+// unpacked weight tiles, twelve packed tiles.  kTiles = 6 (scale groups of several K blocks, token tiles of at most
+// 64 rows): six 8 KB token slots, six unpacked tiles, ten packed tiles.  There a K block's unpacked tile stays
+// in its slot from the start of the unpack to the end of its MMAs, about as long as unpacking a tile takes
+// again: with four slots for four unpack warps every warp waited that long for "its" slot.
+template <int kTiles>
 struct W4A8Smem {
-    static constexpr int kTokenBytes = kW4Tokens * 128;     // 16 KB: UMMA B operand
+    static_assert(kTiles == 4 || kTiles == 6, "tile slots");
+    static constexpr int kTokenSlotBytes = (kTiles == 6 ? 64 : kW4Tokens) * 128;  // UMMA B operand
+    static constexpr int kTokenRingBytes = kTiles * kTokenSlotBytes;
     static constexpr int kCookedBytes = kW4Channels * 128;  // 16 KB: unpacked int8 weights, UMMA A operand
     static constexpr int kPackedBytes = kW4Channels * 64;   //  8 KB: packed weights as loaded
+    static constexpr int kPackedSlots = kTiles == 6 ? 10 : 12;
+    static constexpr int kPackedLoads = kPackedSlots / kW4Load;
     static constexpr int kTokenRing = 0;
-    static constexpr int kCookedRing = kTokenRing + kW4Tiles * kTokenBytes;
-    static constexpr int kPackedRing = kCookedRing + kW4Tiles * kCookedBytes;
-    static constexpr int kRingBytes = kPackedRing + kW4PackedSlots * kPackedBytes;
+    static constexpr int kCookedRing = kTokenRing + kTokenRingBytes;
+    static constexpr int kPackedRing = kCookedRing + kTiles * kCookedBytes;
+    static constexpr int kRingBytes = kPackedRing + kPackedSlots * kPackedBytes;
     // after the K loop the ring is idle and holds this CTA's fp32 sums (64 KB) followed by the other CTAs'
     // partial sums: (splits - 1) x (128 / splits) token columns x 128 channels x fp32 <= 48 KB
     static constexpr int kLandingBytes =
         kW4Tokens * kW4Channels * 4 + (kW4MaxSplits - 1) * (kW4Tokens / kW4MaxSplits) * kW4Channels * 4;
     // p_full, p_empty [packed loads]; x_full, x_free [token loads]; c_full, tiles_free [tiles]; acc_full,
     // acc_empty [accumulator pairs]
-    static constexpr int kBarriers = 2 * kW4PackedLoads + 2 * kW4MaxTokenLoads + 2 * kW4Tiles + 2 * kW4AccPairs;
+    static constexpr int kBarriers =
+        2 * kW4MaxPackedLoads + 2 * kW4MaxTokenLoads + 2 * kW4MaxTiles + 2 * kW4AccPairs;
     static constexpr int kBarrierBytes = kBarriers * 8 + 16;
     static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
+    static_assert(kPackedSlots % kW4Load == 0 && kPackedSlots <= kW4MaxPackedSlots && kTiles <= kW4MaxTiles, "rings");
+    static_assert(kTotalBytes <= 227 * 1024, "shared memory budget");
+    static_assert(kLandingBytes <= kRingBytes, "the landing buffer aliases the ring");
 };
-static_assert(W4A8Smem::kTotalBytes <= 227 * 1024, "shared memory budget");
-static_assert(W4A8Smem::kLandingBytes <= W4A8Smem::kRingBytes, "the landing buffer aliases the ring");
 static_assert(kW4Accs * kW4Tokens <= 512, "TMEM budget");
-static_assert(kW4Tiles == 4, "one tile slot per unpack warp");
 
 // The running sums y are kept as pairs of fp32 in 64-bit registers so that the per-group update is exactly four
 // instructions per two outputs (two integer adds, one packed subtract, one packed fused multiply-add) with no
@@ -195,12 +207,16 @@ __device__ __forceinline__ void accumulate16(unsigned long long (&y2)[32], const
 
 // kOneBlockGroups: the scale group is exactly one 128-wide K block (the common case): the int->float step can
 // then use the add-a-constant form.
-template <bool kOneBlockGroups>
+// kTiles: tile slots of the ring (see W4A8Smem); 6 only with scale groups of several K blocks and token tiles of at
+// most 64 rows.
+template <bool kOneBlockGroups, int kTiles = kW4Tiles>
 __global__ void __launch_bounds__(kW4Threads, 1)
 w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                  const W4A8Params p)
 {
-    using S = W4A8Smem;
+    using S = W4A8Smem<kTiles>;
+    static_assert(kTiles == kW4Tiles || !kOneBlockGroups, "one-block groups: one tile slot per unpack warp");
+    constexpr uint32_t kPackedSlots = S::kPackedSlots, kPackedLoads = S::kPackedLoads;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -209,12 +225,12 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
 
     uint64_t* s_bars = reinterpret_cast<uint64_t*>(smem + S::kRingBytes);
     const uint32_t bar_p_full = smem_u32(s_bars);                    // packed tile landed (TMA bytes)
-    const uint32_t bar_p_empty = bar_p_full + kW4PackedLoads * 8;    // the unpack warps have read both tiles
-    const uint32_t bar_x_full = bar_p_empty + kW4PackedLoads * 8;    // a pair of token tiles landed
+    const uint32_t bar_p_empty = bar_p_full + kW4MaxPackedLoads * 8;    // the unpack warps have read both tiles
+    const uint32_t bar_x_full = bar_p_empty + kW4MaxPackedLoads * 8;    // a pair of token tiles landed
     const uint32_t bar_x_free = bar_x_full + kW4MaxTokenLoads * 8;   // the MMAs that read the pair completed
     const uint32_t bar_c_full = bar_x_free + kW4MaxTokenLoads * 8;   // unpacked tile written
-    const uint32_t bar_tiles_free = bar_c_full + kW4Tiles * 8;       // the MMAs that read the unpacked tile completed
-    const uint32_t bar_acc_full = bar_tiles_free + kW4Tiles * 8;     // all MMAs of a pair of scale groups completed
+    const uint32_t bar_tiles_free = bar_c_full + kW4MaxTiles * 8;       // the MMAs that read the unpacked tile completed
+    const uint32_t bar_acc_full = bar_tiles_free + kW4MaxTiles * 8;     // all MMAs of a pair of scale groups completed
     const uint32_t bar_acc_empty = bar_acc_full + kW4AccPairs * 8;   // the epilogue has read the pair's accumulators
     uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + S::kBarriers);
     volatile uint32_t* s_abort = s_tmem_ptr + 1;
@@ -238,12 +254,12 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     // fewer.  Token tiles come from L2 with ~1-2 us of latency while every CTA of the grid asks for the same lines,
     // so the bytes in flight decide the rate; the ring is independent of the four unpacked-tile slots.
     const uint32_t x_load_bytes = kW4Load * p.mt * 128;
-    const uint32_t x_loads_fit = (kW4Tiles * S::kTokenBytes) / x_load_bytes;
+    const uint32_t x_loads_fit = S::kTokenRingBytes / x_load_bytes;
     const uint32_t x_loads = x_loads_fit < p.token_loads_max ? x_loads_fit : p.token_loads_max;
 
     if (threadIdx.x == 0) {
         *s_abort = 0;
-        for (int i = 0; i < kW4PackedLoads; ++i) {
+        for (int i = 0; i < kW4MaxPackedLoads; ++i) {
             mbar_init(bar_p_full + i * 8, 1);
             mbar_init(bar_p_empty + i * 8, kW4Load);  // one arrival per tile of the load
         }
@@ -251,7 +267,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             mbar_init(bar_x_full + i * 8, 1);
             mbar_init(bar_x_free + i * 8, kW4Load);  // one commit per K block of the load
         }
-        for (int i = 0; i < kW4Tiles; ++i) {
+        for (int i = 0; i < kW4MaxTiles; ++i) {
             // longer groups: the slot's token tile lands on the same barrier (the producer's expect_tx arrival)
             mbar_init(bar_c_full + i * 8, kOneBlockGroups ? 1 : 2);
             mbar_init(bar_tiles_free + i * 8, 1);
@@ -281,7 +297,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         y2[i] = 0ull;
     }
 
-    // Ring discipline: local K block i uses packed slot i % kW4PackedSlots and tile slot i % kW4Tiles; local
+    // Ring discipline: local K block i uses packed slot i % kPackedSlots and tile slot i % kTiles; local
     // group j uses accumulator j % kW4Accs.  "The previous user of this slot is done" = wait with the inverted
     // parity of the use count (passes at once for the first use).
 
@@ -296,9 +312,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             bool ok = true;
             const uint32_t loads = (my_kb + kW4Load - 1) / kW4Load;
             for (uint32_t l = 0; ok && l < loads; ++l) {
-                const uint32_t slot = l % kW4PackedLoads;
+                const uint32_t slot = l % kPackedLoads;
                 W4_PROBE_BEGIN();
-                ok = mbar_wait(bar_p_empty + slot * 8, ((l / kW4PackedLoads) & 1) ^ 1, s_abort, p.status,
+                ok = mbar_wait(bar_p_empty + slot * 8, ((l / kPackedLoads) & 1) ^ 1, s_abort, p.status,
                                kDevTimeoutProducer);
                 W4_PROBE_END(0);
                 if (ok) {
@@ -322,20 +338,20 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             grid_dependency_wait();
             bool ok = true;
             if constexpr (!kOneBlockGroups) {
-                // Longer groups: K block i's token tile shares tile slot i % kW4Tiles with its unpacked weight tile:
+                // Longer groups: K block i's token tile shares tile slot i % kTiles with its unpacked weight tile:
                 // it is loaded once the MMAs of the slot's previous block are done (the barrier the unpack warp
                 // waits on, too) and lands on the slot's "full" barrier, so an MMA issuer probes one barrier and
                 // commits one per K block.  (The tensor map's box is one K block deep in this mode.)
                 for (uint32_t i = 0; ok && i < my_kb; ++i) {
-                    const uint32_t slot = i % kW4Tiles;
+                    const uint32_t slot = i % kTiles;
                     W4_PROBE_BEGIN();
-                    ok = mbar_wait(bar_tiles_free + slot * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
+                    ok = mbar_wait(bar_tiles_free + slot * 8, ((i / kTiles) & 1) ^ 1, s_abort, p.status,
                                    kDevTimeoutProducer);
                     W4_PROBE_END(1);
                     if (ok) {
                         const uint32_t full = bar_c_full + slot * 8;
                         mbar_expect_tx(full, p.mt * 128);
-                        tma_load_3d(ring + S::kTokenRing + slot * S::kTokenBytes, &tmap_x, full, 0, m0,
+                        tma_load_3d(ring + S::kTokenRing + slot * S::kTokenSlotBytes, &tmap_x, full, 0, m0,
                                     static_cast<int32_t>(kb_begin + i));
                     }
                 }
@@ -366,15 +382,15 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         // longer group owns an accumulator PAIR: each issuer sums its blocks of the group into its own
         // accumulator of the pair (its MMAs into that accumulator are issued in order), both commit the pair's
         // "full" barrier after their last block, and the epilogue adds the two int32 sums.
-        static_assert(kW4Tiles % 2 == 0 && kW4Accs % 2 == 0, "slot ownership of the two issuers");
+        static_assert(kTiles % 2 == 0 && kW4Accs % 2 == 0, "slot ownership of the two issuers");
         if (lane == 0) {
             const uint32_t idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, false, false, kW4Channels, p.mt);
             const uint32_t w = warp == 1 ? 0u : 1u;
             bool ok = true;
             // one K block: wait for its token tile and its unpacked tile, four MMAs, free both
             auto issue_block = [&](uint32_t i, uint32_t tmem_d, bool first) -> bool {
-                const uint32_t slot = i % kW4Tiles;
-                const uint32_t ph = (i / kW4Tiles) & 1;
+                const uint32_t slot = i % kTiles;
+                const uint32_t ph = (i / kTiles) & 1;
                 if constexpr (!kOneBlockGroups) {
                     // token tile and unpacked tile share the slot and its barriers (see the token producer)
                     bool got;
@@ -389,7 +405,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                     W4_PROBE_BEGIN();
                     tcgen05_fence_after();
                     const uint32_t sw_tile = ring + S::kCookedRing + slot * S::kCookedBytes;  // UMMA A operand
-                    const uint32_t sx_tile = ring + S::kTokenRing + slot * S::kTokenBytes;    // UMMA B operand
+                    const uint32_t sx_tile = ring + S::kTokenRing + slot * S::kTokenSlotBytes;    // UMMA B operand
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint64_t da = make_smem_desc_sw128(sw_tile + q * kUmmaK, 16, 1024);
@@ -487,10 +503,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t c = lane & 3;
         const uint32_t rsub = lane >> 2;  // 0..7: row inside a group of eight (= row & 7)
         for (uint32_t i = u; i < my_kb; i += 4) {
-            const uint32_t pl = (i / kW4Load) % kW4PackedLoads;          // load slot of this block's packed tile
-            const uint32_t pph = ((i / kW4Load) / kW4PackedLoads) & 1;
-            const uint32_t ps = i % kW4PackedSlots;                      // tile slot inside the ring
-            const uint32_t cs = i % kW4Tiles;
+            const uint32_t pl = (i / kW4Load) % kPackedLoads;          // load slot of this block's packed tile
+            const uint32_t pph = ((i / kW4Load) / kPackedLoads) & 1;
+            const uint32_t ps = i % kPackedSlots;                      // tile slot inside the ring
+            const uint32_t cs = i % kTiles;
             bool ok;
             {
                 W4_PROBE_BEGIN();
@@ -501,7 +517,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             }
             {
                 W4_PROBE_BEGIN();
-                ok = ok && mbar_wait(bar_tiles_free + cs * 8, ((i / kW4Tiles) & 1) ^ 1, s_abort, p.status,
+                ok = ok && mbar_wait(bar_tiles_free + cs * 8, ((i / kTiles) & 1) ^ 1, s_abort, p.status,
                                      kDevTimeoutConvert);
                 if (lane == 0 && u == 0) {
                     W4_PROBE_END(11);

@@ -88,6 +88,8 @@ def _run(cuda, a, packed, sw, sa, m, n, k, gs, split_k=False):
 @pytest.mark.parametrize("m,n,k,gs", [
     (128, 512, 1024, 128), (16, 256, 256, 128), (77, 200, 384, 128), (64, 128, 2048, 256),
     (130, 136, 512, 128), (1, 128, 128, 128), (257, 392, 8192, 1024), (130, 136, 2048, 256), (257, 64, 256, 128), (128, 4096, 2048, 128), (128, 256, 1024, 1024), (300, 384, 1280, 256), (33, 1000, 4096, 128), (40, 192, 1536, 512), (16, 64, 384, 128), (24, 128, 768, 384),
+    # scale groups of several K blocks: odd block counts, a single group, an odd number of groups
+    (48, 256, 1152, 1152), (128, 128, 640, 640), (20, 128, 1280, 640), (64, 256, 768, 256), (200, 256, 3840, 768),
 ])
 def test_w4a8_per_group_matches_oracle(cuda, exact, m, n, k, gs):
     a, w, packed, sw, sa = _problem(m, n, k, gs, seed=m + n + k)
