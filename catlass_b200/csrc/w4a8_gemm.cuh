@@ -229,7 +229,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t bar_x_full = bar_p_empty + kW4MaxPackedLoads * 8;    // a pair of token tiles landed
     const uint32_t bar_x_free = bar_x_full + kW4MaxTokenLoads * 8;   // the MMAs that read the pair completed
     const uint32_t bar_c_full = bar_x_free + kW4MaxTokenLoads * 8;   // unpacked tile written
-    const uint32_t bar_tiles_free = bar_c_full + kW4MaxTiles * 8;       // the MMAs that read the unpacked tile completed
+    const uint32_t bar_tiles_free = bar_c_full + kW4MaxTiles * 8;    // the MMAs that read the unpacked tile completed
     const uint32_t bar_acc_full = bar_tiles_free + kW4MaxTiles * 8;     // all MMAs of a pair of scale groups completed
     const uint32_t bar_acc_empty = bar_acc_full + kW4AccPairs * 8;   // the epilogue has read the pair's accumulators
     uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + S::kBarriers);
@@ -249,6 +249,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         g_begin + groups_per_rank <= p.num_groups ? groups_per_rank : p.num_groups - g_begin;
     const uint32_t kb_begin = g_begin * bpg;
     const uint32_t my_kb = my_groups * bpg;
+    // One scale group for the whole K range of this CTA: the epilogue has nothing to do until the last MMA, and what
+    // sets the pace is the unpacking (one warp needs ~1350 cycles per tile).  Four of the epilogue warps then take
+    // the lower half of every tile's rows off the unpack warps.
+    const bool unpack_helpers = !kOneBlockGroups && my_groups == 1;
     constexpr uint32_t kTmemCols = 512;
     // The token ring (64 KB) holds as many K blocks of mt x 128 bytes as fit: 4 blocks of 128 tokens, 8 of 64, 16 of
     // fewer.  Token tiles come from L2 with ~1-2 us of latency while every CTA of the grid asks for the same lines,
@@ -261,7 +265,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         *s_abort = 0;
         for (int i = 0; i < kW4MaxPackedLoads; ++i) {
             mbar_init(bar_p_full + i * 8, 1);
-            mbar_init(bar_p_empty + i * 8, kW4Load);  // one arrival per tile of the load
+            mbar_init(bar_p_empty + i * 8, kW4Load * (unpack_helpers ? 2 : 1));  // one arrival per tile (half)
         }
         for (int i = 0; i < kW4MaxTokenLoads; ++i) {
             mbar_init(bar_x_full + i * 8, 1);
@@ -269,7 +273,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
         for (int i = 0; i < kW4MaxTiles; ++i) {
             // longer groups: the slot's token tile lands on the same barrier (the producer's expect_tx arrival)
-            mbar_init(bar_c_full + i * 8, kOneBlockGroups ? 1 : 2);
+            mbar_init(bar_c_full + i * 8, kOneBlockGroups ? 1 : (unpack_helpers ? 3 : 2));
             mbar_init(bar_tiles_free + i * 8, 1);
         }
         for (int i = 0; i < kW4AccPairs; ++i) {
@@ -300,6 +304,92 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     // Ring discipline: local K block i uses packed slot i % kPackedSlots and tile slot i % kTiles; local
     // group j uses accumulator j % kW4Accs.  "The previous user of this slot is done" = wait with the inverted
     // parity of the use count (passes at once for the first use).
+
+    // ------------------------------------------------------- unpacking (warps 2..5; with helpers: also warps 6..9)
+    // Unpack warp u handles the local K blocks i = u, u+4, ... : sixteen 16-byte chunks per lane (rounds 0..3 of four
+    // chunks), one fence and one arrival per block; with helpers it does rounds 0..1 and epilogue warp 6+u rounds
+    // 2..3 of the same blocks.  A block's tile slot was last used kTiles blocks earlier; the warps that wait for it
+    // walk the same blocks one after the other: a parity wait can tell "the previous use is over" from "not yet"
+    // only if the waiter is never two uses ahead (kTiles = 6: the MMAs of block i-10, which this warp waited for
+    // at block i-4, were committed by the issuer of block i-12 after that block's).
+    // Lane l, step s works on row = s*8 + l/4, packed chunk c = l%4.
+    auto unpack_loop = [&](const uint32_t u, const uint32_t round_begin, const uint32_t round_end) {
+        // the packed tile was loaded with the 64-byte TMA swizzle: 16-byte chunk c of row r sits at
+        // chunk c ^ ((r >> 1) & 3); the operand tile uses the 128-byte swizzle: chunk j at j ^ (r & 7)
+        const uint32_t c = lane & 3;
+        const uint32_t rsub = lane >> 2;  // 0..7: row inside a group of eight (= row & 7)
+        for (uint32_t i = u; i < my_kb; i += 4) {
+            const uint32_t pl = (i / kW4Load) % kPackedLoads;          // load slot of this block's packed tile
+            const uint32_t pph = ((i / kW4Load) / kPackedLoads) & 1;
+            const uint32_t ps = i % kPackedSlots;                      // tile slot inside the ring
+            const uint32_t cs = i % kTiles;
+            bool ok;
+            {
+                W4_PROBE_BEGIN();
+                ok = mbar_wait(bar_p_full + pl * 8, pph, s_abort, p.status, kDevTimeoutConvert);
+                if (lane == 0 && u == 0 && round_begin == 0) {
+                    W4_PROBE_END(10);
+                }
+            }
+            {
+                W4_PROBE_BEGIN();
+                ok = ok && mbar_wait(bar_tiles_free + cs * 8, ((i / kTiles) & 1) ^ 1, s_abort, p.status,
+                                     kDevTimeoutConvert);
+                if (lane == 0 && u == 0 && round_begin == 0) {
+                    W4_PROBE_END(11);
+                }
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                return;
+            }
+            W4_PROBE_BEGIN();
+            const uint8_t* packed = smem + S::kPackedRing + ps * S::kPackedBytes;
+            uint8_t* cooked = smem + S::kCookedRing + cs * S::kCookedBytes;
+            // (four rounds of four chunks, deliberately not unrolled across rounds: the loop body has to stay
+            // small, the warps of this CTA run five different loops and share one instruction cache)
+#pragma unroll 1
+            for (uint32_t round = round_begin; round < round_end; ++round) {
+                uint4 q[4];
+#pragma unroll
+                for (uint32_t s = 0; s < 4; ++s) {
+                    const uint32_t row = (round * 4 + s) * 8 + rsub;
+                    q[s] = *reinterpret_cast<const uint4*>(packed + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
+                }
+                if (round + 1 == round_end) {
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(bar_p_empty + pl * 8);  // this tile is in registers (the slot refills after both)
+                    }
+                }
+#pragma unroll
+                for (uint32_t s = 0; s < 4; ++s) {
+                    const uint32_t row = (round * 4 + s) * 8 + rsub;
+                    const uint32_t w[4] = {q[s].x, q[s].y, q[s].z, q[s].w};
+                    uint32_t o[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t lo = (w[j] << 4) & 0xF0F0F0F0u;  // even k: low nibbles, moved up
+                        const uint32_t hi = w[j] & 0xF0F0F0F0u;         // odd k: high nibbles, in place
+                        o[2 * j] = __byte_perm(lo, hi, 0x5140);
+                        o[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
+                    }
+                    uint8_t* crow = cooked + row * 128;
+                    *reinterpret_cast<uint4*>(crow + (((2 * c) ^ rsub) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(crow + (((2 * c + 1) ^ rsub) << 4)) =
+                        make_uint4(o[4], o[5], o[6], o[7]);
+                }
+            }
+            fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar_c_full + cs * 8);
+            }
+            if (lane == 0 && u == 0 && round_begin == 0) {
+                W4_PROBE_END(12);
+            }
+        }
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------- packed-weight producer
@@ -491,91 +581,13 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
         __syncwarp();
     } else if (warp < 6) {
-        // ------------------------------------------------------- unpack warps (2..5)
-        // Warp u of the four handles the local K blocks i = u, u+4, ... on its own: sixteen 16-byte chunks per
-        // lane, one fence and one arrival per block.  With as many tile slots
-        // as unpack warps, slot u is only ever written by warp u, one block after the other: a parity wait can
-        // tell "the previous use is over" from "not yet" only if the waiter is never two uses ahead.
-        // Lane l, step s works on row = s*8 + l/4, packed chunk c = l%4.
-        const uint32_t u = warp - 2;
-        // the packed tile was loaded with the 64-byte TMA swizzle: 16-byte chunk c of row r sits at
-        // chunk c ^ ((r >> 1) & 3); the operand tile uses the 128-byte swizzle: chunk j at j ^ (r & 7)
-        const uint32_t c = lane & 3;
-        const uint32_t rsub = lane >> 2;  // 0..7: row inside a group of eight (= row & 7)
-        for (uint32_t i = u; i < my_kb; i += 4) {
-            const uint32_t pl = (i / kW4Load) % kPackedLoads;          // load slot of this block's packed tile
-            const uint32_t pph = ((i / kW4Load) / kPackedLoads) & 1;
-            const uint32_t ps = i % kPackedSlots;                      // tile slot inside the ring
-            const uint32_t cs = i % kTiles;
-            bool ok;
-            {
-                W4_PROBE_BEGIN();
-                ok = mbar_wait(bar_p_full + pl * 8, pph, s_abort, p.status, kDevTimeoutConvert);
-                if (lane == 0 && u == 0) {
-                    W4_PROBE_END(10);
-                }
-            }
-            {
-                W4_PROBE_BEGIN();
-                ok = ok && mbar_wait(bar_tiles_free + cs * 8, ((i / kTiles) & 1) ^ 1, s_abort, p.status,
-                                     kDevTimeoutConvert);
-                if (lane == 0 && u == 0) {
-                    W4_PROBE_END(11);
-                }
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-                break;
-            }
-            W4_PROBE_BEGIN();
-            const uint8_t* packed = smem + S::kPackedRing + ps * S::kPackedBytes;
-            uint8_t* cooked = smem + S::kCookedRing + cs * S::kCookedBytes;
-            // (four rounds of four chunks, deliberately not unrolled across rounds: the loop body has to stay
-            // small, the warps of this CTA run five different loops and share one instruction cache)
-#pragma unroll 1
-            for (uint32_t round = 0; round < 4; ++round) {
-                uint4 q[4];
-#pragma unroll
-                for (uint32_t s = 0; s < 4; ++s) {
-                    const uint32_t row = (round * 4 + s) * 8 + rsub;
-                    q[s] = *reinterpret_cast<const uint4*>(packed + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
-                }
-                if (round == 3) {
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(bar_p_empty + pl * 8);  // this tile is in registers (the slot refills after both)
-                    }
-                }
-#pragma unroll
-                for (uint32_t s = 0; s < 4; ++s) {
-                    const uint32_t row = (round * 4 + s) * 8 + rsub;
-                    const uint32_t w[4] = {q[s].x, q[s].y, q[s].z, q[s].w};
-                    uint32_t o[8];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t lo = (w[j] << 4) & 0xF0F0F0F0u;  // even k: low nibbles, moved up
-                        const uint32_t hi = w[j] & 0xF0F0F0F0u;         // odd k: high nibbles, in place
-                        o[2 * j] = __byte_perm(lo, hi, 0x5140);
-                        o[2 * j + 1] = __byte_perm(lo, hi, 0x7362);
-                    }
-                    uint8_t* crow = cooked + row * 128;
-                    *reinterpret_cast<uint4*>(crow + (((2 * c) ^ rsub) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4*>(crow + (((2 * c + 1) ^ rsub) << 4)) =
-                        make_uint4(o[4], o[5], o[6], o[7]);
-                }
-            }
-            fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_c_full + cs * 8);
-            }
-            if (lane == 0 && u == 0) {
-                W4_PROBE_END(12);
-            }
-        }
+        unpack_loop(warp - 2, 0, unpack_helpers ? 2u : 4u);
     } else {
         // ------------------------------------------------------- epilogue warps 6..13
         const uint32_t ew = warp - 6;     // 0..7
+        if (unpack_helpers && ew < 4) {
+            unpack_loop(ew, 2, 4);  // the lower halves of unpack warp ew's tiles, then the epilogue of the one group
+        }
         const uint32_t quad = warp & 3;   // TMEM lane quarter this warp may read: channels quad*32 .. +31
         const uint32_t half = ew >> 2;    // which part of the token columns (see hcols)
         // the two warps of a lane quarter split the token columns: 64 each, or 32 each when the tile has <= 64
