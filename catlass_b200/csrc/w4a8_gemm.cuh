@@ -81,9 +81,18 @@ __device__ unsigned long long g_w4a8_probe[64];
             atomicAdd(&g_w4a8_probe[slot], static_cast<unsigned long long>(clock64() - probe_t0__)); \
         }                                                                                     \
     } while (0)
+#define W4_STAMP(slot)                                                                        \
+    do {                                                                                      \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {                  \
+            atomicAdd(&g_w4a8_probe[slot], static_cast<unsigned long long>(clock64() - kernel_t0__)); \
+        }                                                                                     \
+    } while (0)
+#define W4_STAMP_INIT() const long long kernel_t0__ = clock64()
 #else
 #define W4_PROBE_BEGIN() do { } while (0)
 #define W4_PROBE_END(slot) do { } while (0)
+#define W4_STAMP(slot) do { } while (0)
+#define W4_STAMP_INIT() do { } while (0)
 #endif
 
 struct W4A8Params {
@@ -128,7 +137,7 @@ struct W4A8Smem {
     // acc_empty [accumulator pairs]
     static constexpr int kBarriers =
         2 * kW4MaxPackedLoads + 2 * kW4MaxTokenLoads + 2 * kW4MaxTiles + 2 * kW4AccPairs;
-    static constexpr int kBarrierBytes = kBarriers * 8 + 16;
+    static constexpr int kBarrierBytes = kBarriers * 8 + 16 + kW4Tokens * 4;  // + the tile's per-token scales
     static constexpr int kTotalBytes = 1024 + kRingBytes + kBarrierBytes;
     static_assert(kPackedSlots % kW4Load == 0 && kPackedSlots <= kW4MaxPackedSlots && kTiles <= kW4MaxTiles, "rings");
     static_assert(kTotalBytes <= 227 * 1024, "shared memory budget");
@@ -218,6 +227,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     static_assert(kTiles == kW4Tiles || !kOneBlockGroups, "one-block groups: one tile slot per unpack warp");
     constexpr uint32_t kPackedSlots = S::kPackedSlots, kPackedLoads = S::kPackedLoads;
     extern __shared__ uint8_t smem_raw[];
+    W4_STAMP_INIT();
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t* smem = smem_raw + pad;
@@ -234,6 +244,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const uint32_t bar_acc_empty = bar_acc_full + kW4AccPairs * 8;   // the epilogue has read the pair's accumulators
     uint32_t* s_tmem_ptr = reinterpret_cast<uint32_t*>(s_bars + S::kBarriers);
     volatile uint32_t* s_abort = s_tmem_ptr + 1;
+    float* s_sa = reinterpret_cast<float*>(s_tmem_ptr + 4);  // per-token scales of this tile's rows (see the epilogue)
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -293,6 +304,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem_ptr;
     grid_launch_dependents();  // a dependent launch may start its own set-up and weight prefetch from here on
+    if (warp == 6) {
+        W4_STAMP(20);  // set-up done
+    }
 
     // running sums of this thread's channel over its 64 token columns, two fp32 per register (epilogue warps)
     unsigned long long y2[32];
@@ -605,6 +619,14 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             return j < my_groups ? __ldg(sw_col + static_cast<size_t>(j) * p.n) : 0.0f;
         };
         float s_now = load_sw(0), s_next1 = load_sw(1), s_next2 = load_sw(2);
+        if (ew >= 4) {
+            // The per-token scales of this tile's rows, fetched now for the output loop at the end: there a load
+            // from global memory per step of the loop was 0.35 us each time, on the kernel's tail.  (They may depend
+            // on the kernel before this one on the stream; the barrier before the output loop orders the stores.)
+            grid_dependency_wait();
+            const uint32_t t = (ew - 4) * 32 + lane;
+            s_sa[t] = static_cast<uint32_t>(m0) + t < p.m ? __ldg(p.sa + m0 + t) : 0.0f;
+        }
         auto scale_of = [&](uint32_t j) -> float {
             const float s = s_now;
             s_now = s_next1;
@@ -744,6 +766,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     //   landing [splits - 1][128 / splits columns][128 channels] fp32: the other CTAs' sums for the columns
     //           this CTA reduces and stores
     const bool is_epi = warp >= 6 && warp < 14;
+    if (warp == 6) {
+        W4_STAMP(21);  // K loop and the last group's sums done
+    }
     float* ytile = reinterpret_cast<float*>(smem);
     float* landing = ytile + kW4Tokens * kW4Channels;
     const uint32_t split_log2 = splits == 4 ? 2u : (splits == 2 ? 1u : 0u);
@@ -788,6 +813,9 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     } else if (is_epi) {
         asm volatile("bar.sync 1, 256;" ::: "memory");  // ytile complete (epilogue warps only)
     }
+    if (warp == 6) {
+        W4_STAMP(22);  // sums in shared memory
+    }
     if (is_epi && *s_abort == 0) {
         // each thread: one token row, eight channels -> one 16-byte store
         const bool vec_ok = (p.n & 7u) == 0;
@@ -808,7 +836,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
                 b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
             }
-            const float sa = __ldg(p.sa + mrow);
+            const float sa = s_sa[col];
             const float y[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
             uint16_t* drow = p.d + static_cast<size_t>(mrow) * p.n + ncol;
             const bool f16 = p.out_f16 != 0;
@@ -827,11 +855,15 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         }
     }
 
+    if (warp == 6) {
+        W4_STAMP(23);  // output stored
+    }
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc<1>(tmem_base, kTmemCols);
+        W4_STAMP(24);  // TMEM released
     }
 }
 
