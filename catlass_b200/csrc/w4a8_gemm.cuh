@@ -198,9 +198,10 @@ __device__ __forceinline__ unsigned long long pack_pair(float lo, float hi)
 
 // y2[kOff .. kOff+7] (16 token columns) += group sums r[0..15] * s.
 // kMagic: |r| < 2^22 (one 128-wide K block per group).
-template <bool kMagic, int kOff>
-__device__ __forceinline__ void accumulate16(unsigned long long (&y2)[32], const uint32_t (&r)[16], float s)
+template <bool kMagic, int kOff, int kSums>
+__device__ __forceinline__ void accumulate16(unsigned long long (&y2)[kSums], const uint32_t (&r)[16], float s)
 {
+    static_assert(kOff + 8 <= kSums, "running sums of this thread");
     const unsigned long long s2 = pack_pair(s, s);
 #pragma unroll
     for (int v = 0; v < 8; ++v) {
@@ -309,9 +310,11 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     }
 
     // running sums of this thread's channel over its 64 token columns, two fp32 per register (epilogue warps)
-    unsigned long long y2[32];
+    // (six tile slots: token tiles of at most 64 rows, 32 columns per epilogue thread)
+    constexpr int kSums = kTiles == 6 ? 16 : 32;
+    unsigned long long y2[kSums];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
+    for (int i = 0; i < kSums; ++i) {
         y2[i] = 0ull;
     }
 
@@ -694,19 +697,21 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                 piece(0);
                 accumulate16<false, 0>(y2, ra, s);
                 piece(1);
-                if (np == 2) {
-                    accumulate16<false, 8>(y2, ra, s);
-                    piece(2);
-                    accumulate16<false, 16>(y2, ra, s);
-                    piece(3);
-                    release(j);
-                    accumulate16<false, 24>(y2, ra, s);
-                } else {
-                    release(j);
-                    accumulate16<false, 8>(y2, ra, s);
+                if constexpr (kSums == 32) {
+                    if (np == 2) {
+                        accumulate16<false, 8>(y2, ra, s);
+                        piece(2);
+                        accumulate16<false, 16>(y2, ra, s);
+                        piece(3);
+                        release(j);
+                        accumulate16<false, 24>(y2, ra, s);
+                        continue;
+                    }
                 }
+                release(j);
+                accumulate16<false, 8>(y2, ra, s);
             }
-        } else {
+        } else if constexpr (kSums == 32) {
             // Two register sets alternate over the 16-column pieces of a group; the read of the next piece (of
             // the next group, at the end) is in flight while the sums of the current one are updated.
             uint32_t ra[16], rb[16];
@@ -780,7 +785,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         const uint32_t hcols = p.mt > 64 ? 64u : 32u;  // token columns per warp, as in the epilogue loop
         float* dst = ytile + ((warp - 6) >> 2) * hcols * kW4Channels + ch;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < kSums; ++i) {
             if (2u * i < hcols) {
                 float lo, hi;
                 unpack_pair(y2[i], lo, hi);
