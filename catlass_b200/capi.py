@@ -101,6 +101,11 @@ class MxGroupedSwigluQuantArgs(ctypes.Structure):
     ]
 
 
+class QuantizeInt8Args(ctypes.Structure):
+    _fields_ = [("rows", _u32), ("k", _u32), ("x_type", _u32), ("reserved", _u32), ("x_pitch", _u64), ("x", _vp),
+                ("q", _vp), ("scale", _vp)]
+
+
 class MxQuantizeArgs(ctypes.Structure):
     _fields_ = [
         ("rows", _u32), ("k", _u32), ("format", _u32), ("x_type", _u32), ("x_pitch", _u64),
@@ -164,6 +169,10 @@ def load():
     lib.cb200_mx_quantize.restype = ctypes.c_int
     lib.cb200_mx_quantize_can_implement.argtypes = [ctypes.POINTER(MxQuantizeArgs)]
     lib.cb200_mx_quantize_can_implement.restype = ctypes.c_int
+    lib.cb200_quantize_per_token_int8.argtypes = [ctypes.POINTER(QuantizeInt8Args), _vp]
+    lib.cb200_quantize_per_token_int8.restype = ctypes.c_int
+    lib.cb200_quantize_per_token_int8_can_implement.argtypes = [ctypes.POINTER(QuantizeInt8Args)]
+    lib.cb200_quantize_per_token_int8_can_implement.restype = ctypes.c_int
     lib.cb200_mx_matmul_static.argtypes = [ctypes.POINTER(MxMatmulArgs), _vp]
     lib.cb200_mx_matmul_static.restype = ctypes.c_int
     lib.cb200_mx_matmul_static_scratch_bytes.restype = _u64
@@ -426,3 +435,11 @@ def grouped_quant_matmul_host(a_host, group_list_host, per_token_host, d_host, b
                       chunks, workspace)
     _check("cb200_grouped_quant_matmul_slice_m_host",
            load().cb200_grouped_quant_matmul_slice_m_host(ctypes.byref(args), _stream(stream)))
+
+
+def quantize_per_token_int8(x, q, scale, rows, k, x_type=DTYPE_F32, x_pitch=0, stream=None):
+    """x: fp32 / bf16 [rows][k] -> q int8 [rows][k] and scale fp32 [rows] (amax / 127), the A operand and the
+    per-token scale of the W8A8 entry points."""
+    args = QuantizeInt8Args(rows=rows, k=k, x_type=x_type, reserved=0, x_pitch=x_pitch, x=_p(x), q=_p(q), scale=_p(scale))
+    _check("cb200_quantize_per_token_int8", load().cb200_quantize_per_token_int8(ctypes.byref(args), _stream(stream)))
+

@@ -12,6 +12,7 @@
 #include "w8a8_gemm_pair.cuh"
 #include "w8a8_smallm.cuh"
 #include "w4a8_gemm.cuh"
+#include "quant_int8.cuh"
 #include "mx_gemm.cuh"
 #include "mx_gemm_pair.cuh"
 #include "routing.cuh"
@@ -2055,6 +2056,90 @@ int cb200_grouped_quant_matmul_slice_m_host(const cb200_grouped_quant_matmul_hos
     // the caller's stream completes only after the last copy-out
     CB200_CUDA_TRY(cudaEventRecord(hp->all_out, hp->out));
     CB200_CUDA_TRY(cudaStreamWaitEvent(stream, hp->all_out, 0));
+    return CB200_SUCCESS;
+}
+
+}  // extern "C"
+
+extern "C" {
+
+int cb200_quantize_per_token_int8_can_implement(const cb200_quantize_int8_args* args)
+{
+    if (args == nullptr || args->reserved != 0) {
+        return CB200_INVALID;
+    }
+    if (args->rows == 0 || args->k == 0) {
+        return CB200_SUCCESS;
+    }
+    if (args->x == nullptr || args->q == nullptr || args->scale == nullptr ||
+        (args->x_type != CB200_DTYPE_F32 && args->x_type != CB200_DTYPE_BF16) || args->k % 16u != 0) {
+        return CB200_INVALID;
+    }
+    const uint64_t pitch = args->x_pitch != 0 ? args->x_pitch : args->k;
+    const uint64_t elem = args->x_type == CB200_DTYPE_F32 ? 4u : 2u;
+    if (pitch < args->k || (pitch * elem) % 16u != 0 || (reinterpret_cast<uintptr_t>(args->x) & 15u) != 0 ||
+        (reinterpret_cast<uintptr_t>(args->q) & 15u) != 0 || (reinterpret_cast<uintptr_t>(args->scale) & 3u) != 0) {
+        return CB200_INVALID;
+    }
+    return CB200_SUCCESS;
+}
+
+int cb200_quantize_per_token_int8(const cb200_quantize_int8_args* args, void* stream_v)
+{
+    int rc = cb200_quantize_per_token_int8_can_implement(args);
+    if (rc != CB200_SUCCESS || args->rows == 0 || args->k == 0) {
+        return rc;
+    }
+    DeviceState* dev = nullptr;
+    rc = device_state(&dev);
+    if (rc != CB200_SUCCESS) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const uint64_t pitch = args->x_pitch != 0 ? args->x_pitch : args->k;
+    // one warp per row, eight warps per CTA, eight CTAs per SM at most
+    const uint32_t want = (args->rows + 7u) / 8u;
+    const uint32_t cap = static_cast<uint32_t>(dev->sm_count) * 8u;
+    const uint32_t blocks = want < cap ? want : cap;
+    int8_t* q = static_cast<int8_t*>(args->q);
+    float* scale = static_cast<float*>(args->scale);
+    const bool bf16 = args->x_type == CB200_DTYPE_BF16;
+    const uint64_t row_bytes = static_cast<uint64_t>(args->k) * (bf16 ? 2u : 4u);
+    if (row_bytes <= kQuantInt8StageBytes) {
+        // rows staged through shared memory, one CTA of eight warps per SM
+        constexpr uint32_t kSmem = 8u * kQuantInt8StageBytes + 2u * 8u * 8u + 16u;
+        static PerDeviceOnce once;
+        int devid = 0;
+        rc = current_device(&devid);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        rc = once.run(devid, [&]() -> int {
+            CB200_CUDA_TRY(cudaFuncSetAttribute(quant_int8_staged_kernel<true>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+            CB200_CUDA_TRY(cudaFuncSetAttribute(quant_int8_staged_kernel<false>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+            return CB200_SUCCESS;
+        });
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        const uint32_t sms = static_cast<uint32_t>(dev->sm_count);
+        const uint32_t grid = want < sms ? want : sms;
+        if (bf16) {
+            quant_int8_staged_kernel<true><<<grid, kQuantInt8Threads, kSmem, stream>>>(args->x, q, scale, args->rows,
+                                                                                        args->k, pitch, dev->status);
+        } else {
+            quant_int8_staged_kernel<false><<<grid, kQuantInt8Threads, kSmem, stream>>>(args->x, q, scale, args->rows,
+                                                                                         args->k, pitch, dev->status);
+        }
+    } else if (bf16) {
+        quant_int8_kernel<true><<<blocks, kQuantInt8Threads, 0, stream>>>(args->x, q, scale, args->rows, args->k, pitch);
+    } else {
+        quant_int8_kernel<false><<<blocks, kQuantInt8Threads, 0, stream>>>(args->x, q, scale, args->rows, args->k, pitch);
+    }
+    CB200_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     return CB200_SUCCESS;
 }
 

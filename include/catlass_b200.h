@@ -550,6 +550,31 @@ typedef struct cb200_mx_quantize_args {
 CB200_API int cb200_mx_quantize_can_implement(const cb200_mx_quantize_args *args);
 CB200_API int cb200_mx_quantize(const cb200_mx_quantize_args *args, void *stream);
 
+/*
+ * Per-token int8 quantisation of activations on the device: x (fp32 or bf16, rows x k, row pitch x_pitch elements)
+ * -> the A operand and the per-token scale of cb200_quant_matmul and the grouped W8A8 entry points:
+ *     q      [rows][k] int8 (row pitch k)
+ *     scale  [rows] fp32
+ * Rule: amax = max |x| over the row; scale = amax / 127; q = clamp(rint(x * (127 / amax)), -127, 127) with one fp32
+ * multiply per element and round-half-to-even; an all-zero row gives scale 0 and codes 0.  Inputs are expected to
+ * be finite.  The reference has no device kernel for this step (its quantised examples start from int8 data made
+ * on the host, examples/12_quant_matmul/gen_data.py); the entry is the stand-alone step in front of the W8A8
+ * matmuls, as cb200_mx_quantize is in front of the MX ones.  No workspace.
+ * Requirements: k a multiple of 16; x, q and the rows of x (x_pitch) 16-byte aligned.
+ */
+typedef struct cb200_quantize_int8_args {
+    uint32_t rows, k;
+    uint32_t x_type;      /* CB200_DTYPE_F32 or CB200_DTYPE_BF16 */
+    uint32_t reserved;    /* 0 */
+    uint64_t x_pitch;     /* elements between rows of x; 0 = k */
+    const void *x;
+    void *q;
+    void *scale;
+} cb200_quantize_int8_args;
+
+CB200_API int cb200_quantize_per_token_int8_can_implement(const cb200_quantize_int8_args *args);
+CB200_API int cb200_quantize_per_token_int8(const cb200_quantize_int8_args *args, void *stream);
+
 /* ---- library / device state ---- */
 
 /* Reads and clears the status word kernels of this library write on the current device when a bounded

@@ -358,6 +358,24 @@ static uint8_t snap_magnitude(float mag, int fmt)
     return ((mag - lower) <= (upper - mag)) ? (uint8_t)lo : (uint8_t)(lo + 1);
 }
 
+void orc_quantize_per_token_int8(uint32_t rows, uint32_t cols, const float *x, int8_t *q, float *scale)
+{
+    for (uint32_t r = 0; r < rows; ++r) {
+        const float *xr = x + (size_t)r * cols;
+        float amax = 0.0f;
+        for (uint32_t c = 0; c < cols; ++c) {
+            const float a = fabsf(xr[c]);
+            amax = a > amax ? a : amax;
+        }
+        const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+        scale[r] = amax / 127.0f;
+        for (uint32_t c = 0; c < cols; ++c) {
+            const float t = nearbyintf(xr[c] * inv);  /* round half to even (default rounding mode) */
+            q[(size_t)r * cols + c] = (int8_t)(t > 127.0f ? 127.0f : (t < -127.0f ? -127.0f : t));
+        }
+    }
+}
+
 void orc_mx_quantize(uint32_t rows, uint32_t cols, int fmt, const float *x, uint8_t *q, uint8_t *sf,
                      float *deq)
 {

@@ -128,6 +128,14 @@ static inline int orc_int4(uint8_t nibble) { return (int)((nibble & 0xF) ^ 8) - 
 void orc_mx_quantize(uint32_t rows, uint32_t cols, int fmt, const float *x, uint8_t *q, uint8_t *sf,
                      float *deq);
 float orc_e4m3_to_float(uint8_t v);
+
+/*
+ * Per-token int8 quantisation of activations (the step in front of the W8A8 matmuls; the reference has no
+ * implementation of it: parity unpinned, this file is the definition the library's header states):
+ *   amax = max |x| over the row; scale = amax / 127; inv = 127 / amax (0 for an all-zero row);
+ *   q = clamp(rint(x * inv), -127, 127), one fp32 multiply, round half to even.
+ */
+void orc_quantize_per_token_int8(uint32_t rows, uint32_t cols, const float *x, int8_t *q, float *scale);
 float orc_e2m1_to_float(uint8_t v);
 float orc_e8m0_to_float(uint8_t v);
 

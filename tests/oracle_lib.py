@@ -152,6 +152,16 @@ def w4a8_per_tensor(a, w_packed, scalar, m, n, k):
     return out
 
 
+def quantize_per_token_int8(x):
+    """x: fp32 [rows, cols] -> (q int8 [rows, cols], scale fp32 [rows])."""
+    x = _c(x, np.float32)
+    rows, cols = x.shape
+    q = np.empty((rows, cols), np.int8)
+    scale = np.empty(rows, np.float32)
+    lib().orc_quantize_per_token_int8(_c_u32(rows), _c_u32(cols), _ptr(x), _ptr(q), _ptr(scale))
+    return q, scale
+
+
 def mx_quantize(x, fmt, want_deq=False):
     """x: fp32 [rows, cols], blocks of 32 along cols. Returns (codes u8 [rows,cols], sf u8 [rows,ceil(cols/32)])."""
     x = _c(x, np.float32)

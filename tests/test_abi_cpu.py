@@ -72,6 +72,7 @@ def test_struct_layout_matches_the_header(lib):
         ("cb200_mx_grouped_swiglu_quant_args", capi.MxGroupedSwigluQuantArgs),
         ("cb200_mx_grouped_finalize_routing_args", capi.MxGroupedFinalizeRoutingArgs),
         ("cb200_mx_quantize_args", capi.MxQuantizeArgs),
+        ("cb200_quantize_int8_args", capi.QuantizeInt8Args),
     ]
     lines = []
     for cname, ctype in pairs:

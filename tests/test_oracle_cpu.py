@@ -311,3 +311,22 @@ def test_zn_storage_helper_matches_the_reference_layout(w8a8_golden):
             assert flat.size == int(row[4])   # Capacity()
             for r, c in coords:
                 assert flat[P.zn_offset(rows, cols, int(r), int(c))] == b[int(r), int(c)]
+
+
+def test_quantize_per_token_int8_definition():
+    """The int8 activation quantiser's oracle against its definition written with numpy (round half to even, one
+    fp32 multiply per element, scale = amax / 127, all-zero rows)."""
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal((37, 96)) * rng.uniform(1e-4, 30.0, (37, 1))).astype(np.float32)
+    x[3] = 0.0
+    x[4, :8] = np.float32(0.5) * np.abs(x[4]).max() / 127 * np.arange(-4, 4)
+    q, s = O.quantize_per_token_int8(x)
+    amax = np.abs(x).max(axis=1)
+    assert np.array_equal(s, (amax / np.float32(127.0)).astype(np.float32))
+    with np.errstate(divide="ignore"):
+        inv = np.where(amax > 0, np.float32(127.0) / amax, np.float32(0.0)).astype(np.float32)
+    want = np.clip(np.rint((x * inv[:, None]).astype(np.float32)), -127, 127).astype(np.int8)
+    assert np.array_equal(q, want)
+    assert (q[3] == 0).all() and s[3] == 0.0
+    assert np.abs(q).max(axis=1)[np.arange(37) != 3].min() == 127
+
