@@ -10,7 +10,7 @@ One step = one pass over all routed rows.  Prints ONE JSON line on rank 0.
 The line's `value` is timed over exactly K steps.  Next to it the line carries
   sustained   the same launch repeated for >= 2 s (power-capped clocks), with the clock samples of that region
   secondary   (1 GPU only) the other workloads of the metric - decode_a, decode_b, prefill, w4a8, w4a8_per_tensor,
-              mxfp8, mxfp4, mx_swiglu, mx_routing, quant_int8 -
+              mxfp8, mxfp4, mx_swiglu, mx_routing, quant_int8, quant_mx -
               each replayed from a CUDA graph for >= 1.5 s so that its clock record holds >= 10 samples
   verify      the shard outputs of all ranks assembled with one all-gather and sampled rows of every expert,
               including the rows on both sides of every shard and tile boundary, compared with the CPU oracle
@@ -44,7 +44,7 @@ DENSE = {
     "decode_b": (16, 4096, 14336),
 }
 SECONDARY = ["decode_a", "decode_b", "prefill", "w4a8", "w4a8_per_tensor", "mxfp8", "mxfp4", "mx_swiglu", "mx_routing",
-             "quant_int8"]
+             "quant_int8", "quant_mx"]
 INT8_PER_BF16 = 2.0  # kind::i8 issues at twice the bf16 rate on the same tensor cores
 L2_BYTES = 126e6
 
@@ -717,6 +717,43 @@ def run_quant_int8(sampler, seconds):
     }
 
 
+def run_quant_mx(sampler, seconds):
+    """MX quantisation (E4M3 codes + E8M0 scales) of bf16 activations, 32768 x 7168: the step in front of the MX
+    matmuls, HBM-bound by its bytes, bound by its per-element arithmetic in practice."""
+    import torch
+    from catlass_b200 import capi
+    rows, k = 32768, 7168
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(98)
+    copies = 2
+    xs = [torch.randn((rows, k), dtype=torch.float32, device=dev, generator=gen).to(torch.bfloat16) for _ in range(copies)]
+    q = torch.empty((rows, k), dtype=torch.uint8, device=dev)
+    sf = torch.empty((rows, k // 32), dtype=torch.uint8, device=dev)
+
+    def launch(i):
+        capi.mx_quantize(xs[i % copies], q, sf, rows, k, capi.MX_E4M3, x_type=capi.DTYPE_BF16)
+
+    r = graph_region(launch, copies, seconds, sampler)
+    check_device_status()
+    nbytes = 2 * rows * k + rows * k + rows * (k // 32)
+    peaks = measured_peaks()
+    value = nbytes / (r["ms"] * 1e-3) / 1e9
+    burst = nbytes / (r["burst_ms"] * 1e-3) / 1e9
+    return {
+        "name": "quant_mx", "metric": "quantize_mx_hbm_gbs", "value": value, "unit": "GB/s", "ms_per_step": r["ms"],
+        "burst_value": burst, "burst_ms_per_step": r["burst_ms"],
+        "regime": f"sustained: {r['launches_timed']} launches back to back, {r['region_s']:.2f} s",
+        "config": {"workload": f"quant_mx: bf16 [{rows}][{k}] -> E4M3 codes + E8M0 scales per 32 elements",
+                   "l2": f"inputs rotate over {copies} copies of 470 MB: every pass reads HBM"},
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": value / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": f"{peaks['source']} HBM copy rate", "burst_frac": burst / peaks["hbm_gbs"],
+                     "algorithmic_bytes": nbytes, "frac_of_8TBs": value / 8000.0},
+        "gpu_launches": r["launches_timed"], "cuda_graph": r["cuda_graph"], "clocks": r["clocks"],
+    }
+
+
 def run_mx(name, sampler, seconds):
     """MXFP8 / MXFP4 block-scaled matmul at M=N=K=8192 (random element codes and exponents: timing only)."""
     import torch
@@ -873,6 +910,8 @@ def run_secondary(name, sampler, seconds, args):
         return run_dense(name, sampler, seconds)
     if name == "quant_int8":
         return run_quant_int8(sampler, seconds)
+    if name == "quant_mx":
+        return run_quant_mx(sampler, seconds)
     if name in ("w4a8", "w4a8_per_tensor"):
         return run_w4a8(sampler, seconds, split_k=bool(args.w4a8_split_k), per_tensor=name == "w4a8_per_tensor")
     return run_mx(name, sampler, seconds)
@@ -883,7 +922,7 @@ def standalone_line(entry, args):
     line = {"metric": entry["metric"], "value": entry["value"], "unit": entry["unit"], "n_gpus": 1,
             "steps": entry["gpu_launches"], "warmup": args.warmup, "ms_per_step": entry["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"w4a8": "int4xint8->int32->f32", "w4a8_per_tensor": "int4xint8->int32->f32", "quant_int8": "bf16->int8", "mxfp8": "e4m3xe8m0", "mxfp4": "e2m1xe8m0"}.get(entry["name"], "int8"),
+            "dtype": {"w4a8": "int4xint8->int32->f32", "w4a8_per_tensor": "int4xint8->int32->f32", "quant_int8": "bf16->int8", "quant_mx": "bf16->e4m3xe8m0", "mxfp8": "e4m3xe8m0", "mxfp4": "e2m1xe8m0"}.get(entry["name"], "int8"),
             "data": "synthetic"}
     line.update({k: v for k, v in entry.items() if k not in ("name", "metric", "value", "unit", "ms_per_step")})
     return line

@@ -2265,7 +2265,50 @@ int cb200_mx_quantize(const cb200_mx_quantize_args* args, void* stream_v)
     const uint32_t blocks = static_cast<uint32_t>(dev->sm_count) * 8u;
     uint8_t* q = static_cast<uint8_t*>(args->q);
     uint8_t* sf = static_cast<uint8_t*>(args->scale);
-    if (fp4) {
+    const uint64_t row_bytes = static_cast<uint64_t>(args->k) * (bf16 ? 2u : 4u);
+    if (args->k % 64u == 0 && row_bytes <= kMxQuantStageBytes && (x_pitch * (bf16 ? 2u : 4u)) % 16u == 0 &&
+        (reinterpret_cast<uintptr_t>(args->q) & 15u) == 0) {
+        // the aligned case: rows staged through shared memory, one CTA of eight warps per SM
+        constexpr uint32_t kSmem = 8u * kMxQuantStageBytes + 2u * 8u * 8u + 16u;
+        static PerDeviceOnce once;
+        int devid = 0;
+        rc = current_device(&devid);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        rc = once.run(devid, [&]() -> int {
+            CB200_CUDA_TRY(cudaFuncSetAttribute(mx_quantize_staged_kernel<false, false>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+            CB200_CUDA_TRY(cudaFuncSetAttribute(mx_quantize_staged_kernel<false, true>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+            CB200_CUDA_TRY(cudaFuncSetAttribute(mx_quantize_staged_kernel<true, false>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+            CB200_CUDA_TRY(cudaFuncSetAttribute(mx_quantize_staged_kernel<true, true>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+            return CB200_SUCCESS;
+        });
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        const uint32_t want = (args->rows + 7u) / 8u;
+        const uint32_t sms = static_cast<uint32_t>(dev->sm_count);
+        const uint32_t grid = want < sms ? want : sms;
+        if (fp4) {
+            if (bf16) {
+                mx_quantize_staged_kernel<true, true><<<grid, kMxQuantThreads, kSmem, stream>>>(
+                    args->x, q, sf, args->rows, args->k, x_pitch, dev->status);
+            } else {
+                mx_quantize_staged_kernel<true, false><<<grid, kMxQuantThreads, kSmem, stream>>>(
+                    args->x, q, sf, args->rows, args->k, x_pitch, dev->status);
+            }
+        } else if (bf16) {
+            mx_quantize_staged_kernel<false, true><<<grid, kMxQuantThreads, kSmem, stream>>>(
+                args->x, q, sf, args->rows, args->k, x_pitch, dev->status);
+        } else {
+            mx_quantize_staged_kernel<false, false><<<grid, kMxQuantThreads, kSmem, stream>>>(
+                args->x, q, sf, args->rows, args->k, x_pitch, dev->status);
+        }
+    } else if (fp4) {
         if (bf16) {
             mx_quantize_kernel<true, true><<<blocks, 256, 0, stream>>>(args->x, q, sf, args->rows, args->k, x_pitch, q_pitch, sf_pitch);
         } else {

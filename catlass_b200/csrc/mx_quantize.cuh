@@ -12,10 +12,21 @@
 // (experimental/gmm/ascend950_fp8_mx_grouped_matmul_slice_m_swiglu_mx_quant).  HBM-bound: 4 (or 2) bytes read and
 // about one byte written per element; a warp handles 128 consecutive elements (four blocks) per step with 16-byte
 // loads and 4-byte stores.
+//
+// mx_quantize_staged_kernel serves the aligned case (k a multiple of 64, rows of at most 28 KB on 16-byte boundaries):
+// one warp per row, the whole row brought into the warp's shared-memory slot by ONE bulk copy (the next row in
+// flight meanwhile when two fit), a lane working on 16 consecutive elements (half a block) per step, the codes made
+// by the conversion instructions (cvt.rn.satfinite.e4m3x2 / e2m1x2) and then corrected where round-to-nearest-even
+// and the reference's tie rule differ.  mx_quantize_kernel (plain loads, 4 elements per lane and step, any k and
+// pitch) had 256 bytes of loads outstanding per warp and ran at 0.2 of the HBM copy rate on 32768 x 7168 bf16.
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
 #include <stdint.h>
+
+#include "ptx.cuh"
 
 namespace cb200 {
 
@@ -139,6 +150,213 @@ __global__ void mx_quantize_kernel(const void* __restrict__ x, uint8_t* __restri
                     }
                 }
             }
+        }
+    }
+}
+
+constexpr int kMxQuantThreads = 256;
+constexpr uint32_t kMxQuantStageBytes = 28u * 1024u;  // shared memory per warp
+
+// Two scaled values -> two element codes (a in bits 0-7 / 0-3, b above), the reference's rule:
+// nearest, a tie to the smaller magnitude, saturating, zero always +0.
+template <bool kFp4>
+__device__ __forceinline__ uint32_t mx_codes2(float a, float b)
+{
+    if constexpr (kFp4) {
+        uint32_t c = __nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);  // ties to even
+        // the ties between an odd code below and an even code above (0.75, 1.75, 3.5) went up: take them down
+        const float ma = fabsf(a), mb = fabsf(b);
+        c -= (ma == 0.75f || ma == 1.75f || ma == 3.5f) ? 1u : 0u;
+        c -= (mb == 0.75f || mb == 1.75f || mb == 3.5f) ? 0x10u : 0u;
+        c = (c & 0x07u) == 0 ? (c & 0xF0u) : c;   // -0 -> +0
+        c = (c & 0x70u) == 0 ? (c & 0x0Fu) : c;
+        return c;
+    } else {
+        uint32_t c = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);    // ties to even
+        const uint32_t ba = __float_as_uint(a) & 0x7FFFFFFFu, bb = __float_as_uint(b) & 0x7FFFFFFFu;
+        // exactly half way between two normal codes (|v| in [2^-6, 448)), the code below odd: nearest-even went up,
+        // the rule says down (no branches: a tie is common with bf16 inputs, one element in sixteen)
+        c -= ((ba & 0x001FFFFFu) == 0x00180000u && ba - 0x3C800000u < 0x43E00000u - 0x3C800000u) ? 1u : 0u;
+        c -= ((bb & 0x001FFFFFu) == 0x00180000u && bb - 0x3C800000u < 0x43E00000u - 0x3C800000u) ? 0x100u : 0u;
+        // (values below 2^-6, the subnormal codes, are put right by the caller: see mx_quantize_staged_kernel)
+        c = (c & 0x007Fu) == 0 ? (c & 0xFF00u) : c;   // -0 -> +0
+        c = (c & 0x7F00u) == 0 ? (c & 0x00FFu) : c;
+        return c;
+    }
+}
+
+// k a multiple of 64; rows of x on 16-byte boundaries and at most kMxQuantStageBytes long; q rows 16-byte aligned.
+// Dynamic shared memory: 8 warps x kMxQuantStageBytes + barriers.
+template <bool kFp4, bool kBf16In>
+__global__ void __launch_bounds__(kMxQuantThreads, 1)
+mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, uint32_t rows,
+                          uint32_t k, uint64_t x_pitch, unsigned* status)
+{
+    extern __shared__ __align__(128) uint8_t mxq_smem[];
+    constexpr uint32_t kWarps = kMxQuantThreads / 32;
+    constexpr uint32_t kElemBytes = kBf16In ? 2 : 4;
+    constexpr int kEmax = kFp4 ? 2 : 8;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(mxq_smem + kWarps * kMxQuantStageBytes);
+    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(bars + 2 * kWarps);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row_bytes = k * kElemBytes;
+    const uint32_t slots = 2 * row_bytes <= kMxQuantStageBytes ? 2u : 1u;
+    const uint32_t slot_bytes = kMxQuantStageBytes / slots;
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (uint32_t i = 0; i < 2 * kWarps; ++i) {
+            mbar_init(smem_u32(bars + i), 1);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const uint32_t warps_per_grid = gridDim.x * kWarps;
+    const uint32_t stage = smem_u32(mxq_smem) + warp * kMxQuantStageBytes;
+    const uint8_t* stage_ptr = mxq_smem + warp * kMxQuantStageBytes;
+    const uint32_t bar0 = smem_u32(bars + 2 * warp);
+    const uint32_t q_pitch = kFp4 ? k / 2 : k, sf_pitch = k / 32;
+    auto fetch = [&](uint32_t r, uint32_t slot) {  // lane 0 only
+        const uint8_t* src = static_cast<const uint8_t*>(x) + static_cast<uint64_t>(r) * x_pitch * kElemBytes;
+        mbar_expect_tx(bar0 + slot * 8, row_bytes);
+        bulk_load(stage + slot * slot_bytes, src, row_bytes, bar0 + slot * 8);
+    };
+    uint32_t r = blockIdx.x * kWarps + warp;
+    if (r < rows && lane == 0) {
+        fetch(r, 0);
+    }
+    uint32_t slot = 0, phase0 = 0, phase1 = 0;
+    for (; r < rows; r += warps_per_grid) {
+        const uint32_t next = r + warps_per_grid;
+        if (slots == 2 && next < rows && lane == 0) {
+            fetch(next, slot ^ 1);  // (that slot's previous row was worked off before the __syncwarp below)
+        }
+        bool ok = mbar_wait(bar0 + slot * 8, slot == 0 ? phase0 : phase1, s_abort, status, kDevTimeoutProducer);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            break;
+        }
+        if (slot == 0) {
+            phase0 ^= 1;
+        } else {
+            phase1 ^= 1;
+        }
+        const uint8_t* row = stage_ptr + slot * slot_bytes;
+        uint8_t* qr = q + static_cast<uint64_t>(r) * q_pitch;
+        uint8_t* sr = sf + static_cast<uint64_t>(r) * sf_pitch;
+        // (the trip count is the same for every lane: the block maximum below is a full-warp shuffle; k % 64 == 0,
+        // so the two lanes of a block are in range together)
+        for (uint32_t base = 0; base < k; base += 32 * 16) {
+            const uint32_t c0 = base + lane * 16;
+            const bool active = c0 < k;
+            float v[16];
+            if (!active) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    v[i] = 0.0f;
+                }
+            } else if constexpr (kBf16In) {
+                const uint4* src = reinterpret_cast<const uint4*>(row + c0 * 2);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 raw = src[h];
+                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        v[h * 8 + 2 * i] = __uint_as_float(w[i] << 16);
+                        v[h * 8 + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+                    }
+                }
+            } else {
+                const float4* src = reinterpret_cast<const float4*>(row + c0 * 4);
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const float4 raw = src[h];
+                    v[h * 4] = raw.x;
+                    v[h * 4 + 1] = raw.y;
+                    v[h * 4 + 2] = raw.z;
+                    v[h * 4 + 3] = raw.w;
+                }
+            }
+            float mx = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                mx = fmaxf(mx, fabsf(v[i]));
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));  // the block's other half
+            int exp = 0;
+            if (!(mx < 1e-12f)) {
+                exp = static_cast<int>((__float_as_uint(mx) >> 23) & 0xFFu) - 127 - kEmax;
+                exp = exp < -128 ? -128 : (exp > 127 ? 127 : exp);
+            }
+            // x / 2^exp as a multiplication by 2^-exp: exact either way.  exp lies in [-48, 125] (a block's maximum
+            // is at least 1e-12 or the exponent is 0; at most 2^128), so 2^-exp is a normal number.
+            const float inv = __uint_as_float(static_cast<uint32_t>(127 - exp) << 23);
+            // E4M3: the smallest nonzero scaled magnitude of this lane's elements, as a bit pattern minus one (zero
+            // wraps to the largest value): below 2^-6 lie the subnormal codes, where the conversion instruction's
+            // ties are not corrected above.  Rare (2^-15 of the block's largest value): handled after the store.
+            uint32_t min_nonzero = 0xFFFFFFFFu;
+            if constexpr (!kFp4) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    min_nonzero = min(min_nonzero, (__float_as_uint(v[i] * inv) & 0x7FFFFFFFu) - 1u);
+                }
+            }
+            uint32_t words[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                uint32_t word = 0;
+                if constexpr (kFp4) {
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        word |= mx_codes2<true>(v[w * 4 + 2 * b] * inv, v[w * 4 + 2 * b + 1] * inv) << (8 * b);
+                    }
+                } else {
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        word |= mx_codes2<false>(v[w * 4 + 2 * b] * inv, v[w * 4 + 2 * b + 1] * inv) << (16 * b);
+                    }
+                }
+                words[w] = word;
+            }
+            if (!active) {
+                continue;
+            }
+            if constexpr (kFp4) {
+                // 16 elements = 8 bytes
+                *reinterpret_cast<uint2*>(qr + (c0 >> 1)) =
+                    make_uint2(words[0] | words[1] << 16, words[2] | words[3] << 16);
+            } else {
+                *reinterpret_cast<uint4*>(qr + c0) = make_uint4(words[0], words[1], words[2], words[3]);
+                if (min_nonzero < 0x3C7FFFFFu) {
+                    // the exact rule for this lane's values below 2^-6, one by one from shared memory, each code
+                    // stored over the one written above
+#pragma unroll 1
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        float xv;
+                        if constexpr (kBf16In) {
+                            xv = __uint_as_float(static_cast<uint32_t>(
+                                     reinterpret_cast<const uint16_t*>(row)[c0 + i]) << 16);
+                        } else {
+                            xv = reinterpret_cast<const float*>(row)[c0 + i];
+                        }
+                        const float t = xv * inv;
+                        const uint32_t bits = __float_as_uint(t) & 0x7FFFFFFFu;
+                        if (bits - 1u < 0x3C7FFFFFu) {
+                            const uint32_t m = e4m3_code_of(__uint_as_float(bits));
+                            qr[c0 + i] = static_cast<uint8_t>((t < 0.0f && m != 0) ? (m | 0x80u) : m);
+                        }
+                    }
+                }
+            }
+            if ((lane & 1u) == 0) {
+                sr[c0 >> 5] = static_cast<uint8_t>(exp + 127);
+            }
+        }
+        __syncwarp();  // every lane is done with this slot
+        if (slots == 2) {
+            slot ^= 1;
+        } else if (next < rows && lane == 0) {
+            fetch(next, 0);
         }
     }
 }

@@ -20,6 +20,19 @@ def _inputs(rows, k, seed):
         x[4, :] = np.float32(448.0)           # exactly the largest E4M3 value
     # exact grid ties: halves between neighbouring codes
     x[0, :min(k, 8)] = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0], np.float32)[:min(k, 8)]
+    if rows > 8 and k >= 128:
+        # negative ties, and with a block maximum of 256 (E4M3 exponent 0) / 4 (E2M1 exponent 0): ties on the normal
+        # E4M3 grid (half way between neighbours 1/8 apart per octave), values in the subnormal E4M3 range
+        # (multiples and half-multiples of 2^-9), negative values that round to zero
+        x[5, :32] = 0.0
+        x[5, 0] = 256.0
+        x[5, 1:17] = np.array([1.0625, -1.0625, 1.1875, -1.1875, 2.125, 2.375, 0.5625, 432.0, 440.0, 232.0,
+                               2.5 / 512, -2.5 / 512, 3.5 / 512, 0.5 / 512, -0.5 / 512, -0.2 / 512], np.float32)
+        x[5, 17:21] = np.array([7.5 / 512, 8.5 / 512, 1.0 / 64 + 1.0 / 1024, 1.0 / 64 + 3.0 / 1024], np.float32)
+        x[6, 32:64] = 0.0
+        x[6, 32] = 4.0
+        x[6, 33:47] = np.array([-0.25, -0.75, -1.25, -1.75, -2.5, -3.5, 0.1, -0.1, -0.26, 0.74, 0.76, 3.49, 3.51,
+                                -5.0], np.float32)
     return x
 
 
@@ -42,7 +55,8 @@ def _run(cuda, x, fmt, bf16):
 
 @pytest.mark.parametrize("fmt", [O.MX_E4M3, O.MX_E2M1])
 @pytest.mark.parametrize("bf16", [False, True])
-@pytest.mark.parametrize("rows,k", [(64, 1024), (7, 129), (33, 63), (5, 2), (300, 4096), (16, 96)])
+@pytest.mark.parametrize("rows,k", [(64, 1024), (7, 129), (33, 63), (5, 2), (300, 4096), (16, 96), (1200, 7168),
+                                     (9, 14400), (40, 64)])
 def test_mx_quantize_matches_the_oracle_bit_for_bit(cuda, fmt, bf16, rows, k):
     x = _inputs(rows, k, seed=rows + k)
     q, sf, ref_in = _run(cuda, x, fmt, bf16)
