@@ -137,12 +137,26 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
         with self.lock:
             rows = [r for r in self.samples if t0 <= r[0] <= t1]
+            near = None
+            if not rows:
+                # a region shorter than the polling interval (8 GPUs: 20 steps last 7 ms): the samples right
+                # before and after it stand in, and the record says so
+                near = 0.03
+                rows = [r for r in self.samples if t0 - near <= r[0] <= t1 + near]
+        if near is not None and not any(r[0] > t1 for r in rows):
+            time.sleep(0.06)  # the poll after the region may not have been read yet
+            with self.lock:
+                rows = [r for r in self.samples if t0 - near <= r[0] <= t1 + near]
         sm = [r[1] for r in rows]
         reasons = sorted({x for r in rows for x in r[4]})
         watts = [r[3] for r in rows if r[3] is not None]
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_mhz_min": min(sm) if sm else None,
-                "sm_max_mhz": max(r[2] for r in rows) if rows else None, "power_w_max": max(watts) if watts else None,
-                "samples": len(rows), "reasons": reasons}
+        out = {"sm_mhz": float(np.median(sm)) if sm else None, "sm_mhz_min": min(sm) if sm else None,
+               "sm_max_mhz": max(r[2] for r in rows) if rows else None, "power_w_max": max(watts) if watts else None,
+               "samples": len(rows), "reasons": reasons}
+        if near is not None:
+            out["note"] = (f"the {1e3 * (t1 - t0):.1f} ms region fell between two polls: samples within "
+                           f"{int(1e3 * near)} ms of it")
+        return out
 
     def stop(self):
         if self.proc is not None:

@@ -12,7 +12,9 @@ Two placements are offered:
            on multiples of the kernel's 256-row tile, and an expert's weights are replicated only on the ranks
            its rows span (a hot expert with a quarter of all rows spans three of eight ranks).
 What is balanced is the kernel's cost, not the row count: the grouped kernel works in 256-row tiles per expert,
-so an expert costs its full tiles plus one for a partial tile.
+so an expert costs its full tiles plus one for a partial tile, plus a constant per expert present on the rank
+(every expert brings 29 MB of weights of its own through HBM and L2; a rank that holds thirty small experts
+is slower than one that holds two large ones with the same number of tiles).
 """
 from dataclasses import dataclass
 from typing import List
@@ -20,6 +22,11 @@ from typing import List
 # Mirror of the grouped kernel's row tile (kPairTileM in catlass_b200/csrc/w8a8_gemm_pair.cuh; a test compares them):
 # shard cuts fall on its multiples.
 ROW_TILE = 256
+
+
+# Cost of one more expert on a rank, in row tiles.  Measured on one B200 with 64 row tiles of K = 7168, N = 4096 cut
+# into 1, 16, 32 and 64 experts (306, 336, 359, 395 us per launch): 4.76 us per row tile + 1.4 us per expert.
+GROUP_COST = 0.3
 
 
 def tile_cost(rows):
@@ -47,7 +54,7 @@ class RankShard:
     @property
     def cost(self):
         """Kernel cost of this rank's launch in full tiles (pieces of one expert form one group)."""
-        return sum(tile_cost(r) for _, r in self.local_groups())
+        return sum(tile_cost(r) + GROUP_COST for _, r in self.local_groups())
 
     def group_list(self):
         """Local prefix sums, one entry per piece (the group list of the rank's own grouped matmul)."""
@@ -94,7 +101,7 @@ def plan(group_sizes, world_size, mode="split", chunk_rows=None):
         for u in sorted(units, key=lambda p: (-p.rows, p.expert)):
             r = min(range(world_size), key=lambda i: (loads[i], i))
             bins[r].append(u)
-            loads[r] += tile_cost(u.rows)
+            loads[r] += tile_cost(u.rows) + GROUP_COST
     else:
         # units of chunk_rows rows in expert order, each with the cost it adds to its expert
         units = []
@@ -102,7 +109,7 @@ def plan(group_sizes, world_size, mode="split", chunk_rows=None):
             r = 0
             while r < s:
                 take = min(chunk_rows, s - r)
-                units.append((Piece(e, r, take), tile_cost(take)))
+                units.append((Piece(e, r, take), tile_cost(take) + (GROUP_COST if r == 0 else 0.0)))
                 r += take
         total = sum(c for _, c in units)
         done = 0.0
