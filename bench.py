@@ -698,7 +698,7 @@ def run_quant_int8(sampler, seconds):
     """Per-token int8 quantisation of bf16 activations, 32768 x 7168 (a quarter of the MoE workload's routed rows):
     the step in front of the W8A8 matmuls, HBM-bound."""
     import torch
-    from catlass_b200 import capi
+    from catlass_b200 import capi, kernel_facts
     rows, k = 32768, 7168
     dev = torch.device("cuda")
     gen = torch.Generator(device="cuda")
@@ -724,7 +724,8 @@ def run_quant_int8(sampler, seconds):
         "config": {"workload": f"quant_int8: bf16 [{rows}][{k}] -> int8 codes + fp32 per-token scales",
                    "l2": f"inputs rotate over {copies} copies of 470 MB: every pass reads HBM"},
         "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": value / peaks["hbm_gbs"], "traffic": None,
+                     "frac": value / peaks["hbm_gbs"],
+                     "traffic": kernel_facts.traffic("quant_int8_staged_kernel/quant_int8"),
                      "peak_source": f"{peaks['source']} HBM copy rate", "burst_frac": burst / peaks["hbm_gbs"],
                      "algorithmic_bytes": nbytes, "frac_of_8TBs": value / 8000.0},
         "gpu_launches": r["launches_timed"], "cuda_graph": r["cuda_graph"], "clocks": r["clocks"],
@@ -735,7 +736,7 @@ def run_quant_mx(sampler, seconds):
     """MX quantisation (E4M3 codes + E8M0 scales) of bf16 activations, 32768 x 7168: the step in front of the MX
     matmuls, HBM-bound by its bytes, bound by its per-element arithmetic in practice."""
     import torch
-    from catlass_b200 import capi
+    from catlass_b200 import capi, kernel_facts
     rows, k = 32768, 7168
     dev = torch.device("cuda")
     gen = torch.Generator(device="cuda")
@@ -761,7 +762,8 @@ def run_quant_mx(sampler, seconds):
         "config": {"workload": f"quant_mx: bf16 [{rows}][{k}] -> E4M3 codes + E8M0 scales per 32 elements",
                    "l2": f"inputs rotate over {copies} copies of 470 MB: every pass reads HBM"},
         "roofline": {"bound": "hbm", "achieved": value, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": value / peaks["hbm_gbs"], "traffic": None,
+                     "frac": value / peaks["hbm_gbs"],
+                     "traffic": kernel_facts.traffic("mx_quantize_staged_kernel/quant_mx"),
                      "peak_source": f"{peaks['source']} HBM copy rate", "burst_frac": burst / peaks["hbm_gbs"],
                      "algorithmic_bytes": nbytes, "frac_of_8TBs": value / 8000.0},
         "gpu_launches": r["launches_timed"], "cuda_graph": r["cuda_graph"], "clocks": r["clocks"],

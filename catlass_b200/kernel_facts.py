@@ -47,6 +47,15 @@ DRAM_TRAFFIC = {
         "bytes": 184.4e6,
         "facts": {"mx_gemm.cuh": {"kMxBlockN": 256, "kMxStages": 4}},
     },
+    # quantisers, bf16 32768 x 7168 (rows staged through shared memory)
+    "quant_int8_staged_kernel/quant_int8": {
+        "bytes": 669.0e6,
+        "facts": {"quant_int8.cuh": {"kQuantInt8Threads": 256}},
+    },
+    "mx_quantize_staged_kernel/quant_mx": {
+        "bytes": 676.4e6,
+        "facts": {"mx_quantize.cuh": {"kMxQuantThreads": 256}},
+    },
 }
 
 
