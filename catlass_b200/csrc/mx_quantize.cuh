@@ -185,6 +185,24 @@ __device__ __forceinline__ uint32_t mx_codes2(float a, float b)
     }
 }
 
+// The same for values that were moved towards zero by one part in 4096 beforehand (see the kernel): nearest-even
+// then IS the reference's rule, and only -0 is left to put right.
+template <bool kFp4>
+__device__ __forceinline__ uint32_t mx_codes2_nudged(float a, float b)
+{
+    if constexpr (kFp4) {
+        uint32_t c = __nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);
+        c = (c & 0x07u) == 0 ? (c & 0xF0u) : c;
+        c = (c & 0x70u) == 0 ? (c & 0x0Fu) : c;
+        return c;
+    } else {
+        uint32_t c = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        c = (c & 0x007Fu) == 0 ? (c & 0xFF00u) : c;
+        c = (c & 0x7F00u) == 0 ? (c & 0x00FFu) : c;
+        return c;
+    }
+}
+
 // k a multiple of 64; rows of x on 16-byte boundaries and at most kMxQuantStageBytes long; q rows 16-byte aligned.
 // Dynamic shared memory: 8 warps x kMxQuantStageBytes + barriers.
 template <bool kFp4, bool kBf16In>
@@ -290,12 +308,19 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
             }
             // x / 2^exp as a multiplication by 2^-exp: exact either way.  exp lies in [-48, 125] (a block's maximum
             // is at least 1e-12 or the exponent is 0; at most 2^128), so 2^-exp is a normal number.
-            const float inv = __uint_as_float(static_cast<uint32_t>(127 - exp) << 23);
+            // bf16 inputs: the factor is (1 - 2^-12) * 2^-exp instead.  A bf16 value has 8 significant bits and the
+            // factor 12, so the product is still exact; it lies below x / 2^exp by one part in 4096, which moves
+            // an exact tie (and nothing else: any other value is at least one part in 256 away from the nearest
+            // half-way point, in the subnormal range at least 2^-10 against a shift below 2^-18) to the side of
+            // the smaller magnitude, where the reference's rule sends it.  The conversion instruction's nearest-
+            // even result is then the rule's result, for normal and subnormal codes alike.
+            const float inv = kBf16In ? __uint_as_float((static_cast<uint32_t>(126 - exp) << 23) | 0x007FF000u)
+                                      : __uint_as_float(static_cast<uint32_t>(127 - exp) << 23);
             // E4M3: the smallest nonzero scaled magnitude of this lane's elements, as a bit pattern minus one (zero
             // wraps to the largest value): below 2^-6 lie the subnormal codes, where the conversion instruction's
             // ties are not corrected above.  Rare (2^-15 of the block's largest value): handled after the store.
             uint32_t min_nonzero = 0xFFFFFFFFu;
-            if constexpr (!kFp4) {
+            if constexpr (!kFp4 && !kBf16In) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     min_nonzero = min(min_nonzero, (__float_as_uint(v[i] * inv) & 0x7FFFFFFFu) - 1u);
@@ -305,16 +330,11 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 uint32_t word = 0;
-                if constexpr (kFp4) {
 #pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        word |= mx_codes2<true>(v[w * 4 + 2 * b] * inv, v[w * 4 + 2 * b + 1] * inv) << (8 * b);
-                    }
-                } else {
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        word |= mx_codes2<false>(v[w * 4 + 2 * b] * inv, v[w * 4 + 2 * b + 1] * inv) << (16 * b);
-                    }
+                for (int b = 0; b < 2; ++b) {
+                    const float t0 = v[w * 4 + 2 * b] * inv, t1 = v[w * 4 + 2 * b + 1] * inv;
+                    const uint32_t pair = kBf16In ? mx_codes2_nudged<kFp4>(t0, t1) : mx_codes2<kFp4>(t0, t1);
+                    word |= pair << ((kFp4 ? 8 : 16) * b);
                 }
                 words[w] = word;
             }
