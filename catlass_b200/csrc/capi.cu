@@ -2266,8 +2266,15 @@ int cb200_mx_quantize(const cb200_mx_quantize_args* args, void* stream_v)
     uint8_t* q = static_cast<uint8_t*>(args->q);
     uint8_t* sf = static_cast<uint8_t*>(args->scale);
     const uint64_t row_bytes = static_cast<uint64_t>(args->k) * (bf16 ? 2u : 4u);
-    if (args->k % 64u == 0 && row_bytes <= kMxQuantStageBytes && (x_pitch * (bf16 ? 2u : 4u)) % 16u == 0 &&
-        (reinterpret_cast<uintptr_t>(args->q) & 15u) == 0) {
+    const uint64_t segs_if_cut = (args->k + kMxQuantStageBytes / 2u / (bf16 ? 2u : 4u) - 1u) /
+                                 (kMxQuantStageBytes / 2u / (bf16 ? 2u : 4u));
+    if (args->k % 64u == 0 && (x_pitch * (bf16 ? 2u : 4u)) % 16u == 0 &&
+        (reinterpret_cast<uintptr_t>(args->q) & 15u) == 0 &&
+        static_cast<uint64_t>(args->rows) * segs_if_cut < (1ull << 31)) {
+        // whole rows when they fit a warp's slot, else segments of half a slot (a multiple of 512 elements)
+        const uint32_t seg = row_bytes <= kMxQuantStageBytes ? args->k : kMxQuantStageBytes / 2u / (bf16 ? 2u : 4u);
+        static_assert((kMxQuantStageBytes / 2u / 2u) % 512u == 0 && (kMxQuantStageBytes / 2u / 4u) % 512u == 0,
+                      "segment length");
         // the aligned case: rows staged through shared memory, one CTA of eight warps per SM
         constexpr uint32_t kSmem = 8u * kMxQuantStageBytes + 2u * 8u * 8u + 16u;
         static PerDeviceOnce once;
@@ -2290,23 +2297,24 @@ int cb200_mx_quantize(const cb200_mx_quantize_args* args, void* stream_v)
         if (rc != CB200_SUCCESS) {
             return rc;
         }
-        const uint32_t want = (args->rows + 7u) / 8u;
+        const uint64_t items = static_cast<uint64_t>(args->rows) * ((args->k + seg - 1u) / seg);
+        const uint64_t want = (items + 7u) / 8u;
         const uint32_t sms = static_cast<uint32_t>(dev->sm_count);
-        const uint32_t grid = want < sms ? want : sms;
+        const uint32_t grid = want < sms ? static_cast<uint32_t>(want) : sms;
         if (fp4) {
             if (bf16) {
                 mx_quantize_staged_kernel<true, true><<<grid, kMxQuantThreads, kSmem, stream>>>(
-                    args->x, q, sf, args->rows, args->k, x_pitch, dev->status);
+                    args->x, q, sf, args->rows, args->k, x_pitch, seg, dev->status);
             } else {
                 mx_quantize_staged_kernel<true, false><<<grid, kMxQuantThreads, kSmem, stream>>>(
-                    args->x, q, sf, args->rows, args->k, x_pitch, dev->status);
+                    args->x, q, sf, args->rows, args->k, x_pitch, seg, dev->status);
             }
         } else if (bf16) {
             mx_quantize_staged_kernel<false, true><<<grid, kMxQuantThreads, kSmem, stream>>>(
-                args->x, q, sf, args->rows, args->k, x_pitch, dev->status);
+                args->x, q, sf, args->rows, args->k, x_pitch, seg, dev->status);
         } else {
             mx_quantize_staged_kernel<false, false><<<grid, kMxQuantThreads, kSmem, stream>>>(
-                args->x, q, sf, args->rows, args->k, x_pitch, dev->status);
+                args->x, q, sf, args->rows, args->k, x_pitch, seg, dev->status);
         }
     } else if (fp4) {
         if (bf16) {

@@ -203,12 +203,14 @@ __device__ __forceinline__ uint32_t mx_codes2_nudged(float a, float b)
     }
 }
 
-// k a multiple of 64; rows of x on 16-byte boundaries and at most kMxQuantStageBytes long; q rows 16-byte aligned.
+// k a multiple of 64; rows of x on 16-byte boundaries; q rows 16-byte aligned.  A row is worked off in segments of
+// `seg` elements (a multiple of 512, or k itself when the whole row fits a warp's kMxQuantStageBytes; blocks of 32
+// are independent of each other, so a long row is simply several work items).
 // Dynamic shared memory: 8 warps x kMxQuantStageBytes + barriers.
 template <bool kFp4, bool kBf16In>
 __global__ void __launch_bounds__(kMxQuantThreads, 1)
 mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, uint32_t rows,
-                          uint32_t k, uint64_t x_pitch, unsigned* status)
+                          uint32_t k, uint64_t x_pitch, uint32_t seg, unsigned* status)
 {
     extern __shared__ __align__(128) uint8_t mxq_smem[];
     constexpr uint32_t kWarps = kMxQuantThreads / 32;
@@ -217,8 +219,7 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
     uint64_t* bars = reinterpret_cast<uint64_t*>(mxq_smem + kWarps * kMxQuantStageBytes);
     volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(bars + 2 * kWarps);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t row_bytes = k * kElemBytes;
-    const uint32_t slots = 2 * row_bytes <= kMxQuantStageBytes ? 2u : 1u;
+    const uint32_t slots = 2 * seg * kElemBytes <= kMxQuantStageBytes ? 2u : 1u;
     const uint32_t slot_bytes = kMxQuantStageBytes / slots;
     if (threadIdx.x == 0) {
         *s_abort = 0;
@@ -233,20 +234,26 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
     const uint8_t* stage_ptr = mxq_smem + warp * kMxQuantStageBytes;
     const uint32_t bar0 = smem_u32(bars + 2 * warp);
     const uint32_t q_pitch = kFp4 ? k / 2 : k, sf_pitch = k / 32;
-    auto fetch = [&](uint32_t r, uint32_t slot) {  // lane 0 only
-        const uint8_t* src = static_cast<const uint8_t*>(x) + static_cast<uint64_t>(r) * x_pitch * kElemBytes;
-        mbar_expect_tx(bar0 + slot * 8, row_bytes);
-        bulk_load(stage + slot * slot_bytes, src, row_bytes, bar0 + slot * 8);
+    const uint32_t segs = (k + seg - 1) / seg;
+    const uint32_t items = rows * segs;  // (row, segment) pairs, a row's segments adjacent (the host checks the range)
+    auto fetch = [&](uint32_t item, uint32_t slot) {  // lane 0 only
+        const uint32_t r = segs == 1 ? item : item / segs;
+        const uint32_t c_begin = (item - r * segs) * seg;
+        const uint32_t bytes = (k - c_begin < seg ? k - c_begin : seg) * kElemBytes;
+        const uint8_t* src =
+            static_cast<const uint8_t*>(x) + (static_cast<uint64_t>(r) * x_pitch + c_begin) * kElemBytes;
+        mbar_expect_tx(bar0 + slot * 8, bytes);
+        bulk_load(stage + slot * slot_bytes, src, bytes, bar0 + slot * 8);
     };
-    uint32_t r = blockIdx.x * kWarps + warp;
-    if (r < rows && lane == 0) {
-        fetch(r, 0);
+    uint32_t item = blockIdx.x * kWarps + warp;
+    if (item < items && lane == 0) {
+        fetch(item, 0);
     }
     uint32_t slot = 0, phase0 = 0, phase1 = 0;
-    for (; r < rows; r += warps_per_grid) {
-        const uint32_t next = r + warps_per_grid;
-        if (slots == 2 && next < rows && lane == 0) {
-            fetch(next, slot ^ 1);  // (that slot's previous row was worked off before the __syncwarp below)
+    for (; item < items; item += warps_per_grid) {
+        const uint32_t next = item + warps_per_grid;  // (items + warps_per_grid < 2^32: checked by the host)
+        if (slots == 2 && next < items && lane == 0) {
+            fetch(next, slot ^ 1);  // (that slot's previous segment was worked off before the __syncwarp below)
         }
         bool ok = mbar_wait(bar0 + slot * 8, slot == 0 ? phase0 : phase1, s_abort, status, kDevTimeoutProducer);
         ok = __all_sync(0xffffffffu, ok);
@@ -258,14 +265,17 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
         } else {
             phase1 ^= 1;
         }
+        const uint32_t r = segs == 1 ? item : item / segs;
+        const uint32_t c_begin = (item - r * segs) * seg;
+        const uint32_t len = k - c_begin < seg ? k - c_begin : seg;
         const uint8_t* row = stage_ptr + slot * slot_bytes;
-        uint8_t* qr = q + static_cast<uint64_t>(r) * q_pitch;
-        uint8_t* sr = sf + static_cast<uint64_t>(r) * sf_pitch;
-        // (the trip count is the same for every lane: the block maximum below is a full-warp shuffle; k % 64 == 0,
-        // so the two lanes of a block are in range together)
-        for (uint32_t base = 0; base < k; base += 32 * 16) {
+        uint8_t* qr = q + static_cast<uint64_t>(r) * q_pitch + (kFp4 ? c_begin / 2 : c_begin);
+        uint8_t* sr = sf + static_cast<uint64_t>(r) * sf_pitch + c_begin / 32;
+        // (the trip count is the same for every lane: the block maximum below is a full-warp shuffle; the length is
+        // a multiple of 64, so the two lanes of a block are in range together)
+        for (uint32_t base = 0; base < len; base += 32 * 16) {
             const uint32_t c0 = base + lane * 16;
-            const bool active = c0 < k;
+            const bool active = c0 < len;
             float v[16];
             if (!active) {
 #pragma unroll
@@ -375,7 +385,7 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
         __syncwarp();  // every lane is done with this slot
         if (slots == 2) {
             slot ^= 1;
-        } else if (next < rows && lane == 0) {
+        } else if (next < items && lane == 0) {
             fetch(next, 0);
         }
     }
