@@ -268,6 +268,115 @@ __device__ __forceinline__ void mx_tile_coords(uint32_t idx, uint32_t m_tiles, u
     mt = band * band_rows + (r - nt * rows);
 }
 
+// Finalize routing for one epilogue thread: its accumulator row's 64 columns r (fp32 bit patterns) starting at column
+// col_base are added into row `target` of the fp32 output as weight * (C + bias[group]).  Every lane of the warp
+// calls this (lanes without a valid target take part in the exchange only).
+__device__ __forceinline__ void mx_route_row(const MxParams& p, const uint32_t (&r)[2][32], uint32_t lane,
+                                             uint32_t col_base, int32_t group, long long target, float weight)
+{
+    const bool mine = target >= 0 && target < static_cast<long long>(p.batch);
+    float* orow = static_cast<float*>(p.d) + static_cast<size_t>(mine ? target : 0) * p.n;
+    const __nv_bfloat16* brow = p.bias != nullptr ? p.bias + static_cast<size_t>(group) * p.n : nullptr;
+    if ((p.n & 7u) == 0 && col_base + 64 <= p.n) {
+        // Two neighbouring lanes (two rows of C) work together so that every reduction instruction
+        // carries 32 contiguous bytes per output row, a whole L2 sector, instead of 16: of each 8
+        // columns the even lane keeps its columns 0-3 and hands its columns 4-7 to the odd lane, which
+        // hands over its columns 0-3 in return; instruction A then adds the even lane's row (columns
+        // 0-3 from the even lane, 4-7 from the odd lane), instruction B the odd lane's row.  With one
+        // lane per row every instruction touched 32 sectors half-way: twice the sector operations on
+        // the way to L2 (ncu: the L1-to-crossbar request path two thirds busy); worth 3 % here.
+        const bool odd = (lane & 1u) != 0;
+        const unsigned long long mine_ptr = reinterpret_cast<unsigned long long>(orow);
+        const unsigned long long peer_ptr = __shfl_xor_sync(0xffffffffu, mine_ptr, 1);
+        const bool peer_ok = __shfl_xor_sync(0xffffffffu, mine ? 1 : 0, 1) != 0;
+        float* row_a = reinterpret_cast<float*>(odd ? peer_ptr : mine_ptr);   // the even lane's row
+        float* row_b = reinterpret_cast<float*>(odd ? mine_ptr : peer_ptr);   // the odd lane's row
+        const bool ok_a = odd ? peer_ok : mine, ok_b = odd ? mine : peer_ok;
+        const uint32_t off = odd ? 4u : 0u;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {   // 8 columns at a time
+                const uint32_t col = col_base + c * 32 + v * 8;
+                float x[8];
+                if (brow != nullptr) {
+                    const uint4 braw = __ldg(reinterpret_cast<const uint4*>(brow + col));
+                    const uint32_t bw[4] = {braw.x, braw.y, braw.z, braw.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        x[2 * e] = __fadd_rn(__uint_as_float(r[c][8 * v + 2 * e]),
+                                             __uint_as_float(bw[e] << 16));
+                        x[2 * e + 1] = __fadd_rn(__uint_as_float(r[c][8 * v + 2 * e + 1]),
+                                                 __uint_as_float(bw[e] & 0xFFFF0000u));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        x[e] = __uint_as_float(r[c][8 * v + e]);
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    x[e] = __fmul_rn(x[e], weight);
+                }
+                float keep[4], got[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    keep[e] = odd ? x[4 + e] : x[e];           // stays: the lane's own half of its own row
+                    const float send = odd ? x[e] : x[4 + e];  // goes: the other half, to the neighbour
+                    got[e] = __shfl_xor_sync(0xffffffffu, send, 1);
+                }
+                // even lane: A = own row, own columns 0-3;   B = odd's row, its columns 0-3 (received)
+                // odd lane:  A = even's row, columns 4-7 (received);   B = own row, own columns 4-7
+                const float* va = odd ? got : keep;
+                const float* vb = odd ? keep : got;
+                if (ok_a) {
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(row_a + col + off),
+                                 "f"(va[0]), "f"(va[1]), "f"(va[2]), "f"(va[3])
+                                 : "memory");
+                }
+                if (ok_b) {
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(row_b + col + off),
+                                 "f"(vb[0]), "f"(vb[1]), "f"(vb[2]), "f"(vb[3])
+                                 : "memory");
+                }
+            }
+        }
+        return;
+    }
+    if (!mine) {
+        return;
+    }
+    const bool vec4 = (p.n & 3u) == 0;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+            float x[4];
+            const uint32_t col = col_base + c * 32 + v * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float y = __uint_as_float(r[c][4 * v + e]);
+                if (brow != nullptr && col + e < p.n) {
+                    y = __fadd_rn(y, __bfloat162float(brow[col + e]));
+                }
+                x[e] = __fmul_rn(y, weight);
+            }
+            if (vec4 && col + 4 <= p.n) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(orow + col), "f"(x[0]),
+                             "f"(x[1]), "f"(x[2]), "f"(x[3])
+                             : "memory");
+            } else {
+                for (int e = 0; e < 4; ++e) {
+                    if (col + e < p.n) {
+                        atomicAdd(orow + col + e, x[e]);
+                    }
+                }
+            }
+        }
+    }
+}
+
 // kGrouped: slice-M groups (the reference's GroupedMxMatmulSliceMTla, example 55): row tiles come from the tile
 // table, every group has its own weight matrix (third coordinate of B's tensor map) and B scales.
 template <bool kFp4, bool kGrouped, int kEpi = kMxEpiPlain>
@@ -504,16 +613,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (uint32_t idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
             uint32_t mt, nt;
             mx_tile_coords(idx, m_tiles, n_tiles, p.band_rows, mt, nt);
+            int32_t row0, row_end, group;
+            row_tile(mt, row0, row_end, group);
+            const uint32_t row = static_cast<uint32_t>(row0) + quad * 32 + lane;
+            const bool row_ok = static_cast<int32_t>(row) < row_end;
+            // finalize routing: this row's target and weight are fetched while the tile's MMAs still run (after the
+            // accumulator's hand-over they were a trip to L2 on every tile's critical path)
+            long long route_target = -1;
+            float route_weight = 0.0f;
+            if constexpr (kEpi == kMxEpiRouting) {
+                if (row_ok) {
+                    route_target = p.row_index_i32
+                                       ? static_cast<long long>(static_cast<const int32_t*>(p.row_index)[row])
+                                       : static_cast<const long long*>(p.row_index)[row];
+                    route_weight = __ldg(p.logit + row);
+                }
+            }
             ok = mbar_wait(bar_tmem_full + acc * 8, acc_phase, s_abort, p.status, kDevTimeoutEpilogue);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
             }
             tcgen05_fence_after();
-            int32_t row0, row_end, group;
-            row_tile(mt, row0, row_end, group);
-            const uint32_t row = static_cast<uint32_t>(row0) + quad * 32 + lane;
-            const bool row_ok = static_cast<int32_t>(row) < row_end;
             if constexpr (kSwiglu) {
                 // This warp: output columns [half * 64, half * 64 + 64) of the tile's 128, as two blocks of 32; "act"
                 // sits in accumulator columns 0..127, "gate" in 128..255.
@@ -583,46 +704,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 continue;
             }
             if constexpr (kEpi == kMxEpiRouting) {
-                long long target = -1;
-                float weight = 0.0f;
-                if (row_ok) {
-                    target = p.row_index_i32 ? static_cast<long long>(static_cast<const int32_t*>(p.row_index)[row])
-                                             : static_cast<const long long*>(p.row_index)[row];
-                    weight = __ldg(p.logit + row);
-                }
-                if (target < 0 || target >= static_cast<long long>(p.batch)) {
-                    continue;
-                }
-                float* orow = static_cast<float*>(p.d) + static_cast<size_t>(target) * p.n;
-                const __nv_bfloat16* brow = p.bias != nullptr ? p.bias + static_cast<size_t>(group) * p.n : nullptr;
-                const bool vec4 = (p.n & 3u) == 0;
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-#pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        float x[4];
-                        const uint32_t col = col_base + c * 32 + v * 4;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float y = __uint_as_float(r[c][4 * v + e]);
-                            if (brow != nullptr && col + e < p.n) {
-                                y = __fadd_rn(y, __bfloat162float(brow[col + e]));
-                            }
-                            x[e] = __fmul_rn(y, weight);
-                        }
-                        if (vec4 && col + 4 <= p.n) {
-                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(orow + col), "f"(x[0]),
-                                         "f"(x[1]), "f"(x[2]), "f"(x[3])
-                                         : "memory");
-                        } else {
-                            for (int e = 0; e < 4; ++e) {
-                                if (col + e < p.n) {
-                                    atomicAdd(orow + col + e, x[e]);
-                                }
-                            }
-                        }
-                    }
-                }
+                mx_route_row(p, r, lane, col_base, group, route_target, route_weight);
                 continue;
             }
             if (!row_ok) {
