@@ -16,9 +16,10 @@
 // mx_quantize_staged_kernel serves the aligned case (k a multiple of 64, rows of at most 28 KB on 16-byte boundaries):
 // one warp per row, the whole row brought into the warp's shared-memory slot by ONE bulk copy (the next row in
 // flight meanwhile when two fit), a lane working on 16 consecutive elements (half a block) per step, the codes made
-// by the conversion instructions (cvt.rn.satfinite.e4m3x2 / e2m1x2) and then corrected where round-to-nearest-even
-// and the reference's tie rule differ.  mx_quantize_kernel (plain loads, 4 elements per lane and step, any k and
-// pitch) had 256 bytes of loads outstanding per warp and ran at 0.2 of the HBM copy rate on 32768 x 7168 bf16.
+// by the conversion instructions (cvt.rn.satfinite.e4m3x2 / e2m1x2) from values shifted towards zero by one part in
+// 4096, which turns the instructions' nearest-even into the reference's tie rule (see the kernel).
+// mx_quantize_kernel (plain loads, 4 elements per lane and step, any k and pitch) had 256 bytes of loads outstanding
+// per warp and ran at 0.2 of the HBM copy rate on 32768 x 7168 bf16.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -157,36 +158,9 @@ __global__ void mx_quantize_kernel(const void* __restrict__ x, uint8_t* __restri
 constexpr int kMxQuantThreads = 256;
 constexpr uint32_t kMxQuantStageBytes = 28u * 1024u;  // shared memory per warp
 
-// Two scaled values -> two element codes (a in bits 0-7 / 0-3, b above), the reference's rule:
-// nearest, a tie to the smaller magnitude, saturating, zero always +0.
-template <bool kFp4>
-__device__ __forceinline__ uint32_t mx_codes2(float a, float b)
-{
-    if constexpr (kFp4) {
-        uint32_t c = __nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);  // ties to even
-        // the ties between an odd code below and an even code above (0.75, 1.75, 3.5) went up: take them down
-        const float ma = fabsf(a), mb = fabsf(b);
-        c -= (ma == 0.75f || ma == 1.75f || ma == 3.5f) ? 1u : 0u;
-        c -= (mb == 0.75f || mb == 1.75f || mb == 3.5f) ? 0x10u : 0u;
-        c = (c & 0x07u) == 0 ? (c & 0xF0u) : c;   // -0 -> +0
-        c = (c & 0x70u) == 0 ? (c & 0x0Fu) : c;
-        return c;
-    } else {
-        uint32_t c = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);    // ties to even
-        const uint32_t ba = __float_as_uint(a) & 0x7FFFFFFFu, bb = __float_as_uint(b) & 0x7FFFFFFFu;
-        // exactly half way between two normal codes (|v| in [2^-6, 448)), the code below odd: nearest-even went up,
-        // the rule says down (no branches: a tie is common with bf16 inputs, one element in sixteen)
-        c -= ((ba & 0x001FFFFFu) == 0x00180000u && ba - 0x3C800000u < 0x43E00000u - 0x3C800000u) ? 1u : 0u;
-        c -= ((bb & 0x001FFFFFu) == 0x00180000u && bb - 0x3C800000u < 0x43E00000u - 0x3C800000u) ? 0x100u : 0u;
-        // (values below 2^-6, the subnormal codes, are put right by the caller: see mx_quantize_staged_kernel)
-        c = (c & 0x007Fu) == 0 ? (c & 0xFF00u) : c;   // -0 -> +0
-        c = (c & 0x7F00u) == 0 ? (c & 0x00FFu) : c;
-        return c;
-    }
-}
-
-// The same for values that were moved towards zero by one part in 4096 beforehand (see the kernel): nearest-even
-// then IS the reference's rule, and only -0 is left to put right.
+// Two scaled values -> two element codes (a in bits 0-7 / 0-3, b above).  The values were moved towards zero by one
+// part in 4096 beforehand (see the kernel): the conversion instruction's nearest-even then IS the reference's rule
+// (nearest, a tie to the smaller magnitude, saturating), and only -0 is left to put right (zero is always +0).
 template <bool kFp4>
 __device__ __forceinline__ uint32_t mx_codes2_nudged(float a, float b)
 {
@@ -324,16 +298,17 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
             // half-way point, in the subnormal range at least 2^-10 against a shift below 2^-18) to the side of
             // the smaller magnitude, where the reference's rule sends it.  The conversion instruction's nearest-
             // even result is then the rule's result, for normal and subnormal codes alike.
-            const float inv = kBf16In ? __uint_as_float((static_cast<uint32_t>(126 - exp) << 23) | 0x007FF000u)
-                                      : __uint_as_float(static_cast<uint32_t>(127 - exp) << 23);
-            // E4M3: the smallest nonzero scaled magnitude of this lane's elements, as a bit pattern minus one (zero
-            // wraps to the largest value): below 2^-6 lie the subnormal codes, where the conversion instruction's
-            // ties are not corrected above.  Rare (2^-15 of the block's largest value): handled after the store.
-            uint32_t min_nonzero = 0xFFFFFFFFu;
-            if constexpr (!kFp4 && !kBf16In) {
+            // fp32 inputs get there in two steps: the value is first cut to 11 significant bits plus a twelfth that
+            // says whether anything was cut off (every code and every half-way point has at most 6 significant
+            // bits, so the cut changes neither on which side of a half-way point the value lies nor whether it
+            // sits exactly on one), then multiplied by the same factor (12 + 12 bits: exact).  A value off a
+            // half-way point is now at least half a unit of the 11-bit grid away from it, more than the shift.
+            const float inv = __uint_as_float((static_cast<uint32_t>(126 - exp) << 23) | 0x007FF000u);
+            if constexpr (!kBf16In) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    min_nonzero = min(min_nonzero, (__float_as_uint(v[i] * inv) & 0x7FFFFFFFu) - 1u);
+                    const uint32_t bits = __float_as_uint(v[i]);
+                    v[i] = __uint_as_float((bits & 0xFFFFE000u) | ((bits & 0x00001FFFu) != 0 ? 0x00001000u : 0u));
                 }
             }
             uint32_t words[4];
@@ -343,7 +318,7 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
                     const float t0 = v[w * 4 + 2 * b] * inv, t1 = v[w * 4 + 2 * b + 1] * inv;
-                    const uint32_t pair = kBf16In ? mx_codes2_nudged<kFp4>(t0, t1) : mx_codes2<kFp4>(t0, t1);
+                    const uint32_t pair = mx_codes2_nudged<kFp4>(t0, t1);
                     word |= pair << ((kFp4 ? 8 : 16) * b);
                 }
                 words[w] = word;
@@ -357,26 +332,6 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
                     make_uint2(words[0] | words[1] << 16, words[2] | words[3] << 16);
             } else {
                 *reinterpret_cast<uint4*>(qr + c0) = make_uint4(words[0], words[1], words[2], words[3]);
-                if (min_nonzero < 0x3C7FFFFFu) {
-                    // the exact rule for this lane's values below 2^-6, one by one from shared memory, each code
-                    // stored over the one written above
-#pragma unroll 1
-                    for (uint32_t i = 0; i < 16; ++i) {
-                        float xv;
-                        if constexpr (kBf16In) {
-                            xv = __uint_as_float(static_cast<uint32_t>(
-                                     reinterpret_cast<const uint16_t*>(row)[c0 + i]) << 16);
-                        } else {
-                            xv = reinterpret_cast<const float*>(row)[c0 + i];
-                        }
-                        const float t = xv * inv;
-                        const uint32_t bits = __float_as_uint(t) & 0x7FFFFFFFu;
-                        if (bits - 1u < 0x3C7FFFFFu) {
-                            const uint32_t m = e4m3_code_of(__uint_as_float(bits));
-                            qr[c0 + i] = static_cast<uint8_t>((t < 0.0f && m != 0) ? (m | 0x80u) : m);
-                        }
-                    }
-                }
             }
             if ((lane & 1u) == 0) {
                 sr[c0 >> 5] = static_cast<uint8_t>(exp + 127);
