@@ -68,19 +68,27 @@ __device__ __forceinline__ float quant_int8_amax16(const float (&v)[16], float a
     return amax;
 }
 
+// (c << 16) | (sat8(a) << 8) | sat8(b): two int32 packed as saturated int8 below the low half of c
+__device__ __forceinline__ uint32_t pack_sat_s8(int a, int b, uint32_t c)
+{
+    uint32_t d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 __device__ __forceinline__ uint4 quant_int8_codes16(const float (&v)[16], float inv)
 {
     uint32_t out[4];
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-        uint32_t word = 0;
+        int code[4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            int code = __float2int_rn(__fmul_rn(v[w * 4 + b], inv));
-            code = code > 127 ? 127 : (code < -127 ? -127 : code);
-            word |= (static_cast<uint32_t>(code) & 0xFFu) << (8 * b);
+            code[b] = __float2int_rn(__fmul_rn(v[w * 4 + b], inv));
         }
-        out[w] = word;
+        // |x * inv| <= 127 (1 + 2^-23): the rounded value never leaves [-127, 127]; the saturating pack is the clamp
+        // for anything that is not a number
+        out[w] = pack_sat_s8(code[1], code[0], pack_sat_s8(code[3], code[2], 0u));
     }
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
