@@ -2133,6 +2133,35 @@ int cb200_quantize_per_token_int8(const cb200_quantize_int8_args* args, void* st
             quant_int8_staged_kernel<false><<<grid, kQuantInt8Threads, kSmem, stream>>>(args->x, q, scale, args->rows,
                                                                                          args->k, pitch, dev->status);
         }
+    } else if (row_bytes <= 4ull * kQuantInt8StageBytes) {
+        // one CTA per row, eight segments of at most half a slot
+        constexpr uint32_t kSmem = 8u * kQuantInt8StageBytes + 2u * 8u * 8u + 16u;
+        static PerDeviceOnce once_wide;
+        int devid = 0;
+        rc = current_device(&devid);
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        rc = once_wide.run(devid, [&]() -> int {
+            CB200_CUDA_TRY(cudaFuncSetAttribute(quant_int8_wide_kernel<true>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+            CB200_CUDA_TRY(cudaFuncSetAttribute(quant_int8_wide_kernel<false>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+            return CB200_SUCCESS;
+        });
+        if (rc != CB200_SUCCESS) {
+            return rc;
+        }
+        const uint32_t seg = ((args->k + 7u) / 8u + 15u) & ~15u;
+        const uint32_t sms = static_cast<uint32_t>(dev->sm_count);
+        const uint32_t grid = args->rows < sms ? args->rows : sms;
+        if (bf16) {
+            quant_int8_wide_kernel<true><<<grid, kQuantInt8Threads, kSmem, stream>>>(args->x, q, scale, args->rows,
+                                                                                      args->k, pitch, seg, dev->status);
+        } else {
+            quant_int8_wide_kernel<false><<<grid, kQuantInt8Threads, kSmem, stream>>>(args->x, q, scale, args->rows,
+                                                                                       args->k, pitch, seg, dev->status);
+        }
     } else if (bf16) {
         quant_int8_kernel<true><<<blocks, kQuantInt8Threads, 0, stream>>>(args->x, q, scale, args->rows, args->k, pitch);
     } else {

@@ -16,6 +16,7 @@
 //                             in flight while this one is worked on), both passes read shared memory.  Eight
 //                             warps keep up to 224 KB of loads outstanding per SM; with plain loads a warp had
 //                             1 KB outstanding and the kernel ran at 0.6 of the HBM copy rate.
+//   quant_int8_wide_kernel    rows of 28 to 112 KB: one CTA per row, a segment per warp staged the same way.
 //   quant_int8_kernel         any row length: the row is read twice with plain loads, the second time from L2
 //                             where the first pass left it.
 #pragma once
@@ -168,6 +169,99 @@ quant_int8_staged_kernel(const void* __restrict__ x, int8_t* __restrict__ q, flo
         } else if (next < rows && lane == 0) {
             fetch(next, 0);
         }
+    }
+}
+
+// Rows of 28 KB to 112 KB: one CTA per row, the row cut into eight segments of `seg` elements (a multiple of 16, at
+// most half a warp's slot), one per warp; every warp keeps the next row's segment in flight in its second slot.
+// The row's maximum goes through shared memory (one CTA-wide barrier per row).  Same dynamic shared memory.
+template <bool kBf16In>
+__global__ void __launch_bounds__(kQuantInt8Threads, 1)
+quant_int8_wide_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, uint32_t rows,
+                       uint32_t k, uint64_t x_pitch, uint32_t seg, unsigned* status)
+{
+    extern __shared__ __align__(128) uint8_t quant_smem[];
+    constexpr uint32_t kWarps = kQuantInt8Threads / 32;
+    constexpr uint32_t kElemBytes = kBf16In ? 2 : 4;
+    constexpr uint32_t kSlotBytes = kQuantInt8StageBytes / 2;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(quant_smem + kWarps * kQuantInt8StageBytes);
+    volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(bars + 2 * kWarps);
+    __shared__ float s_part[2][kWarps];  // the warps' partial maxima, one set per slot
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        *s_abort = 0;
+        for (uint32_t i = 0; i < 2 * kWarps; ++i) {
+            mbar_init(smem_u32(bars + i), 1);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const uint32_t c_begin = warp * seg;                                   // this warp's elements of every row
+    const uint32_t len = c_begin < k ? (k - c_begin < seg ? k - c_begin : seg) : 0u;
+    const uint32_t stage = smem_u32(quant_smem) + warp * kQuantInt8StageBytes;
+    const uint8_t* stage_ptr = quant_smem + warp * kQuantInt8StageBytes;
+    const uint32_t bar0 = smem_u32(bars + 2 * warp);
+    auto fetch = [&](uint32_t r, uint32_t slot) {  // lane 0 only, len != 0
+        const uint8_t* src =
+            static_cast<const uint8_t*>(x) + (static_cast<uint64_t>(r) * x_pitch + c_begin) * kElemBytes;
+        mbar_expect_tx(bar0 + slot * 8, len * kElemBytes);
+        bulk_load(stage + slot * kSlotBytes, src, len * kElemBytes, bar0 + slot * 8);
+    };
+    uint32_t r = blockIdx.x;
+    if (r < rows && lane == 0 && len != 0) {
+        fetch(r, 0);
+    }
+    uint32_t slot = 0, phase0 = 0, phase1 = 0;
+    // (every thread of the CTA makes the same number of trips and meets the barrier in each of them)
+    for (; r < rows; r += gridDim.x) {
+        const uint32_t next = r + gridDim.x;
+        if (next < rows && lane == 0 && len != 0) {
+            fetch(next, slot ^ 1);  // (that slot's previous row was worked off before the __syncwarp below)
+        }
+        const uint8_t* row = stage_ptr + slot * kSlotBytes;
+        float amax = 0.0f;
+        if (len != 0) {
+            const bool got = mbar_wait(bar0 + slot * 8, slot == 0 ? phase0 : phase1, s_abort, status, kDevTimeoutProducer);
+            if (slot == 0) {
+                phase0 ^= 1;
+            } else {
+                phase1 ^= 1;
+            }
+            if (got) {
+                for (uint32_t c0 = lane * 16; c0 < len; c0 += 32 * 16) {
+                    float v[16];
+                    quant_int8_load16<kBf16In>(row, c0, v);
+                    amax = quant_int8_amax16(v, amax);
+                }
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        }
+        if (lane == 0) {
+            s_part[slot][warp] = amax;
+        }
+        __syncthreads();
+        if (*s_abort != 0) {
+            break;  // (the same for every thread: the flag was read after the barrier)
+        }
+#pragma unroll
+        for (uint32_t w = 0; w < kWarps; ++w) {
+            amax = fmaxf(amax, s_part[slot][w]);
+        }
+        const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+        if (threadIdx.x == 0) {
+            scale[r] = __fdiv_rn(amax, 127.0f);
+        }
+        int8_t* qr = q + static_cast<uint64_t>(r) * k + c_begin;
+        for (uint32_t c0 = lane * 16; c0 < len; c0 += 32 * 16) {
+            float v[16];
+            quant_int8_load16<kBf16In>(row, c0, v);
+            *reinterpret_cast<uint4*>(qr + c0) = quant_int8_codes16(v, inv);
+        }
+        __syncwarp();  // every lane is done with this slot
+        slot ^= 1;
     }
 }
 

@@ -17,7 +17,9 @@ def _bf16_round(x):
 @pytest.mark.parametrize("rows,k,pitch,bf16", [
     (1, 16, 0, False), (7, 48, 0, False), (33, 512, 0, True), (130, 7168, 0, True), (64, 1040, 1056, False),
     (19, 2064, 2080, True), (300, 4096, 0, False),
-    (5, 8192, 0, False), (9, 16400, 16416, True),   # rows beyond the staged kernel's 28 KB: the plain-load kernel
+    (5, 8192, 0, False), (9, 16400, 16416, True),   # rows of 28 to 112 KB: one CTA per row, a segment per warp
+    (400, 16384, 0, True), (2, 28672, 0, False),    # ... more rows than CTAs; the longest such row
+    (3, 65536, 0, True),                            # beyond that: the plain-load kernel
     (1500, 256, 0, True),                            # more rows than warps in the grid: several rows per warp
 ])
 def test_quantize_per_token_int8_matches_the_oracle(cuda, rows, k, pitch, bf16):
