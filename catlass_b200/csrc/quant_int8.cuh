@@ -220,8 +220,10 @@ quant_int8_wide_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float
         }
         const uint8_t* row = stage_ptr + slot * kSlotBytes;
         float amax = 0.0f;
+        bool failed = false;
         if (len != 0) {
             const bool got = mbar_wait(bar0 + slot * 8, slot == 0 ? phase0 : phase1, s_abort, status, kDevTimeoutProducer);
+            failed = !got;
             if (slot == 0) {
                 phase0 ^= 1;
             } else {
@@ -242,9 +244,8 @@ quant_int8_wide_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float
         if (lane == 0) {
             s_part[slot][warp] = amax;
         }
-        __syncthreads();
-        if (*s_abort != 0) {
-            break;  // (the same for every thread: the flag was read after the barrier)
+        if (__syncthreads_or(failed ? 1 : 0) != 0) {
+            break;  // (the barrier hands every thread the same answer: all leave in the same trip)
         }
 #pragma unroll
         for (uint32_t w = 0; w < kWarps; ++w) {
