@@ -58,6 +58,22 @@ def test_whole_expert_placement_is_capped_by_the_hot_expert():
     assert 131072 / max(s.rows for s in sharding.plan(sizes, 8, mode="whole")) < 4.2
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_split_placement_balances_tiles_plus_a_cost_per_expert(world):
+    """What is balanced is row tiles plus GROUP_COST per expert on the rank (an expert brings its own weights through
+    HBM): the costs of the ranks stay within a tile and a half of each other, and the rank that gets the tail of small
+    experts holds fewer rows than the rank that gets the hot expert."""
+    sizes = P.zipf_group_sizes(131072, 64, seed=20240)
+    shards = sharding.plan(sizes, world, mode="split")
+    costs = [sh.cost for sh in shards]
+    assert max(costs) - min(costs) <= 1.5 + sharding.GROUP_COST
+    for sh in shards:
+        want = sum(sharding.tile_cost(r) + sharding.GROUP_COST for _, r in sh.local_groups())
+        assert abs(sh.cost - want) < 1e-9
+    experts = [len(sh.local_groups()) for sh in shards]
+    assert experts[-1] > experts[0] and shards[-1].rows < shards[0].rows
+
+
 def test_local_groups_merge_pieces_of_one_expert():
     shards = sharding.plan([1000, 10, 0, 300], 2, mode="split", chunk_rows=256)
     _check_partition([1000, 10, 0, 300], shards)
