@@ -2297,7 +2297,7 @@ int cb200_mx_quantize(const cb200_mx_quantize_args* args, void* stream_v)
     const uint64_t row_bytes = static_cast<uint64_t>(args->k) * (bf16 ? 2u : 4u);
     const uint64_t segs_if_cut = (args->k + kMxQuantStageBytes / 2u / (bf16 ? 2u : 4u) - 1u) /
                                  (kMxQuantStageBytes / 2u / (bf16 ? 2u : 4u));
-    if (args->k % 64u == 0 && (x_pitch * (bf16 ? 2u : 4u)) % 16u == 0 &&
+    if (args->k % 32u == 0 && (x_pitch * (bf16 ? 2u : 4u)) % 16u == 0 &&
         (reinterpret_cast<uintptr_t>(args->q) & 15u) == 0 &&
         static_cast<uint64_t>(args->rows) * segs_if_cut < (1ull << 31)) {
         // whole rows when they fit a warp's slot, else segments of half a slot (a multiple of 512 elements)

@@ -13,7 +13,7 @@
 // about one byte written per element; a warp handles 128 consecutive elements (four blocks) per step with 16-byte
 // loads and 4-byte stores.
 //
-// mx_quantize_staged_kernel serves the aligned case (k a multiple of 64, rows of at most 28 KB on 16-byte boundaries):
+// mx_quantize_staged_kernel serves the aligned case (k a multiple of 32, rows on 16-byte boundaries):
 // one warp per row, the whole row brought into the warp's shared-memory slot by ONE bulk copy (the next row in
 // flight meanwhile when two fit), a lane working on 16 consecutive elements (half a block) per step, the codes made
 // by the conversion instructions (cvt.rn.satfinite.e4m3x2 / e2m1x2) from values shifted towards zero by one part in
@@ -177,7 +177,7 @@ __device__ __forceinline__ uint32_t mx_codes2_nudged(float a, float b)
     }
 }
 
-// k a multiple of 64; rows of x on 16-byte boundaries; q rows 16-byte aligned.  A row is worked off in segments of
+// k a multiple of 32; rows of x on 16-byte boundaries; q rows 16-byte aligned.  A row is worked off in segments of
 // `seg` elements (a multiple of 512, or k itself when the whole row fits a warp's kMxQuantStageBytes; blocks of 32
 // are independent of each other, so a long row is simply several work items).
 // Dynamic shared memory: 8 warps x kMxQuantStageBytes + barriers.
@@ -207,7 +207,8 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
     const uint32_t stage = smem_u32(mxq_smem) + warp * kMxQuantStageBytes;
     const uint8_t* stage_ptr = mxq_smem + warp * kMxQuantStageBytes;
     const uint32_t bar0 = smem_u32(bars + 2 * warp);
-    const uint32_t q_pitch = kFp4 ? k / 2 : k, sf_pitch = k / 32;
+    const uint32_t q_pitch = kFp4 ? k / 2 : k;
+    const uint32_t sf_pitch = (k / 32 + 1u) & ~1u;  // an even number of scale columns; the odd one out holds 2^0
     const uint32_t segs = (k + seg - 1) / seg;
     const uint32_t items = rows * segs;  // (row, segment) pairs, a row's segments adjacent (the host checks the range)
     auto fetch = [&](uint32_t item, uint32_t slot) {  // lane 0 only
@@ -246,7 +247,7 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
         uint8_t* qr = q + static_cast<uint64_t>(r) * q_pitch + (kFp4 ? c_begin / 2 : c_begin);
         uint8_t* sr = sf + static_cast<uint64_t>(r) * sf_pitch + c_begin / 32;
         // (the trip count is the same for every lane: the block maximum below is a full-warp shuffle; the length is
-        // a multiple of 64, so the two lanes of a block are in range together)
+        // a multiple of 32, so the two lanes of a block are in range together)
         for (uint32_t base = 0; base < len; base += 32 * 16) {
             const uint32_t c0 = base + lane * 16;
             const bool active = c0 < len;
@@ -335,6 +336,9 @@ mx_quantize_staged_kernel(const void* __restrict__ x, uint8_t* __restrict__ q, u
             }
             if ((lane & 1u) == 0) {
                 sr[c0 >> 5] = static_cast<uint8_t>(exp + 127);
+                if (c_begin + c0 + 32 == k && ((k >> 5) & 1u) != 0) {
+                    sr[(c0 >> 5) + 1] = 127;  // the padding column behind the row's last block
+                }
             }
         }
         __syncwarp();  // every lane is done with this slot

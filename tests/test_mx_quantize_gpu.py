@@ -70,7 +70,7 @@ def _run(cuda, x, fmt, bf16):
 @pytest.mark.parametrize("fmt", [O.MX_E4M3, O.MX_E2M1])
 @pytest.mark.parametrize("bf16", [False, True])
 @pytest.mark.parametrize("rows,k", [(64, 1024), (7, 129), (33, 63), (5, 2), (300, 4096), (16, 96), (1200, 7168),
-                                     (9, 14400), (40, 64), (3, 16384)])
+                                     (9, 14400), (40, 64), (3, 16384), (10, 7200)])
 def test_mx_quantize_matches_the_oracle_bit_for_bit(cuda, fmt, bf16, rows, k):
     x = _inputs(rows, k, seed=rows + k)
     q, sf, ref_in = _run(cuda, x, fmt, bf16)
